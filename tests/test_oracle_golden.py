@@ -1,0 +1,229 @@
+"""Pins the CPU oracle against the literal known-answer fixtures of the reference's own tests.
+
+Each case cites the reference test file it replays (paths relative to the reference root).
+"""
+import numpy as np
+import pytest
+
+import oracle as O
+
+O.build()
+
+
+def test_softmax_known_answers():
+    # device/cpu/attention/softmax_test.go:10-40
+    inf = np.float32(np.inf)
+    assert O.stable_softmax_row([1, inf, 2]).tolist() == [0, 1, 0]
+    assert O.stable_softmax_row([inf, 1, inf]).tolist() == [0.5, 0, 0.5]
+    assert O.stable_softmax_row([-inf, -inf]).tolist() == [0, 0]
+
+
+def test_gated_residual_known_answer():
+    # execution/math_gated_residual_intrinsic_test.go:17-65
+    residual = np.arange(1, 13, dtype=np.float32)
+    branch = np.ones(12, np.float32)
+    modulation = np.array([0, 0, 0, 0, 0, 0, 0.5, 1, 2, 0, 0, 0, 0, 0, 0, 3, 4, 5], np.float32)
+    got = O.gated_residual(O.F32, residual, branch, modulation, rows=4, last_dim=3, rows_per_batch=2, mod_cols=9,
+                           set_index=0)
+    assert got.tolist() == [1.5, 3, 5, 4.5, 6, 8, 10, 12, 14, 13, 15, 17]
+
+
+def test_gated_residual_device_hook_layout():
+    # execution/math_gated_residual_intrinsic_test.go:69-129: rows=8,lastDim=3,rowsPerBatch=4,modCols=18,set=1
+    rng = np.random.default_rng(5)
+    res = rng.standard_normal(24).astype(np.float32)
+    br = rng.standard_normal(24).astype(np.float32)
+    mod = rng.uniform(0, 1, 2 * 18).astype(np.float32)
+    got = O.gated_residual(O.F32, res, br, mod, 8, 3, 4, 18, 1).reshape(8, 3)
+    for r in range(8):
+        gate = mod.reshape(2, 18)[r // 4, 1 * 9 + 6:1 * 9 + 9]
+        want = res.reshape(8, 3)[r] + gate * br.reshape(8, 3)[r]
+        assert np.array_equal(got[r], want.astype(np.float32))
+
+
+def test_page_write_gather_known_answer():
+    # execution/page_intrinsic_test.go:15-72,403-470: storage [2,3,2,1,1] zeros, layer 1, ids [1,1], offsets [0,1]
+    storage = np.zeros(2 * 3 * 2, np.float32)
+    layer_elems = 3 * 2 * 1 * 1
+    out = O.page_write(O.F32, storage, np.array([7, 8], np.float32), [1, 1], [0, 1], page_count=3, page_size=2, inner=1,
+                       storage_offset=1 * layer_elems)
+    assert out[8] == 7 and out[9] == 8 and out.sum() == 15
+    got = O.page_gather(O.F32, out, [1], page_count=3, page_size=2, inner=1, out_rows=2, storage_offset=layer_elems)
+    assert got.ravel().tolist() == [7, 8]
+
+
+@pytest.mark.parametrize("n", [1, 7, 64, 1024, 8192])
+@pytest.mark.parametrize("dt", [O.F32, O.F16, O.BF16])
+def test_page_roundtrip_identity(n, dt):
+    # device/cpu/shape/page_parity_test.go:59-118: P=4, inner=8, write then gather is the identity
+    rng = np.random.default_rng(n)
+    page_size, inner = 4, 8
+    pages = (n + page_size - 1) // page_size
+    vals = rng.integers(0, 65536, (n, inner)).astype(O.np_dtype(dt)) if dt != O.F32 else rng.standard_normal(
+        (n, inner)).astype(np.float32)
+    perm = rng.permutation(pages).astype(np.int32)
+    ids = perm[np.arange(n) // page_size]
+    offs = (np.arange(n) % page_size).astype(np.int32)
+    storage = np.zeros(pages * page_size * inner, O.np_dtype(dt))
+    st = O.page_write(dt, storage, vals, ids, offs, pages, page_size, inner)
+    back = O.page_gather(dt, st, perm, pages, page_size, inner, n)
+    assert np.array_equal(back, vals)
+
+
+def test_decode_gqa_causal_known_answer():
+    # device/metal/attention/multihead_parity_darwin_test.go:16-37 (bottom-right causal: all 3 keys live)
+    q = np.zeros((1, 4), np.float32)
+    k = np.zeros((3, 2), np.float32)
+    v = np.array([[1, 10], [2, 20], [3, 30]], np.float32)
+    got = O.mha(O.F32, q, k, v, 1, 3, 2, 1, 2, causal=True)
+    assert got.ravel().tolist() == [2, 20, 2, 20]
+
+
+def test_prefill_gqa_3x3_fixture_matches_float64_softmax():
+    # inputs of device/metal/attention/multihead_parity_darwin_test.go:39-67; expected = CPU semantics,
+    # re-derived here in float64 numpy (bottom-right == top-left when seqQ == seqK)
+    q = np.array([0.25, -0.50, 0.75, 0.10, -0.30, 0.20, 0.40, -0.80, 0.60, 0.90, -0.20, 0.35], np.float32).reshape(3, 4)
+    k = np.array([0.10, 0.20, -0.40, 0.30, 0.50, -0.70], np.float32).reshape(3, 2)
+    v = np.array([1, 10, 2, 20, 3, 30], np.float32).reshape(3, 2)
+    got = O.mha(O.F32, q, k, v, 3, 3, 2, 1, 2, causal=True).reshape(3, 2, 2)
+    for h in range(2):
+        s = (q.reshape(3, 2, 2)[:, h, :].astype(np.float64) @ k.astype(np.float64).T) / np.sqrt(2.0)
+        s[np.triu_indices(3, 1)] = -np.inf
+        p = np.exp(s - s.max(1, keepdims=True))
+        p /= p.sum(1, keepdims=True)
+        want = p @ v.astype(np.float64)
+        assert np.allclose(got[:, h, :], want, rtol=2e-6, atol=0)
+
+
+def test_attention_sanity_2x3():
+    # device/cpu/attention/attention_test.go:11-63 (tolerance 0.1): row i attends to key i
+    q = np.array([[1, 0, 0], [0, 1, 0]], np.float32)
+    k = np.array([[10, 0, 0], [0, 10, 0]], np.float32)
+    v = np.array([[1, 2, 3, 4], [5, 6, 7, 8]], np.float32)
+    got = O.sdpa(O.F32, q, k, v, 2, 2, 3, 4, causal=False)
+    assert np.allclose(got[0], [1, 2, 3, 4], atol=0.1) and np.allclose(got[1], [5, 6, 7, 8], atol=0.1)
+
+
+def _reference_rope(x, cfg, seq, heads, dim):
+    # restatement of the in-test scalar reference, device/cpu/rope/compute_test.go:92-167
+    out = np.empty_like(x)
+    half = dim // 2
+    for s in range(seq):
+        pos = float(s + cfg["start"])
+        for p in range(half):
+            inv = cfg["base"] ** (-(2.0 * p) / dim)
+            if cfg["scaling"] == 1:
+                wl = 2.0 * np.pi / inv
+                lo, hi = cfg["orig"] / cfg["low"], cfg["orig"] / cfg["high"]
+                if wl > lo:
+                    inv = inv / cfg["factor"]
+                elif wl >= hi:
+                    sm = (cfg["orig"] / wl - cfg["low"]) / (cfg["high"] - cfg["low"])
+                    inv = (1.0 - sm) * (inv / cfg["factor"]) + sm * inv
+            th = pos * inv
+            c, sn = np.float32(np.cos(th)), np.float32(np.sin(th))
+            for h in range(heads):
+                ro = (s * heads + h) * dim
+                ei, oi = (ro + p, ro + half + p) if cfg["mode"] == 1 else (ro + 2 * p, ro + 2 * p + 1)
+                e, o = x[ei], x[oi]
+                out[ei] = np.float32(e * c) - np.float32(o * sn)
+                out[oi] = np.float32(e * sn) + np.float32(o * c)
+    return out
+
+
+@pytest.mark.parametrize("seq", [1, 7, 64, 1024])
+def test_rope_llama3_half_mode_zero_ulp(seq):
+    # device/cpu/rope/compute_test.go:16-43,68-79: base 5e5, start 3, factor 32, low 1, high 4, orig 8192, H=2, D=8
+    cfg = dict(base=500000.0, start=3, mode=1, scaling=1, factor=32.0, low=1.0, high=4.0, orig=8192)
+    rng = np.random.default_rng(0x7300 + seq)
+    x = ((rng.random(seq * 2 * 8) - 0.5) * 4).astype(np.float32)
+    got = O.rope(O.F32, x, seq, 2, 8, base=cfg["base"], start=3, mode=1, scaling=1, factor=32.0, low=1.0, high=4.0,
+                 orig_ctx=8192)
+    want = _reference_rope(x, cfg, seq, 2, 8)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+def test_rope_default_interleaved_zero_ulp():
+    cfg = dict(base=10000.0, start=0, mode=0, scaling=0)
+    rng = np.random.default_rng(11)
+    x = rng.standard_normal(64 * 4 * 16).astype(np.float32)
+    got = O.rope(O.F32, x, 64, 4, 16)
+    assert np.array_equal(got.view(np.uint32), _reference_rope(x, cfg, 64, 4, 16).view(np.uint32))
+
+
+def test_fast_exp32_matches_polynomial_definition():
+    # device/cpu/math/f32.go:21-47 evaluated independently in numpy float32
+    xs = np.linspace(-87, 88, 4001, dtype=np.float32)
+    for x in xs[::40]:
+        z = np.float32(x) * np.float32(1.4426950408889634)
+        k = np.int32(z)
+        if z < 0:
+            k -= 1
+        f = np.float32(z - np.float32(k))
+        c = [np.float32(v) for v in (0.69314718, 0.24022650, 0.05550410, 0.00961812, 0.00133389)]
+        poly = np.float32(1) + f * (c[0] + f * (c[1] + f * (c[2] + f * (c[3] + f * c[4]))))
+        want = (np.array([poly], np.float32).view(np.uint32) + (np.uint32(np.int64(k) & 0xFFFFFFFF) << np.uint32(23))).view(np.float32)[0]
+        got = O.lib().oracle_fast_exp32(float(x))
+        assert np.float32(got) == want, (x, got, want)
+    assert O.lib().oracle_fast_exp32(-100.0) == 0.0
+    assert np.float32(O.lib().oracle_fast_exp32(100.0)) == np.finfo(np.float32).max
+
+
+def test_converter_reference_round_trips():
+    # convert/convert_test.go:54-178: round trips on exactly representable grids are exact
+    n = 8192
+    a = (np.arange(n) % 19).astype(np.float32) * 0.5
+    assert np.array_equal(O.convert(O.convert(a, O.F32, O.BF16), O.BF16, O.F32), a)
+    a = ((np.arange(n) % 13) - 6).astype(np.float32) * 0.25
+    assert np.array_equal(O.convert(O.convert(a, O.F32, O.F16), O.F16, O.F32), a)
+    a = ((np.arange(n) % 9) - 4).astype(np.float32) * 0.5
+    assert np.array_equal(O.convert(O.convert(a, O.F32, O.E4M3), O.E4M3, O.F32), a)
+    assert np.array_equal(O.convert(O.convert(a, O.F32, O.E5M2), O.E5M2, O.F32), a)
+
+
+def test_converters_against_independent_implementations():
+    ml_dtypes = pytest.importorskip("ml_dtypes")
+    import torch
+
+    all16 = np.arange(65536, dtype=np.uint16)
+    all8 = np.arange(256, dtype=np.uint8)
+    got = O.convert(all16, O.BF16, O.F32)
+    assert np.array_equal(got.view(np.uint32), all16.view(ml_dtypes.bfloat16).astype(np.float32).view(np.uint32))
+    for src, dt, view in ((all16, O.F16, np.float16), (all8, O.E4M3, ml_dtypes.float8_e4m3fn), (all8, O.E5M2, ml_dtypes.float8_e5m2)):
+        got = O.convert(src, dt, O.F32)
+        want = src.view(view).astype(np.float32)
+        nan = np.isnan(want)
+        assert np.array_equal(np.isnan(got), nan)
+        assert np.array_equal(got.view(np.uint32)[~nan], want.view(np.uint32)[~nan])
+        assert np.array_equal(np.signbit(got), np.signbit(want))
+    rng = np.random.default_rng(20)
+    f = rng.integers(0, 2**32, 1 << 20, dtype=np.uint64).astype(np.uint32).view(np.float32)
+    nan = np.isnan(f)
+    with np.errstate(all="ignore"):
+        assert np.array_equal(O.convert(f, O.F32, O.BF16)[~nan], f.astype(ml_dtypes.bfloat16).view(np.uint16)[~nan])
+        assert np.array_equal(O.convert(f, O.F32, O.F16)[~nan], f.astype(np.float16).view(np.uint16)[~nan])
+        tb = torch.from_numpy(f).to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16)
+        assert np.array_equal(O.convert(f, O.F32, O.BF16)[~nan], tb[~nan])
+        inr = (~nan) & (np.abs(f) <= 448)
+        assert np.array_equal(O.convert(f, O.F32, O.E4M3)[inr], f.astype(ml_dtypes.float8_e4m3fn).view(np.uint8)[inr])
+        inr = (~nan) & (np.abs(f) <= 57344)
+        assert np.array_equal(O.convert(f, O.F32, O.E5M2)[inr], f.astype(ml_dtypes.float8_e5m2).view(np.uint8)[inr])
+
+
+def test_converter_edge_rules():
+    f = np.array([np.inf, -np.inf, 1e9, -1e9, 464.0, 465.0, 0.0, -0.0], np.float32)
+    assert O.convert(f, O.F32, O.E4M3).tolist() == [0x7E, 0xFE, 0x7E, 0xFE, 0x7E, 0x7E, 0x00, 0x80]
+    assert O.convert(f, O.F32, O.E5M2).tolist()[:4] == [0x7B, 0xFB, 0x7B, 0xFB]
+    nan = np.array([0x7FC00000, 0xFFC00001, 0x7F800001], np.uint32).view(np.float32)
+    assert O.convert(nan, O.F32, O.BF16).tolist() == [0x7FC0, 0xFFC0, 0x7FC0]
+    assert O.convert(nan, O.F32, O.E4M3).tolist() == [0x7F, 0xFF, 0x7F]
+    ties = np.array([0x3F808000, 0x3F818000], np.uint32).view(np.float32)  # halfway: to even
+    assert O.convert(ties, O.F32, O.BF16).tolist() == [0x3F80, 0x3F82]
+
+
+def test_bf16_dot_result_is_rounded_to_storage():
+    # device/cpu/dot/bf16_generic.go:9-21 feeds RMSNorm (layernorm/compute.go:365-374)
+    x = O.from_f32(np.full((1, 300), 1.0009765625, np.float32), O.BF16)  # rounds to 1.0 in bf16
+    g = O.from_f32(np.ones(300, np.float32), O.BF16)
+    out = O.to_f32(O.rmsnorm(O.BF16, x, g, 1e-6), O.BF16)
+    assert np.all(out == out[0, 0])
