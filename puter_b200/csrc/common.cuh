@@ -1,0 +1,264 @@
+// Shared device helpers: status/context plumbing, storage-dtype load/store with the exact
+// rounding rules of the reference's convert package, and the reference's polynomial math.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <stdint.h>
+#include <string.h>
+#include <stdio.h>
+
+#include "../../include/puter_b200.h"
+
+namespace puter {
+
+// ---------------------------------------------------------------------------------------------
+// host-side context (one per GPU ordinal)
+// ---------------------------------------------------------------------------------------------
+struct Buffer {
+    void* ptr;
+    long long bytes;
+    int owned;
+    int device;
+};
+
+struct Context {
+    int device;
+    int ccMajor;
+    int smCount;
+    long long totalMem;
+    cudaStream_t ownStream;
+    cudaStream_t uploadStream;
+    cudaStream_t stream;  // the stream launches go to (ownStream or an adopted one)
+    int exact;
+    unsigned long long launches;
+    // grow-only scratch for split-KV partials, RoPE tables and staged conversions
+    void* workspace;
+    size_t workspaceBytes;
+    void* pinned[2];
+    size_t pinnedBytes;
+    cudaEvent_t stageEvents[4];
+    int* errorFlag;  // device int32 owned by the context
+};
+
+int fail(CUDAStatus* status, int code, const char* fmt, ...);
+int ok(CUDAStatus* status);
+Context* ctx_of(CUDADeviceRef ref, CUDAStatus* status);
+// device pointer of a handle, or nullptr (and status -2) when the handle is null
+void* dev_ptr(CUDABufferRef ref);
+int check_buffer(CUDAStatus* status, CUDABufferRef ref, const char* name, size_t needBytes);
+int check_launch(Context* ctx, CUDAStatus* status, const char* what);
+void* ensure_workspace(Context* ctx, size_t bytes, CUDAStatus* status);
+
+inline size_t dtype_size(int dt) {
+    switch (dt) {
+        case CUDAElementDTypeFloat32: return 4;
+        case CUDAElementDTypeFloat16:
+        case CUDAElementDTypeBFloat16: return 2;
+        case CUDAElementDTypeFloat64: return 8;
+        case CUDAElementDTypeFloat8E4M3:
+        case CUDAElementDTypeFloat8E5M2: return 1;
+    }
+    return 0;
+}
+
+#define PUTER_ENTER(ctxVar)                          \
+    cuda_status_clear(status);                       \
+    puter::Context* ctxVar = puter::ctx_of(contextRef, status); \
+    if (!ctxVar) return status ? status->code : -1;  \
+    cudaSetDevice(ctxVar->device);
+
+#define PUTER_REQUIRE(ref, name, bytes)                                   \
+    do {                                                                  \
+        int _rc = puter::check_buffer(status, ref, name, (size_t)(bytes)); \
+        if (_rc != 0) return _rc;                                         \
+    } while (0)
+
+// ---------------------------------------------------------------------------------------------
+// device-side conversions (bit rules identical to the CPU oracle / the reference's convert package)
+// ---------------------------------------------------------------------------------------------
+enum : int { DT_F32 = 0, DT_F16 = 1, DT_BF16 = 2, DT_F64 = 3, DT_E4M3 = 4, DT_E5M2 = 5 };
+
+__device__ __forceinline__ float bf16_bits_to_f32(uint32_t b) { return __uint_as_float(b << 16); }
+
+// RNE by bits + 0x7FFF + lsb; NaN quieted as (bits >> 16) | 0x40.
+__device__ __forceinline__ uint32_t f32_to_bf16_bits(float f) {
+    uint32_t u = __float_as_uint(f);
+    uint32_t r = (u + 0x7FFFu + ((u >> 16) & 1u)) >> 16;
+    return ((u & 0x7FFFFFFFu) > 0x7F800000u) ? ((u >> 16) | 0x40u) : r;
+}
+
+// exact widening; NaN keeps sign + payload with the quiet bit set.
+__device__ __forceinline__ float f16_bits_to_f32(uint32_t h) {
+    float f = __half2float(__ushort_as_half((unsigned short)h));
+    if ((h & 0x7FFFu) > 0x7C00u) f = __uint_as_float(((h & 0x8000u) << 16) | 0x7FC00000u | ((h & 0x3FFu) << 13));
+    return f;
+}
+
+// IEEE RNE (overflow -> Inf, gradual underflow); NaN -> sign | 0x7E00 | payload >> 13.
+__device__ __forceinline__ uint32_t f32_to_f16_bits(float f) {
+    uint32_t u = __float_as_uint(f);
+    uint32_t r = __half_as_ushort(__float2half_rn(f));
+    if ((u & 0x7FFFFFFFu) > 0x7F800000u) r = ((u >> 16) & 0x8000u) | 0x7E00u | ((u >> 13) & 0x3FFu);
+    return r;
+}
+
+// E4M3 "FN": 0x7F / 0xFF are NaN, no Inf.  Every other code is exact in f16, so widen through it.
+__device__ __forceinline__ float e4m3_bits_to_f32(uint32_t b) {
+    __half_raw h = __nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)b, __NV_E4M3);
+    float f = __half2float(__half(h));
+    if ((b & 0x7Fu) == 0x7Fu) f = __uint_as_float(((b & 0x80u) << 24) | 0x7FC00000u);
+    return f;
+}
+// E5M2 is the top byte of an f16.
+__device__ __forceinline__ float e5m2_bits_to_f32(uint32_t b) { return f16_bits_to_f32(b << 8); }
+
+// saturating RNE: finite overflow and +-Inf -> largest finite code, NaN -> sign | 0x7F.
+__device__ __forceinline__ uint32_t f32_to_e4m3_bits(float f) {
+    uint32_t u = __float_as_uint(f);
+    uint32_t r = __nv_cvt_float_to_fp8(f, __NV_SATFINITE, __NV_E4M3);
+    if ((u & 0x7FFFFFFFu) > 0x7F800000u) r = ((u >> 24) & 0x80u) | 0x7Fu;
+    return r;
+}
+__device__ __forceinline__ uint32_t f32_to_e5m2_bits(float f) {
+    uint32_t u = __float_as_uint(f);
+    uint32_t r = __nv_cvt_float_to_fp8(f, __NV_SATFINITE, __NV_E5M2);
+    if ((u & 0x7FFFFFFFu) > 0x7F800000u) r = ((u >> 24) & 0x80u) | 0x7Fu;
+    return r;
+}
+
+template <int DT> struct Storage;
+template <> struct Storage<DT_F32> {
+    using type = float;
+    static __device__ __forceinline__ float load(const float* p, size_t i) { return p[i]; }
+    static __device__ __forceinline__ void store(float* p, size_t i, float v) { p[i] = v; }
+    static __device__ __forceinline__ float widen(float v) { return v; }
+    static __device__ __forceinline__ float narrow(float v) { return v; }
+};
+template <> struct Storage<DT_BF16> {
+    using type = uint16_t;
+    static __device__ __forceinline__ float load(const uint16_t* p, size_t i) { return bf16_bits_to_f32(p[i]); }
+    static __device__ __forceinline__ void store(uint16_t* p, size_t i, float v) { p[i] = (uint16_t)f32_to_bf16_bits(v); }
+    static __device__ __forceinline__ float widen(uint16_t v) { return bf16_bits_to_f32(v); }
+    static __device__ __forceinline__ uint16_t narrow(float v) { return (uint16_t)f32_to_bf16_bits(v); }
+};
+template <> struct Storage<DT_F16> {
+    using type = uint16_t;
+    static __device__ __forceinline__ float load(const uint16_t* p, size_t i) { return f16_bits_to_f32(p[i]); }
+    static __device__ __forceinline__ void store(uint16_t* p, size_t i, float v) { p[i] = (uint16_t)f32_to_f16_bits(v); }
+    static __device__ __forceinline__ float widen(uint16_t v) { return f16_bits_to_f32(v); }
+    static __device__ __forceinline__ uint16_t narrow(float v) { return (uint16_t)f32_to_f16_bits(v); }
+};
+
+// ---------------------------------------------------------------------------------------------
+// the reference's scalar math, reproduced operation by operation with unfused multiplies and adds
+// (the Go compiler on amd64 never contracts a*b+c)
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ float mul(float a, float b) { return __fmul_rn(a, b); }
+__device__ __forceinline__ float add(float a, float b) { return __fadd_rn(a, b); }
+__device__ __forceinline__ float sub(float a, float b) { return __fsub_rn(a, b); }
+__device__ __forceinline__ float divf(float a, float b) { return __fdiv_rn(a, b); }
+
+// FastExp32 (device/cpu/math/f32.go:21-47): 2^k * degree-5 polynomial in the fractional part.
+__device__ __forceinline__ float fast_exp32(float x) {
+    if (x < -87.33654f) return 0.0f;
+    if (x > 88.72283f) return 3.40282346638528859812e+38f;
+    float z = mul(x, 1.4426950408889634f);
+    int k = (int)z;
+    if (z < 0.0f) k--;
+    float f = sub(z, (float)k);
+    float p = mul(f, 0.00133389f);
+    p = mul(f, add(0.00961812f, p));
+    p = mul(f, add(0.05550410f, p));
+    p = mul(f, add(0.24022650f, p));
+    p = mul(f, add(0.69314718f, p));
+    p = add(1.0f, p);
+    return __uint_as_float(__float_as_uint(p) + ((uint32_t)k << 23));
+}
+__device__ __forceinline__ float fast_tanh32(float x) {  // f32.go:71-86
+    if (x > 4.92f) return 1.0f;
+    if (x < -4.92f) return -1.0f;
+    float x2 = mul(x, x);
+    float num = mul(x, add(135135.0f, mul(x2, add(17325.0f, mul(x2, add(378.0f, x2))))));
+    float den = add(135135.0f, mul(x2, add(62370.0f, mul(x2, add(3150.0f, mul(x2, 28.0f))))));
+    return divf(num, den);
+}
+__device__ __forceinline__ float fast_sigmoid32(float v) {  // f32.go:88-95
+    if (v >= 0.0f) return divf(1.0f, add(1.0f, fast_exp32(-v)));
+    float e = fast_exp32(v);
+    return divf(e, add(1.0f, e));
+}
+__device__ __forceinline__ float fast_silu32(float v) { return divf(v, add(1.0f, fast_exp32(-v))); }  // f32.go:97-99
+__device__ __forceinline__ float fast_gelu32(float v) {  // math/activation.go:54-57
+    double x = (double)v;
+    return (float)__dmul_rn(__dmul_rn(0.5, x), __dadd_rn(1.0, erf(__dmul_rn(x, 0.7071067811865475))));
+}
+__device__ __forceinline__ float fast_gelu_tanh32(float v) {  // f32.go:101-105
+    double x = (double)v;
+    double cube = __dmul_rn(__dmul_rn(__dmul_rn(0.044715, x), x), x);
+    double inner = __dmul_rn(0.7978845608028654, __dadd_rn(x, cube));
+    return (float)__dmul_rn(__dmul_rn(0.5, x), __dadd_rn(1.0, (double)fast_tanh32((float)inner)));
+}
+__device__ __forceinline__ float fast_relu32(float v) { return v > 0.0f ? v : 0.0f; }
+
+// f64 variants used by the 16-bit LUT semantics (device/cpu/activation/lut.go:48-61, math/f64.go)
+__device__ __forceinline__ double fast_exp64(double x) {
+    if (x < -708.3964185322641) return 0.0;
+    if (x > 709.782712893384) return 1.7976931348623157e+308;
+    double z = __dmul_rn(x, 1.4426950408889634);
+    long long k = (long long)z;
+    if (z < 0.0) k--;
+    double f = __dsub_rn(z, (double)k);
+    double p = __dmul_rn(f, 0.001333899727232439);
+    p = __dmul_rn(f, __dadd_rn(0.009618127167766223, p));
+    p = __dmul_rn(f, __dadd_rn(0.05550410706910451, p));
+    p = __dmul_rn(f, __dadd_rn(0.2402265069591007, p));
+    p = __dmul_rn(f, __dadd_rn(0.6931471805599453, p));
+    p = __dadd_rn(1.0, p);
+    return ldexp(p, (int)k);
+}
+__device__ __forceinline__ double fast_tanh64(double x) {
+    if (x > 4.92) return 1.0;
+    if (x < -4.92) return -1.0;
+    double x2 = __dmul_rn(x, x);
+    double num = __dmul_rn(x, __dadd_rn(135135.0, __dmul_rn(x2, __dadd_rn(17325.0, __dmul_rn(x2, __dadd_rn(378.0, x2))))));
+    double den = __dadd_rn(13.0, x2);
+    den = __dadd_rn(693.0, __dmul_rn(x2, den));
+    den = __dadd_rn(7335.0, __dmul_rn(x2, den));
+    den = __dadd_rn(31185.0, __dmul_rn(x2, den));
+    den = __dadd_rn(62370.0, __dmul_rn(x2, den));
+    den = __dadd_rn(135135.0, __dmul_rn(x2, den));
+    return __ddiv_rn(num, den);
+}
+__device__ __forceinline__ double fast_sigmoid64(double v) {
+    if (v >= 0.0) return __ddiv_rn(1.0, __dadd_rn(1.0, fast_exp64(-v)));
+    double e = fast_exp64(v);
+    return __ddiv_rn(e, __dadd_rn(1.0, e));
+}
+__device__ __forceinline__ double fast_silu64(double v) { return __ddiv_rn(v, __dadd_rn(1.0, fast_exp64(-v))); }
+__device__ __forceinline__ double fast_gelu64(double v) {
+    return __dmul_rn(__dmul_rn(0.5, v), __dadd_rn(1.0, erf(__dmul_rn(v, 0.7071067811865475))));
+}
+__device__ __forceinline__ double fast_gelu_tanh64(double v) {
+    double cube = __dmul_rn(__dmul_rn(__dmul_rn(0.044715, v), v), v);
+    double inner = __dmul_rn(0.7978845608028654, __dadd_rn(v, cube));
+    return __dmul_rn(__dmul_rn(0.5, v), __dadd_rn(1.0, fast_tanh64(inner)));
+}
+
+// 16-byte vector of raw storage elements
+struct __align__(16) Vec16 { uint32_t w[4]; };
+
+__device__ __forceinline__ Vec16 ld_stream(const void* p) {  // read-once data: bypass L1 allocation
+    Vec16 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.w[0]), "=r"(v.w[1]), "=r"(v.w[2]), "=r"(v.w[3]) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ void st_stream(void* p, const Vec16& v) {
+    asm volatile("st.global.L1::no_allocate.v4.u32 [%0], {%1,%2,%3,%4};"
+                 :: "l"(p), "r"(v.w[0]), "r"(v.w[1]), "r"(v.w[2]), "r"(v.w[3]) : "memory");
+}
+
+}  // namespace puter

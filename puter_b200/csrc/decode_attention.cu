@@ -1,0 +1,603 @@
+// Paged decode attention: one new token per sequence, K/V read in place from the page pool.
+//
+// Equivalent, per sequence, to the reference composition page_gather(K), page_gather(V)
+// (execution/page_intrinsic.go:217-352, device/cpu/shape/page_generic.go:30-50) followed by
+// MultiHeadAttention with seqQ = 1, seqK = ctx and the bottom-right causal mask, under which every
+// live key is visible (device/cpu/attention/typed_compute.go:142-237).  The 16-bit reference rounds
+// each q.k dot product to the storage type before scaling (device/cpu/dot/bf16_generic.go:9-21);
+// this kernel reproduces that rounding.  Softmax weights are kept in float32 (split into a high and a
+// low 16-bit part for the tensor-core product), so results differ from the sequential CPU sums only by
+// accumulation order.
+//
+// The kernel is HBM-bound (every K/V byte is read exactly once), so it is organised around the memory
+// system rather than the math:
+//   * the pool layout is [page, token, kvHead, headDim]; the eight warps of a CTA walk the same tokens,
+//     one KV head each, so a CTA consumes whole 2 KB token rows / 32 KB pages while every warp owns a
+//     private cp.async pipeline (no block-wide barrier anywhere in the main loop);
+//   * work is split "stream-K" style: the global list of 16-token tiles of all sequences is cut into equal
+//     contiguous ranges, one per worker (a CTA, or a fraction of one when there are fewer than 8 KV
+//     heads), so every SM reads the same number of bytes whatever the context-length mix; a range may
+//     span several sequences and a sequence several ranges;
+//   * each (worker, sequence) pair leaves an un-normalised partial (max, sum, accumulator) in scratch
+//     memory; a second small kernel merges the partials of a sequence and writes the rounded output;
+//   * the GQA group (<= 16 query heads per KV head) forms the M=16 rows of mma.sync m16n8k16 tiles fed by
+//     ldmatrix from XOR-swizzled shared memory; tensor-core throughput is irrelevant here, the point is to
+//     keep the instruction count per byte far below the issue limit.
+//   * fp8-e4m3 KV pages are converted to f16 (exact) on the way from the staging buffer to the tile; the
+//     per-KV-head scales are applied to the scores and to the output.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace puter {
+
+static constexpr int kHeadDim = 128;
+static constexpr int kTile = 16;       // tokens per tile
+static constexpr int kWarps = 8;
+static constexpr int kThreads = kWarps * 32;
+
+struct DecodeParams {
+    const void* q;            // [batch, numHeads*128]
+    const void* kPages;       // [pageCount, pageSize, kvHeads*128]
+    const void* vPages;
+    const int32_t* pageTable; // [batch, maxPages] or nullptr: pages are consecutive (contiguous K/V per sequence)
+    const int32_t* ctxLens;   // [batch]
+    const float* kScale;      // [kvHeads] or nullptr (fp8 only)
+    const float* vScale;
+    const long long* tileStart;  // [batch+1] exclusive prefix of tiles per sequence
+    float* partAcc;           // [slots, numHeads, 128]
+    float2* partML;           // [slots, numHeads]  (max in log2 domain, sum)
+    int* errorFlag;
+    long long seqStrideKV;    // contiguous mode: elements between consecutive sequences' K (and V)
+    int batch, maxPages, pageCount, pageSize, numHeads, kvHeads, group;
+    int headsPerPass, groups, workers;  // warps-as-heads per pass, sub-ranges per CTA, total workers
+    float scaleLog2;          // (1/sqrt(headDim)) * log2(e)
+    float scale;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+
+template <bool BF16>
+__device__ __forceinline__ void mma16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    if (BF16) {
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                     : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    } else {
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                     : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    }
+}
+
+// packs two f32 into the 16-bit MMA operand type (truncation-free: RNE)
+template <bool BF16> __device__ __forceinline__ uint32_t pack16(float lo, float hi) {
+    if (BF16) {
+        __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+        return *(uint32_t*)&v;
+    }
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *(uint32_t*)&v;
+}
+template <bool BF16> __device__ __forceinline__ float unpack16_lo(uint32_t w) {
+    if (BF16) return __uint_as_float(w << 16);
+    return __half2float(__ushort_as_half((unsigned short)(w & 0xFFFFu)));
+}
+template <bool BF16> __device__ __forceinline__ float unpack16_hi(uint32_t w) {
+    if (BF16) return __uint_as_float(w & 0xFFFF0000u);
+    return __half2float(__ushort_as_half((unsigned short)(w >> 16)));
+}
+// rounds an f32 to the 16-bit storage type and back (the reference's rounded dot product)
+template <bool BF16> __device__ __forceinline__ float round16(float v) {
+    if (BF16) return __uint_as_float(f32_to_bf16_bits(v) << 16);
+    return __half2float(__float2half_rn(v));
+}
+
+// exclusive prefix sum of tiles per sequence (one block); clamps over-long contexts and flags them
+__global__ void decode_prefix_kernel(const int32_t* __restrict__ ctxLens, long long* __restrict__ tileStart, int batch, int maxPages,
+                                     int pageSize, int* __restrict__ errorFlag) {
+    __shared__ long long warpSums[32];
+    __shared__ long long carry;
+    if (threadIdx.x == 0) carry = 0;
+    __syncthreads();
+    const long long cap = (long long)maxPages * pageSize;
+    for (int base = 0; base < batch; base += blockDim.x) {
+        int b = base + threadIdx.x;
+        long long t = 0;
+        if (b < batch) {
+            long long ctx = ctxLens[b];
+            if (ctx < 0) { ctx = 0; atomicExch(errorFlag, 1); }
+            if (maxPages > 0 && ctx > cap) { ctx = cap; atomicExch(errorFlag, 1); }
+            t = (ctx + kTile - 1) / kTile;
+        }
+        long long incl = t;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            long long n = __shfl_up_sync(0xffffffffu, incl, o);
+            if ((threadIdx.x & 31) >= o) incl += n;
+        }
+        int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        if (lane == 31) warpSums[warp] = incl;
+        __syncthreads();
+        long long before = carry;
+        for (int w = 0; w < warp; w++) before += warpSums[w];
+        if (b < batch) tileStart[b] = before + incl - t;
+        __syncthreads();
+        if (threadIdx.x == blockDim.x - 1) carry = before + incl;
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) tileStart[batch] = carry;
+}
+
+// worker index that owns global tile g when T tiles are cut into NV equal contiguous ranges [v*T/NV, (v+1)*T/NV)
+__device__ __forceinline__ long long worker_of_tile(long long g, long long T, long long NV) { return ((g + 1) * NV - 1) / T; }
+
+template <bool BF16, bool FP8KV, int NS>
+struct DecodeSmem {
+    static constexpr int kRawStage = FP8KV ? 2 * kTile * kHeadDim : 0;      // fp8 staging (K + V) per stage
+    static constexpr int kTileBytes = 2 * kTile * kHeadDim * 2;             // 16-bit K + V tile
+    static constexpr int kPerWarp = FP8KV ? NS * kRawStage + kTileBytes : NS * kTileBytes;
+    static constexpr int kTotal = kPerWarp * kWarps;
+};
+
+template <bool BF16, bool FP8KV, int NS, bool SPLIT_P>
+__global__ void __launch_bounds__(kThreads, 1) paged_decode_kernel(DecodeParams p) {
+    extern __shared__ __align__(128) unsigned char smemRaw[];
+    using SM = DecodeSmem<BF16, FP8KV, NS>;
+    constexpr bool MMA_BF16 = BF16 && !FP8KV;  // fp8 pages are widened to f16, so that path multiplies in f16
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    if (warp >= p.groups * p.headsPerPass) return;
+    const int sub = warp / p.headsPerPass;
+    const int head0 = warp % p.headsPerPass;
+    const long long worker = (long long)blockIdx.x * p.groups + sub;
+    const long long T = p.tileStart[p.batch];
+    if (T == 0) return;
+    const long long lo = worker * T / p.workers, hi = (worker + 1) * T / p.workers;
+    if (lo >= hi) return;
+
+    unsigned char* wsm = smemRaw + (size_t)warp * SM::kPerWarp;
+    const uint32_t wsmAddr = smem_u32(wsm);
+    const int es = FP8KV ? 1 : 2;
+    const size_t tokenStride = (size_t)p.kvHeads * kHeadDim * es;  // bytes between tokens of a page
+    const bool page16 = (p.pageSize % kTile) == 0;
+
+    // first sequence of the range: largest b with tileStart[b] <= lo
+    int seq;
+    {
+        int a = 0, z = p.batch;
+        while (z - a > 1) {
+            int m = (a + z) >> 1;
+            if (p.tileStart[m] <= lo) a = m; else z = m;
+        }
+        seq = a;
+    }
+
+    for (int kvh = head0; kvh < p.kvHeads; kvh += p.headsPerPass) {
+        int b = seq;
+        long long cur = lo;
+        while (cur < hi) {
+            while (p.tileStart[b + 1] <= cur) b++;  // skip empty sequences
+            const long long segStart = p.tileStart[b];
+            const long long segEndAll = p.tileStart[b + 1];
+            const long long segEnd = segEndAll < hi ? segEndAll : hi;
+            const int tile0 = (int)(cur - segStart), tile1 = (int)(segEnd - segStart);  // local tile range [tile0, tile1)
+            long long ctxl = p.ctxLens[b];
+            const long long capTok = (long long)(segEndAll - segStart) * kTile;
+            const int ctx = (int)(ctxl < capTok ? ctxl : capTok);
+            const int32_t* table = p.pageTable ? p.pageTable + (size_t)b * p.maxPages : nullptr;
+            const unsigned char* kBase = (const unsigned char*)p.kPages + (size_t)kvh * kHeadDim * es;
+            const unsigned char* vBase = (const unsigned char*)p.vPages + (size_t)kvh * kHeadDim * es;
+            if (!table) {
+                kBase += (size_t)b * p.seqStrideKV * es;
+                vBase += (size_t)b * p.seqStrideKV * es;
+            }
+
+            // ---- Q fragments (A operand, rows = query heads of this KV head's group) ----
+            uint32_t qa[8][4];
+            {
+                const size_t qRow = (size_t)b * p.numHeads * kHeadDim;
+                const int h0 = kvh * p.group + g, h1 = h0 + 8;
+                const bool v0 = g < p.group, v1 = g + 8 < p.group;
+#pragma unroll
+                for (int kk = 0; kk < 8; kk++) {
+#pragma unroll
+                    for (int part = 0; part < 4; part++) {
+                        const bool valid = (part & 1) ? v1 : v0;
+                        const int h = (part & 1) ? h1 : h0;
+                        const int d = kk * 16 + (part >> 1) * 8 + 2 * t;
+                        uint32_t w = 0;
+                        if (valid) {
+                            w = *(const uint32_t*)((const uint16_t*)p.q + qRow + (size_t)h * kHeadDim + d);
+                            if (BF16 && !MMA_BF16) {  // bf16 query, f16 multiply
+                                w = pack16<false>(__uint_as_float(w << 16), __uint_as_float(w & 0xFFFF0000u));
+                            }
+                        }
+                        qa[kk][part] = w;
+                    }
+                }
+            }
+
+            float oacc[16][4];
+#pragma unroll
+            for (int j = 0; j < 16; j++) oacc[j][0] = oacc[j][1] = oacc[j][2] = oacc[j][3] = 0.f;
+            float mrow[2] = {-INFINITY, -INFINITY}, lrow[2] = {0.f, 0.f};
+            const float kS = (FP8KV && p.kScale) ? p.kScale[kvh] : 1.0f;
+
+            // page-id cache: lane i holds table[cbase + i]
+            int cbase = -0x40000000, cval = 0;
+            auto page_of = [&](int entry) -> int {
+                if (!table) return entry;
+                if (entry - cbase >= 32 || entry < cbase) {
+                    cbase = entry;
+                    int idx = entry + lane;
+                    cval = idx < p.maxPages ? table[idx] : 0;
+                }
+                int pg = __shfl_sync(0xffffffffu, cval, entry - cbase);
+                if (pg < 0 || pg >= p.pageCount) {
+                    if (lane == 0) atomicExch(p.errorFlag, 1);
+                    pg = 0;  // never dereference an out-of-range page
+                }
+                return pg;
+            };
+
+            // issue the async copies of local tile `lt` into stage `st`
+            auto issue = [&](int lt, int st) {
+                const int tok0 = lt * kTile;
+                uint32_t dstK, dstV;
+                if (FP8KV) {
+                    dstK = wsmAddr + st * SM::kRawStage;
+                    dstV = dstK + kTile * kHeadDim;
+                } else {
+                    dstK = wsmAddr + st * SM::kTileBytes;
+                    dstV = dstK + kTile * kHeadDim * 2;
+                }
+                constexpr int kChunksPerRow = FP8KV ? 8 : 16;    // 16-byte chunks per (token, head) row
+                constexpr int kRowsPerIter = 32 / kChunksPerRow; // rows covered by one warp-wide copy
+                const int c = lane % kChunksPerRow;
+                size_t pageOff = 0;
+                int inPage0 = 0;
+                if (page16 || !table) {
+                    const int ps = table ? p.pageSize : kTile;
+                    const int entry = tok0 / ps;
+                    inPage0 = tok0 % ps;
+                    pageOff = (size_t)page_of(entry) * ps * tokenStride;
+                }
+#pragma unroll
+                for (int i = 0; i < kTile / kRowsPerIter; i++) {
+                    const int r = i * kRowsPerIter + lane / kChunksPerRow;
+                    const int tok = tok0 + r;
+                    size_t off;
+                    if (page16 || !table) {
+                        off = pageOff + (size_t)(inPage0 + r) * tokenStride;
+                    } else {
+                        int pg = 0;
+                        const int entry = tok / p.pageSize;
+                        if (tok < ctx && entry < p.maxPages) {
+                            pg = table[entry];
+                            if (pg < 0 || pg >= p.pageCount) { atomicExch(p.errorFlag, 1); pg = 0; }
+                        }
+                        off = ((size_t)pg * p.pageSize + tok % p.pageSize) * tokenStride;
+                    }
+                    const int bytes = tok < ctx ? 16 : 0;  // rows past the context are zero-filled, never read
+                    if (bytes == 0) off = 0;
+                    uint32_t so;
+                    if (FP8KV) so = r * kHeadDim + c * 16;                       // raw staging, linear
+                    else so = r * 256 + ((c ^ (r & 7)) * 16);                   // swizzled 16-bit tile
+                    cp_async16(dstK + so, kBase + off + c * 16, bytes);
+                    cp_async16(dstV + so, vBase + off + c * 16, bytes);
+                }
+            };
+
+            const int nTiles = tile1 - tile0;
+#pragma unroll
+            for (int s = 0; s < NS - 1; s++) {
+                if (s < nTiles) issue(tile0 + s, s);
+                cp_async_commit();
+            }
+
+            for (int it = 0; it < nTiles; it++) {
+                cp_async_wait<NS - 2>();
+                __syncwarp();
+                {
+                    const int nx = it + NS - 1;
+                    if (nx < nTiles) issue(tile0 + nx, nx % NS);
+                    cp_async_commit();
+                }
+                const int st = it % NS;
+                uint32_t tileK, tileV;
+                if (FP8KV) {
+                    // widen the staged fp8 bytes into the (swizzled) f16 tile: lane handles 16-byte chunks
+                    const unsigned char* raw = wsm + st * SM::kRawStage;
+                    unsigned char* tile = wsm + NS * SM::kRawStage;
+#pragma unroll
+                    for (int i = 0; i < (2 * kTile * kHeadDim / 16) / 32; i++) {
+                        const int chunk = i * 32 + lane;              // 0..255: K chunks then V chunks
+                        const int which = chunk >> 7;                 // 0 = K, 1 = V
+                        const int r = (chunk & 127) >> 3, c8 = chunk & 7;
+                        const Vec16 in = *(const Vec16*)(raw + chunk * 16);
+                        Vec16 o0, o1;
+#pragma unroll
+                        for (int w = 0; w < 4; w++) {
+                            __half2_raw a = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(in.w[w] & 0xFFFFu), __NV_E4M3);
+                            __half2_raw bq = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(in.w[w] >> 16), __NV_E4M3);
+                            uint32_t lo2 = (uint32_t)a.x | ((uint32_t)a.y << 16);
+                            uint32_t hi2 = (uint32_t)bq.x | ((uint32_t)bq.y << 16);
+                            if (w < 2) { o0.w[2 * w] = lo2; o0.w[2 * w + 1] = hi2; }
+                            else { o1.w[2 * (w - 2)] = lo2; o1.w[2 * (w - 2) + 1] = hi2; }
+                        }
+                        unsigned char* dst = tile + which * (kTile * 256) + r * 256;
+                        *(Vec16*)(dst + (((2 * c8) ^ (r & 7)) * 16)) = o0;
+                        *(Vec16*)(dst + (((2 * c8 + 1) ^ (r & 7)) * 16)) = o1;
+                    }
+                    __syncwarp();
+                    tileK = wsmAddr + NS * SM::kRawStage;
+                    tileV = tileK + kTile * 256;
+                } else {
+                    tileK = wsmAddr + st * SM::kTileBytes;
+                    tileV = tileK + kTile * 256;
+                }
+
+                // ---- S = Q K^T : 16 x 16 ----
+                float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+                {
+                    const int mi = lane >> 3, r = lane & 7;
+                    const int tok = (mi >> 1) * 8 + r;
+#pragma unroll
+                    for (int kk = 0; kk < 8; kk++) {
+                        const int chunk = 2 * kk + (mi & 1);
+                        uint32_t b0, b1, b2, b3;
+                        ldmatrix_x4(tileK + tok * 256 + ((chunk ^ (tok & 7)) * 16), b0, b1, b2, b3);
+                        mma16816<MMA_BF16>(s0, qa[kk], b0, b1);
+                        mma16816<MMA_BF16>(s1, qa[kk], b2, b3);
+                    }
+                }
+                // ---- scale, mask, online softmax (log2 domain) ----
+                const int tokBase = (tile0 + it) * kTile;
+                float pv[2][4];  // [row half][4 tokens: 2t, 2t+1, 8+2t, 9+2t]
+#pragma unroll
+                for (int hrow = 0; hrow < 2; hrow++) {
+                    float x[4] = {s0[2 * hrow], s0[2 * hrow + 1], s1[2 * hrow], s1[2 * hrow + 1]};
+                    float mx = -INFINITY;
+#pragma unroll
+                    for (int c = 0; c < 4; c++) {
+                        const int tok = tokBase + (c >> 1) * 8 + 2 * t + (c & 1);
+                        float sc;
+                        if (FP8KV) sc = x[c] * kS * p.scaleLog2;
+                        else sc = round16<BF16>(x[c]) * p.scaleLog2;   // the reference rounds the dot to storage first
+                        x[c] = tok < ctx ? sc : -INFINITY;
+                        mx = fmaxf(mx, x[c]);
+                    }
+                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+                    const float mNew = fmaxf(mrow[hrow], mx);
+                    const float alpha = (mNew == -INFINITY) ? 1.0f : exp2f(mrow[hrow] - mNew);
+                    float sum = 0.f;
+#pragma unroll
+                    for (int c = 0; c < 4; c++) {
+                        const float e = (x[c] == -INFINITY) ? 0.f : exp2f(x[c] - mNew);
+                        pv[hrow][c] = e;
+                        sum += e;
+                    }
+                    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+                    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+                    lrow[hrow] = lrow[hrow] * alpha + sum;
+                    mrow[hrow] = mNew;
+                    if (alpha != 1.0f) {
+#pragma unroll
+                        for (int j = 0; j < 16; j++) {
+                            oacc[j][2 * hrow] *= alpha;
+                            oacc[j][2 * hrow + 1] *= alpha;
+                        }
+                    }
+                }
+                // ---- O += P V ----
+                uint32_t pa[4], pl[4];
+                pa[0] = pack16<MMA_BF16>(pv[0][0], pv[0][1]);
+                pa[1] = pack16<MMA_BF16>(pv[1][0], pv[1][1]);
+                pa[2] = pack16<MMA_BF16>(pv[0][2], pv[0][3]);
+                pa[3] = pack16<MMA_BF16>(pv[1][2], pv[1][3]);
+                if (SPLIT_P) {
+                    // low part: what the 16-bit rounding of P dropped
+                    pl[0] = pack16<MMA_BF16>(pv[0][0] - unpack16_lo<MMA_BF16>(pa[0]), pv[0][1] - unpack16_hi<MMA_BF16>(pa[0]));
+                    pl[1] = pack16<MMA_BF16>(pv[1][0] - unpack16_lo<MMA_BF16>(pa[1]), pv[1][1] - unpack16_hi<MMA_BF16>(pa[1]));
+                    pl[2] = pack16<MMA_BF16>(pv[0][2] - unpack16_lo<MMA_BF16>(pa[2]), pv[0][3] - unpack16_hi<MMA_BF16>(pa[2]));
+                    pl[3] = pack16<MMA_BF16>(pv[1][2] - unpack16_lo<MMA_BF16>(pa[3]), pv[1][3] - unpack16_hi<MMA_BF16>(pa[3]));
+                }
+                {
+                    const int mi = lane >> 3, r = lane & 7;
+                    const int tok = (mi & 1) * 8 + r;
+#pragma unroll
+                    for (int jj = 0; jj < 8; jj++) {
+                        const int chunk = 2 * jj + (mi >> 1);
+                        uint32_t b0, b1, b2, b3;
+                        ldmatrix_x4_trans(tileV + tok * 256 + ((chunk ^ (tok & 7)) * 16), b0, b1, b2, b3);
+                        mma16816<MMA_BF16>(oacc[2 * jj], pa, b0, b1);
+                        mma16816<MMA_BF16>(oacc[2 * jj + 1], pa, b2, b3);
+                        if (SPLIT_P) {
+                            mma16816<MMA_BF16>(oacc[2 * jj], pl, b0, b1);
+                            mma16816<MMA_BF16>(oacc[2 * jj + 1], pl, b2, b3);
+                        }
+                    }
+                }
+            }
+            cp_async_wait<0>();
+            __syncwarp();
+
+            // ---- write the partial of (worker, sequence b) ----
+            {
+                const long long slot = worker + b;
+                const float vS = (FP8KV && p.vScale) ? p.vScale[kvh] : 1.0f;
+#pragma unroll
+                for (int hrow = 0; hrow < 2; hrow++) {
+                    const int gi = g + 8 * hrow;
+                    if (gi < p.group) {
+                        const int head = kvh * p.group + gi;
+                        float* acc = p.partAcc + ((size_t)slot * p.numHeads + head) * kHeadDim;
+#pragma unroll
+                        for (int j = 0; j < 16; j++)
+                            *(float2*)(acc + 8 * j + 2 * t) = make_float2(oacc[j][2 * hrow] * vS, oacc[j][2 * hrow + 1] * vS);
+                        if (t == 0) p.partML[(size_t)slot * p.numHeads + head] = make_float2(mrow[hrow], lrow[hrow]);
+                    }
+                }
+            }
+            cur = segEnd;
+            if (cur >= segEndAll) b++;
+        }
+    }
+}
+
+// merges the partials of each (sequence, head) and writes the output row in the storage dtype
+template <bool BF16>
+__global__ void __launch_bounds__(kHeadDim) decode_merge_kernel(DecodeParams p, void* __restrict__ out) {
+    const int b = blockIdx.x, head = blockIdx.y, d = threadIdx.x;
+    const long long T = p.tileStart[p.batch];
+    const long long s0 = p.tileStart[b], s1 = p.tileStart[b + 1];
+    if (s1 <= s0 || T == 0) return;  // empty context: row left untouched
+    const long long v0 = worker_of_tile(s0, T, p.workers), v1 = worker_of_tile(s1 - 1, T, p.workers);
+    float M = -INFINITY;
+    // workers whose own range is empty (fewer tiles than workers) never wrote a partial
+    auto owns = [&](long long v) { return (v + 1) * T / p.workers > v * T / p.workers; };
+    for (long long v = v0; v <= v1; v++)
+        if (owns(v)) M = fmaxf(M, p.partML[(size_t)(v + b) * p.numHeads + head].x);
+    float num = 0.f, den = 0.f;
+    for (long long v = v0; v <= v1; v++) {
+        if (!owns(v)) continue;
+        const float2 ml = p.partML[(size_t)(v + b) * p.numHeads + head];
+        const float w = (ml.x == -INFINITY) ? 0.f : exp2f(ml.x - M);
+        den += ml.y * w;
+        num += p.partAcc[((size_t)(v + b) * p.numHeads + head) * kHeadDim + d] * w;
+    }
+    const float o = den > 0.f ? num / den : 0.f;
+    uint16_t* orow = (uint16_t*)out + ((size_t)b * p.numHeads + head) * kHeadDim;
+    orow[d] = BF16 ? (uint16_t)f32_to_bf16_bits(o) : (uint16_t)f32_to_f16_bits(o);
+}
+
+// Host launcher shared by the paged entry point and the seqQ == 1 fast path of MultiHeadAttention.
+// pageTable == nullptr selects contiguous K/V ([ctx, kvHeads*128] per sequence, sequences seqStrideKV apart).
+int launch_paged_decode(Context* ctx, int dt, int kvDT, const void* q, const void* kPages, const void* vPages, const int32_t* pageTable,
+                        const int32_t* ctxLens, const float* kScale, const float* vScale, void* out, int* errorFlag, uint32_t batch,
+                        uint32_t maxPages, uint32_t pageCount, uint32_t pageSize, uint32_t numHeads, uint32_t kvHeads,
+                        long long seqStrideKV, long long totalTilesHint, CUDAStatus* status) {
+    const int group = (int)(numHeads / kvHeads);
+    DecodeParams p{};
+    p.q = q; p.kPages = kPages; p.vPages = vPages; p.pageTable = pageTable; p.ctxLens = ctxLens;
+    p.kScale = kScale; p.vScale = vScale;
+    p.errorFlag = errorFlag ? errorFlag : ctx->errorFlag;
+    p.seqStrideKV = seqStrideKV;
+    p.batch = (int)batch; p.maxPages = (int)maxPages; p.pageCount = (int)pageCount; p.pageSize = (int)pageSize;
+    p.numHeads = (int)numHeads; p.kvHeads = (int)kvHeads; p.group = group;
+    p.headsPerPass = kvHeads < (uint32_t)kWarps ? (int)kvHeads : kWarps;
+    p.groups = kWarps / p.headsPerPass;
+    // grid: one CTA per SM, fewer when the problem is tiny (a worker should own at least ~4 tiles)
+    long long ctas = ctx->smCount;
+    if (totalTilesHint >= 0) {
+        long long want = (totalTilesHint + 4LL * p.groups - 1) / (4LL * p.groups);
+        if (want < 1) want = 1;
+        if (want < ctas) ctas = want;
+    }
+    p.workers = (int)(ctas * p.groups);
+    p.scale = (float)(1.0 / sqrt((double)kHeadDim));
+    p.scaleLog2 = p.scale * 1.4426950408889634f;
+
+    const size_t slots = (size_t)p.workers + batch;
+    const size_t accBytes = slots * numHeads * kHeadDim * sizeof(float);
+    const size_t mlBytes = slots * numHeads * sizeof(float2);
+    const size_t prefBytes = ((size_t)batch + 1) * sizeof(long long);
+    char* ws = (char*)ensure_workspace(ctx, accBytes + mlBytes + prefBytes + 512, status);
+    if (!ws) return status ? status->code : -7;
+    p.partAcc = (float*)ws;
+    p.partML = (float2*)(ws + accBytes);
+    p.tileStart = (long long*)(ws + accBytes + ((mlBytes + 255) & ~(size_t)255));
+
+    decode_prefix_kernel<<<1, 1024, 0, ctx->stream>>>(ctxLens, (long long*)p.tileStart, (int)batch, pageTable ? (int)maxPages : 0,
+                                                       (int)pageSize, p.errorFlag);
+    int rc = check_launch(ctx, status, "decode prefix");
+    if (rc != 0) return rc;
+
+    const bool bf16 = dt == DT_BF16;
+    const bool fp8 = kvDT == DT_E4M3;
+#define DECODE_LAUNCH(B, F, NSTAGE)                                                                                      \
+    do {                                                                                                                 \
+        constexpr int smem = DecodeSmem<B, F, NSTAGE>::kTotal;                                                           \
+        cudaFuncSetAttribute(paged_decode_kernel<B, F, NSTAGE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); \
+        paged_decode_kernel<B, F, NSTAGE, true><<<(unsigned)ctas, kThreads, smem, ctx->stream>>>(p);                     \
+    } while (0)
+    if (fp8) {
+        if (bf16) DECODE_LAUNCH(true, true, 5);
+        else DECODE_LAUNCH(false, true, 5);
+    } else {
+        if (bf16) DECODE_LAUNCH(true, false, 3);
+        else DECODE_LAUNCH(false, false, 3);
+    }
+#undef DECODE_LAUNCH
+    rc = check_launch(ctx, status, "paged decode attention");
+    if (rc != 0) return rc;
+    dim3 mgrid(batch, numHeads);
+    if (bf16) decode_merge_kernel<true><<<mgrid, kHeadDim, 0, ctx->stream>>>(p, out);
+    else decode_merge_kernel<false><<<mgrid, kHeadDim, 0, ctx->stream>>>(p, out);
+    return check_launch(ctx, status, "decode merge");
+}
+
+bool decode_supported(int dt, int kvDT, uint32_t numHeads, uint32_t kvHeads, uint32_t headDim) {
+    if (dt != DT_BF16 && dt != DT_F16) return false;
+    if (kvDT != dt && kvDT != DT_E4M3) return false;
+    if (headDim != (uint32_t)kHeadDim || kvHeads == 0 || numHeads % kvHeads != 0) return false;
+    return numHeads / kvHeads <= 16;
+}
+
+}  // namespace puter
+
+using namespace puter;
+
+extern "C" int cuda_dispatch_paged_decode_attention(CUDADeviceRef contextRef, int elementDType, int kvDType, CUDABufferRef queryRef,
+                                                    CUDABufferRef kPagesRef, CUDABufferRef vPagesRef, CUDABufferRef pageTableRef,
+                                                    CUDABufferRef ctxLensRef, CUDABufferRef kScaleRef, CUDABufferRef vScaleRef,
+                                                    CUDABufferRef outRef, CUDABufferRef errorFlagRef, uint32_t batch, uint32_t maxPagesPerSeq,
+                                                    uint32_t pageCount, uint32_t pageSize, uint32_t numHeads, uint32_t kvHeads,
+                                                    uint32_t headDim, uint64_t completionToken, CUDAStatus* status) {
+    (void)completionToken;
+    PUTER_ENTER(ctx);
+    if (batch == 0 || numHeads == 0) return ok(status);
+    if (kvHeads == 0) kvHeads = numHeads;
+    if (!decode_supported(elementDType, kvDType, numHeads, kvHeads, headDim))
+        return fail(status, -6,
+                    "paged decode attention: supported are bf16/f16 queries, KV pages of the same type or fp8-e4m3, head_dim 128, "
+                    "<= 16 query heads per KV head (got dtype %d, kv dtype %d, heads %u/%u, head_dim %u)",
+                    elementDType, kvDType, numHeads, kvHeads, headDim);
+    if (pageSize == 0 || pageCount == 0 || maxPagesPerSeq == 0) return fail(status, -2, "paged decode attention: empty page geometry");
+    const size_t kvEs = dtype_size(kvDType);
+    const size_t poolBytes = (size_t)pageCount * pageSize * kvHeads * headDim * kvEs;
+    PUTER_REQUIRE(queryRef, "query", (size_t)batch * numHeads * headDim * 2);
+    PUTER_REQUIRE(outRef, "out", (size_t)batch * numHeads * headDim * 2);
+    PUTER_REQUIRE(kPagesRef, "kPages", poolBytes);
+    PUTER_REQUIRE(vPagesRef, "vPages", poolBytes);
+    PUTER_REQUIRE(pageTableRef, "pageTable", (size_t)batch * maxPagesPerSeq * 4);
+    PUTER_REQUIRE(ctxLensRef, "ctxLens", (size_t)batch * 4);
+    const float* ks = nullptr;
+    const float* vs = nullptr;
+    if (kvDType == DT_E4M3 && kvDType != elementDType) {
+        if (kScaleRef) { PUTER_REQUIRE(kScaleRef, "kScale", (size_t)kvHeads * 4); ks = (const float*)dev_ptr(kScaleRef); }
+        if (vScaleRef) { PUTER_REQUIRE(vScaleRef, "vScale", (size_t)kvHeads * 4); vs = (const float*)dev_ptr(vScaleRef); }
+    }
+    int* flag = nullptr;
+    if (errorFlagRef) { PUTER_REQUIRE(errorFlagRef, "errorFlag", 4); flag = (int*)dev_ptr(errorFlagRef); }
+    if ((((uintptr_t)dev_ptr(kPagesRef) | (uintptr_t)dev_ptr(vPagesRef)) & 15u) != 0 || ((uintptr_t)dev_ptr(queryRef) & 3u) != 0)
+        return fail(status, -2, "paged decode attention: K/V pools must be 16-byte aligned");
+    return launch_paged_decode(ctx, elementDType, kvDType, dev_ptr(queryRef), dev_ptr(kPagesRef), dev_ptr(vPagesRef),
+                               (const int32_t*)dev_ptr(pageTableRef), (const int32_t*)dev_ptr(ctxLensRef), ks, vs, dev_ptr(outRef), flag,
+                               batch, maxPagesPerSeq, pageCount, pageSize, numHeads, kvHeads, 0, -1, status);
+}

@@ -1,0 +1,327 @@
+// RMSNorm and the fused residual-add + RMSNorm + gated-residual row kernel.
+//
+// Reference semantics (device/cpu/layernorm/compute.go:35-59,129-143,177-207,350-385):
+//   f32     ss = float32(sum in float64 of x^2);  inv = float32(1/sqrt(float64(ss)/n + eps));  out = x * (inv * gamma)
+//   16-bit  ss = storage-rounded(sum in float32 of x^2) — the dot product result is rounded to bf16/f16
+//           (device/cpu/dot/bf16_generic.go:9-21);  ms = ss / n;  inv = float32(1/sqrt(float64(ms) + eps));
+//           out = narrow((x * inv) * gamma)
+// The row sum is formed by a tree reduction here instead of a sequential loop; for f32 it is carried in
+// float64 so the float32 result is the same, for 16-bit types the float32 sum can differ in the last bits,
+// which only matters when it falls within ~1e-6 of a bf16/f16 rounding boundary.
+//
+// Layout: one 256-thread block per row (grid-stride over rows, grid = multiple of the SM count); a row is
+// read once with 16-byte loads and kept in registers between the reduction and the scaling pass.
+#include "common.cuh"
+
+namespace puter {
+
+template <int DT> struct Lanes { static constexpr int kPer = DT == DT_F32 ? 4 : 8; };
+
+template <int DT> __device__ __forceinline__ void unpack(const Vec16& v, float* f) {
+    if (DT == DT_F32) {
+#pragma unroll
+        for (int i = 0; i < 4; i++) f[i] = __uint_as_float(v.w[i]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            f[2 * i] = Storage<DT>::widen((uint16_t)(v.w[i] & 0xFFFFu));
+            f[2 * i + 1] = Storage<DT>::widen((uint16_t)(v.w[i] >> 16));
+        }
+    }
+}
+template <int DT> __device__ __forceinline__ Vec16 pack(const float* f) {
+    Vec16 v;
+    if (DT == DT_F32) {
+#pragma unroll
+        for (int i = 0; i < 4; i++) v.w[i] = __float_as_uint(f[i]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 4; i++)
+            v.w[i] = (uint32_t)Storage<DT>::narrow(f[2 * i]) | ((uint32_t)Storage<DT>::narrow(f[2 * i + 1]) << 16);
+    }
+    return v;
+}
+// rounds to the storage dtype and back (identity for f32)
+template <int DT> __device__ __forceinline__ float round_storage(float v) {
+    if (DT == DT_F32) return v;
+    return Storage<DT>::widen(Storage<DT>::narrow(v));
+}
+
+template <typename T> __device__ __forceinline__ T block_sum(T v, T* smem) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    __syncthreads();  // smem may still be read from the previous row
+    if (lane == 0) smem[warp] = v;
+    __syncthreads();
+    T t = lane < nw ? smem[lane] : T(0);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    return t;
+}
+
+template <int DT> __device__ __forceinline__ float inv_rms(double sumsq, size_t cols, double eps) {
+    if (DT == DT_F32) {
+        float ss = (float)sumsq;
+        return (float)(1.0 / sqrt((double)ss / (double)cols + eps));
+    }
+    float ss = round_storage<DT>((float)sumsq);
+    float ms = __fdiv_rn(ss, (float)cols);
+    return (float)(1.0 / sqrt((double)ms + eps));
+}
+
+struct RowArgs {
+    const void* x;         // input rows
+    const void* residual;  // FUSED: added to x first
+    const void* scale;     // gamma [cols]
+    const void* branch;    // FUSED + gated: branch rows
+    const void* mod;       // FUSED + gated: modulation [batches, modCols]
+    void* hOut;            // FUSED: x + residual (optional)
+    void* normOut;         // RMSNorm result
+    void* gatedOut;        // FUSED + gated
+    size_t rows, cols, rowsPerBatch, modCols, set;
+    double eps;
+};
+
+// MAXV 16-byte vectors per thread are cached in registers; rows longer than MAXV*blockDim vectors re-read.
+template <int DT, int MAXV, bool FUSED>
+__global__ void __launch_bounds__(256) rmsnorm_rows_kernel(RowArgs a) {
+    constexpr int PER = Lanes<DT>::kPer;
+    constexpr size_t ES = DT == DT_F32 ? 4 : 2;
+    __shared__ double smemD[32];
+    __shared__ float smemF[32];
+    const size_t nvec = a.cols / PER;
+    const bool gated = FUSED && a.branch != nullptr;
+    for (size_t row = blockIdx.x; row < a.rows; row += gridDim.x) {
+        const char* xr = (const char*)a.x + row * a.cols * ES;
+        const char* rr = FUSED ? (const char*)a.residual + row * a.cols * ES : nullptr;
+        Vec16 cache[MAXV];
+        double accD = 0.0;
+        float accF = 0.f;
+#pragma unroll
+        for (int i = 0; i < MAXV; i++) {
+            size_t v = threadIdx.x + (size_t)i * blockDim.x;
+            if (v < nvec) {
+                Vec16 in = ld_stream(xr + v * 16);
+                float f[PER];
+                unpack<DT>(in, f);
+                if (FUSED) {
+                    Vec16 rin = ld_stream(rr + v * 16);
+                    float g[PER];
+                    unpack<DT>(rin, g);
+#pragma unroll
+                    for (int j = 0; j < PER; j++) f[j] = round_storage<DT>(add(f[j], g[j]));
+                    in = pack<DT>(f);
+                    if (a.hOut) st_stream((char*)a.hOut + row * a.cols * ES + v * 16, in);
+                }
+                cache[i] = in;
+#pragma unroll
+                for (int j = 0; j < PER; j++) {
+                    if (DT == DT_F32) accD += (double)f[j] * (double)f[j];
+                    else accF = fmaf(f[j], f[j], accF);
+                }
+            }
+        }
+        // rows that do not fit the register cache: keep summing from memory
+        for (size_t v = threadIdx.x + (size_t)MAXV * blockDim.x; v < nvec; v += blockDim.x) {
+            Vec16 in = *(const Vec16*)(xr + v * 16);
+            float f[PER];
+            unpack<DT>(in, f);
+            if (FUSED) {
+                Vec16 rin = *(const Vec16*)(rr + v * 16);
+                float g[PER];
+                unpack<DT>(rin, g);
+#pragma unroll
+                for (int j = 0; j < PER; j++) f[j] = round_storage<DT>(add(f[j], g[j]));
+                if (a.hOut) *(Vec16*)((char*)a.hOut + row * a.cols * ES + v * 16) = pack<DT>(f);
+            }
+#pragma unroll
+            for (int j = 0; j < PER; j++) {
+                if (DT == DT_F32) accD += (double)f[j] * (double)f[j];
+                else accF = fmaf(f[j], f[j], accF);
+            }
+        }
+        double total = DT == DT_F32 ? block_sum<double>(accD, smemD) : (double)block_sum<float>(accF, smemF);
+        const float inv = inv_rms<DT>(total, a.cols, a.eps);
+        const size_t mo = gated ? (row / a.rowsPerBatch) * a.modCols + a.set * a.cols * 3 + a.cols * 2 : 0;
+
+        auto finish = [&](size_t v, const Vec16& hv) {
+            float h[PER], g[PER], o[PER];
+            unpack<DT>(hv, h);
+            unpack<DT>(*(const Vec16*)((const char*)a.scale + v * 16), g);
+#pragma unroll
+            for (int j = 0; j < PER; j++) {
+                if (DT == DT_F32) o[j] = mul(h[j], mul(inv, g[j]));   // x * (inv * gamma), compute.go:358-362
+                else o[j] = mul(mul(h[j], inv), g[j]);                // (x * inv) * gamma, compute.go:370-373
+            }
+            st_stream((char*)a.normOut + row * a.cols * ES + v * 16, pack<DT>(o));
+            if (gated) {
+                float b[PER], m[PER];
+                unpack<DT>(ld_stream((const char*)a.branch + row * a.cols * ES + v * 16), b);
+                unpack<DT>(*(const Vec16*)((const char*)a.mod + (mo + v * PER) * ES), m);
+#pragma unroll
+                for (int j = 0; j < PER; j++) o[j] = add(h[j], mul(m[j], b[j]));
+                st_stream((char*)a.gatedOut + row * a.cols * ES + v * 16, pack<DT>(o));
+            }
+        };
+#pragma unroll
+        for (int i = 0; i < MAXV; i++) {
+            size_t v = threadIdx.x + (size_t)i * blockDim.x;
+            if (v < nvec) finish(v, cache[i]);
+        }
+        for (size_t v = threadIdx.x + (size_t)MAXV * blockDim.x; v < nvec; v += blockDim.x) {
+            Vec16 hv;
+            if (FUSED) {
+                float f[PER], g[PER];
+                unpack<DT>(*(const Vec16*)(xr + v * 16), f);
+                unpack<DT>(*(const Vec16*)(rr + v * 16), g);
+#pragma unroll
+                for (int j = 0; j < PER; j++) f[j] = round_storage<DT>(add(f[j], g[j]));
+                hv = pack<DT>(f);
+            } else {
+                hv = *(const Vec16*)(xr + v * 16);
+            }
+            finish(v, hv);
+        }
+    }
+}
+
+// any alignment, any column count: scalar loads, same arithmetic
+template <int DT, bool FUSED>
+__global__ void __launch_bounds__(256) rmsnorm_rows_scalar_kernel(RowArgs a) {
+    using T = typename Storage<DT>::type;
+    __shared__ double smemD[32];
+    __shared__ float smemF[32];
+    const bool gated = FUSED && a.branch != nullptr;
+    for (size_t row = blockIdx.x; row < a.rows; row += gridDim.x) {
+        const T* xr = (const T*)a.x + row * a.cols;
+        const T* rr = FUSED ? (const T*)a.residual + row * a.cols : nullptr;
+        double accD = 0.0;
+        float accF = 0.f;
+        for (size_t c = threadIdx.x; c < a.cols; c += blockDim.x) {
+            float h = Storage<DT>::load(xr, c);
+            if (FUSED) h = round_storage<DT>(add(h, Storage<DT>::load(rr, c)));
+            if (DT == DT_F32) accD += (double)h * (double)h;
+            else accF = fmaf(h, h, accF);
+        }
+        double total = DT == DT_F32 ? block_sum<double>(accD, smemD) : (double)block_sum<float>(accF, smemF);
+        const float inv = inv_rms<DT>(total, a.cols, a.eps);
+        const size_t mo = gated ? (row / a.rowsPerBatch) * a.modCols + a.set * a.cols * 3 + a.cols * 2 : 0;
+        for (size_t c = threadIdx.x; c < a.cols; c += blockDim.x) {
+            float h = Storage<DT>::load(xr, c);
+            if (FUSED) {
+                h = round_storage<DT>(add(h, Storage<DT>::load(rr, c)));
+                if (a.hOut) Storage<DT>::store((T*)a.hOut, row * a.cols + c, h);
+            }
+            float g = Storage<DT>::load((const T*)a.scale, c);
+            float o = DT == DT_F32 ? mul(h, mul(inv, g)) : mul(mul(h, inv), g);
+            Storage<DT>::store((T*)a.normOut, row * a.cols + c, o);
+            if (gated) {
+                float b = Storage<DT>::load((const T*)a.branch, row * a.cols + c);
+                float m = Storage<DT>::load((const T*)a.mod, mo + c);
+                Storage<DT>::store((T*)a.gatedOut, row * a.cols + c, add(h, mul(m, b)));
+            }
+        }
+    }
+}
+
+template <int DT, bool FUSED>
+static int launch_rows(Context* ctx, const RowArgs& a, CUDAStatus* status) {
+    constexpr int PER = Lanes<DT>::kPer;
+    uintptr_t bits = (uintptr_t)a.x | (uintptr_t)a.residual | (uintptr_t)a.scale | (uintptr_t)a.branch | (uintptr_t)a.mod |
+                     (uintptr_t)a.hOut | (uintptr_t)a.normOut | (uintptr_t)a.gatedOut;
+    bool vec = (bits & 15u) == 0 && a.cols % PER == 0 && (a.branch == nullptr || a.modCols % PER == 0);
+    size_t cap = (size_t)ctx->smCount * 8;
+    int grid = (int)(a.rows < cap ? a.rows : cap);
+    if (vec) rmsnorm_rows_kernel<DT, 4, FUSED><<<grid, 256, 0, ctx->stream>>>(a);
+    else rmsnorm_rows_scalar_kernel<DT, FUSED><<<grid, 256, 0, ctx->stream>>>(a);
+    return check_launch(ctx, status, FUSED ? "add+rmsnorm+gated residual" : "rmsnorm");
+}
+
+template <bool FUSED>
+static int dispatch_rows(Context* ctx, int dt, const RowArgs& a, CUDAStatus* status) {
+    if (dt == DT_F32) return launch_rows<DT_F32, FUSED>(ctx, a, status);
+    if (dt == DT_BF16) return launch_rows<DT_BF16, FUSED>(ctx, a, status);
+    if (dt == DT_F16) return launch_rows<DT_F16, FUSED>(ctx, a, status);
+    return fail(status, -6, "layernorm: unsupported dtype %d", dt);
+}
+
+}  // namespace puter
+
+using namespace puter;
+
+extern "C" int cuda_dispatch_rmsnorm_f64(CUDADeviceRef contextRef, int elementDType, CUDABufferRef inputRef, CUDABufferRef scaleRef,
+                                         CUDABufferRef outputRef, uint32_t rows, uint32_t cols, double epsilon, uint64_t completionToken,
+                                         CUDAStatus* status) {
+    (void)completionToken;
+    PUTER_ENTER(ctx);
+    if (rows == 0 || cols == 0) return ok(status);
+    if (!(epsilon > 0)) return fail(status, -2, "rmsnorm: epsilon must be positive, got %g", epsilon);
+    size_t es = dtype_size(elementDType);
+    if (elementDType != DT_F32 && elementDType != DT_F16 && elementDType != DT_BF16)
+        return fail(status, -6, "layernorm: unsupported dtype %d", elementDType);
+    PUTER_REQUIRE(inputRef, "input", (size_t)rows * cols * es);
+    PUTER_REQUIRE(scaleRef, "scale", (size_t)cols * es);
+    PUTER_REQUIRE(outputRef, "output", (size_t)rows * cols * es);
+    RowArgs a{};
+    a.x = dev_ptr(inputRef);
+    a.scale = dev_ptr(scaleRef);
+    a.normOut = dev_ptr(outputRef);
+    a.rows = rows;
+    a.cols = cols;
+    a.eps = epsilon;
+    return dispatch_rows<false>(ctx, elementDType, a, status);
+}
+
+extern "C" int cuda_dispatch_rmsnorm(CUDADeviceRef contextRef, int elementDType, CUDABufferRef inputRef, CUDABufferRef scaleRef,
+                                     CUDABufferRef outputRef, uint32_t rows, uint32_t cols, float epsilon, uint64_t completionToken,
+                                     CUDAStatus* status) {
+    return cuda_dispatch_rmsnorm_f64(contextRef, elementDType, inputRef, scaleRef, outputRef, rows, cols, (double)epsilon,
+                                     completionToken, status);
+}
+
+extern "C" int cuda_dispatch_add_rmsnorm_gated_residual(CUDADeviceRef contextRef, int elementDType, CUDABufferRef xRef,
+                                                        CUDABufferRef residualRef, CUDABufferRef scaleRef, CUDABufferRef branchRef,
+                                                        CUDABufferRef modulationRef, CUDABufferRef hOutRef, CUDABufferRef normOutRef,
+                                                        CUDABufferRef gatedOutRef, uint32_t rows, uint32_t cols, double epsilon,
+                                                        uint32_t rowsPerBatch, uint32_t modulationCols, uint32_t set,
+                                                        uint64_t completionToken, CUDAStatus* status) {
+    (void)completionToken;
+    PUTER_ENTER(ctx);
+    if (rows == 0 || cols == 0) return ok(status);
+    if (!(epsilon > 0)) return fail(status, -2, "rmsnorm: epsilon must be positive, got %g", epsilon);
+    size_t es = dtype_size(elementDType);
+    if (elementDType != DT_F32 && elementDType != DT_F16 && elementDType != DT_BF16)
+        return fail(status, -6, "layernorm: unsupported dtype %d", elementDType);
+    size_t bytes = (size_t)rows * cols * es;
+    PUTER_REQUIRE(xRef, "x", bytes);
+    PUTER_REQUIRE(residualRef, "residual", bytes);
+    PUTER_REQUIRE(scaleRef, "scale", (size_t)cols * es);
+    PUTER_REQUIRE(normOutRef, "normOut", bytes);
+    RowArgs a{};
+    a.x = dev_ptr(xRef);
+    a.residual = dev_ptr(residualRef);
+    a.scale = dev_ptr(scaleRef);
+    a.normOut = dev_ptr(normOutRef);
+    a.hOut = hOutRef ? dev_ptr(hOutRef) : nullptr;
+    a.rows = rows;
+    a.cols = cols;
+    a.eps = epsilon;
+    if (branchRef) {
+        if (rowsPerBatch == 0) return fail(status, -2, "gated residual: rows per batch must be positive");
+        if ((uint64_t)modulationCols < ((uint64_t)set * 3 + 3) * cols)
+            return fail(status, -2, "gated residual: modulation has %u columns, set %u needs %llu", modulationCols, set,
+                        (unsigned long long)(((uint64_t)set * 3 + 3) * cols));
+        size_t batches = ((size_t)rows + rowsPerBatch - 1) / rowsPerBatch;
+        PUTER_REQUIRE(branchRef, "branch", bytes);
+        PUTER_REQUIRE(modulationRef, "modulation", batches * modulationCols * es);
+        PUTER_REQUIRE(gatedOutRef, "gatedOut", bytes);
+        a.branch = dev_ptr(branchRef);
+        a.mod = dev_ptr(modulationRef);
+        a.gatedOut = dev_ptr(gatedOutRef);
+        a.rowsPerBatch = rowsPerBatch;
+        a.modCols = modulationCols;
+        a.set = set;
+    }
+    return dispatch_rows<true>(ctx, elementDType, a, status);
+}

@@ -1,0 +1,260 @@
+// Rotary position embedding (device.RoPE.RoPE / RoPEPairs).
+//
+// Reference semantics (device/cpu/rope/compute.go:55-193): per position the angle
+// theta = float64(seq + StartPosition) * inverseFrequency(pair) is formed in float64, with
+// inverseFrequency = BaseFreq^(-2*pair/headDim) optionally rescaled by the Llama-3 rule (:109-126);
+// cos/sin are taken in float64 and cast to float32; pairs are rotated in float32 with separate
+// multiplies and a subtract/add (no fused multiply-add): e' = e*c - o*s, o' = e*s + o*c.
+// Interleaved mode pairs (2i, 2i+1); half mode pairs (i, i + headDim/2).  Layout [seq, heads, headDim].
+//
+// Two kernels: a table kernel evaluates the float64 angles once per (position, pair) into a
+// float32 cos/sin table (a few MB, L2-resident); the rotate kernel streams the activations with
+// 16-byte vectors and reads the table through the cache.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace puter {
+
+struct InvFreq {
+    double v[128];  // head dimensions up to 256
+};
+
+__global__ void rope_table_kernel(float* __restrict__ cosT, float* __restrict__ sinT, InvFreq inv, int half, long long seqLen,
+                                  long long startPos) {
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= seqLen * half) return;
+    long long s = i / half;
+    int p = (int)(i % half);
+    double theta = __dmul_rn((double)(s + startPos), inv.v[p]);
+    double sn, cs;
+    sincos(theta, &sn, &cs);
+    cosT[i] = (float)cs;
+    sinT[i] = (float)sn;
+}
+
+template <int DT> struct Lanes { static constexpr int kPer = DT == DT_F32 ? 4 : 8; };
+template <int DT> __device__ __forceinline__ void unpack(const Vec16& v, float* f) {
+    if (DT == DT_F32) {
+#pragma unroll
+        for (int i = 0; i < 4; i++) f[i] = __uint_as_float(v.w[i]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            f[2 * i] = Storage<DT>::widen((uint16_t)(v.w[i] & 0xFFFFu));
+            f[2 * i + 1] = Storage<DT>::widen((uint16_t)(v.w[i] >> 16));
+        }
+    }
+}
+template <int DT> __device__ __forceinline__ Vec16 pack(const float* f) {
+    Vec16 v;
+    if (DT == DT_F32) {
+#pragma unroll
+        for (int i = 0; i < 4; i++) v.w[i] = __float_as_uint(f[i]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 4; i++)
+            v.w[i] = (uint32_t)Storage<DT>::narrow(f[2 * i]) | ((uint32_t)Storage<DT>::narrow(f[2 * i + 1]) << 16);
+    }
+    return v;
+}
+
+// vector path: headDim % (2*PER) == 0 and 16-byte aligned buffers
+template <int DT, bool HALF>
+__global__ void __launch_bounds__(256) rope_rotate_kernel(const void* __restrict__ in, void* __restrict__ out,
+                                                         const float* __restrict__ cosT, const float* __restrict__ sinT,
+                                                         size_t seqLen, size_t heads, size_t headDim) {
+    constexpr int PER = Lanes<DT>::kPer;
+    constexpr size_t ES = DT == DT_F32 ? 4 : 2;
+    const size_t half = headDim / 2;
+    // HALF: a work item rotates PER pairs (two vectors PER apart by `half`); interleaved: PER/2 pairs (one vector)
+    const size_t itemsPerHead = HALF ? half / PER : headDim / PER;
+    const size_t total = seqLen * heads * itemsPerHead;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t it = (size_t)blockIdx.x * blockDim.x + threadIdx.x; it < total; it += stride) {
+        size_t j = it % itemsPerHead;
+        size_t sh = it / itemsPerHead;  // seq * heads + head
+        size_t s = sh / heads;
+        size_t base = sh * headDim;
+        if (HALF) {
+            size_t p0 = j * PER;
+            Vec16 ve = ld_stream((const char*)in + (base + p0) * ES);
+            Vec16 vo = ld_stream((const char*)in + (base + half + p0) * ES);
+            float e[PER], o[PER], re[PER], ro[PER];
+            unpack<DT>(ve, e);
+            unpack<DT>(vo, o);
+#pragma unroll
+            for (int i = 0; i < PER; i++) {
+                float c = __ldg(cosT + s * half + p0 + i), sn = __ldg(sinT + s * half + p0 + i);
+                re[i] = sub(mul(e[i], c), mul(o[i], sn));
+                ro[i] = add(mul(e[i], sn), mul(o[i], c));
+            }
+            st_stream((char*)out + (base + p0) * ES, pack<DT>(re));
+            st_stream((char*)out + (base + half + p0) * ES, pack<DT>(ro));
+        } else {
+            size_t p0 = j * (PER / 2);
+            Vec16 v = ld_stream((const char*)in + (base + 2 * p0) * ES);
+            float f[PER], r[PER];
+            unpack<DT>(v, f);
+#pragma unroll
+            for (int i = 0; i < PER / 2; i++) {
+                float c = __ldg(cosT + s * half + p0 + i), sn = __ldg(sinT + s * half + p0 + i);
+                r[2 * i] = sub(mul(f[2 * i], c), mul(f[2 * i + 1], sn));
+                r[2 * i + 1] = add(mul(f[2 * i], sn), mul(f[2 * i + 1], c));
+            }
+            st_stream((char*)out + (base + 2 * p0) * ES, pack<DT>(r));
+        }
+    }
+}
+
+// scalar path: one thread per pair
+template <int DT>
+__global__ void __launch_bounds__(256) rope_rotate_scalar_kernel(const void* __restrict__ in, void* __restrict__ out,
+                                                                const float* __restrict__ cosT, const float* __restrict__ sinT,
+                                                                size_t seqLen, size_t heads, size_t headDim, int halfMode) {
+    using T = typename Storage<DT>::type;
+    const size_t half = headDim / 2;
+    const size_t total = seqLen * heads * half;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t it = (size_t)blockIdx.x * blockDim.x + threadIdx.x; it < total; it += stride) {
+        size_t p = it % half, sh = it / half, s = sh / heads, base = sh * headDim;
+        size_t ei = halfMode ? base + p : base + 2 * p;
+        size_t oi = halfMode ? base + half + p : ei + 1;
+        float e = Storage<DT>::load((const T*)in, ei), o = Storage<DT>::load((const T*)in, oi);
+        float c = cosT[s * half + p], sn = sinT[s * half + p];
+        Storage<DT>::store((T*)out, ei, sub(mul(e, c), mul(o, sn)));
+        Storage<DT>::store((T*)out, oi, add(mul(e, sn), mul(o, c)));
+    }
+}
+
+__global__ void rope_pairs_kernel(const float* __restrict__ in, float* __restrict__ out, const float* __restrict__ cosB,
+                                  const float* __restrict__ sinB, size_t half) {
+    size_t p = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (p >= half) return;
+    float e = in[2 * p], o = in[2 * p + 1], c = cosB[p], s = sinB[p];
+    out[2 * p] = sub(mul(e, c), mul(o, s));
+    out[2 * p + 1] = add(mul(e, s), mul(o, c));
+}
+
+// host: inverse frequencies in float64, as ropeInverseFrequency / llama3ScaledInverseFrequency
+// (device/cpu/rope/compute.go:98-126)
+static void fill_inv_freq(InvFreq* inv, int half, int headDim, double base, int scaling, double factor, double low, double high,
+                          int origCtx) {
+    for (int p = 0; p < half; p++) {
+        double exponent = -(double)(2 * p) / (double)headDim;
+        double f = pow(base, exponent);
+        if (scaling == 1) {
+            double wavelength = (2.0 * M_PI) / f;
+            double lowW = (double)origCtx / low;
+            double highW = (double)origCtx / high;
+            if (wavelength > lowW) f = f / factor;
+            else if (!(wavelength < highW)) {
+                double smooth = ((double)origCtx / wavelength - low) / (high - low);
+                f = (1.0 - smooth) * (f / factor) + smooth * f;
+            }
+        }
+        inv->v[p] = f;
+    }
+}
+
+// Validates the config the way device.RoPEConfig.Validate does (device/config.go:215-258).
+int validate_rope(CUDAStatus* status, double base, uint32_t halfMode, uint32_t scaling, double factor, double low, double high,
+                  uint32_t origCtx) {
+    if (!(base > 0)) return fail(status, -2, "rope: base frequency must be positive, got %g", base);
+    if (halfMode > 1) return fail(status, -2, "rope: unsupported mode %u", halfMode);
+    if (scaling > 1) return fail(status, -2, "rope: unsupported scaling %u", scaling);
+    if (scaling == 1) {
+        if (!(factor > 0)) return fail(status, -2, "rope: scaling factor must be positive, got %g", factor);
+        if (!(low > 0)) return fail(status, -2, "rope: low frequency factor must be positive, got %g", low);
+        if (!(high > low)) return fail(status, -2, "rope: high frequency factor %g must exceed low frequency factor %g", high, low);
+        if (origCtx == 0) return fail(status, -2, "rope: original context must be positive, got 0");
+    }
+    return 0;
+}
+
+// Builds the cos/sin table for positions startPos .. startPos+seqLen-1 at `table` (cos then sin, seqLen*half floats each).
+int build_rope_table(Context* ctx, float* table, size_t seqLen, int headDim, double base, long long startPos, int scaling,
+                     double factor, double low, double high, int origCtx, CUDAStatus* status) {
+    int half = headDim / 2;
+    if (half > 128) return fail(status, -6, "rope: head dimension %d exceeds the supported maximum of 256", headDim);
+    InvFreq inv;
+    fill_inv_freq(&inv, half, headDim, base, scaling, factor, low, high, origCtx);
+    size_t n = seqLen * (size_t)half;
+    rope_table_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(table, table + n, inv, half, (long long)seqLen, startPos);
+    return check_launch(ctx, status, "rope table");
+}
+
+}  // namespace puter
+
+using namespace puter;
+
+extern "C" int cuda_dispatch_rope_f64(CUDADeviceRef contextRef, int elementDType, CUDABufferRef inputRef, CUDABufferRef outRef,
+                                      uint32_t seqLen, uint32_t numHeads, uint32_t headDim, double baseFreq, int64_t startPosition,
+                                      uint32_t halfMode, uint32_t scaling, double scalingFactor, double lowFreqFactor,
+                                      double highFreqFactor, uint32_t originalContext, uint64_t completionToken, CUDAStatus* status) {
+    (void)completionToken;
+    PUTER_ENTER(ctx);
+    // device/cpu/rope/compute.go:17-19: empty or odd head dimension is a silent no-op
+    if (seqLen == 0 || numHeads == 0 || headDim == 0 || headDim % 2 != 0) return ok(status);
+    int rc = validate_rope(status, baseFreq, halfMode, scaling, scalingFactor, lowFreqFactor, highFreqFactor, originalContext);
+    if (rc != 0) return rc;
+    if (elementDType != DT_F32 && elementDType != DT_F16 && elementDType != DT_BF16)
+        return fail(status, -6, "rope: unsupported dtype %d", elementDType);
+    size_t es = dtype_size(elementDType);
+    size_t elems = (size_t)seqLen * numHeads * headDim;
+    PUTER_REQUIRE(inputRef, "input", elems * es);
+    PUTER_REQUIRE(outRef, "out", elems * es);
+    size_t half = headDim / 2;
+    float* table = (float*)ensure_workspace(ctx, (size_t)seqLen * half * 2 * sizeof(float), status);
+    if (!table) return status ? status->code : -7;
+    rc = build_rope_table(ctx, table, seqLen, (int)headDim, baseFreq, (long long)startPosition, (int)scaling, scalingFactor,
+                          lowFreqFactor, highFreqFactor, (int)originalContext, status);
+    if (rc != 0) return rc;
+    const float* cosT = table;
+    const float* sinT = table + (size_t)seqLen * half;
+    const void* in = dev_ptr(inputRef);
+    void* out = dev_ptr(outRef);
+    int per = elementDType == DT_F32 ? 4 : 8;
+    bool vec = (((uintptr_t)in | (uintptr_t)out) & 15u) == 0 && (halfMode ? half % per == 0 : headDim % per == 0);
+    size_t items = vec ? elems / per : elems / 2;
+    size_t blocks = (items + 255) / 256, cap = (size_t)ctx->smCount * 16;
+    int grid = (int)(blocks < cap ? (blocks ? blocks : 1) : cap);
+#define ROPE_LAUNCH(DT)                                                                                                  \
+    do {                                                                                                                 \
+        if (!vec) rope_rotate_scalar_kernel<DT><<<grid, 256, 0, ctx->stream>>>(in, out, cosT, sinT, seqLen, numHeads, headDim, (int)halfMode); \
+        else if (halfMode) rope_rotate_kernel<DT, true><<<grid, 256, 0, ctx->stream>>>(in, out, cosT, sinT, seqLen, numHeads, headDim); \
+        else rope_rotate_kernel<DT, false><<<grid, 256, 0, ctx->stream>>>(in, out, cosT, sinT, seqLen, numHeads, headDim); \
+    } while (0)
+    if (elementDType == DT_F32) ROPE_LAUNCH(DT_F32);
+    else if (elementDType == DT_BF16) ROPE_LAUNCH(DT_BF16);
+    else ROPE_LAUNCH(DT_F16);
+#undef ROPE_LAUNCH
+    return check_launch(ctx, status, "rope");
+}
+
+extern "C" int cuda_dispatch_rope(CUDADeviceRef contextRef, int elementDType, CUDABufferRef inputRef, CUDABufferRef outRef,
+                                  uint32_t seqLen, uint32_t numHeads, uint32_t headDim, uint32_t pairCount, float theta, float ropeFactor,
+                                  float lowFreqFactor, float highFreqFactor, uint32_t originalContext, uint32_t halfMode,
+                                  uint32_t positionOffset, uint64_t completionToken, CUDAStatus* status) {
+    (void)pairCount;
+    uint32_t scaling = (ropeFactor > 0.0f && originalContext > 0 && ropeFactor != 1.0f) ? 1u : 0u;
+    return cuda_dispatch_rope_f64(contextRef, elementDType, inputRef, outRef, seqLen, numHeads, headDim, (double)theta,
+                                  (int64_t)positionOffset, halfMode, scaling, (double)ropeFactor, (double)lowFreqFactor,
+                                  (double)highFreqFactor, originalContext, completionToken, status);
+}
+
+extern "C" int cuda_dispatch_rope_pairs(CUDADeviceRef contextRef, int elementDType, CUDABufferRef inputRef, CUDABufferRef outRef,
+                                        CUDABufferRef cosRef, CUDABufferRef sinRef, uint32_t halfDim, uint64_t completionToken,
+                                        CUDAStatus* status) {
+    (void)completionToken;
+    PUTER_ENTER(ctx);
+    if (elementDType != DT_F32) return fail(status, -6, "rope: RoPEPairs unsupported dtype");  // device/cpu/rope/ops.go:10-14
+    if (halfDim == 0) return ok(status);
+    PUTER_REQUIRE(inputRef, "input", (size_t)halfDim * 8);
+    PUTER_REQUIRE(outRef, "out", (size_t)halfDim * 8);
+    PUTER_REQUIRE(cosRef, "cos", (size_t)halfDim * 4);
+    PUTER_REQUIRE(sinRef, "sin", (size_t)halfDim * 4);
+    rope_pairs_kernel<<<(halfDim + 255) / 256, 256, 0, ctx->stream>>>((const float*)dev_ptr(inputRef), (float*)dev_ptr(outRef),
+                                                                      (const float*)dev_ptr(cosRef), (const float*)dev_ptr(sinRef), halfDim);
+    return check_launch(ctx, status, "rope pairs");
+}

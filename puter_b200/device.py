@@ -1,0 +1,323 @@
+"""``Device``: the hot-path subset of puter's ``device.Backend`` over the C ABI.
+
+Method names, argument order and error behaviour follow ``device/interface.go``; configs follow
+``device/config.go``.  Tensor arguments are CUDA ``torch.Tensor`` objects used purely as device memory
+(their ``data_ptr`` is wrapped in a non-owning ``CUDABufferRef``); dims and the element ``format`` are passed
+explicitly, as in the Go interface.  A failing call raises ``DeviceError`` — the counterpart of the panic in
+the reference's void methods (device/cuda/compute_host.go:42-46).  Zero-sized problems are silent no-ops.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+
+from . import _lib, dtypes
+
+# op codes (include/puter_b200.h)
+UNARY = {"Relu": 0, "Tanh": 12, "Sigmoid": 13, "Silu": 14, "Gelu": 22, "GeluTanh": 29}
+BINARY = {"Add": 0, "Sub": 1, "Mul": 2, "Div": 3, "Max": 4, "Min": 5}
+GATED = {"SwiGLU": "swiglu", "GeGLU": "geglu", "GLU": "glu", "ReGLU": "reglu", "SiGLU": "siglu", "GeGLUTanh": "geglu_tanh"}
+
+RoPEModeInterleaved, RoPEModeHalf = 0, 1
+RoPEScalingNone, RoPEScalingLlama3 = 0, 1
+
+
+class DeviceError(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__(f"[{code}] {message}")
+        self.code = code
+        self.message = message
+
+
+@dataclass
+class RMSNormConfig:  # device/config.go:82-92
+    Epsilon: float = 1e-5
+
+
+@dataclass
+class RoPEConfig:  # device/config.go:123-134; defaults device/cpu/rope/config.go:7-15
+    BaseFreq: float = 10000.0
+    StartPosition: int = 0
+    Mode: int = RoPEModeInterleaved
+    Scaling: int = RoPEScalingNone
+    ScalingFactor: float = 1.0
+    LowFreqFactor: float = 0.0
+    HighFreqFactor: float = 0.0
+    OriginalContext: int = 0
+
+
+@dataclass
+class FlashAttentionConfig:  # device/config.go:278-281
+    BlockSize: int = 64
+    Causal: bool = False
+
+
+@dataclass
+class MultiHeadAttentionConfig:  # device/config.go:283-290
+    NumHeads: int = 1
+    HeadDim: int = 1
+    Causal: bool = False
+    WindowSize: int = 0
+    ALiBiSlope: float = 0.0
+    KVHeadCount: int = 0
+
+
+class Device:
+    """One context on one GPU.  ``Device()`` opens the current torch CUDA device."""
+
+    def __init__(self, ordinal: int | None = None, follow_torch_stream: bool = True):
+        import torch
+
+        self._torch = torch
+        self.lib = _lib.load()
+        if ordinal is None:
+            ordinal = torch.cuda.current_device() if torch.cuda.is_available() else 0
+        self.ordinal = ordinal
+        self._status = _lib.CUDAStatus()
+        ref = ctypes.c_void_p()
+        rc = self.lib.cuda_open_device_index(ordinal, ctypes.byref(ref), ctypes.byref(self._status))
+        if rc != 0 or not ref.value:
+            raise DeviceError(rc, self._status.message.decode(errors="replace"))
+        self.ref = ref
+        self.follow_torch_stream = follow_torch_stream
+
+    # ---- plumbing -------------------------------------------------------------------------------------
+    def close(self):
+        if getattr(self, "ref", None):
+            self.lib.cuda_close_device(self.ref)
+            self.ref = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _check(self, rc: int):
+        if rc != 0:
+            raise DeviceError(self._status.code, self._status.message.decode(errors="replace"))
+
+    def _enter(self):
+        if self.follow_torch_stream:
+            s = self._torch.cuda.current_stream(self.ordinal).cuda_stream
+            self.lib.cuda_context_set_stream(self.ref, ctypes.c_void_p(s), ctypes.byref(self._status))
+
+    class _Bufs:
+        def __init__(self, dev, tensors):
+            self.dev = dev
+            self.refs = []
+            for t in tensors:
+                if t is None:
+                    self.refs.append(None)
+                    continue
+                assert t.is_cuda and t.is_contiguous(), "device tensors must be contiguous CUDA memory"
+                r = dev.lib.cuda_buffer_wrap(dev.ref, ctypes.c_void_p(t.data_ptr()), t.numel() * t.element_size())
+                self.refs.append(ctypes.c_void_p(r))
+
+        def __enter__(self):
+            return self.refs
+
+        def __exit__(self, *exc):
+            for r in self.refs:
+                if r is not None:
+                    self.dev.lib.cuda_buffer_release(r)
+            return False
+
+    def _call(self, name, tensors, build_args):
+        self._enter()
+        with Device._Bufs(self, tensors) as refs:
+            args = build_args(refs)
+            rc = getattr(self.lib, name)(self.ref, *args, ctypes.byref(self._status))
+        self._check(rc)
+
+    def set_exact(self, exact: bool):
+        self._check(self.lib.cuda_context_set_exact(self.ref, int(exact), ctypes.byref(self._status)))
+
+    def launch_count(self) -> int:
+        return int(self.lib.cuda_context_launch_count(self.ref))
+
+    def take_error(self) -> int:
+        self._enter()
+        flag = ctypes.c_int(0)
+        self._check(self.lib.cuda_context_take_error(self.ref, ctypes.byref(flag), ctypes.byref(self._status)))
+        return flag.value
+
+    def synchronize(self):
+        stream = self.lib.cuda_context_default_stream(self.ref)
+        self._check(self.lib.cuda_stream_synchronize(ctypes.c_void_p(stream), ctypes.byref(self._status)))
+
+    # ---- convert package ------------------------------------------------------------------------------
+    def Convert(self, dst, src, count, dst_format, src_format):
+        """Device-side cast (execution/shape_cast_intrinsic.go:57-114 on the host in the reference)."""
+        self._call("cuda_dispatch_convert", [src, dst], lambda r: (src_format, dst_format, r[0], r[1], count, 0))
+
+    def ConvertHost(self, dst_np, src_np, dst_format, src_format):
+        """convert.<X>To<Y>(dst, src): host slices in and out (convert/bf16_f32.go:11-22 etc.).
+
+        Unequal lengths raise DeviceError(-2) like ErrLenMismatch (convert/errors.go:10-15)."""
+        self._enter()
+        rc = self.lib.cuda_convert_host(self.ref, src_format, dst_format, ctypes.c_void_p(src_np.ctypes.data), src_np.size,
+                                        ctypes.c_void_p(dst_np.ctypes.data), dst_np.size, ctypes.byref(self._status))
+        self._check(rc)
+
+    # ---- Activation -----------------------------------------------------------------------------------
+    def _unary(self, op, dst, src, count, format):
+        self._call("cuda_dispatch_unary_elementwise", [src, dst], lambda r: (UNARY[op], format, r[0], r[1], count, 0))
+
+    def Silu(self, dst, src, count, format):
+        self._unary("Silu", dst, src, count, format)
+
+    def Gelu(self, dst, src, count, format):
+        self._unary("Gelu", dst, src, count, format)
+
+    def GeluTanh(self, dst, src, count, format):
+        self._unary("GeluTanh", dst, src, count, format)
+
+    def Sigmoid(self, dst, src, count, format):
+        self._unary("Sigmoid", dst, src, count, format)
+
+    def Tanh(self, dst, src, count, format):
+        self._unary("Tanh", dst, src, count, format)
+
+    def Relu(self, dst, src, count, format):
+        self._unary("Relu", dst, src, count, format)
+
+    def _gated_packed(self, variant, dst, packed, batch, halfCount, format):
+        # the C ABI takes (inner = halfCount, count = batch): device/cuda/compute_host.go:1215-1231
+        self._call(f"cuda_dispatch_{GATED[variant]}_packed", [dst, packed], lambda r: (format, r[0], r[1], halfCount, batch, 0))
+
+    def _gated_tensors(self, variant, dst, gate, up, count, format):
+        self._call(f"cuda_dispatch_{GATED[variant]}", [dst, gate, up], lambda r: (format, r[0], r[1], r[2], count, 0))
+
+    def SwiGLU(self, dst, packed, batch, halfCount, format):
+        self._gated_packed("SwiGLU", dst, packed, batch, halfCount, format)
+
+    def SwiGLUTensors(self, dst, gate, up, count, format):
+        self._gated_tensors("SwiGLU", dst, gate, up, count, format)
+
+    def GeGLU(self, dst, packed, batch, halfCount, format):
+        self._gated_packed("GeGLU", dst, packed, batch, halfCount, format)
+
+    def GeGLUTensors(self, dst, gate, up, count, format):
+        self._gated_tensors("GeGLU", dst, gate, up, count, format)
+
+    def GeGLUTanh(self, dst, packed, batch, halfCount, format):
+        self._gated_packed("GeGLUTanh", dst, packed, batch, halfCount, format)
+
+    def GeGLUTanhTensors(self, dst, gate, up, count, format):
+        self._gated_tensors("GeGLUTanh", dst, gate, up, count, format)
+
+    def GLU(self, dst, packed, batch, halfCount, format):
+        self._gated_packed("GLU", dst, packed, batch, halfCount, format)
+
+    def GLUTensors(self, dst, gate, up, count, format):
+        self._gated_tensors("GLU", dst, gate, up, count, format)
+
+    def ReGLU(self, dst, packed, batch, halfCount, format):
+        self._gated_packed("ReGLU", dst, packed, batch, halfCount, format)
+
+    def ReGLUTensors(self, dst, gate, up, count, format):
+        self._gated_tensors("ReGLU", dst, gate, up, count, format)
+
+    def SiGLU(self, dst, packed, batch, halfCount, format):
+        self._gated_packed("SiGLU", dst, packed, batch, halfCount, format)
+
+    def SiGLUTensors(self, dst, gate, up, count, format):
+        self._gated_tensors("SiGLU", dst, gate, up, count, format)
+
+    # ---- Elementwise ----------------------------------------------------------------------------------
+    def _binary(self, op, dst, left, right, count, format):
+        self._call("cuda_dispatch_binary_elementwise", [left, right, dst], lambda r: (BINARY[op], format, r[0], r[1], r[2], count, 0))
+
+    def Add(self, dst, left, right, count, format):
+        self._binary("Add", dst, left, right, count, format)
+
+    def Sub(self, dst, left, right, count, format):
+        self._binary("Sub", dst, left, right, count, format)
+
+    def Mul(self, dst, left, right, count, format):
+        self._binary("Mul", dst, left, right, count, format)
+
+    def Div(self, dst, left, right, count, format):
+        self._binary("Div", dst, left, right, count, format)
+
+    def Max(self, dst, left, right, count, format):
+        self._binary("Max", dst, left, right, count, format)
+
+    def Min(self, dst, left, right, count, format):
+        self._binary("Min", dst, left, right, count, format)
+
+    # ---- LayerNorm ------------------------------------------------------------------------------------
+    def RMSNorm(self, config: RMSNormConfig, input, scale, output, rows, lastDim, format):
+        self._call("cuda_dispatch_rmsnorm_f64", [input, scale, output],
+                   lambda r: (format, r[0], r[1], r[2], rows, lastDim, float(config.Epsilon), 0))
+
+    def GatedResidual(self, residual, branch, modulation, output, rows, lastDim, rowsPerBatch, modulationCols, set, format):
+        """execution/math_gated_residual_intrinsic.go:11-17 (gatedResidualDevice)."""
+        self._call("cuda_dispatch_gated_residual", [residual, branch, modulation, output],
+                   lambda r: (format, r[0], r[1], r[2], r[3], rows, lastDim, rowsPerBatch, modulationCols, set, 0))
+
+    def AddRMSNormGatedResidual(self, config: RMSNormConfig, x, residual, scale, branch, modulation, hOut, normOut, gatedOut, rows,
+                                lastDim, rowsPerBatch, modulationCols, set, format):
+        """Fused Add -> RMSNorm (+ GatedResidual on the sum); catalog-style fusion (fusion/catalog.go:183-205)."""
+        self._call("cuda_dispatch_add_rmsnorm_gated_residual", [x, residual, scale, branch, modulation, hOut, normOut, gatedOut],
+                   lambda r: (format, r[0], r[1], r[2], r[3], r[4], r[5], r[6], r[7], rows, lastDim, float(config.Epsilon),
+                              rowsPerBatch, modulationCols, set, 0))
+
+    # ---- RoPE -----------------------------------------------------------------------------------------
+    def RoPE(self, config: RoPEConfig, input, output, seqLen, numHeads, headDim, format):
+        self._call("cuda_dispatch_rope_f64", [input, output],
+                   lambda r: (format, r[0], r[1], seqLen, numHeads, headDim, float(config.BaseFreq), int(config.StartPosition),
+                              int(config.Mode), int(config.Scaling), float(config.ScalingFactor), float(config.LowFreqFactor),
+                              float(config.HighFreqFactor), int(config.OriginalContext), 0))
+
+    def RoPEPairs(self, output, input, cosBuffer, sinBuffer, halfDim, format):
+        self._call("cuda_dispatch_rope_pairs", [input, output, cosBuffer, sinBuffer], lambda r: (format, r[0], r[1], r[2], r[3], halfDim, 0))
+
+    # ---- Shape: paged KV ------------------------------------------------------------------------------
+    def KVPageWrite(self, storage, values, pageIDs, offsets, output, pageCount, pageSize, inner, valueRows, storageOffset, format):
+        """execution/page_intrinsic.go:13-18 (pageIntrinsicDevice)."""
+        same = output is storage or output.data_ptr() == storage.data_ptr()
+        tensors = [storage, values, pageIDs, offsets] + ([] if same else [output])
+        self._call("cuda_dispatch_kv_page_write", tensors,
+                   lambda r: (format, r[0], r[1], r[2], r[3], r[0] if same else r[4], pageCount, pageSize, inner, valueRows,
+                              storageOffset, 0))
+
+    def KVPageGather(self, storage, pageTable, output, pageCount, pageSize, inner, outRows, storageOffset, format):
+        self._call("cuda_dispatch_kv_page_gather", [storage, pageTable, output],
+                   lambda r: (format, r[0], r[1], r[2], pageCount, pageSize, inner, outRows, storageOffset, 0))
+
+    # ---- Attention ------------------------------------------------------------------------------------
+    def MultiHeadAttention(self, config: MultiHeadAttentionConfig, query, key, value, output, seqQ, seqK, format):
+        if config.ALiBiSlope != 0:
+            raise DeviceError(-6, "attention: ALiBi is not part of this library's path (the router never sets it)")
+        kv = config.KVHeadCount if config.KVHeadCount > 0 else config.NumHeads
+        variant = 2 if config.WindowSize > 0 else (1 if kv != config.NumHeads else 0)
+        self._call("cuda_dispatch_multi_head_attention", [query, key, value, output],
+                   lambda r: (format, variant, r[0], r[1], r[2], r[3], seqQ, seqK, config.NumHeads, kv, config.HeadDim,
+                              config.WindowSize, int(config.Causal), 0))
+
+    def FlashAttention(self, config: FlashAttentionConfig, query, key, value, output, seqQ, seqK, depth, valueDim, format):
+        self._call("cuda_dispatch_flash_attention_causal", [query, key, value, output],
+                   lambda r: (format, r[0], r[1], r[2], r[3], seqQ, seqK, depth, valueDim, int(config.Causal), 0))
+
+    ScaledDotProductAttention = FlashAttention
+
+    def RoPEAttentionPrefill(self, rope: RoPEConfig | None, attn: MultiHeadAttentionConfig, query, key, value, output, batch, seqLen, format):
+        """Batched prefill: per batch item RoPE(q), RoPE(k) then causal MultiHeadAttention.  rope=None: inputs already rotated."""
+        kv = attn.KVHeadCount if attn.KVHeadCount > 0 else attn.NumHeads
+        rc = rope or RoPEConfig()
+        mode = 2 if rope is None else int(rc.Mode)
+        self._call("cuda_dispatch_rope_attention_prefill", [query, key, value, output],
+                   lambda r: (format, r[0], r[1], r[2], r[3], batch, seqLen, attn.NumHeads, kv, attn.HeadDim, int(attn.Causal), mode,
+                              float(rc.BaseFreq), int(rc.StartPosition), int(rc.Scaling), float(rc.ScalingFactor),
+                              float(rc.LowFreqFactor), float(rc.HighFreqFactor), int(rc.OriginalContext), 0))
+
+    def PagedDecodeAttention(self, attn: MultiHeadAttentionConfig, query, kPages, vPages, pageTable, ctxLens, output, batch,
+                             maxPagesPerSeq, pageCount, pageSize, format, kvFormat=None, kScale=None, vScale=None, errorFlag=None):
+        """KVPageGather(K), KVPageGather(V), MultiHeadAttention(seqQ=1, causal) per sequence, without the gathers."""
+        kv = attn.KVHeadCount if attn.KVHeadCount > 0 else attn.NumHeads
+        kvf = format if kvFormat is None else kvFormat
+        self._call("cuda_dispatch_paged_decode_attention", [query, kPages, vPages, pageTable, ctxLens, kScale, vScale, output, errorFlag],
+                   lambda r: (format, kvf, r[0], r[1], r[2], r[3], r[4], r[5], r[6], r[7], r[8], batch, maxPagesPerSeq, pageCount,
+                              pageSize, attn.NumHeads, kv, attn.HeadDim, 0))

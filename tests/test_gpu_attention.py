@@ -1,0 +1,216 @@
+"""GPU parity: attention family through the C ABI vs the CPU oracle (and the reference's literal fixtures)."""
+import numpy as np
+import pytest
+
+import oracle as O
+from gpu_util import dev, empty, host, rel_err
+
+pytestmark = pytest.mark.gpu
+ES = {O.F32: 4, O.F16: 2, O.BF16: 2, O.E4M3: 1}
+
+
+@pytest.fixture(scope="module")
+def d():
+    import puter_b200
+
+    O.build()
+    return puter_b200.Device()
+
+
+def run_mha(d, dt, q, k, v, sq, sk, hq, hkv, dim, causal=True, window=0):
+    import puter_b200
+
+    out = empty(q.size * ES[dt])
+    cfg = puter_b200.MultiHeadAttentionConfig(NumHeads=hq, HeadDim=dim, Causal=causal, WindowSize=window, KVHeadCount=hkv)
+    d.MultiHeadAttention(cfg, dev(q), dev(k), dev(v), out, sq, sk, dt)
+    return host(out, O.np_dtype(dt), (sq, hq * dim))
+
+
+def test_decode_gqa_causal_known_answer(d):
+    # device/metal/attention/multihead_parity_darwin_test.go:16-37
+    q = np.zeros((1, 4), np.float32)
+    k = np.zeros((3, 2), np.float32)
+    v = np.array([[1, 10], [2, 20], [3, 30]], np.float32)
+    got = run_mha(d, O.F32, q, k, v, 1, 3, 2, 1, 2)
+    assert np.abs(got.ravel() - np.array([2, 20, 2, 20], np.float32)).max() <= 4e-6  # <= 2 ULP as in the reference test
+
+
+def test_prefill_gqa_3x3_fixture(d):
+    # device/metal/attention/multihead_parity_darwin_test.go:39-72 (<= 8 ULP vs CPU there)
+    q = np.array([0.25, -0.50, 0.75, 0.10, -0.30, 0.20, 0.40, -0.80, 0.60, 0.90, -0.20, 0.35], np.float32).reshape(3, 4)
+    k = np.array([0.10, 0.20, -0.40, 0.30, 0.50, -0.70], np.float32).reshape(3, 2)
+    v = np.array([1, 10, 2, 20, 3, 30], np.float32).reshape(3, 2)
+    want = O.mha(O.F32, q, k, v, 3, 3, 2, 1, 2, True)
+    got = run_mha(d, O.F32, q, k, v, 3, 3, 2, 1, 2)
+    assert rel_err(got, want) <= 1e-6
+
+
+def test_softmax_infinity_rows_through_attention(d):
+    # device/cpu/attention/softmax_test.go:10-40, reached through scores: q.k = +Inf for chosen keys
+    big = np.float32(3e38)
+    q = np.array([[big, 0]], np.float32)
+    k = np.array([[1, 0], [big, 0], [2, 0]], np.float32)  # dot with key 1 overflows to +Inf
+    v = np.array([[1, 1], [5, 7], [9, 9]], np.float32)
+    want = O.mha(O.F32, q, k, v, 1, 3, 1, 1, 2, False)
+    got = run_mha(d, O.F32, q, k, v, 1, 3, 1, 1, 2, causal=False)
+    assert np.array_equal(got, want) and got.ravel().tolist() == [5, 7]
+
+
+@pytest.mark.parametrize("sq,sk,hq,hkv,dim,causal,window", [(128, 128, 8, 8, 64, True, 0), (7, 64, 4, 2, 16, True, 0),
+                                                            (33, 33, 6, 3, 40, False, 0), (1, 1024, 4, 1, 128, True, 0),
+                                                            (64, 64, 2, 2, 32, True, 9), (5, 3, 2, 1, 8, True, 0)])
+def test_mha_f32_matches_cpu_within_1e5(d, sq, sk, hq, hkv, dim, causal, window):
+    rng = np.random.default_rng(sq * sk + dim)
+    q = rng.standard_normal((sq, hq * dim)).astype(np.float32)
+    k = rng.standard_normal((sk, hkv * dim)).astype(np.float32)
+    v = rng.standard_normal((sk, hkv * dim)).astype(np.float32)
+    want = O.mha(O.F32, q, k, v, sq, sk, hq, hkv, dim, causal, window)
+    got = run_mha(d, O.F32, q, k, v, sq, sk, hq, hkv, dim, causal, window)
+    assert rel_err(got, want) <= 1e-5
+    assert (got.view(np.uint32) != want.view(np.uint32)).mean() < 0.01  # same operation order: almost always bit-equal
+
+
+@pytest.mark.parametrize("dt", [O.BF16, O.F16])
+@pytest.mark.parametrize("sq,sk,hq,hkv,dim", [(16, 16, 4, 2, 64), (9, 40, 2, 1, 32), (64, 64, 8, 8, 16)])
+def test_mha_16bit_exact_path_reproduces_rounded_scores(d, dt, sq, sk, hq, hkv, dim):
+    rng = np.random.default_rng(sq + sk)
+    q = O.from_f32(rng.standard_normal((sq, hq * dim)).astype(np.float32), dt)
+    k = O.from_f32(rng.standard_normal((sk, hkv * dim)).astype(np.float32), dt)
+    v = O.from_f32(rng.standard_normal((sk, hkv * dim)).astype(np.float32), dt)
+    want = O.mha(dt, q, k, v, sq, sk, hq, hkv, dim, True)
+    got = run_mha(d, dt, q, k, v, sq, sk, hq, hkv, dim)
+    assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("dt", [O.F32, O.BF16, O.F16])
+@pytest.mark.parametrize("sq,sk,depth,vd,causal", [(2, 2, 3, 4, False), (64, 64, 32, 32, True), (17, 50, 24, 40, False), (128, 128, 64, 64, True)])
+def test_flash_attention_single_head(d, dt, sq, sk, depth, vd, causal):
+    import puter_b200
+
+    rng = np.random.default_rng(sq * depth)
+    q = O.from_f32(rng.standard_normal((sq, depth)).astype(np.float32), dt)
+    k = O.from_f32(rng.standard_normal((sk, depth)).astype(np.float32), dt)
+    v = O.from_f32(rng.standard_normal((sk, vd)).astype(np.float32), dt)
+    want = O.sdpa(dt, q, k, v, sq, sk, depth, vd, causal)
+    out = empty(sq * vd * ES[dt])
+    d.FlashAttention(puter_b200.FlashAttentionConfig(Causal=causal), dev(q), dev(k), dev(v), out, sq, sk, depth, vd, dt)
+    got = host(out, O.np_dtype(dt), (sq, vd))
+    if dt == O.F32:
+        assert rel_err(got, want) <= 1e-5
+    else:
+        assert np.abs(O.to_f32(got, dt) - O.to_f32(want, dt)).max() <= 2e-2
+    assert (got.view(np.uint8) != want.view(np.uint8)).mean() < 0.01
+
+
+def make_paged(rng, batch, ctx_lens, page_size, hkv, dim, kv_dt, extra_pages=3):
+    pages_per = [(c + page_size - 1) // page_size for c in ctx_lens]
+    total = sum(pages_per) + extra_pages
+    max_pages = max(max(pages_per), 1)
+    perm = rng.permutation(total).astype(np.int32)
+    table = np.zeros((batch, max_pages), np.int32)
+    at = 0
+    for b, n in enumerate(pages_per):
+        table[b, :n] = perm[at:at + n]
+        at += n
+    kf = rng.standard_normal((total, page_size, hkv * dim)).astype(np.float32)
+    vf = rng.standard_normal((total, page_size, hkv * dim)).astype(np.float32)
+    ks = vs = None
+    if kv_dt == O.E4M3:
+        ks = rng.uniform(0.01, 0.1, hkv).astype(np.float32)
+        vs = rng.uniform(0.01, 0.1, hkv).astype(np.float32)
+        kq = O.from_f32((kf.reshape(total, page_size, hkv, dim) / ks[None, None, :, None]).reshape(kf.shape), O.E4M3)
+        vq = O.from_f32((vf.reshape(total, page_size, hkv, dim) / vs[None, None, :, None]).reshape(vf.shape), O.E4M3)
+    else:
+        kq, vq = O.from_f32(kf, kv_dt), O.from_f32(vf, kv_dt)
+    return table, kq, vq, ks, vs, total, max_pages
+
+
+@pytest.mark.parametrize("dt,kv_dt", [(O.BF16, O.BF16), (O.F16, O.F16), (O.BF16, O.E4M3)])
+@pytest.mark.parametrize("ctx_lens,page_size,hq,hkv", [([1], 16, 32, 8), ([3, 17, 0, 512, 100], 16, 32, 8), ([700, 33], 16, 8, 8),
+                                                       ([250, 1, 77], 16, 16, 1), ([90, 300], 32, 12, 4), ([45, 130], 4, 8, 2),
+                                                       ([2048, 1500, 16, 999], 16, 32, 8), ([64, 65], 16, 48, 16)])
+def test_paged_decode_matches_gather_then_mha(d, dt, kv_dt, ctx_lens, page_size, hq, hkv):
+    import puter_b200
+
+    dim = 128
+    batch = len(ctx_lens)
+    rng = np.random.default_rng(sum(ctx_lens) + page_size + hq)
+    table, kq, vq, ks, vs, total, max_pages = make_paged(rng, batch, ctx_lens, page_size, hkv, dim, kv_dt)
+    q = O.from_f32(rng.standard_normal((batch, hq * dim)).astype(np.float32), dt)
+    ctx = np.array(ctx_lens, np.int32)
+    want = O.paged_decode(dt, kv_dt, q, kq, vq, table, ctx, page_size, hq, hkv, dim, ks, vs)
+    sentinel = np.full(q.shape, 0x5151, np.uint16)
+    out = dev(sentinel)
+    cfg = puter_b200.MultiHeadAttentionConfig(NumHeads=hq, HeadDim=dim, Causal=True, KVHeadCount=hkv)
+    d.PagedDecodeAttention(cfg, dev(q), dev(kq), dev(vq), dev(table), dev(ctx), out, batch, max_pages, total, page_size, dt,
+                           kvFormat=kv_dt, kScale=None if ks is None else dev(ks), vScale=None if vs is None else dev(vs))
+    got = host(out, np.uint16, q.shape)
+    assert d.take_error() == 0
+    for b, c in enumerate(ctx_lens):
+        if c == 0:
+            assert np.array_equal(got[b], sentinel[b])  # empty context: row untouched
+        else:
+            err = np.abs(O.to_f32(got[b], dt) - O.to_f32(want[b], dt)).max()
+            assert err <= 2e-2, (b, c, err)
+    live = np.array(ctx_lens) > 0
+    assert (got[live] != want[live]).mean() < 0.05  # rounded scores are reproduced: nearly all outputs bit-equal
+
+
+def test_paged_decode_flags_bad_page_ids_and_long_contexts(d):
+    import puter_b200
+
+    rng = np.random.default_rng(5)
+    hq, hkv, dim, ps = 8, 2, 128, 16
+    table, kq, vq, _, _, total, max_pages = make_paged(rng, 2, [40, 40], ps, hkv, dim, O.BF16)
+    q = O.from_f32(rng.standard_normal((2, hq * dim)).astype(np.float32), O.BF16)
+    cfg = puter_b200.MultiHeadAttentionConfig(NumHeads=hq, HeadDim=dim, Causal=True, KVHeadCount=hkv)
+    bad = table.copy()
+    bad[0, 1] = total + 100
+    out = empty(q.nbytes)
+    d.PagedDecodeAttention(cfg, dev(q), dev(kq), dev(vq), dev(bad), dev(np.array([40, 40], np.int32)), out, 2, max_pages, total, ps, O.BF16)
+    assert d.take_error() == 1
+    d.PagedDecodeAttention(cfg, dev(q), dev(kq), dev(vq), dev(table), dev(np.array([40, 4000], np.int32)), out, 2, max_pages, total, ps, O.BF16)
+    assert d.take_error() == 1
+    with pytest.raises(puter_b200.DeviceError):  # unsupported head_dim is refused, not approximated
+        bad_cfg = puter_b200.MultiHeadAttentionConfig(NumHeads=8, HeadDim=64, Causal=True, KVHeadCount=2)
+        d.PagedDecodeAttention(bad_cfg, dev(q), dev(kq), dev(vq), dev(table), dev(np.array([40, 40], np.int32)), out, 2, max_pages, total, ps, O.BF16)
+
+
+@pytest.mark.parametrize("dt", [O.BF16, O.F16])
+@pytest.mark.parametrize("sk,hq,hkv", [(1, 8, 2), (100, 32, 8), (3000, 4, 4)])
+def test_mha_decode_fast_path_seqq1(d, dt, sk, hq, hkv):
+    rng = np.random.default_rng(sk)
+    dim = 128
+    q = O.from_f32(rng.standard_normal((1, hq * dim)).astype(np.float32), dt)
+    k = O.from_f32(rng.standard_normal((sk, hkv * dim)).astype(np.float32), dt)
+    v = O.from_f32(rng.standard_normal((sk, hkv * dim)).astype(np.float32), dt)
+    want = O.mha(dt, q, k, v, 1, sk, hq, hkv, dim, True)
+    got = run_mha(d, dt, q, k, v, 1, sk, hq, hkv, dim)
+    assert np.abs(O.to_f32(got, dt) - O.to_f32(want, dt)).max() <= 2e-2
+    d.set_exact(True)
+    try:
+        assert np.array_equal(run_mha(d, dt, q, k, v, 1, sk, hq, hkv, dim), want)
+    finally:
+        d.set_exact(False)
+
+
+@pytest.mark.parametrize("mode", [0, 1])
+@pytest.mark.parametrize("batch,seq,hq,hkv,dim", [(2, 40, 4, 2, 64), (1, 130, 8, 2, 128), (2, 256, 8, 2, 128)])
+def test_rope_attention_prefill_small(d, mode, batch, seq, hq, hkv, dim):
+    import puter_b200
+
+    dt = O.BF16
+    rng = np.random.default_rng(seq + mode)
+    q = O.from_f32(rng.standard_normal((batch, seq, hq * dim)).astype(np.float32), dt)
+    k = O.from_f32(rng.standard_normal((batch, seq, hkv * dim)).astype(np.float32), dt)
+    v = O.from_f32(rng.standard_normal((batch, seq, hkv * dim)).astype(np.float32), dt)
+    out = empty(q.nbytes)
+    rope = puter_b200.RoPEConfig(BaseFreq=500000.0, Mode=mode)
+    attn = puter_b200.MultiHeadAttentionConfig(NumHeads=hq, HeadDim=dim, Causal=True, KVHeadCount=hkv)
+    d.RoPEAttentionPrefill(rope, attn, dev(q), dev(k), dev(v), out, batch, seq, dt)
+    got = host(out, np.uint16, q.shape)
+    for b in range(batch):
+        qr = O.rope(dt, q[b], seq, hq, dim, base=500000.0, mode=mode)
+        kr = O.rope(dt, k[b], seq, hkv, dim, base=500000.0, mode=mode)
+        want = O.mha(dt, qr, kr, v[b], seq, seq, hq, hkv, dim, True)
+        assert np.abs(O.to_f32(got[b], dt) - O.to_f32(want.reshape(seq, -1), dt)).max() <= 2e-2
