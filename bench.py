@@ -95,9 +95,12 @@ class ClockSampler:
 # ------------------------------------------------------------------------------------------------------------
 # workloads
 # ------------------------------------------------------------------------------------------------------------
+CTX_RANGE = [512, 32768]  # --ctx-min / --ctx-max shrink the workload for profiler captures only
+
+
 def decode_context_lengths(seed: int, batch: int = 64):
     rng = np.random.default_rng(seed)
-    return rng.integers(512, 32768, batch, endpoint=True).astype(np.int32)
+    return rng.integers(CTX_RANGE[0], CTX_RANGE[1], batch, endpoint=True).astype(np.int32)
 
 
 def decode_bytes(ctx, esize):
@@ -187,7 +190,7 @@ class DecodeWorkload:
 
     def config(self):
         return {"workload": self.name, "batch": self.batch, "query_heads": HQ, "kv_heads": HKV, "head_dim": DIM, "page_size": PAGE,
-                "ctx_len": "U[512,32768] seed 2", "kv_tokens": int(self.ctx.sum()), "kv_dtype": "e4m3+f32 scale" if self.fp8 else "bf16",
+                "ctx_len": "U[%d,%d] seed 2" % tuple(CTX_RANGE), "kv_tokens": int(self.ctx.sum()), "kv_dtype": "e4m3+f32 scale" if self.fp8 else "bf16",
                 "l2": "inputs larger than L2 (KV pool %.2f GB)" % (self.working_set / 1e9)}
 
     def metric(self):
@@ -285,10 +288,14 @@ def main():
     ap.add_argument("--workload", default="decode", choices=["decode", "decode_fp8", "prefill", "convert", "chain"])
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--ref-seqs", type=int, default=4, help="sequences in the CPU sample")
+    ap.add_argument("--ctx-min", type=int, default=512)
+    ap.add_argument("--ctx-max", type=int, default=32768, help="smaller values give a profiler-sized case; not a bench number")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-secondary", action="store_true")
     args = ap.parse_args()
-    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    CTX_RANGE[0], CTX_RANGE[1] = args.ctx_min, args.ctx_max
+    profiling = (args.ctx_min, args.ctx_max) != (512, 32768)
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" and not profiling else args.warmup
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -107,8 +107,10 @@ int cuda_stream_synchronize(CUDAStreamRef stream, CUDAStatus* status); /* runtim
 CUDADeviceRef cuda_default_context(void);                             /* runtime.c:244 */
 CUDAStreamRef cuda_context_upload_stream(CUDADeviceRef device);       /* runtime.c:248 */
 CUDAStreamRef cuda_context_default_stream(CUDADeviceRef device);      /* core_private.h:97 */
-/* NEW: launch on a stream owned by the embedding framework (NULL restores the context's own) */
+/* NEW: launch on a stream owned by the embedding framework; NULL is the legacy default stream (stream 0) */
 int cuda_context_set_stream(CUDADeviceRef device, void* cudaStream, CUDAStatus* status);
+/* NEW: go back to the context's own non-blocking stream */
+int cuda_context_reset_stream(CUDADeviceRef device, CUDAStatus* status);
 /* NEW: 1 = always use the kernels that reproduce device/cpu operation order exactly
    (sequential sums); 0 (default) = use the tensor-core / split-KV kernels where they apply */
 int cuda_context_set_exact(CUDADeviceRef device, int exact, CUDAStatus* status);

@@ -44,6 +44,7 @@ SIGNATURES = {
     "cuda_context_upload_stream": (vp, [vp]),
     "cuda_context_default_stream": (vp, [vp]),
     "cuda_context_set_stream": (cint, [vp, vp, SP]),
+    "cuda_context_reset_stream": (cint, [vp, SP]),
     "cuda_context_set_exact": (cint, [vp, cint, SP]),
     "cuda_context_take_error": (cint, [vp, ctypes.POINTER(cint), SP]),
     "cuda_context_launch_count": (ctypes.c_ulonglong, [vp]),

@@ -242,7 +242,15 @@ int cuda_context_set_stream(CUDADeviceRef device, void* cudaStream, CUDAStatus* 
     cuda_status_clear(status);
     Context* ctx = ctx_of(device, status);
     if (!ctx) return -1;
-    ctx->stream = cudaStream ? (cudaStream_t)cudaStream : ctx->ownStream;
+    ctx->stream = (cudaStream_t)cudaStream;  // NULL = the legacy default stream
+    return ok(status);
+}
+
+int cuda_context_reset_stream(CUDADeviceRef device, CUDAStatus* status) {
+    cuda_status_clear(status);
+    Context* ctx = ctx_of(device, status);
+    if (!ctx) return -1;
+    ctx->stream = ctx->ownStream;
     return ok(status);
 }
 

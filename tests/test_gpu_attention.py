@@ -49,7 +49,7 @@ def test_softmax_infinity_rows_through_attention(d):
     # device/cpu/attention/softmax_test.go:10-40, reached through scores: q.k = +Inf for chosen keys
     big = np.float32(3e38)
     q = np.array([[big, 0]], np.float32)
-    k = np.array([[1, 0], [big, 0], [2, 0]], np.float32)  # dot with key 1 overflows to +Inf
+    k = np.array([[1, 0], [big, 0], [0.5, 0]], np.float32)  # only the dot with key 1 overflows to +Inf
     v = np.array([[1, 1], [5, 7], [9, 9]], np.float32)
     want = O.mha(O.F32, q, k, v, 1, 3, 1, 1, 2, False)
     got = run_mha(d, O.F32, q, k, v, 1, 3, 1, 1, 2, causal=False)
