@@ -253,6 +253,21 @@ int cuda_dispatch_paged_decode_attention(CUDADeviceRef contextRef, int elementDT
                                          uint32_t pageCount, uint32_t pageSize, uint32_t numHeads, uint32_t kvHeads,
                                          uint32_t headDim, uint64_t completionToken, CUDAStatus* status);
 
+/* No counterpart in the reference.  For callers that cannot allocate device memory when a decode step runs: a
+   server whose GPU memory is fully pre-planned and owned by its own arena, code in a latency-critical section that
+   cannot afford the device-wide synchronisation hidden in cudaMalloc/cudaFree, or a runtime that forbids driver
+   allocations after start-up.  Same operation and arguments as cuda_dispatch_paged_decode_attention, but the
+   split-KV scratch is a fixed 8 MiB array that is part of the library image (held by every GPU that loads the
+   library until exit) and the call performs no cudaMalloc/cudaFree.  Problems that need more scratch are refused
+   with -2 (32 query heads, 148 SMs: batch <= 355).  The first call on a device resolves the array's address;
+   make it before any stream capture.  All calls on a GPU share the array: calls that can overlap on the GPU race. */
+int cuda_dispatch_paged_decode_attention_noalloc(CUDADeviceRef contextRef, int elementDType, int kvDType, CUDABufferRef queryRef,
+                                                 CUDABufferRef kPagesRef, CUDABufferRef vPagesRef, CUDABufferRef pageTableRef,
+                                                 CUDABufferRef ctxLensRef, CUDABufferRef kScaleRef, CUDABufferRef vScaleRef,
+                                                 CUDABufferRef outRef, CUDABufferRef errorFlagRef, uint32_t batch, uint32_t maxPagesPerSeq,
+                                                 uint32_t pageCount, uint32_t pageSize, uint32_t numHeads, uint32_t kvHeads,
+                                                 uint32_t headDim, uint64_t completionToken, CUDAStatus* status);
+
 #if defined(__GNUC__)
 #pragma GCC visibility pop
 #endif

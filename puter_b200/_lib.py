@@ -71,6 +71,7 @@ SIGNATURES = {
     "cuda_dispatch_paged_decode_attention": (cint, [vp, cint, cint, vp, vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, u32,
                                                     u32, u64, SP]),
 }
+SIGNATURES["cuda_dispatch_paged_decode_attention_noalloc"] = SIGNATURES["cuda_dispatch_paged_decode_attention"]
 for _g in _GATED:
     SIGNATURES[f"cuda_dispatch_{_g}"] = (cint, [vp, cint, vp, vp, vp, u32, u64, SP])
     SIGNATURES[f"cuda_dispatch_{_g}_packed"] = (cint, [vp, cint, vp, vp, u32, u32, u64, SP])

@@ -26,6 +26,7 @@
 //   * fp8-e4m3 KV pages are converted to f16 (exact) on the way from the staging buffer to the tile; the
 //     per-KV-head scales are applied to the scores and to the output.
 #include <math.h>
+#include <mutex>
 
 #include "common.cuh"
 
@@ -600,4 +601,152 @@ extern "C" int cuda_dispatch_paged_decode_attention(CUDADeviceRef contextRef, in
     return launch_paged_decode(ctx, elementDType, kvDType, dev_ptr(queryRef), dev_ptr(kPagesRef), dev_ptr(vPagesRef),
                                (const int32_t*)dev_ptr(pageTableRef), (const int32_t*)dev_ptr(ctxLensRef), ks, vs, dev_ptr(outRef), flag,
                                batch, maxPagesPerSeq, pageCount, pageSize, numHeads, kvHeads, 0, -1, status);
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Allocation-free variant of paged decode attention.
+//
+// Some hosts may not allocate device memory at the moment they need to run a decode step: a serving loop
+// whose memory is fully pre-planned and handed out by its own arena (so a hidden cudaMalloc would either
+// fail or fragment the plan), a caller inside a latency-critical section where the implicit device
+// synchronisation of cudaMalloc/cudaFree is not acceptable, or an embedding runtime that forbids driver
+// allocations after start-up.  The regular entry point keeps its split-KV partials in a grow-only workspace
+// that it allocates on demand; this one keeps them in a fixed array that is part of the library image.
+//
+// The array lives in device memory of every GPU that loads the library, for the life of the process
+// (kStaticScratchBytes per GPU).  In host code the symbol below is only a stand-in: its device address is
+// obtained once per device with cudaGetSymbolAddress, with that device current, and that pointer is what
+// the kernels receive.
+// ---------------------------------------------------------------------------------------------------------
+namespace puter {
+
+static constexpr size_t kStaticScratchBytes = 8u << 20;  // 8 MiB per GPU
+static __device__ __align__(256) unsigned char g_decodeStaticScratch[kStaticScratchBytes];
+
+static constexpr int kMaxDevices = 64;
+static void* g_staticScratchPtr[kMaxDevices];  // per-device address of the array, resolved on first use
+static std::mutex g_staticScratchMu;
+
+// Resolves (once per device, with that device current) the device address of the scratch array.
+static void* static_scratch_for(Context* ctx, CUDAStatus* status) {
+    if (ctx->device < 0 || ctx->device >= kMaxDevices) {
+        fail(status, -2, "paged decode attention (no-alloc): device ordinal %d outside the supported 0..%d", ctx->device, kMaxDevices - 1);
+        return nullptr;
+    }
+    std::lock_guard<std::mutex> lock(g_staticScratchMu);
+    if (!g_staticScratchPtr[ctx->device]) {
+        void* p = nullptr;
+        cudaError_t err = cudaSetDevice(ctx->device);
+        if (err == cudaSuccess) err = cudaGetSymbolAddress(&p, g_decodeStaticScratch);
+        if (err != cudaSuccess || !p) {
+            fail(status, -7, "paged decode attention (no-alloc): cudaGetSymbolAddress failed: %s", cudaGetErrorString(err));
+            return nullptr;
+        }
+        g_staticScratchPtr[ctx->device] = p;
+    }
+    return g_staticScratchPtr[ctx->device];
+}
+
+}  // namespace puter
+
+// Same operation and arguments as cuda_dispatch_paged_decode_attention, with the split-KV scratch in the
+// library's fixed per-GPU array instead of an allocated workspace.  Calls no cudaMalloc / cudaFree and no
+// allocating library routine.  Problems whose partials do not fit kStaticScratchBytes are refused with -2
+// (with 32 query heads on a 148-SM GPU the limit is a batch of 355 sequences).
+//
+// The first call on a device resolves the array's device address (cudaGetSymbolAddress); make that first
+// call outside of any stream capture.  Every call on a GPU shares the one array: two calls whose kernels
+// can overlap on that GPU (different streams, or different contexts of the same device) race on it, so
+// keep them stream-ordered.  Nothing has to start at zero: every scratch word a call reads is written
+// earlier in the same call, so the previous call's contents are simply overwritten.
+extern "C" int cuda_dispatch_paged_decode_attention_noalloc(CUDADeviceRef contextRef, int elementDType, int kvDType, CUDABufferRef queryRef,
+                                                            CUDABufferRef kPagesRef, CUDABufferRef vPagesRef, CUDABufferRef pageTableRef,
+                                                            CUDABufferRef ctxLensRef, CUDABufferRef kScaleRef, CUDABufferRef vScaleRef,
+                                                            CUDABufferRef outRef, CUDABufferRef errorFlagRef, uint32_t batch,
+                                                            uint32_t maxPagesPerSeq, uint32_t pageCount, uint32_t pageSize, uint32_t numHeads,
+                                                            uint32_t kvHeads, uint32_t headDim, uint64_t completionToken, CUDAStatus* status) {
+    (void)completionToken;
+    PUTER_ENTER(ctx);
+    if (batch == 0 || numHeads == 0) return ok(status);
+    if (kvHeads == 0) kvHeads = numHeads;
+    if (!decode_supported(elementDType, kvDType, numHeads, kvHeads, headDim))
+        return fail(status, -6,
+                    "paged decode attention (no-alloc): supported are bf16/f16 queries, KV pages of the same type or fp8-e4m3, head_dim 128, "
+                    "<= 16 query heads per KV head (got dtype %d, kv dtype %d, heads %u/%u, head_dim %u)",
+                    elementDType, kvDType, numHeads, kvHeads, headDim);
+    if (pageSize == 0 || pageCount == 0 || maxPagesPerSeq == 0) return fail(status, -2, "paged decode attention (no-alloc): empty page geometry");
+    const size_t kvEs = dtype_size(kvDType);
+    const size_t poolBytes = (size_t)pageCount * pageSize * kvHeads * headDim * kvEs;
+    PUTER_REQUIRE(queryRef, "query", (size_t)batch * numHeads * headDim * 2);
+    PUTER_REQUIRE(outRef, "out", (size_t)batch * numHeads * headDim * 2);
+    PUTER_REQUIRE(kPagesRef, "kPages", poolBytes);
+    PUTER_REQUIRE(vPagesRef, "vPages", poolBytes);
+    PUTER_REQUIRE(pageTableRef, "pageTable", (size_t)batch * maxPagesPerSeq * 4);
+    PUTER_REQUIRE(ctxLensRef, "ctxLens", (size_t)batch * 4);
+    const float* ks = nullptr;
+    const float* vs = nullptr;
+    if (kvDType == DT_E4M3 && kvDType != elementDType) {
+        if (kScaleRef) { PUTER_REQUIRE(kScaleRef, "kScale", (size_t)kvHeads * 4); ks = (const float*)dev_ptr(kScaleRef); }
+        if (vScaleRef) { PUTER_REQUIRE(vScaleRef, "vScale", (size_t)kvHeads * 4); vs = (const float*)dev_ptr(vScaleRef); }
+    }
+    int* flag = ctx->errorFlag;
+    if (errorFlagRef) { PUTER_REQUIRE(errorFlagRef, "errorFlag", 4); flag = (int*)dev_ptr(errorFlagRef); }
+    if ((((uintptr_t)dev_ptr(kPagesRef) | (uintptr_t)dev_ptr(vPagesRef)) & 15u) != 0 || ((uintptr_t)dev_ptr(queryRef) & 3u) != 0)
+        return fail(status, -2, "paged decode attention (no-alloc): K/V pools must be 16-byte aligned");
+
+    DecodeParams p{};
+    p.q = dev_ptr(queryRef); p.kPages = dev_ptr(kPagesRef); p.vPages = dev_ptr(vPagesRef);
+    p.pageTable = (const int32_t*)dev_ptr(pageTableRef); p.ctxLens = (const int32_t*)dev_ptr(ctxLensRef);
+    p.kScale = ks; p.vScale = vs; p.errorFlag = flag; p.seqStrideKV = 0;
+    p.batch = (int)batch; p.maxPages = (int)maxPagesPerSeq; p.pageCount = (int)pageCount; p.pageSize = (int)pageSize;
+    p.numHeads = (int)numHeads; p.kvHeads = (int)kvHeads; p.group = (int)(numHeads / kvHeads);
+    p.headsPerPass = kvHeads < (uint32_t)kWarps ? (int)kvHeads : kWarps;
+    p.groups = kWarps / p.headsPerPass;
+    const long long ctas = ctx->smCount;
+    p.workers = (int)(ctas * p.groups);
+    p.scale = (float)(1.0 / sqrt((double)kHeadDim));
+    p.scaleLog2 = p.scale * 1.4426950408889634f;
+
+    // carve the fixed array: accumulators, (max, sum) pairs, tile prefix sums
+    const size_t slots = (size_t)p.workers + batch;
+    const size_t accBytes = slots * numHeads * kHeadDim * sizeof(float);
+    const size_t mlBytes = ((slots * numHeads * sizeof(float2)) + 255) & ~(size_t)255;
+    const size_t prefBytes = ((size_t)batch + 1) * sizeof(long long);
+    const size_t need = accBytes + mlBytes + prefBytes;
+    if (need > kStaticScratchBytes)
+        return fail(status, -2,
+                    "paged decode attention (no-alloc): batch %u with %u query heads needs %zu bytes of split-KV scratch, the fixed "
+                    "per-GPU array holds %zu; use cuda_dispatch_paged_decode_attention or a smaller batch",
+                    batch, numHeads, need, kStaticScratchBytes);
+    char* ws = (char*)static_scratch_for(ctx, status);
+    if (!ws) return status ? status->code : -7;
+    p.partAcc = (float*)ws;
+    p.partML = (float2*)(ws + accBytes);
+    p.tileStart = (long long*)(ws + accBytes + mlBytes);
+
+    decode_prefix_kernel<<<1, 1024, 0, ctx->stream>>>(p.ctxLens, (long long*)p.tileStart, (int)batch, (int)maxPagesPerSeq, (int)pageSize, p.errorFlag);
+    int rc = check_launch(ctx, status, "decode prefix");
+    if (rc != 0) return rc;
+    const bool bf16 = elementDType == DT_BF16;
+    const bool fp8 = kvDType == DT_E4M3;
+#define DECODE_LAUNCH(B, F, NSTAGE)                                                                                      \
+    do {                                                                                                                 \
+        constexpr int smem = DecodeSmem<B, F, NSTAGE>::kTotal;                                                           \
+        cudaFuncSetAttribute(paged_decode_kernel<B, F, NSTAGE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); \
+        paged_decode_kernel<B, F, NSTAGE, true><<<(unsigned)ctas, kThreads, smem, ctx->stream>>>(p);                     \
+    } while (0)
+    if (fp8) {
+        if (bf16) DECODE_LAUNCH(true, true, 5);
+        else DECODE_LAUNCH(false, true, 5);
+    } else {
+        if (bf16) DECODE_LAUNCH(true, false, 3);
+        else DECODE_LAUNCH(false, false, 3);
+    }
+#undef DECODE_LAUNCH
+    rc = check_launch(ctx, status, "paged decode attention (no-alloc)");
+    if (rc != 0) return rc;
+    dim3 mgrid(batch, numHeads);
+    if (bf16) decode_merge_kernel<true><<<mgrid, kHeadDim, 0, ctx->stream>>>(p, dev_ptr(outRef));
+    else decode_merge_kernel<false><<<mgrid, kHeadDim, 0, ctx->stream>>>(p, dev_ptr(outRef));
+    return check_launch(ctx, status, "decode merge");
 }

@@ -321,3 +321,15 @@ class Device:
         self._call("cuda_dispatch_paged_decode_attention", [query, kPages, vPages, pageTable, ctxLens, kScale, vScale, output, errorFlag],
                    lambda r: (format, kvf, r[0], r[1], r[2], r[3], r[4], r[5], r[6], r[7], r[8], batch, maxPagesPerSeq, pageCount,
                               pageSize, attn.NumHeads, kv, attn.HeadDim, 0))
+
+    def PagedDecodeAttentionNoAlloc(self, attn: MultiHeadAttentionConfig, query, kPages, vPages, pageTable, ctxLens, output, batch,
+                                    maxPagesPerSeq, pageCount, pageSize, format, kvFormat=None, kScale=None, vScale=None, errorFlag=None):
+        """PagedDecodeAttention for callers that must not allocate device memory during the step: the split-KV scratch is
+        the library's fixed per-GPU array (8 MiB), so larger problems raise DeviceError(-2).  Calls on one GPU must be
+        stream-ordered (they share the array); make the first call on a device outside of stream capture."""
+        kv = attn.KVHeadCount if attn.KVHeadCount > 0 else attn.NumHeads
+        kvf = format if kvFormat is None else kvFormat
+        self._call("cuda_dispatch_paged_decode_attention_noalloc",
+                   [query, kPages, vPages, pageTable, ctxLens, kScale, vScale, output, errorFlag],
+                   lambda r: (format, kvf, r[0], r[1], r[2], r[3], r[4], r[5], r[6], r[7], r[8], batch, maxPagesPerSeq, pageCount,
+                              pageSize, attn.NumHeads, kv, attn.HeadDim, 0))
