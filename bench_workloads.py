@@ -285,7 +285,7 @@ def secondary_lines(dev, rank, world, timed, peaks, decode_cls, free=()):
                 setattr(w, k, None)
     torch.cuda.empty_cache()
     out = {}
-    for name in ("decode_fp8", "chain", "convert"):
+    for name in ("decode_fp8", "prefill", "chain", "convert"):
         try:
             wl = make_workload(name, dev, rank, decode_cls)
             for _ in range(3):

@@ -1,19 +1,553 @@
-// Placeholder translation unit for the tensor-core prefill kernel (filled in below).
+// Causal GQA prefill attention on the 5th-generation tensor cores (tcgen05 + TMEM), fed by TMA.
+//
+// Reference semantics: per batch item RoPE(q), RoPE(k) (device/cpu/rope/compute.go:55-193, results rounded to the
+// 16-bit storage type) followed by MultiHeadAttention with the causal mask (device/cpu/attention/typed_compute.go:142-237):
+// score = dot(q,k) * 1/sqrt(D), softmax over the visible keys, out = sum_k p[k] v[k], stored with round-to-nearest-even.
+//
+// Shape of the kernel (head_dim 128, 16-bit inputs):
+//   * one CTA owns a tile of 128 query rows of one (batch, query head); heavy (late) tiles are scheduled first;
+//   * a TMA warp streams 128-key K and V tiles through a 2-stage shared-memory ring (SWIZZLE_128B boxes of 64 x 128);
+//   * one elected thread of the MMA warp issues tcgen05.mma (kind::f16, M=128, N=128, K=16):  S = Q K^T into TMEM,
+//     then O += P V with P read back from TMEM as the A operand and V as an MN-major B operand;
+//   * four softmax warps own one S row per thread (TMEM lane = row): tcgen05.ld, online softmax in the log2 domain,
+//     P packed to 16 bits and written with tcgen05.st; the O accumulator is rescaled lazily (only when a row maximum
+//     grew by more than 2^8), so most iterations never touch it;
+//   * RoPE is fused into the Q load: the raw Q tile lands by TMA and is rotated in shared memory (float32 math, unfused
+//     multiplies, rounded to storage) before the first MMA.  K rows are each reused by 32 query tiles x 4 heads, so K is
+//     rotated once by a streaming pre-pass into scratch, not once per tile.
+//   * every wait on an mbarrier is bounded: on expiry the kernel raises the error flag, all roles drain and TMEM is freed.
+#include <cuda.h>
+#include <math.h>
+
 #include "common.cuh"
 
 namespace puter {
 
-bool prefill_supported(int dt, uint32_t seqQ, uint32_t seqK, uint32_t numHeads, uint32_t kvHeads, uint32_t headDim, uint32_t causal) {
-    (void)dt; (void)seqQ; (void)seqK; (void)numHeads; (void)kvHeads; (void)headDim; (void)causal;
+namespace pf {
+
+constexpr int kD = 128;          // head dimension
+constexpr int kBM = 128;         // query rows per CTA
+constexpr int kBN = 128;         // keys per tile
+constexpr int kStages = 2;
+constexpr int kThreads = 192;    // warps 0-3 softmax, warp 4 MMA, warp 5 TMA
+constexpr uint32_t kTileBytes = kBN * kD * 2;          // one K or V tile: 32 KB
+constexpr uint32_t kHalfTile = kTileBytes / 2;         // one 64-column swizzled block: 16 KB
+constexpr uint32_t kSmemQ = 0;
+constexpr uint32_t kSmemK = kSmemQ + kTileBytes;
+constexpr uint32_t kSmemV = kSmemK + kStages * kTileBytes;
+constexpr uint32_t kSmemBar = kSmemV + kStages * kTileBytes;
+constexpr uint32_t kSmemTotal = kSmemBar + 256 + 1024;  // + alignment slack
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kColS = 0, kColO = 128, kColP = 256;
+constexpr long long kSpinLimit = 1ll << 24;
+
+struct Params {
+    CUtensorMap tmQ, tmK, tmV;
+    void* out;               // [B, S, Hq*D]
+    const float* ropeTable;  // cos [S, D/2] then sin [S, D/2], or nullptr
+    int* errorFlag;
+    int batch, seqLen, numHeads, kvHeads, causal, ropeMode;
+    float scaleLog2;
+    uint32_t vLBO, vSBO;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// bounded wait: returns false when the limit expired (the caller raises the abort flag)
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abortFlag) {
+    for (long long i = 0; i < kSpinLimit; i++) {
+        uint32_t done;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
+                     : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+        if (done) return true;
+        if ((i & 1023) == 1023 && *abortFlag) return false;
+    }
     return false;
+}
+
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* tm, uint32_t bar, int c0, int c1, int c2, int c3) {
+    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+                 ::"r"(dst), "l"(tm), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+
+// shared-memory matrix descriptor (sm_100 format: version 1 in bits 46-47, swizzle mode in bits 61-63; 2 = 128-byte swizzle)
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lboBytes, uint32_t sboBytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)((lboBytes >> 4) & 0x3FFFu) << 16;
+    d |= (uint64_t)((sboBytes >> 4) & 0x3FFFu) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+// instruction descriptor, kind::f16: D = f32, A/B = bf16 (1) or f16 (0), M = 128, N = 128; bMajorMN = B is MN-major
+__device__ __forceinline__ uint32_t make_idesc(bool bf16, bool bMajorMN) {
+    uint32_t d = 0;
+    d |= 1u << 4;                      // accumulator format f32
+    d |= (bf16 ? 1u : 0u) << 7;        // A format
+    d |= (bf16 ? 1u : 0u) << 10;       // B format
+    d |= (bMajorMN ? 1u : 0u) << 16;   // B major
+    d |= (uint32_t)(kBN >> 3) << 17;   // N
+    d |= (uint32_t)(kBM >> 4) << 24;   // M
+    return d;
+}
+
+__device__ __forceinline__ void mma_ss(uint32_t dTmem, uint64_t aDesc, uint64_t bDesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(dTmem), "l"(aDesc), "l"(bDesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void mma_ts(uint32_t dTmem, uint32_t aTmem, uint64_t bDesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+                 ::"r"(dTmem), "r"(aTmem), "l"(bDesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+          "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]),
+          "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
+          "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+template <bool BF16> __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    if (BF16) {
+        __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+        return *(uint32_t*)&v;
+    }
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *(uint32_t*)&v;
+}
+template <bool BF16> __device__ __forceinline__ float widen16(uint32_t b) {
+    if (BF16) return __uint_as_float(b << 16);
+    return __half2float(__ushort_as_half((unsigned short)b));
+}
+template <bool BF16> __device__ __forceinline__ uint32_t narrow16(float f) {
+    if (BF16) return f32_to_bf16_bits(f);
+    return f32_to_f16_bits(f);
+}
+
+// barrier slots (8 bytes each) inside the barrier area
+enum : uint32_t { BAR_Q = 0, BAR_QREADY = 1, BAR_KV_FULL = 2, BAR_KV_EMPTY = 4, BAR_S = 6, BAR_P = 7, BAR_O = 8, BAR_COUNT = 9 };
+
+template <bool BF16, bool ROUND_SCORES>
+__global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const __grid_constant__ Params p) {
+    extern __shared__ unsigned char smemRaw[];
+    // the swizzled TMA boxes need 1024-byte alignment
+    unsigned char* smem = (unsigned char*)(((uintptr_t)smemRaw + 1023) & ~(uintptr_t)1023);
+    const uint32_t sBase = smem_u32(smem);
+    const uint32_t barBase = sBase + kSmemBar;
+    auto bar = [&](uint32_t i) { return barBase + i * 8; };
+    __shared__ uint32_t tmemBaseShared;
+    __shared__ int abortShared;
+    volatile int* abortFlag = &abortShared;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // heavy tiles first: blockIdx.x = 0 is the last (longest) query tile
+    const int numQTiles = (p.seqLen + kBM - 1) / kBM;
+    const int qTile = numQTiles - 1 - (int)blockIdx.x;
+    const int head = blockIdx.y, b = blockIdx.z;
+    const int kvHead = head / (p.numHeads / p.kvHeads);
+    const int q0 = qTile * kBM;
+    const int lastKey = p.causal ? min(p.seqLen, q0 + kBM) : p.seqLen;  // keys [0, lastKey) can be visible to this tile
+    const int numKTiles = (lastKey + kBN - 1) / kBN;
+
+    if (threadIdx.x == 0) {
+        abortShared = 0;
+        mbar_init(bar(BAR_Q), 1);
+        mbar_init(bar(BAR_QREADY), 128);
+        for (int s = 0; s < kStages; s++) {
+            mbar_init(bar(BAR_KV_FULL + s), 1);
+            mbar_init(bar(BAR_KV_EMPTY + s), 1);
+        }
+        mbar_init(bar(BAR_S), 1);
+        mbar_init(bar(BAR_P), 128);
+        mbar_init(bar(BAR_O), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 4) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmemBaseShared)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    fence_before();
+    __syncthreads();
+    fence_after();
+    const uint32_t tmem = tmemBaseShared;
+
+    if (warp == 5) {
+        // ------------------------------------------------ TMA producer ------------------------------------------------
+        if (lane == 0) {
+            mbar_expect_tx(bar(BAR_Q), kTileBytes);
+            tma_load_4d(sBase + kSmemQ, &p.tmQ, bar(BAR_Q), 0, head, q0, b);
+            tma_load_4d(sBase + kSmemQ + kHalfTile, &p.tmQ, bar(BAR_Q), 64, head, q0, b);
+            for (int j = 0; j < numKTiles; j++) {
+                const int st = j % kStages;
+                if (j >= kStages) {
+                    if (!mbar_wait(bar(BAR_KV_EMPTY + st), ((j / kStages) - 1) & 1, abortFlag)) { *abortFlag = 1; break; }
+                }
+                mbar_expect_tx(bar(BAR_KV_FULL + st), 2 * kTileBytes);
+                const uint32_t kDst = sBase + kSmemK + st * kTileBytes, vDst = sBase + kSmemV + st * kTileBytes;
+                tma_load_4d(kDst, &p.tmK, bar(BAR_KV_FULL + st), 0, kvHead, j * kBN, b);
+                tma_load_4d(kDst + kHalfTile, &p.tmK, bar(BAR_KV_FULL + st), 64, kvHead, j * kBN, b);
+                tma_load_4d(vDst, &p.tmV, bar(BAR_KV_FULL + st), 0, kvHead, j * kBN, b);
+                tma_load_4d(vDst + kHalfTile, &p.tmV, bar(BAR_KV_FULL + st), 64, kvHead, j * kBN, b);
+            }
+        }
+    } else if (warp == 4) {
+        // ------------------------------------------------ MMA issuer --------------------------------------------------
+        if (lane == 0) {
+            const uint32_t idescQK = make_idesc(BF16, false);
+            const uint32_t idescPV = make_idesc(BF16, true);
+            bool okay = mbar_wait(bar(BAR_QREADY), 0, abortFlag);
+            for (int j = 0; j < numKTiles && okay; j++) {
+                const int st = j % kStages;
+                okay = mbar_wait(bar(BAR_KV_FULL + st), (j / kStages) & 1, abortFlag);
+                if (!okay) break;
+                fence_after();
+                const uint32_t kAddr = sBase + kSmemK + st * kTileBytes, vAddr = sBase + kSmemV + st * kTileBytes;
+                // S = Q K^T: 8 steps of K=16 over the 128 head dimensions (two 64-column swizzled blocks)
+#pragma unroll
+                for (int kk = 0; kk < 8; kk++) {
+                    const uint32_t off = (kk >> 2) * kHalfTile + (kk & 3) * 32;
+                    mma_ss(tmem + kColS, make_desc(sBase + kSmemQ + off, 16, 1024), make_desc(kAddr + off, 16, 1024), idescQK, kk > 0);
+                }
+                mma_commit(bar(BAR_S));
+                okay = mbar_wait(bar(BAR_P), j & 1, abortFlag);
+                if (!okay) break;
+                fence_after();
+                // O += P V: 8 steps of K=16 keys; P from TMEM (8 columns per step), V MN-major from shared memory
+#pragma unroll
+                for (int kk = 0; kk < 8; kk++) {
+                    mma_ts(tmem + kColO, tmem + kColP + kk * 8, make_desc(vAddr + kk * 16 * 128, p.vLBO, p.vSBO), idescPV, (j > 0 || kk > 0));
+                }
+                mma_commit(bar(BAR_KV_EMPTY + st));
+            }
+            mma_commit(bar(BAR_O));
+            if (!okay) *abortFlag = 1;
+        }
+    } else {
+        // ------------------------------------------------ softmax / epilogue warps ------------------------------------
+        const int row = threadIdx.x;             // 0..127 = TMEM lane = query row within the tile
+        const int qPos = q0 + row;
+        const uint32_t laneBase = tmem + ((uint32_t)(warp * 32) << 16);
+        bool okay = __all_sync(0xffffffffu, mbar_wait(bar(BAR_Q), 0, abortFlag));
+        if (okay && p.ropeMode != 2 && p.ropeTable != nullptr && qPos < p.seqLen) {
+            // rotate the raw Q row in shared memory (float32 math, unfused, rounded to storage)
+            const int half = kD / 2;
+            const float* cosT = p.ropeTable + (size_t)qPos * half;
+            const float* sinT = p.ropeTable + (size_t)p.seqLen * half + (size_t)qPos * half;
+            unsigned char* qRow0 = smem + kSmemQ + row * 128;
+            unsigned char* qRow1 = qRow0 + kHalfTile;
+#pragma unroll 1
+            for (int c = 0; c < 8; c++) {
+                const int sw = (c ^ (row & 7)) * 16;
+                if (p.ropeMode == 1) {
+                    // half mode: element i of block 0 pairs with element i of block 1
+                    Vec16 a = *(Vec16*)(qRow0 + sw), bq = *(Vec16*)(qRow1 + sw);
+#pragma unroll
+                    for (int w = 0; w < 4; w++) {
+                        uint32_t ra = 0, rb = 0;
+#pragma unroll
+                        for (int hsel = 0; hsel < 2; hsel++) {
+                            const int pi = c * 8 + w * 2 + hsel;
+                            const float e = widen16<BF16>((a.w[w] >> (16 * hsel)) & 0xFFFFu), o = widen16<BF16>((bq.w[w] >> (16 * hsel)) & 0xFFFFu);
+                            const float cs = __ldg(cosT + pi), sn = __ldg(sinT + pi);
+                            ra |= narrow16<BF16>(sub(mul(e, cs), mul(o, sn))) << (16 * hsel);
+                            rb |= narrow16<BF16>(add(mul(e, sn), mul(o, cs))) << (16 * hsel);
+                        }
+                        a.w[w] = ra;
+                        bq.w[w] = rb;
+                    }
+                    *(Vec16*)(qRow0 + sw) = a;
+                    *(Vec16*)(qRow1 + sw) = bq;
+                } else {
+                    // interleaved mode: pairs (2i, 2i+1) sit in one 32-bit word; both blocks hold their own pairs
+#pragma unroll
+                    for (int blk = 0; blk < 2; blk++) {
+                        unsigned char* ptr = (blk ? qRow1 : qRow0) + sw;
+                        Vec16 a = *(Vec16*)ptr;
+#pragma unroll
+                        for (int w = 0; w < 4; w++) {
+                            const int pi = blk * 32 + c * 4 + w;
+                            const float e = widen16<BF16>(a.w[w] & 0xFFFFu), o = widen16<BF16>(a.w[w] >> 16);
+                            const float cs = __ldg(cosT + pi), sn = __ldg(sinT + pi);
+                            a.w[w] = narrow16<BF16>(sub(mul(e, cs), mul(o, sn))) | (narrow16<BF16>(add(mul(e, sn), mul(o, cs))) << 16);
+                        }
+                        *(Vec16*)ptr = a;
+                    }
+                }
+            }
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the tensor core
+        mbar_arrive(bar(BAR_QREADY));
+
+        float mUsed = -INFINITY;   // the maximum the stored P and O are relative to (log2 domain)
+        float lsum = 0.f;
+        for (int j = 0; j < numKTiles && okay; j++) {
+            okay = __all_sync(0xffffffffu, mbar_wait(bar(BAR_S), j & 1, abortFlag));  // keep the warp convergent
+            if (!okay) break;
+            fence_after();
+            uint32_t sreg[128];
+#pragma unroll
+            for (int c = 0; c < 4; c++) tmem_ld32(laneBase + kColS + c * 32, sreg + c * 32);
+            tmem_wait_ld();
+            const int key0 = j * kBN;
+            const bool needMask = (p.causal && key0 + kBN - 1 > q0) || (key0 + kBN > p.seqLen);
+            float mx = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < 128; i++) {
+                float s = __uint_as_float(sreg[i]);
+                if (ROUND_SCORES) s = widen16<BF16>(narrow16<BF16>(s));  // the reference rounds the dot product to storage
+                s *= p.scaleLog2;
+                if (needMask) {
+                    const int key = key0 + i;
+                    if ((p.causal && key > qPos) || key >= p.seqLen) s = -INFINITY;
+                }
+                sreg[i] = __float_as_uint(s);
+                mx = fmaxf(mx, s);
+            }
+            // lazy rescale: keep the old reference maximum unless the row maximum grew by more than 8 (factor 256)
+            float mNew = mUsed;
+            const bool grow = mx > mUsed + 8.0f || (mUsed == -INFINITY && mx > -INFINITY);
+            if (grow) mNew = mx;
+            const float alpha = (grow && mUsed != -INFINITY) ? exp2f(mUsed - mNew) : 1.0f;
+            if (j > 0 && __any_sync(0xffffffffu, grow && mUsed != -INFINITY)) {
+                // some row of this warp moved its maximum: rescale the O accumulator rows (alpha = 1 for the others)
+#pragma unroll 1
+                for (int c = 0; c < 4; c++) {
+                    uint32_t oreg[32];
+                    tmem_ld32(laneBase + kColO + c * 32, oreg);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; i++) oreg[i] = __float_as_uint(__uint_as_float(oreg[i]) * alpha);
+                    tmem_st32(laneBase + kColO + c * 32, oreg);
+                }
+                tmem_wait_st();
+            }
+            lsum *= alpha;
+            mUsed = mNew;
+            float sum = 0.f;
+            uint32_t preg[64];
+#pragma unroll
+            for (int i = 0; i < 64; i++) {
+                const float s0 = __uint_as_float(sreg[2 * i]), s1 = __uint_as_float(sreg[2 * i + 1]);
+                const float e0 = (mUsed == -INFINITY) ? 0.f : exp2f(s0 - mUsed);
+                const float e1 = (mUsed == -INFINITY) ? 0.f : exp2f(s1 - mUsed);
+                sum += e0 + e1;
+                preg[i] = pack2<BF16>(e0, e1);
+            }
+            lsum += sum;
+            tmem_st32(laneBase + kColP, preg);
+            tmem_st32(laneBase + kColP + 32, preg + 32);
+            tmem_wait_st();
+            fence_before();
+            mbar_arrive(bar(BAR_P));
+        }
+        // epilogue: wait for the last P V product, normalise and store
+        if (okay) okay = __all_sync(0xffffffffu, mbar_wait(bar(BAR_O), 0, abortFlag));
+        if (okay) {
+            fence_after();
+            const float inv = lsum > 0.f ? 1.0f / lsum : 0.f;
+            uint16_t* orow = (uint16_t*)p.out + (((size_t)b * p.seqLen + qPos) * p.numHeads + head) * kD;
+#pragma unroll 1
+            for (int c = 0; c < 4; c++) {
+                uint32_t oreg[32];
+                tmem_ld32(laneBase + kColO + c * 32, oreg);
+                tmem_wait_ld();
+                if (qPos < p.seqLen) {
+#pragma unroll
+                    for (int v4 = 0; v4 < 4; v4++) {
+                        Vec16 o;
+#pragma unroll
+                        for (int w = 0; w < 4; w++) {
+                            const float a = __uint_as_float(oreg[v4 * 8 + 2 * w]) * inv, bq = __uint_as_float(oreg[v4 * 8 + 2 * w + 1]) * inv;
+                            o.w[w] = narrow16<BF16>(a) | (narrow16<BF16>(bq) << 16);
+                        }
+                        *(Vec16*)(orow + c * 32 + v4 * 8) = o;
+                    }
+                }
+            }
+        } else {
+            *abortFlag = 1;
+        }
+    }
+    // ---------------------------------------------------- teardown ----------------------------------------------------
+    fence_before();
+    __syncthreads();
+    if (abortShared && threadIdx.x == 0) atomicExch(p.errorFlag, 2);
+    if (warp == 4) {
+        fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+    }
+}
+
+}  // namespace pf
+
+// ---- host side ----
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)sym;
+    }
+    return fn;
+}
+
+// [B, S, H, 128] 16-bit tensor -> 4-D map (d, head, s, b) with a 64 x 1 x 128 x 1 box and 128-byte swizzle
+static bool make_map(CUtensorMap* tm, const void* base, bool bf16, uint32_t batch, uint32_t seq, uint32_t heads) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[4] = {128, heads, seq, batch};
+    cuuint64_t strides[3] = {256, (cuuint64_t)heads * 256, (cuuint64_t)seq * heads * 256};
+    cuuint32_t box[4] = {64, 1, 128, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = fn(tm, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, (void*)base, dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+bool prefill_supported(int dt, uint32_t seqQ, uint32_t seqK, uint32_t numHeads, uint32_t kvHeads, uint32_t headDim, uint32_t causal) {
+    if (dt != DT_BF16 && dt != DT_F16) return false;
+    if (headDim != 128 || seqQ != seqK || seqQ < 128) return false;  // square (self-attention) problems; short ones use the exact kernel
+    if (kvHeads == 0 || numHeads % kvHeads != 0) return false;
+    (void)causal;
+    return encode_fn() != nullptr;
+}
+
+// K pre-pass: rotates [B, S, Hkv, 128] rows with the per-position table (positions restart for every batch item)
+template <bool BF16>
+__global__ void __launch_bounds__(256) rope_k_prepass_kernel(const uint16_t* __restrict__ in, uint16_t* __restrict__ out,
+                                                            const float* __restrict__ table, size_t batch, size_t seqLen, size_t heads,
+                                                            int halfMode) {
+    const size_t half = 64;
+    const float* cosT = table;
+    const float* sinT = table + seqLen * half;
+    const size_t itemsPerHead = halfMode ? 8 : 16;  // 16-byte work items per head row
+    const size_t total = batch * seqLen * heads * itemsPerHead;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t it = (size_t)blockIdx.x * blockDim.x + threadIdx.x; it < total; it += stride) {
+        const size_t j = it % itemsPerHead, row = it / itemsPerHead;  // row = (b*S + s)*heads + h
+        const size_t s = (row / heads) % seqLen;
+        const uint16_t* src = in + row * 128;
+        uint16_t* dst = out + row * 128;
+        if (halfMode) {
+            Vec16 a = ld_stream(src + j * 8), bq = ld_stream(src + 64 + j * 8);
+#pragma unroll
+            for (int w = 0; w < 4; w++) {
+                uint32_t ra = 0, rb = 0;
+#pragma unroll
+                for (int hsel = 0; hsel < 2; hsel++) {
+                    const size_t pi = j * 8 + w * 2 + hsel;
+                    const float e = pf::widen16<BF16>((a.w[w] >> (16 * hsel)) & 0xFFFFu), o = pf::widen16<BF16>((bq.w[w] >> (16 * hsel)) & 0xFFFFu);
+                    const float cs = __ldg(cosT + s * half + pi), sn = __ldg(sinT + s * half + pi);
+                    ra |= pf::narrow16<BF16>(sub(mul(e, cs), mul(o, sn))) << (16 * hsel);
+                    rb |= pf::narrow16<BF16>(add(mul(e, sn), mul(o, cs))) << (16 * hsel);
+                }
+                a.w[w] = ra;
+                bq.w[w] = rb;
+            }
+            st_stream(dst + j * 8, a);
+            st_stream(dst + 64 + j * 8, bq);
+        } else {
+            Vec16 a = ld_stream(src + j * 8);
+#pragma unroll
+            for (int w = 0; w < 4; w++) {
+                const size_t pi = j * 4 + w;
+                const float e = pf::widen16<BF16>(a.w[w] & 0xFFFFu), o = pf::widen16<BF16>(a.w[w] >> 16);
+                const float cs = __ldg(cosT + s * half + pi), sn = __ldg(sinT + s * half + pi);
+                a.w[w] = pf::narrow16<BF16>(sub(mul(e, cs), mul(o, sn))) | (pf::narrow16<BF16>(add(mul(e, sn), mul(o, cs))) << 16);
+            }
+            st_stream(dst + j * 8, a);
+        }
+    }
 }
 
 int launch_prefill(Context* ctx, int dt, const void* q, const void* k, const void* v, void* out, uint32_t batch, uint32_t seqLen,
                    uint32_t numHeads, uint32_t kvHeads, uint32_t headDim, uint32_t causal, int ropeMode, const float* ropeTable,
                    CUDAStatus* status) {
-    (void)ctx; (void)dt; (void)q; (void)k; (void)v; (void)out; (void)batch; (void)seqLen; (void)numHeads; (void)kvHeads;
-    (void)headDim; (void)causal; (void)ropeMode; (void)ropeTable;
-    return fail(status, -6, "prefill attention: tensor-core kernel not available for this shape");
+    if (!prefill_supported(dt, seqLen, seqLen, numHeads, kvHeads, headDim, causal))
+        return fail(status, -6, "prefill attention: tensor-core kernel not available for this shape");
+    const bool bf16 = dt == DT_BF16;
+    const void* kUse = k;
+    if (ropeMode != 2) {
+        if (!ropeTable) return fail(status, -2, "prefill attention: missing rope table");
+        // rotated K lives in the workspace right after the table (the caller sized the workspace for both)
+        const size_t tableBytes = (size_t)seqLen * 64 * 2 * sizeof(float);
+        const size_t kBytes = (size_t)batch * seqLen * kvHeads * 128 * 2;
+        if (ctx->workspaceBytes < tableBytes + kBytes + 1024 || (const char*)ropeTable != (const char*)ctx->workspace)
+            return fail(status, -7, "prefill attention: workspace not prepared");
+        uint16_t* kRot = (uint16_t*)((char*)ctx->workspace + ((tableBytes + 255) & ~(size_t)255));
+        const size_t items = (size_t)batch * seqLen * kvHeads * 16;
+        size_t blocks = (items + 255) / 256, cap = (size_t)ctx->smCount * 16;
+        if (blocks > cap) blocks = cap;
+        if (bf16) rope_k_prepass_kernel<true><<<(unsigned)blocks, 256, 0, ctx->stream>>>((const uint16_t*)k, kRot, ropeTable, batch, seqLen, kvHeads, ropeMode);
+        else rope_k_prepass_kernel<false><<<(unsigned)blocks, 256, 0, ctx->stream>>>((const uint16_t*)k, kRot, ropeTable, batch, seqLen, kvHeads, ropeMode);
+        int rc = check_launch(ctx, status, "rope K pre-pass");
+        if (rc != 0) return rc;
+        kUse = kRot;
+    }
+    pf::Params p;
+    memset(&p, 0, sizeof(p));
+    if (!make_map(&p.tmQ, q, bf16, batch, seqLen, numHeads) || !make_map(&p.tmK, kUse, bf16, batch, seqLen, kvHeads) ||
+        !make_map(&p.tmV, v, bf16, batch, seqLen, kvHeads))
+        return fail(status, -7, "prefill attention: tensor map encoding failed");
+    p.out = out;
+    p.ropeTable = ropeMode != 2 ? ropeTable : nullptr;
+    p.errorFlag = ctx->errorFlag;
+    p.batch = (int)batch; p.seqLen = (int)seqLen; p.numHeads = (int)numHeads; p.kvHeads = (int)kvHeads;
+    p.causal = (int)causal; p.ropeMode = ropeMode;
+    p.scaleLog2 = (float)(1.0 / sqrt(128.0)) * 1.4426950408889634f;
+    p.vLBO = pf::kHalfTile;  // next 64 head dimensions (next swizzled block)
+    p.vSBO = 1024;           // next 8 keys
+    if (const char* e = getenv("PUTER_PREFILL_V_LBO")) p.vLBO = (uint32_t)atoi(e);
+    if (const char* e = getenv("PUTER_PREFILL_V_SBO")) p.vSBO = (uint32_t)atoi(e);
+    dim3 grid((seqLen + pf::kBM - 1) / pf::kBM, numHeads, batch);
+    const bool roundScores = getenv("PUTER_PREFILL_FAST") == nullptr;
+#define PF_LAUNCH(B, R)                                                                                                        \
+    do {                                                                                                                       \
+        cudaFuncSetAttribute(pf::prefill_kernel<B, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pf::kSmemTotal);      \
+        pf::prefill_kernel<B, R><<<grid, pf::kThreads, pf::kSmemTotal, ctx->stream>>>(p);                                     \
+    } while (0)
+    if (bf16) { if (roundScores) PF_LAUNCH(true, true); else PF_LAUNCH(true, false); }
+    else { if (roundScores) PF_LAUNCH(false, true); else PF_LAUNCH(false, false); }
+#undef PF_LAUNCH
+    return check_launch(ctx, status, "prefill attention");
 }
 
 }  // namespace puter

@@ -214,3 +214,52 @@ def test_rope_attention_prefill_small(d, mode, batch, seq, hq, hkv, dim):
         kr = O.rope(dt, k[b], seq, hkv, dim, base=500000.0, mode=mode)
         want = O.mha(dt, qr, kr, v[b], seq, seq, hq, hkv, dim, True)
         assert np.abs(O.to_f32(got[b], dt) - O.to_f32(want.reshape(seq, -1), dt)).max() <= 2e-2
+
+
+@pytest.mark.parametrize("dt", [O.BF16, O.F16])
+@pytest.mark.parametrize("seq,hq,hkv,causal", [(128, 1, 1, True), (256, 4, 2, True), (384, 2, 2, False), (1024, 8, 2, True), (200, 4, 1, True)])
+def test_tensor_core_prefill_through_mha_entry(d, dt, seq, hq, hkv, causal):
+    """bf16/f16 self-attention with head_dim 128 runs on the tcgen05 kernel; compared with the CPU semantics."""
+    dim = 128
+    rng = np.random.default_rng(seq + hq)
+    q = O.from_f32(rng.standard_normal((seq, hq * dim)).astype(np.float32), dt)
+    k = O.from_f32(rng.standard_normal((seq, hkv * dim)).astype(np.float32), dt)
+    v = O.from_f32(rng.standard_normal((seq, hkv * dim)).astype(np.float32), dt)
+    want = O.mha(dt, q, k, v, seq, seq, hq, hkv, dim, causal)
+    got = run_mha(d, dt, q, k, v, seq, seq, hq, hkv, dim, causal=causal)
+    assert d.take_error() == 0
+    err = np.abs(O.to_f32(got, dt) - O.to_f32(want, dt))
+    assert err.max() <= 2e-2, (float(err.max()), np.unravel_index(err.argmax(), err.shape))
+    assert err.mean() <= 2e-3
+
+
+def test_prefill_config3_full_size_on_a_row_sample(d):
+    """Config 3 at full size (B=4, S=4096, 32/8 heads, head_dim 128, RoPE theta 5e5 fused): sampled rows vs the oracle."""
+    import puter_b200
+    import torch
+
+    B, S, HQ, HKV, D_ = 4, 4096, 32, 8, 128
+    dt = O.BF16
+    rng = np.random.default_rng(1)
+    q = O.from_f32(rng.standard_normal((B, S, HQ * D_), dtype=np.float32), dt)
+    k = O.from_f32(rng.standard_normal((B, S, HKV * D_), dtype=np.float32), dt)
+    v = O.from_f32(rng.standard_normal((B, S, HKV * D_), dtype=np.float32), dt)
+    out = empty(q.nbytes)
+    rope = puter_b200.RoPEConfig(BaseFreq=500000.0, Mode=1)
+    attn = puter_b200.MultiHeadAttentionConfig(NumHeads=HQ, HeadDim=D_, Causal=True, KVHeadCount=HKV)
+    d.RoPEAttentionPrefill(rope, attn, dev(q), dev(k), dev(v), out, B, S, dt)
+    got = host(out, np.uint16, q.shape)
+    assert d.take_error() == 0
+    worst = 0.0
+    for b in (0, 3):
+        qr = O.rope(dt, q[b], S, HQ, D_, base=500000.0, mode=1)
+        kr = O.rope(dt, k[b], S, HKV, D_, base=500000.0, mode=1)
+        rows = np.concatenate([np.arange(8), np.arange(S - 8, S), rng.integers(0, S, 48)]).astype(np.int32)
+        heads = rng.integers(0, HQ, rows.size).astype(np.int32)
+        want = O.mha_rows(dt, qr, kr, v[b], S, S, HQ, HKV, D_, rows, heads, causal=True)
+        g = got[b].reshape(S, HQ, D_)[rows, heads, :]
+        worst = max(worst, float(np.abs(O.to_f32(g, dt) - O.to_f32(want, dt)).max()))
+    assert worst <= 2e-2, worst
+    # size-independent property: row 0 attends only to key 0, so out[0] == v[0] of its KV head, exactly
+    v0 = v[:, 0, :].reshape(B, HKV, D_)
+    assert np.array_equal(got[:, 0, :].reshape(B, HQ, D_), np.repeat(v0, HQ // HKV, axis=1))
