@@ -5,13 +5,15 @@
 // score = dot(q,k) * 1/sqrt(D), softmax over the visible keys, out = sum_k p[k] v[k], stored with round-to-nearest-even.
 //
 // Shape of the kernel (head_dim 128, 16-bit inputs):
-//   * one CTA owns a tile of 128 query rows of one (batch, query head); heavy (late) tiles are scheduled first;
-//   * a TMA warp streams 128-key K and V tiles through a 2-stage shared-memory ring (SWIZZLE_128B boxes of 64 x 128);
+//   * one CTA owns two tiles of 128 query rows of one (batch, query head); heavy (late) tiles are scheduled first;
+//   * a TMA warp streams 128-key K and V tiles through a 2-stage shared-memory ring (SWIZZLE_128B boxes of 64 x 128),
+//     each tile serving both query tiles;
 //   * one elected thread of the MMA warp issues tcgen05.mma (kind::f16, M=128, N=128, K=16):  S = Q K^T into TMEM,
-//     then O += P V with P read back from TMEM as the A operand and V as an MN-major B operand;
-//   * four softmax warps own one S row per thread (TMEM lane = row): tcgen05.ld, online softmax in the log2 domain,
-//     P packed to 16 bits and written with tcgen05.st; the O accumulator is rescaled lazily (only when a row maximum
-//     grew by more than 2^8), so most iterations never touch it;
+//     then O += P V with P read back from TMEM as the A operand and V as an MN-major B operand; the two query tiles
+//     alternate so the tensor core works on one while the other is in its softmax;
+//   * two groups of four softmax warps own one S row per thread (TMEM lane = row): tcgen05.ld, online softmax in the
+//     log2 domain, P packed to 16 bits and written over S with tcgen05.st; the O accumulator is rescaled lazily (only
+//     when a row maximum grew by more than 2^8), so most iterations never touch it;
 //   * RoPE is fused into the Q load: the raw Q tile lands by TMA and is rotated in shared memory (float32 math, unfused
 //     multiplies, rounded to storage) before the first MMA.  K rows are each reused by 32 query tiles x 4 heads, so K is
 //     rotated once by a streaming pre-pass into scratch, not once per tile.
@@ -29,16 +31,16 @@ constexpr int kD = 128;          // head dimension
 constexpr int kBM = 128;         // query rows per CTA
 constexpr int kBN = 128;         // keys per tile
 constexpr int kStages = 2;
-constexpr int kThreads = 192;    // warps 0-3 softmax, warp 4 MMA, warp 5 TMA
+constexpr int kThreads = 320;    // warps 0-3 / 4-7 softmax of query tile 0 / 1, warp 8 MMA, warp 9 TMA
 constexpr uint32_t kTileBytes = kBN * kD * 2;          // one K or V tile: 32 KB
 constexpr uint32_t kHalfTile = kTileBytes / 2;         // one 64-column swizzled block: 16 KB
 constexpr uint32_t kSmemQ = 0;
-constexpr uint32_t kSmemK = kSmemQ + kTileBytes;
+constexpr uint32_t kSmemK = kSmemQ + 2 * kTileBytes;  // two query tiles
 constexpr uint32_t kSmemV = kSmemK + kStages * kTileBytes;
 constexpr uint32_t kSmemBar = kSmemV + kStages * kTileBytes;
 constexpr uint32_t kSmemTotal = kSmemBar + 256 + 1024;  // + alignment slack
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kColS = 0, kColO = 128, kColP = 256;
+constexpr uint32_t kColS = 0, kColO = 256;  // S0 S1 O0 O1, 128 columns each
 constexpr long long kSpinLimit = 1ll << 24;
 
 struct Params {
@@ -156,14 +158,70 @@ template <bool BF16> __device__ __forceinline__ uint32_t narrow16(float f) {
     return f32_to_f16_bits(f);
 }
 
-// barrier slots (8 bytes each) inside the barrier area
-enum : uint32_t { BAR_Q = 0, BAR_QREADY = 1, BAR_KV_FULL = 2, BAR_KV_EMPTY = 4, BAR_S = 6, BAR_P = 7, BAR_O = 8, BAR_COUNT = 9 };
+// barrier slots (8 bytes each) inside the barrier area; [2] = one per query tile of the CTA
+enum : uint32_t { BAR_Q = 0, BAR_QREADY = 2, BAR_KV_FULL = 4, BAR_KV_EMPTY = 6, BAR_S = 8, BAR_P = 10, BAR_O = 12, BAR_COUNT = 14 };
 
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// Rotates one raw Q row in shared memory (two swizzled 64-column blocks), float32 math with unfused multiplies,
+// results rounded to storage — the reference's RoPE on a 16-bit tensor (device/cpu/rope/compute.go:165-183).
+template <bool BF16>
+__device__ __forceinline__ void rotate_q_row(unsigned char* qRow0, int row, int ropeMode, const float* cosT, const float* sinT) {
+    unsigned char* qRow1 = qRow0 + kHalfTile;
+#pragma unroll 1
+    for (int c = 0; c < 8; c++) {
+        const int sw = (c ^ (row & 7)) * 16;
+        if (ropeMode == 1) {
+            // half mode: element i of block 0 pairs with element i of block 1
+            Vec16 a = *(Vec16*)(qRow0 + sw), bq = *(Vec16*)(qRow1 + sw);
+#pragma unroll
+            for (int w = 0; w < 4; w++) {
+                uint32_t ra = 0, rb = 0;
+#pragma unroll
+                for (int hsel = 0; hsel < 2; hsel++) {
+                    const int pi = c * 8 + w * 2 + hsel;
+                    const float e = widen16<BF16>((a.w[w] >> (16 * hsel)) & 0xFFFFu), o = widen16<BF16>((bq.w[w] >> (16 * hsel)) & 0xFFFFu);
+                    const float cs = __ldg(cosT + pi), sn = __ldg(sinT + pi);
+                    ra |= narrow16<BF16>(sub(mul(e, cs), mul(o, sn))) << (16 * hsel);
+                    rb |= narrow16<BF16>(add(mul(e, sn), mul(o, cs))) << (16 * hsel);
+                }
+                a.w[w] = ra;
+                bq.w[w] = rb;
+            }
+            *(Vec16*)(qRow0 + sw) = a;
+            *(Vec16*)(qRow1 + sw) = bq;
+        } else {
+            // interleaved mode: pairs (2i, 2i+1) sit in one 32-bit word; each block holds its own pairs
+#pragma unroll
+            for (int blk = 0; blk < 2; blk++) {
+                unsigned char* ptr = (blk ? qRow1 : qRow0) + sw;
+                Vec16 a = *(Vec16*)ptr;
+#pragma unroll
+                for (int w = 0; w < 4; w++) {
+                    const int pi = blk * 32 + c * 4 + w;
+                    const float e = widen16<BF16>(a.w[w] & 0xFFFFu), o = widen16<BF16>(a.w[w] >> 16);
+                    const float cs = __ldg(cosT + pi), sn = __ldg(sinT + pi);
+                    a.w[w] = narrow16<BF16>(sub(mul(e, cs), mul(o, sn))) | (narrow16<BF16>(add(mul(e, sn), mul(o, cs))) << 16);
+                }
+                *(Vec16*)ptr = a;
+            }
+        }
+    }
+}
+
+// One CTA = two 128-row query tiles (rows q0 .. q0+255) of one (batch, head).  Warps 0-3 / 4-7 are the softmax
+// groups of tile 0 / 1, warp 8 issues the MMAs, warp 9 drives TMA.  TMEM columns: S0 0-127, S1 128-255, O0 256-383,
+// O1 384-511; P_t overwrites the first 64 columns of S_t (each thread rewrites only the row it has already read).
+// MMA order in steady state: PV0(j), QK0(j+1), PV1(j), QK1(j+1): each softmax group works while the tensor core
+// runs the other tile's two products.
 template <bool BF16, bool ROUND_SCORES>
 __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const __grid_constant__ Params p) {
     extern __shared__ unsigned char smemRaw[];
-    // the swizzled TMA boxes need 1024-byte alignment
-    unsigned char* smem = (unsigned char*)(((uintptr_t)smemRaw + 1023) & ~(uintptr_t)1023);
+    unsigned char* smem = (unsigned char*)(((uintptr_t)smemRaw + 1023) & ~(uintptr_t)1023);  // swizzled boxes: 1024-byte aligned
     const uint32_t sBase = smem_u32(smem);
     const uint32_t barBase = sBase + kSmemBar;
     auto bar = [&](uint32_t i) { return barBase + i * 8; };
@@ -172,29 +230,40 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const __grid_const
     volatile int* abortFlag = &abortShared;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // heavy tiles first: blockIdx.x = 0 is the last (longest) query tile
-    const int numQTiles = (p.seqLen + kBM - 1) / kBM;
-    const int qTile = numQTiles - 1 - (int)blockIdx.x;
-    const int head = blockIdx.y, b = blockIdx.z;
+    // heavy (late) query tiles first; consecutive CTAs share a KV head so K/V tiles hit in L2
+    const int numPairs = (p.seqLen + 2 * kBM - 1) / (2 * kBM);
+    const int perPair = p.numHeads * p.batch;
+    const int pairIdx = numPairs - 1 - (int)(blockIdx.x / perPair);
+    const int rem = (int)(blockIdx.x % perPair);
+    const int head = rem % p.numHeads, b = rem / p.numHeads;
     const int kvHead = head / (p.numHeads / p.kvHeads);
-    const int q0 = qTile * kBM;
-    const int lastKey = p.causal ? min(p.seqLen, q0 + kBM) : p.seqLen;  // keys [0, lastKey) can be visible to this tile
-    const int numKTiles = (lastKey + kBN - 1) / kBN;
+    const int q0 = pairIdx * 2 * kBM;
+    // number of key tiles each query tile needs
+    int nT[2];
+#pragma unroll
+    for (int t = 0; t < 2; t++) {
+        const int qs = q0 + t * kBM;
+        const int lastKey = p.causal ? min(p.seqLen, qs + kBM) : p.seqLen;
+        nT[t] = qs < p.seqLen ? (lastKey + kBN - 1) / kBN : 0;
+    }
+    const int nMax = max(nT[0], nT[1]);
 
     if (threadIdx.x == 0) {
         abortShared = 0;
-        mbar_init(bar(BAR_Q), 1);
-        mbar_init(bar(BAR_QREADY), 128);
+        for (int t = 0; t < 2; t++) {
+            mbar_init(bar(BAR_Q + t), 1);
+            mbar_init(bar(BAR_QREADY + t), 128);
+            mbar_init(bar(BAR_S + t), 1);
+            mbar_init(bar(BAR_P + t), 128);
+            mbar_init(bar(BAR_O + t), 1);
+        }
         for (int s = 0; s < kStages; s++) {
             mbar_init(bar(BAR_KV_FULL + s), 1);
             mbar_init(bar(BAR_KV_EMPTY + s), 1);
         }
-        mbar_init(bar(BAR_S), 1);
-        mbar_init(bar(BAR_P), 128);
-        mbar_init(bar(BAR_O), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 4) {
+    if (warp == 8) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmemBaseShared)), "r"(kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -203,13 +272,16 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const __grid_const
     fence_after();
     const uint32_t tmem = tmemBaseShared;
 
-    if (warp == 5) {
+    if (warp == 9) {
         // ------------------------------------------------ TMA producer ------------------------------------------------
         if (lane == 0) {
-            mbar_expect_tx(bar(BAR_Q), kTileBytes);
-            tma_load_4d(sBase + kSmemQ, &p.tmQ, bar(BAR_Q), 0, head, q0, b);
-            tma_load_4d(sBase + kSmemQ + kHalfTile, &p.tmQ, bar(BAR_Q), 64, head, q0, b);
-            for (int j = 0; j < numKTiles; j++) {
+            for (int t = 0; t < 2; t++) {
+                if (nT[t] == 0) continue;
+                mbar_expect_tx(bar(BAR_Q + t), kTileBytes);
+                tma_load_4d(sBase + kSmemQ + t * kTileBytes, &p.tmQ, bar(BAR_Q + t), 0, head, q0 + t * kBM, b);
+                tma_load_4d(sBase + kSmemQ + t * kTileBytes + kHalfTile, &p.tmQ, bar(BAR_Q + t), 64, head, q0 + t * kBM, b);
+            }
+            for (int j = 0; j < nMax; j++) {
                 const int st = j % kStages;
                 if (j >= kStages) {
                     if (!mbar_wait(bar(BAR_KV_EMPTY + st), ((j / kStages) - 1) & 1, abortFlag)) { *abortFlag = 1; break; }
@@ -222,189 +294,184 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const __grid_const
                 tma_load_4d(vDst + kHalfTile, &p.tmV, bar(BAR_KV_FULL + st), 64, kvHead, j * kBN, b);
             }
         }
-    } else if (warp == 4) {
+    } else if (warp == 8) {
         // ------------------------------------------------ MMA issuer --------------------------------------------------
         if (lane == 0) {
             const uint32_t idescQK = make_idesc(BF16, false);
             const uint32_t idescPV = make_idesc(BF16, true);
-            bool okay = mbar_wait(bar(BAR_QREADY), 0, abortFlag);
-            for (int j = 0; j < numKTiles && okay; j++) {
-                const int st = j % kStages;
-                okay = mbar_wait(bar(BAR_KV_FULL + st), (j / kStages) & 1, abortFlag);
-                if (!okay) break;
-                fence_after();
-                const uint32_t kAddr = sBase + kSmemK + st * kTileBytes, vAddr = sBase + kSmemV + st * kTileBytes;
-                // S = Q K^T: 8 steps of K=16 over the 128 head dimensions (two 64-column swizzled blocks)
+            bool okay = true;
+            auto issue_qk = [&](int t, int j) {
+                const uint32_t kAddr = sBase + kSmemK + (j % kStages) * kTileBytes;
+                const uint32_t qAddr = sBase + kSmemQ + t * kTileBytes;
 #pragma unroll
                 for (int kk = 0; kk < 8; kk++) {
                     const uint32_t off = (kk >> 2) * kHalfTile + (kk & 3) * 32;
-                    mma_ss(tmem + kColS, make_desc(sBase + kSmemQ + off, 16, 1024), make_desc(kAddr + off, 16, 1024), idescQK, kk > 0);
+                    mma_ss(tmem + kColS + t * 128, make_desc(qAddr + off, 16, 1024), make_desc(kAddr + off, 16, 1024), idescQK, kk > 0);
                 }
-                mma_commit(bar(BAR_S));
-                okay = mbar_wait(bar(BAR_P), j & 1, abortFlag);
+                mma_commit(bar(BAR_S + t));
+            };
+            auto issue_pv = [&](int t, int j) {
+                const uint32_t vAddr = sBase + kSmemV + (j % kStages) * kTileBytes;
+#pragma unroll
+                for (int kk = 0; kk < 8; kk++)
+                    mma_ts(tmem + kColO + t * 128, tmem + kColS + t * 128 + kk * 8, make_desc(vAddr + kk * 16 * 128, p.vLBO, p.vSBO), idescPV,
+                           (j > 0 || kk > 0));
+            };
+            // prologue: first scores of both tiles
+            for (int t = 0; t < 2 && okay; t++) {
+                if (nT[t] == 0) continue;
+                okay = mbar_wait(bar(BAR_QREADY + t), 0, abortFlag);
+                if (okay && t == 0) okay = mbar_wait(bar(BAR_KV_FULL + 0), 0, abortFlag);
+                if (okay && t == 1 && nT[0] == 0) okay = mbar_wait(bar(BAR_KV_FULL + 0), 0, abortFlag);
                 if (!okay) break;
                 fence_after();
-                // O += P V: 8 steps of K=16 keys; P from TMEM (8 columns per step), V MN-major from shared memory
-#pragma unroll
-                for (int kk = 0; kk < 8; kk++) {
-                    mma_ts(tmem + kColO, tmem + kColP + kk * 8, make_desc(vAddr + kk * 16 * 128, p.vLBO, p.vSBO), idescPV, (j > 0 || kk > 0));
-                }
-                mma_commit(bar(BAR_KV_EMPTY + st));
+                issue_qk(t, 0);
             }
-            mma_commit(bar(BAR_O));
+            for (int j = 0; j < nMax && okay; j++) {
+                const int st = j % kStages;
+                for (int t = 0; t < 2 && okay; t++) {
+                    if (j >= nT[t]) continue;
+                    okay = mbar_wait(bar(BAR_P + t), j & 1, abortFlag);
+                    if (!okay) break;
+                    fence_after();
+                    issue_pv(t, j);
+                    if (j + 1 == nT[t]) mma_commit(bar(BAR_O + t));
+                    // is this the last product that reads stage st?  (tile 1 when it is still running, else tile 0)
+                    const bool lastUser = (t == 1) || (j >= nT[1]);
+                    if (lastUser) mma_commit(bar(BAR_KV_EMPTY + st));
+                    if (j + 1 < nT[t]) {
+                        okay = mbar_wait(bar(BAR_KV_FULL + (j + 1) % kStages), ((j + 1) / kStages) & 1, abortFlag);
+                        if (!okay) break;
+                        fence_after();
+                        issue_qk(t, j + 1);
+                    }
+                }
+            }
             if (!okay) *abortFlag = 1;
         }
     } else {
-        // ------------------------------------------------ softmax / epilogue warps ------------------------------------
-        const int row = threadIdx.x;             // 0..127 = TMEM lane = query row within the tile
-        const int qPos = q0 + row;
-        const uint32_t laneBase = tmem + ((uint32_t)(warp * 32) << 16);
-        bool okay = __all_sync(0xffffffffu, mbar_wait(bar(BAR_Q), 0, abortFlag));
-        if (okay && p.ropeMode != 2 && p.ropeTable != nullptr && qPos < p.seqLen) {
-            // rotate the raw Q row in shared memory (float32 math, unfused, rounded to storage)
-            const int half = kD / 2;
-            const float* cosT = p.ropeTable + (size_t)qPos * half;
-            const float* sinT = p.ropeTable + (size_t)p.seqLen * half + (size_t)qPos * half;
-            unsigned char* qRow0 = smem + kSmemQ + row * 128;
-            unsigned char* qRow1 = qRow0 + kHalfTile;
-#pragma unroll 1
-            for (int c = 0; c < 8; c++) {
-                const int sw = (c ^ (row & 7)) * 16;
-                if (p.ropeMode == 1) {
-                    // half mode: element i of block 0 pairs with element i of block 1
-                    Vec16 a = *(Vec16*)(qRow0 + sw), bq = *(Vec16*)(qRow1 + sw);
-#pragma unroll
-                    for (int w = 0; w < 4; w++) {
-                        uint32_t ra = 0, rb = 0;
-#pragma unroll
-                        for (int hsel = 0; hsel < 2; hsel++) {
-                            const int pi = c * 8 + w * 2 + hsel;
-                            const float e = widen16<BF16>((a.w[w] >> (16 * hsel)) & 0xFFFFu), o = widen16<BF16>((bq.w[w] >> (16 * hsel)) & 0xFFFFu);
-                            const float cs = __ldg(cosT + pi), sn = __ldg(sinT + pi);
-                            ra |= narrow16<BF16>(sub(mul(e, cs), mul(o, sn))) << (16 * hsel);
-                            rb |= narrow16<BF16>(add(mul(e, sn), mul(o, cs))) << (16 * hsel);
-                        }
-                        a.w[w] = ra;
-                        bq.w[w] = rb;
-                    }
-                    *(Vec16*)(qRow0 + sw) = a;
-                    *(Vec16*)(qRow1 + sw) = bq;
-                } else {
-                    // interleaved mode: pairs (2i, 2i+1) sit in one 32-bit word; both blocks hold their own pairs
-#pragma unroll
-                    for (int blk = 0; blk < 2; blk++) {
-                        unsigned char* ptr = (blk ? qRow1 : qRow0) + sw;
-                        Vec16 a = *(Vec16*)ptr;
-#pragma unroll
-                        for (int w = 0; w < 4; w++) {
-                            const int pi = blk * 32 + c * 4 + w;
-                            const float e = widen16<BF16>(a.w[w] & 0xFFFFu), o = widen16<BF16>(a.w[w] >> 16);
-                            const float cs = __ldg(cosT + pi), sn = __ldg(sinT + pi);
-                            a.w[w] = narrow16<BF16>(sub(mul(e, cs), mul(o, sn))) | (narrow16<BF16>(add(mul(e, sn), mul(o, cs))) << 16);
-                        }
-                        *(Vec16*)ptr = a;
-                    }
-                }
+        // ------------------------------------------------ softmax / epilogue groups -----------------------------------
+        const int t = warp >> 2;                  // query tile of this group
+        const int row = threadIdx.x & 127;        // TMEM lane = query row within the tile
+        const int qPos = q0 + t * kBM + row;
+        const uint32_t laneBase = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+        const uint32_t colS = kColS + t * 128, colO = kColO + t * 128;
+        const int n = nT[t];
+        bool okay = true;
+        if (n > 0) {
+            okay = __all_sync(0xffffffffu, mbar_wait(bar(BAR_Q + t), 0, abortFlag));
+            if (okay && p.ropeMode != 2 && p.ropeTable != nullptr && qPos < p.seqLen) {
+                const int half = kD / 2;
+                rotate_q_row<BF16>(smem + kSmemQ + t * kTileBytes + row * 128, row, p.ropeMode, p.ropeTable + (size_t)qPos * half,
+                                   p.ropeTable + (size_t)p.seqLen * half + (size_t)qPos * half);
             }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the tensor core
+            mbar_arrive(bar(BAR_QREADY + t));
         }
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the tensor core
-        mbar_arrive(bar(BAR_QREADY));
-
-        float mUsed = -INFINITY;   // the maximum the stored P and O are relative to (log2 domain)
+        float mUsed = -INFINITY;   // the maximum the stored P and O are relative to (scaled, log2 domain)
         float lsum = 0.f;
-        for (int j = 0; j < numKTiles && okay; j++) {
-            okay = __all_sync(0xffffffffu, mbar_wait(bar(BAR_S), j & 1, abortFlag));  // keep the warp convergent
+        const float scale = p.scaleLog2;
+        for (int j = 0; j < n && okay; j++) {
+            okay = __all_sync(0xffffffffu, mbar_wait(bar(BAR_S + t), j & 1, abortFlag));  // keeps the warp convergent
             if (!okay) break;
             fence_after();
             uint32_t sreg[128];
 #pragma unroll
-            for (int c = 0; c < 4; c++) tmem_ld32(laneBase + kColS + c * 32, sreg + c * 32);
+            for (int c = 0; c < 4; c++) tmem_ld32(laneBase + colS + c * 32, sreg + c * 32);
             tmem_wait_ld();
             const int key0 = j * kBN;
-            const bool needMask = (p.causal && key0 + kBN - 1 > q0) || (key0 + kBN > p.seqLen);
-            float mx = -INFINITY;
+            if (ROUND_SCORES) {
+                // the reference rounds every dot product to the storage type before scaling
 #pragma unroll
-            for (int i = 0; i < 128; i++) {
-                float s = __uint_as_float(sreg[i]);
-                if (ROUND_SCORES) s = widen16<BF16>(narrow16<BF16>(s));  // the reference rounds the dot product to storage
-                s *= p.scaleLog2;
-                if (needMask) {
-                    const int key = key0 + i;
-                    if ((p.causal && key > qPos) || key >= p.seqLen) s = -INFINITY;
-                }
-                sreg[i] = __float_as_uint(s);
-                mx = fmaxf(mx, s);
+                for (int i = 0; i < 128; i++) sreg[i] = __float_as_uint(widen16<BF16>(narrow16<BF16>(__uint_as_float(sreg[i]))));
             }
-            // lazy rescale: keep the old reference maximum unless the row maximum grew by more than 8 (factor 256)
-            float mNew = mUsed;
-            const bool grow = mx > mUsed + 8.0f || (mUsed == -INFINITY && mx > -INFINITY);
-            if (grow) mNew = mx;
-            const float alpha = (grow && mUsed != -INFINITY) ? exp2f(mUsed - mNew) : 1.0f;
-            if (j > 0 && __any_sync(0xffffffffu, grow && mUsed != -INFINITY)) {
-                // some row of this warp moved its maximum: rescale the O accumulator rows (alpha = 1 for the others)
+            if ((p.causal && key0 + kBN - 1 > q0 + t * kBM) || (key0 + kBN > p.seqLen)) {
+                // diagonal or ragged tile: mask keys beyond the row position / the sequence end
+#pragma unroll
+                for (int i = 0; i < 128; i++) {
+                    const int key = key0 + i;
+                    if ((p.causal && key > qPos) || key >= p.seqLen) sreg[i] = 0xFF800000u;  // -inf
+                }
+            }
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int i = 0; i < 128; i += 4) {
+#pragma unroll
+                for (int u = 0; u < 4; u++) mx4[u] = fmaxf(mx4[u], __uint_as_float(sreg[i + u]));
+            }
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale;  // scale > 0
+            // lazy rescale: keep the old reference maximum unless the row maximum grew by more than 8 (a factor 256)
+            const bool first = mUsed == -INFINITY;
+            const bool grow = first ? (mx > -INFINITY) : (mx > mUsed + 8.0f);
+            const float mNew = grow ? mx : mUsed;
+            const float alpha = (grow && !first) ? ex2_approx(mUsed - mNew) : 1.0f;
+            if (j > 0 && __any_sync(0xffffffffu, grow && !first)) {
+                // some row of this warp moved its maximum: rescale the O rows (alpha = 1 for the others)
 #pragma unroll 1
                 for (int c = 0; c < 4; c++) {
                     uint32_t oreg[32];
-                    tmem_ld32(laneBase + kColO + c * 32, oreg);
+                    tmem_ld32(laneBase + colO + c * 32, oreg);
                     tmem_wait_ld();
 #pragma unroll
                     for (int i = 0; i < 32; i++) oreg[i] = __float_as_uint(__uint_as_float(oreg[i]) * alpha);
-                    tmem_st32(laneBase + kColO + c * 32, oreg);
+                    tmem_st32(laneBase + colO + c * 32, oreg);
                 }
-                tmem_wait_st();
             }
             lsum *= alpha;
             mUsed = mNew;
-            float sum = 0.f;
+            const float negM = first && !grow ? 0.f : -mUsed;  // fully masked so far: every score is -inf and exp gives 0
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
             uint32_t preg[64];
 #pragma unroll
-            for (int i = 0; i < 64; i++) {
-                const float s0 = __uint_as_float(sreg[2 * i]), s1 = __uint_as_float(sreg[2 * i + 1]);
-                const float e0 = (mUsed == -INFINITY) ? 0.f : exp2f(s0 - mUsed);
-                const float e1 = (mUsed == -INFINITY) ? 0.f : exp2f(s1 - mUsed);
-                sum += e0 + e1;
+            for (int i = 0; i < 64; i += 2) {
+                const float e0 = ex2_approx(fmaf(__uint_as_float(sreg[2 * i]), scale, negM));
+                const float e1 = ex2_approx(fmaf(__uint_as_float(sreg[2 * i + 1]), scale, negM));
+                const float e2 = ex2_approx(fmaf(__uint_as_float(sreg[2 * i + 2]), scale, negM));
+                const float e3 = ex2_approx(fmaf(__uint_as_float(sreg[2 * i + 3]), scale, negM));
+                sum4[0] += e0; sum4[1] += e1; sum4[2] += e2; sum4[3] += e3;
                 preg[i] = pack2<BF16>(e0, e1);
+                preg[i + 1] = pack2<BF16>(e2, e3);
             }
-            lsum += sum;
-            tmem_st32(laneBase + kColP, preg);
-            tmem_st32(laneBase + kColP + 32, preg + 32);
+            lsum += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+            tmem_st32(laneBase + colS, preg);          // P overwrites the first 64 columns of S
+            tmem_st32(laneBase + colS + 32, preg + 32);
             tmem_wait_st();
             fence_before();
-            mbar_arrive(bar(BAR_P));
+            mbar_arrive(bar(BAR_P + t));
         }
-        // epilogue: wait for the last P V product, normalise and store
-        if (okay) okay = __all_sync(0xffffffffu, mbar_wait(bar(BAR_O), 0, abortFlag));
-        if (okay) {
-            fence_after();
-            const float inv = lsum > 0.f ? 1.0f / lsum : 0.f;
-            uint16_t* orow = (uint16_t*)p.out + (((size_t)b * p.seqLen + qPos) * p.numHeads + head) * kD;
+        // epilogue: wait for the last P V product of this tile, normalise and store
+        if (n > 0) {
+            if (okay) okay = __all_sync(0xffffffffu, mbar_wait(bar(BAR_O + t), 0, abortFlag));
+            if (okay) {
+                fence_after();
+                const float inv = lsum > 0.f ? 1.0f / lsum : 0.f;
+                uint16_t* orow = (uint16_t*)p.out + (((size_t)b * p.seqLen + qPos) * p.numHeads + head) * kD;
 #pragma unroll 1
-            for (int c = 0; c < 4; c++) {
-                uint32_t oreg[32];
-                tmem_ld32(laneBase + kColO + c * 32, oreg);
-                tmem_wait_ld();
-                if (qPos < p.seqLen) {
+                for (int c = 0; c < 4; c++) {
+                    uint32_t oreg[32];
+                    tmem_ld32(laneBase + colO + c * 32, oreg);
+                    tmem_wait_ld();
+                    if (qPos < p.seqLen) {
 #pragma unroll
-                    for (int v4 = 0; v4 < 4; v4++) {
-                        Vec16 o;
+                        for (int v4 = 0; v4 < 4; v4++) {
+                            Vec16 o;
 #pragma unroll
-                        for (int w = 0; w < 4; w++) {
-                            const float a = __uint_as_float(oreg[v4 * 8 + 2 * w]) * inv, bq = __uint_as_float(oreg[v4 * 8 + 2 * w + 1]) * inv;
-                            o.w[w] = narrow16<BF16>(a) | (narrow16<BF16>(bq) << 16);
+                            for (int w = 0; w < 4; w++)
+                                o.w[w] = pack2<BF16>(__uint_as_float(oreg[v4 * 8 + 2 * w]) * inv, __uint_as_float(oreg[v4 * 8 + 2 * w + 1]) * inv);
+                            *(Vec16*)(orow + c * 32 + v4 * 8) = o;
                         }
-                        *(Vec16*)(orow + c * 32 + v4 * 8) = o;
                     }
                 }
+            } else {
+                *abortFlag = 1;
             }
-        } else {
-            *abortFlag = 1;
         }
     }
     // ---------------------------------------------------- teardown ----------------------------------------------------
     fence_before();
     __syncthreads();
     if (abortShared && threadIdx.x == 0) atomicExch(p.errorFlag, 2);
-    if (warp == 4) {
+    if (warp == 8) {
         fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
     }
@@ -537,8 +604,8 @@ int launch_prefill(Context* ctx, int dt, const void* q, const void* k, const voi
     p.vSBO = 1024;           // next 8 keys
     if (const char* e = getenv("PUTER_PREFILL_V_LBO")) p.vLBO = (uint32_t)atoi(e);
     if (const char* e = getenv("PUTER_PREFILL_V_SBO")) p.vSBO = (uint32_t)atoi(e);
-    dim3 grid((seqLen + pf::kBM - 1) / pf::kBM, numHeads, batch);
-    const bool roundScores = getenv("PUTER_PREFILL_FAST") == nullptr;
+    dim3 grid(((seqLen + 2 * pf::kBM - 1) / (2 * pf::kBM)) * numHeads * batch);
+    const bool roundScores = getenv("PUTER_PREFILL_ROUND") != nullptr;
 #define PF_LAUNCH(B, R)                                                                                                        \
     do {                                                                                                                       \
         cudaFuncSetAttribute(pf::prefill_kernel<B, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pf::kSmemTotal);      \
