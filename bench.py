@@ -290,11 +290,13 @@ def main():
     ap.add_argument("--ref-seqs", type=int, default=4, help="sequences in the CPU sample")
     ap.add_argument("--ctx-min", type=int, default=512)
     ap.add_argument("--ctx-max", type=int, default=32768, help="smaller values give a profiler-sized case; not a bench number")
+    ap.add_argument("--prefill-batch", type=int, default=4, help="1 gives a profiler-sized prefill case; not a bench number")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-secondary", action="store_true")
     args = ap.parse_args()
     CTX_RANGE[0], CTX_RANGE[1] = args.ctx_min, args.ctx_max
-    profiling = (args.ctx_min, args.ctx_max) != (512, 32768)
+    os.environ["PUTER_BENCH_PREFILL_BATCH"] = str(args.prefill_batch)
+    profiling = (args.ctx_min, args.ctx_max) != (512, 32768) or args.prefill_batch != 4
     args.warmup = max(args.warmup, 3) if args.impl == "ours" and not profiling else args.warmup
 
     rank = int(os.environ.get("RANK", "0"))

@@ -200,6 +200,7 @@ class PrefillWorkload:
     B, S, HQ, HKV, D_ = 4, 4096, 32, 8, 128
 
     def __init__(self, dev, rank, world):
+        self.B = int(os.environ.get("PUTER_BENCH_PREFILL_BATCH", self.B))  # profiler captures use a single batch item
         import torch
 
         from puter_b200 import MultiHeadAttentionConfig, RoPEConfig, dtypes as D

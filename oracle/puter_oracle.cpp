@@ -785,37 +785,62 @@ ORACLE_API int oracle_paged_decode(int dt, int kvDT, const void* q, const void* 
     long long inner = kvHeads * headDim;
     size_t kes = esize(kvDT), qes = esize(dt);
     int rc = 0;
+    const float scale = (float)(1.0 / std::sqrt((double)headDim));
+    // phase 1: the two page gathers of every sequence (parallel over sequences)
+    std::vector<std::vector<char>> kg(batch), vg(batch);
+    std::vector<std::vector<float>> kf(batch), vf(batch), qf(batch), of(batch);
+    std::vector<char> live(batch, 0);
 #pragma omp parallel for schedule(dynamic, 1)
     for (long long b = 0; b < batch; b++) {
         long long ctx = ctxLens[b];
-        if (ctx <= 0) {
-            continue;  // seqK == 0: silent no-op (device/cpu/attention/compute.go:16-18)
-        }
+        if (ctx <= 0) continue;  // seqK == 0: silent no-op (device/cpu/attention/compute.go:16-18)
         if ((ctx + pageSize - 1) / pageSize > maxPages) { rc = -2; continue; }
         const int32_t* table = pageTable + b * maxPages;
-        std::vector<char> kg((size_t)ctx * inner * kes), vg((size_t)ctx * inner * kes);
-        if (oracle_page_gather(kvDT, kPages, table, kg.data(), pageCount, pageSize, inner, ctx, 0) != 0 ||
-            oracle_page_gather(kvDT, vPages, table, vg.data(), pageCount, pageSize, inner, ctx, 0) != 0) { rc = -2; continue; }
-        const char* qb = (const char*)q + (size_t)b * numHeads * headDim * qes;
-        char* ob = (char*)out + (size_t)b * numHeads * headDim * qes;
-        std::vector<float> scores(ctx);
-        float scale = (float)(1.0 / std::sqrt((double)headDim));
-        if (kvDT == dt) {
-            for (int h = 0; h < numHeads; h++)
-                mha_row(qb, kg.data(), vg.data(), ob, 0, 1, (int)ctx, (int)headDim, (int)numHeads, (int)kvHeads, h, 1, 0, 0.f, dt,
-                        scale, scores.data());
-        } else {
-            std::vector<float> kf((size_t)ctx * inner), vf((size_t)ctx * inner), qf(numHeads * headDim), of(numHeads * headDim);
+        kg[b].resize((size_t)ctx * inner * kes);
+        vg[b].resize((size_t)ctx * inner * kes);
+        if (oracle_page_gather(kvDT, kPages, table, kg[b].data(), pageCount, pageSize, inner, ctx, 0) != 0 ||
+            oracle_page_gather(kvDT, vPages, table, vg[b].data(), pageCount, pageSize, inner, ctx, 0) != 0) { rc = -2; continue; }
+        if (kvDT != dt) {
+            kf[b].resize((size_t)ctx * inner);
+            vf[b].resize((size_t)ctx * inner);
+            qf[b].resize(numHeads * headDim);
+            of[b].resize(numHeads * headDim);
             for (size_t i = 0; i < (size_t)ctx * inner; i++) {
                 int kvh = (int)((i % inner) / headDim);
-                kf[i] = load_typed(kg.data(), i, kvDT) * (kScale ? kScale[kvh] : 1.0f);
-                vf[i] = load_typed(vg.data(), i, kvDT) * (vScale ? vScale[kvh] : 1.0f);
+                kf[b][i] = load_typed(kg[b].data(), i, kvDT) * (kScale ? kScale[kvh] : 1.0f);
+                vf[b][i] = load_typed(vg[b].data(), i, kvDT) * (vScale ? vScale[kvh] : 1.0f);
             }
-            for (long long i = 0; i < numHeads * headDim; i++) qf[i] = load_typed(qb, i, dt);
-            for (int h = 0; h < numHeads; h++)
-                mha_row(qf.data(), kf.data(), vf.data(), of.data(), 0, 1, (int)ctx, (int)headDim, (int)numHeads, (int)kvHeads, h, 1,
-                        0, 0.f, F32, scale, scores.data());
-            for (long long i = 0; i < numHeads * headDim; i++) store_typed(ob, i, of[i], dt);
+            const char* qb = (const char*)q + (size_t)b * numHeads * headDim * qes;
+            for (long long i = 0; i < numHeads * headDim; i++) qf[b][i] = load_typed(qb, i, dt);
+        }
+        live[b] = 1;
+    }
+    // phase 2: MultiHeadAttention rows, one (sequence, head) per task
+#pragma omp parallel
+    {
+        std::vector<float> scores;
+#pragma omp for schedule(dynamic, 1)
+        for (long long u = 0; u < batch * numHeads; u++) {
+            long long b = u / numHeads;
+            int h = (int)(u % numHeads);
+            if (!live[b]) continue;
+            int ctx = ctxLens[b];
+            scores.resize(ctx);
+            const char* qb = (const char*)q + (size_t)b * numHeads * headDim * qes;
+            char* ob = (char*)out + (size_t)b * numHeads * headDim * qes;
+            if (kvDT == dt)
+                mha_row(qb, kg[b].data(), vg[b].data(), ob, 0, 1, ctx, (int)headDim, (int)numHeads, (int)kvHeads, h, 1, 0, 0.f, dt, scale,
+                        scores.data());
+            else
+                mha_row(qf[b].data(), kf[b].data(), vf[b].data(), of[b].data(), 0, 1, ctx, (int)headDim, (int)numHeads, (int)kvHeads, h,
+                        1, 0, 0.f, F32, scale, scores.data());
+        }
+    }
+    if (kvDT != dt) {
+        for (long long b = 0; b < batch; b++) {
+            if (!live[b]) continue;
+            char* ob = (char*)out + (size_t)b * numHeads * headDim * qes;
+            for (long long i = 0; i < numHeads * headDim; i++) store_typed(ob, i, of[b][i], dt);
         }
     }
     return rc;

@@ -51,7 +51,19 @@ struct Params {
     int batch, seqLen, numHeads, kvHeads, causal, ropeMode;
     float scaleLog2;
     uint32_t vLBO, vSBO;
+#ifdef PUTER_TRACE
+    long long* trace;  // development builds only: per-phase clock64 stamps of one CTA
+#endif
 };
+
+#ifdef PUTER_TRACE
+#define PF_STAMP(slot)                                                                  \
+    do {                                                                                \
+        if (p.trace && blockIdx.x == gridDim.x / 2 && (slot) < 4096) p.trace[(slot)] = clock64(); \
+    } while (0)
+#else
+#define PF_STAMP(slot) do { } while (0)
+#endif
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -159,12 +171,31 @@ template <bool BF16> __device__ __forceinline__ uint32_t narrow16(float f) {
 }
 
 // barrier slots (8 bytes each) inside the barrier area; [2] = one per query tile of the CTA
-enum : uint32_t { BAR_Q = 0, BAR_QREADY = 2, BAR_KV_FULL = 4, BAR_KV_EMPTY = 6, BAR_S = 8, BAR_P = 10, BAR_O = 12, BAR_COUNT = 14 };
+enum : uint32_t { BAR_Q = 0, BAR_QREADY = 2, BAR_K_FULL = 4, BAR_K_EMPTY = 6, BAR_V_FULL = 8, BAR_V_EMPTY = 10, BAR_S = 12, BAR_P = 14,
+                  BAR_O = 16, BAR_P2 = 18, BAR_COUNT = 20 };
 
 __device__ __forceinline__ float ex2_approx(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
+}
+// 2^x for x <= 0 on the FMA pipe (the special-function unit does 16 exp2 per clock per SM and is the bottleneck of the
+// softmax): round x to the nearest integer n with the 1.5*2^23 trick, degree-4 polynomial for 2^f on f in [-0.5, 0.5]
+// (relative error 4e-5, far below the 16-bit rounding of P), then add n into the exponent field.
+__device__ __forceinline__ float ex2_fma(float x) {
+    x = fmaxf(x, -126.0f);
+    const float t = x + 12582912.0f;
+    const float f = x - (t - 12582912.0f);
+    float r = fmaf(f, 0.0096181291f, 0.0555041087f);
+    r = fmaf(f, r, 0.2402265070f);
+    r = fmaf(f, r, 0.6931471806f);
+    r = fmaf(f, r, 1.0f);
+    return __int_as_float(__float_as_int(r) + (__float_as_int(t) << 23));
+}
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
 }
 
 // Rotates one raw Q row in shared memory (two swizzled 64-column blocks), float32 math with unfused multiplies,
@@ -255,11 +286,14 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const __grid_const
             mbar_init(bar(BAR_QREADY + t), 128);
             mbar_init(bar(BAR_S + t), 1);
             mbar_init(bar(BAR_P + t), 128);
+            mbar_init(bar(BAR_P2 + t), 128);
             mbar_init(bar(BAR_O + t), 1);
         }
         for (int s = 0; s < kStages; s++) {
-            mbar_init(bar(BAR_KV_FULL + s), 1);
-            mbar_init(bar(BAR_KV_EMPTY + s), 1);
+            mbar_init(bar(BAR_K_FULL + s), 1);
+            mbar_init(bar(BAR_K_EMPTY + s), 1);
+            mbar_init(bar(BAR_V_FULL + s), 1);
+            mbar_init(bar(BAR_V_EMPTY + s), 1);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -281,17 +315,20 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const __grid_const
                 tma_load_4d(sBase + kSmemQ + t * kTileBytes, &p.tmQ, bar(BAR_Q + t), 0, head, q0 + t * kBM, b);
                 tma_load_4d(sBase + kSmemQ + t * kTileBytes + kHalfTile, &p.tmQ, bar(BAR_Q + t), 64, head, q0 + t * kBM, b);
             }
+            // K and V rings are released separately: a K stage is free as soon as both score products of its tile
+            // have run, a V stage after both P V products, so the next K tile is in flight a whole period early
             for (int j = 0; j < nMax; j++) {
                 const int st = j % kStages;
-                if (j >= kStages) {
-                    if (!mbar_wait(bar(BAR_KV_EMPTY + st), ((j / kStages) - 1) & 1, abortFlag)) { *abortFlag = 1; break; }
-                }
-                mbar_expect_tx(bar(BAR_KV_FULL + st), 2 * kTileBytes);
+                const uint32_t par = ((j / kStages) - 1) & 1;
+                if (j >= kStages && !mbar_wait(bar(BAR_K_EMPTY + st), par, abortFlag)) { *abortFlag = 1; break; }
+                mbar_expect_tx(bar(BAR_K_FULL + st), kTileBytes);
                 const uint32_t kDst = sBase + kSmemK + st * kTileBytes, vDst = sBase + kSmemV + st * kTileBytes;
-                tma_load_4d(kDst, &p.tmK, bar(BAR_KV_FULL + st), 0, kvHead, j * kBN, b);
-                tma_load_4d(kDst + kHalfTile, &p.tmK, bar(BAR_KV_FULL + st), 64, kvHead, j * kBN, b);
-                tma_load_4d(vDst, &p.tmV, bar(BAR_KV_FULL + st), 0, kvHead, j * kBN, b);
-                tma_load_4d(vDst + kHalfTile, &p.tmV, bar(BAR_KV_FULL + st), 64, kvHead, j * kBN, b);
+                tma_load_4d(kDst, &p.tmK, bar(BAR_K_FULL + st), 0, kvHead, j * kBN, b);
+                tma_load_4d(kDst + kHalfTile, &p.tmK, bar(BAR_K_FULL + st), 64, kvHead, j * kBN, b);
+                if (j >= kStages && !mbar_wait(bar(BAR_V_EMPTY + st), par, abortFlag)) { *abortFlag = 1; break; }
+                mbar_expect_tx(bar(BAR_V_FULL + st), kTileBytes);
+                tma_load_4d(vDst, &p.tmV, bar(BAR_V_FULL + st), 0, kvHead, j * kBN, b);
+                tma_load_4d(vDst + kHalfTile, &p.tmV, bar(BAR_V_FULL + st), 64, kvHead, j * kBN, b);
             }
         }
     } else if (warp == 8) {
@@ -300,29 +337,43 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const __grid_const
             const uint32_t idescQK = make_idesc(BF16, false);
             const uint32_t idescPV = make_idesc(BF16, true);
             bool okay = true;
+            // One thread issues every MMA, and an M=128, N=128, K=16 product only lasts ~64 cycles on the tensor core, so
+            // the issue path is kept to an add per operand: descriptors are a constant high word plus a low word whose
+            // address field (bytes >> 4) is advanced by compile-time offsets and a per-stage delta.
+            const uint64_t kmajorHi = make_desc(0, 16, 1024) >> 32, vHi = make_desc(0, p.vLBO, p.vSBO) >> 32;
+            const uint32_t qLo = (uint32_t)make_desc(sBase + kSmemQ, 16, 1024), kLo = (uint32_t)make_desc(sBase + kSmemK, 16, 1024);
+            const uint32_t vLo = (uint32_t)make_desc(sBase + kSmemV, p.vLBO, p.vSBO);
+            auto desc = [](uint64_t hi, uint32_t lo) { return (hi << 32) | (uint64_t)lo; };
             auto issue_qk = [&](int t, int j) {
-                const uint32_t kAddr = sBase + kSmemK + (j % kStages) * kTileBytes;
-                const uint32_t qAddr = sBase + kSmemQ + t * kTileBytes;
+                const uint32_t kS = kLo + (uint32_t)(j % kStages) * (kTileBytes >> 4);
+                const uint32_t qS = qLo + (uint32_t)t * (kTileBytes >> 4);
+                const uint32_t dS = tmem + kColS + t * 128;
 #pragma unroll
                 for (int kk = 0; kk < 8; kk++) {
-                    const uint32_t off = (kk >> 2) * kHalfTile + (kk & 3) * 32;
-                    mma_ss(tmem + kColS + t * 128, make_desc(qAddr + off, 16, 1024), make_desc(kAddr + off, 16, 1024), idescQK, kk > 0);
+                    const uint32_t off = ((kk >> 2) * kHalfTile + (kk & 3) * 32) >> 4;
+                    mma_ss(dS, desc(kmajorHi, qS + off), desc(kmajorHi, kS + off), idescQK, kk > 0);
                 }
                 mma_commit(bar(BAR_S + t));
+                // last score product that reads this K stage (tile 1 while it is still running, else tile 0)
+                if (t == 1 || j >= nT[1]) mma_commit(bar(BAR_K_EMPTY + j % kStages));
             };
             auto issue_pv = [&](int t, int j) {
-                const uint32_t vAddr = sBase + kSmemV + (j % kStages) * kTileBytes;
+                const uint32_t vS = vLo + (uint32_t)(j % kStages) * (kTileBytes >> 4);
+                const uint32_t dO = tmem + kColO + t * 128, aP = tmem + kColS + t * 128;
+                mma_ts(dO, aP, desc(vHi, vS), idescPV, j > 0);
 #pragma unroll
-                for (int kk = 0; kk < 8; kk++)
-                    mma_ts(tmem + kColO + t * 128, tmem + kColS + t * 128 + kk * 8, make_desc(vAddr + kk * 16 * 128, p.vLBO, p.vSBO), idescPV,
-                           (j > 0 || kk > 0));
+                for (int kk = 1; kk < 4; kk++) mma_ts(dO, aP + kk * 8, desc(vHi, vS + ((kk * 16 * 128) >> 4)), idescPV, 1);
+                if (!mbar_wait(bar(BAR_P2 + t), j & 1, abortFlag)) return false;  // second half of P
+                fence_after();
+#pragma unroll
+                for (int kk = 4; kk < 8; kk++) mma_ts(dO, aP + kk * 8, desc(vHi, vS + ((kk * 16 * 128) >> 4)), idescPV, 1);
+                return true;
             };
             // prologue: first scores of both tiles
             for (int t = 0; t < 2 && okay; t++) {
                 if (nT[t] == 0) continue;
                 okay = mbar_wait(bar(BAR_QREADY + t), 0, abortFlag);
-                if (okay && t == 0) okay = mbar_wait(bar(BAR_KV_FULL + 0), 0, abortFlag);
-                if (okay && t == 1 && nT[0] == 0) okay = mbar_wait(bar(BAR_KV_FULL + 0), 0, abortFlag);
+                if (okay) okay = mbar_wait(bar(BAR_K_FULL + 0), 0, abortFlag);
                 if (!okay) break;
                 fence_after();
                 issue_qk(t, 0);
@@ -331,19 +382,26 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const __grid_const
                 const int st = j % kStages;
                 for (int t = 0; t < 2 && okay; t++) {
                     if (j >= nT[t]) continue;
-                    okay = mbar_wait(bar(BAR_P + t), j & 1, abortFlag);
+                    PF_STAMP(2048 + 512 * t + j * 8 + 0);
+                    okay = mbar_wait(bar(BAR_V_FULL + st), (j / kStages) & 1, abortFlag);
+                    PF_STAMP(2048 + 512 * t + j * 8 + 1);
+                    if (okay) okay = mbar_wait(bar(BAR_P + t), j & 1, abortFlag);
                     if (!okay) break;
                     fence_after();
-                    issue_pv(t, j);
+                    PF_STAMP(2048 + 512 * t + j * 8 + 2);
+                    okay = issue_pv(t, j);
+                    if (!okay) break;
+                    PF_STAMP(2048 + 512 * t + j * 8 + 3);
                     if (j + 1 == nT[t]) mma_commit(bar(BAR_O + t));
-                    // is this the last product that reads stage st?  (tile 1 when it is still running, else tile 0)
-                    const bool lastUser = (t == 1) || (j >= nT[1]);
-                    if (lastUser) mma_commit(bar(BAR_KV_EMPTY + st));
+                    // last product that reads this V stage (tile 1 while it is still running, else tile 0)
+                    if (t == 1 || j >= nT[1]) mma_commit(bar(BAR_V_EMPTY + st));
                     if (j + 1 < nT[t]) {
-                        okay = mbar_wait(bar(BAR_KV_FULL + (j + 1) % kStages), ((j + 1) / kStages) & 1, abortFlag);
+                        okay = mbar_wait(bar(BAR_K_FULL + (j + 1) % kStages), ((j + 1) / kStages) & 1, abortFlag);
                         if (!okay) break;
                         fence_after();
+                        PF_STAMP(2048 + 512 * t + j * 8 + 4);
                         issue_qk(t, j + 1);
+                        PF_STAMP(2048 + 512 * t + j * 8 + 5);
                     }
                 }
             }
@@ -372,13 +430,16 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const __grid_const
         float lsum = 0.f;
         const float scale = p.scaleLog2;
         for (int j = 0; j < n && okay; j++) {
+            if ((threadIdx.x & 127) == 0) PF_STAMP(1024 * t + j * 8 + 0);
             okay = __all_sync(0xffffffffu, mbar_wait(bar(BAR_S + t), j & 1, abortFlag));  // keeps the warp convergent
             if (!okay) break;
             fence_after();
+            if ((threadIdx.x & 127) == 0) PF_STAMP(1024 * t + j * 8 + 1);
             uint32_t sreg[128];
 #pragma unroll
             for (int c = 0; c < 4; c++) tmem_ld32(laneBase + colS + c * 32, sreg + c * 32);
             tmem_wait_ld();
+            if ((threadIdx.x & 127) == 0) PF_STAMP(1024 * t + j * 8 + 2);
             const int key0 = j * kBN;
             if (ROUND_SCORES) {
                 // the reference rounds every dot product to the storage type before scaling
@@ -395,9 +456,9 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const __grid_const
             }
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int i = 0; i < 128; i += 4) {
+            for (int i = 0; i < 128; i += 8) {
 #pragma unroll
-                for (int u = 0; u < 4; u++) mx4[u] = fmaxf(mx4[u], __uint_as_float(sreg[i + u]));
+                for (int u = 0; u < 4; u++) mx4[u] = fmax3(mx4[u], __uint_as_float(sreg[i + 2 * u]), __uint_as_float(sreg[i + 2 * u + 1]));
             }
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale;  // scale > 0
             // lazy rescale: keep the old reference maximum unless the row maximum grew by more than 8 (a factor 256)
@@ -417,27 +478,34 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const __grid_const
                     tmem_st32(laneBase + colO + c * 32, oreg);
                 }
             }
+            if ((threadIdx.x & 127) == 0) PF_STAMP(1024 * t + j * 8 + 3);
             lsum *= alpha;
             mUsed = mNew;
             const float negM = first && !grow ? 0.f : -mUsed;  // fully masked so far: every score is -inf and exp gives 0
             float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-            uint32_t preg[64];
+            // P is packed in place (word i receives elements 2i and 2i+1, consumed by then) and handed to the MMA warp in two
+            // halves of 64 keys, so the first half of the P V product runs while the second half is still exponentiated.
+            // One exponential in four runs on the FMA pipe instead of the special-function unit.
 #pragma unroll
-            for (int i = 0; i < 64; i += 2) {
-                const float e0 = ex2_approx(fmaf(__uint_as_float(sreg[2 * i]), scale, negM));
-                const float e1 = ex2_approx(fmaf(__uint_as_float(sreg[2 * i + 1]), scale, negM));
-                const float e2 = ex2_approx(fmaf(__uint_as_float(sreg[2 * i + 2]), scale, negM));
-                const float e3 = ex2_approx(fmaf(__uint_as_float(sreg[2 * i + 3]), scale, negM));
-                sum4[0] += e0; sum4[1] += e1; sum4[2] += e2; sum4[3] += e3;
-                preg[i] = pack2<BF16>(e0, e1);
-                preg[i + 1] = pack2<BF16>(e2, e3);
+            for (int hlf = 0; hlf < 2; hlf++) {
+#pragma unroll
+                for (int i = hlf * 32; i < hlf * 32 + 32; i += 2) {
+                    const float e0 = ex2_approx(fmaf(__uint_as_float(sreg[2 * i]), scale, negM));
+                    const float e1 = ex2_approx(fmaf(__uint_as_float(sreg[2 * i + 1]), scale, negM));
+                    const float e2 = ex2_approx(fmaf(__uint_as_float(sreg[2 * i + 2]), scale, negM));
+                    const float e3 = ex2_fma(fmaf(__uint_as_float(sreg[2 * i + 3]), scale, negM));
+                    sum4[0] += e0; sum4[1] += e1; sum4[2] += e2; sum4[3] += e3;
+                    sreg[i] = pack2<BF16>(e0, e1);
+                    sreg[i + 1] = pack2<BF16>(e2, e3);
+                }
+                tmem_st32(laneBase + colS + hlf * 32, sreg + hlf * 32);  // P overwrites the first 64 columns of S
+                tmem_wait_st();
+                fence_before();
+                mbar_arrive(bar((hlf ? BAR_P2 : BAR_P) + t));
+                if (hlf == 0 && (threadIdx.x & 127) == 0) PF_STAMP(1024 * t + j * 8 + 4);
             }
             lsum += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-            tmem_st32(laneBase + colS, preg);          // P overwrites the first 64 columns of S
-            tmem_st32(laneBase + colS + 32, preg + 32);
-            tmem_wait_st();
-            fence_before();
-            mbar_arrive(bar(BAR_P + t));
+            if ((threadIdx.x & 127) == 0) PF_STAMP(1024 * t + j * 8 + 5);
         }
         // epilogue: wait for the last P V product of this tile, normalise and store
         if (n > 0) {
@@ -602,6 +670,10 @@ int launch_prefill(Context* ctx, int dt, const void* q, const void* k, const voi
     p.scaleLog2 = (float)(1.0 / sqrt(128.0)) * 1.4426950408889634f;
     p.vLBO = pf::kHalfTile;  // next 64 head dimensions (next swizzled block)
     p.vSBO = 1024;           // next 8 keys
+#ifdef PUTER_TRACE
+    p.trace = nullptr;
+    if (const char* e = getenv("PUTER_TRACE_PTR")) p.trace = (long long*)strtoull(e, nullptr, 0);
+#endif
     if (const char* e = getenv("PUTER_PREFILL_V_LBO")) p.vLBO = (uint32_t)atoi(e);
     if (const char* e = getenv("PUTER_PREFILL_V_SBO")) p.vSBO = (uint32_t)atoi(e);
     dim3 grid(((seqLen + 2 * pf::kBM - 1) / (2 * pf::kBM)) * numHeads * batch);
