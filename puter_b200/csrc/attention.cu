@@ -24,8 +24,8 @@ int launch_prefill(Context* ctx, int dt, const void* q, const void* k, const voi
                    CUDAStatus* status);
 int validate_rope(CUDAStatus* status, double base, uint32_t halfMode, uint32_t scaling, double factor, double low, double high,
                   uint32_t origCtx);
-int build_rope_table(Context* ctx, float* table, size_t seqLen, int headDim, double base, long long startPos, int scaling, double factor,
-                     double low, double high, int origCtx, CUDAStatus* status);
+const float* cached_rope_table(Context* ctx, size_t seqLen, int headDim, double base, long long startPos, int scaling, double factor,
+                               double low, double high, int origCtx, CUDAStatus* status);
 
 __global__ void fill_i32_kernel(int32_t* p, int32_t v, int n) {
     int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -112,14 +112,11 @@ extern "C" int cuda_dispatch_rope_attention_prefill(CUDADeviceRef contextRef, in
     if (!ctx->exact && aligned && prefill_supported(elementDType, seqLen, seqLen, numHeads, kvHeads, headDim, causal)) {
         const float* table = nullptr;
         if (ropeMode != 2) {
-            const size_t tableBytes = (size_t)seqLen * (headDim / 2) * 2 * sizeof(float);
-            // the table sits at the end of the workspace the prefill kernel may also use
-            float* t = (float*)ensure_workspace(ctx, tableBytes + batch * kvElems * es + 1024, status);
-            if (!t) return status ? status->code : -7;
-            int rc = build_rope_table(ctx, t, seqLen, (int)headDim, baseFreq, (long long)startPosition, (int)scaling, scalingFactor,
+            // scratch for the rotated K; the cos/sin table comes from the context's cache
+            if (!ensure_workspace(ctx, batch * kvElems * es + 1024, status)) return status ? status->code : -7;
+            table = cached_rope_table(ctx, seqLen, (int)headDim, baseFreq, (long long)startPosition, (int)scaling, scalingFactor,
                                       lowFreqFactor, highFreqFactor, (int)originalContext, status);
-            if (rc != 0) return rc;
-            table = t;
+            if (!table) return status ? status->code : -7;
         }
         return launch_prefill(ctx, elementDType, q, k, v, o, batch, seqLen, numHeads, kvHeads, headDim, causal, (int)ropeMode, table, status);
     }

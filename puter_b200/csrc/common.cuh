@@ -41,6 +41,11 @@ struct Context {
     size_t pinnedBytes;
     cudaEvent_t stageEvents[4];
     int* errorFlag;  // device int32 owned by the context
+    // cos/sin table of the last RoPE configuration (positions x headDim/2, cos then sin), reused while the config repeats
+    float* ropeTable;
+    size_t ropeTableBytes;
+    double ropeKey[8];
+    int ropeKeyValid;
 };
 
 int fail(CUDAStatus* status, int code, const char* fmt, ...);

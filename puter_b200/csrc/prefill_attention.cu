@@ -170,6 +170,12 @@ template <bool BF16> __device__ __forceinline__ uint32_t narrow16(float f) {
     return f32_to_f16_bits(f);
 }
 
+// how many of every four exponentials run on the FMA pipe instead of the special-function unit (0, 1 or 2).
+// Measured on config 3: 0 -> 964 TFLOP/s, 1 -> 902, 2 -> 784 (the softmax warps are issue-bound, not MUFU-bound), so 0.
+#ifndef PF_EMU_PATTERN
+#define PF_EMU_PATTERN 0
+#endif
+
 // barrier slots (8 bytes each) inside the barrier area; [2] = one per query tile of the CTA
 enum : uint32_t { BAR_Q = 0, BAR_QREADY = 2, BAR_K_FULL = 4, BAR_K_EMPTY = 6, BAR_V_FULL = 8, BAR_V_EMPTY = 10, BAR_S = 12, BAR_P = 14,
                   BAR_O = 16, BAR_P2 = 18, BAR_COUNT = 20 };
@@ -203,40 +209,43 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
 template <bool BF16>
 __device__ __forceinline__ void rotate_q_row(unsigned char* qRow0, int row, int ropeMode, const float* cosT, const float* sinT) {
     unsigned char* qRow1 = qRow0 + kHalfTile;
-#pragma unroll 1
+#pragma unroll 2
     for (int c = 0; c < 8; c++) {
         const int sw = (c ^ (row & 7)) * 16;
         if (ropeMode == 1) {
-            // half mode: element i of block 0 pairs with element i of block 1
+            // half mode: element i of block 0 pairs with element i of block 1; this chunk covers pairs 8c .. 8c+7
+            const float4 c0 = __ldg((const float4*)(cosT + c * 8)), c1 = __ldg((const float4*)(cosT + c * 8 + 4));
+            const float4 s0 = __ldg((const float4*)(sinT + c * 8)), s1 = __ldg((const float4*)(sinT + c * 8 + 4));
+            const float cs[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+            const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
             Vec16 a = *(Vec16*)(qRow0 + sw), bq = *(Vec16*)(qRow1 + sw);
 #pragma unroll
             for (int w = 0; w < 4; w++) {
-                uint32_t ra = 0, rb = 0;
+                float re[2], ro[2];
 #pragma unroll
                 for (int hsel = 0; hsel < 2; hsel++) {
-                    const int pi = c * 8 + w * 2 + hsel;
+                    const int pi = w * 2 + hsel;
                     const float e = widen16<BF16>((a.w[w] >> (16 * hsel)) & 0xFFFFu), o = widen16<BF16>((bq.w[w] >> (16 * hsel)) & 0xFFFFu);
-                    const float cs = __ldg(cosT + pi), sn = __ldg(sinT + pi);
-                    ra |= narrow16<BF16>(sub(mul(e, cs), mul(o, sn))) << (16 * hsel);
-                    rb |= narrow16<BF16>(add(mul(e, sn), mul(o, cs))) << (16 * hsel);
+                    re[hsel] = sub(mul(e, cs[pi]), mul(o, sn[pi]));
+                    ro[hsel] = add(mul(e, sn[pi]), mul(o, cs[pi]));
                 }
-                a.w[w] = ra;
-                bq.w[w] = rb;
+                a.w[w] = pack2<BF16>(re[0], re[1]);   // round-to-nearest-even to storage
+                bq.w[w] = pack2<BF16>(ro[0], ro[1]);
             }
             *(Vec16*)(qRow0 + sw) = a;
             *(Vec16*)(qRow1 + sw) = bq;
         } else {
-            // interleaved mode: pairs (2i, 2i+1) sit in one 32-bit word; each block holds its own pairs
+            // interleaved mode: pairs (2i, 2i+1) sit in one 32-bit word; block blk, chunk c holds pairs 32*blk + 4c .. +3
 #pragma unroll
             for (int blk = 0; blk < 2; blk++) {
                 unsigned char* ptr = (blk ? qRow1 : qRow0) + sw;
+                const float4 c4 = __ldg((const float4*)(cosT + blk * 32 + c * 4)), s4 = __ldg((const float4*)(sinT + blk * 32 + c * 4));
+                const float cs[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
                 Vec16 a = *(Vec16*)ptr;
 #pragma unroll
                 for (int w = 0; w < 4; w++) {
-                    const int pi = blk * 32 + c * 4 + w;
                     const float e = widen16<BF16>(a.w[w] & 0xFFFFu), o = widen16<BF16>(a.w[w] >> 16);
-                    const float cs = __ldg(cosT + pi), sn = __ldg(sinT + pi);
-                    a.w[w] = narrow16<BF16>(sub(mul(e, cs), mul(o, sn))) | (narrow16<BF16>(add(mul(e, sn), mul(o, cs))) << 16);
+                    a.w[w] = pack2<BF16>(sub(mul(e, cs[w]), mul(o, sn[w])), add(mul(e, sn[w]), mul(o, cs[w])));
                 }
                 *(Vec16*)ptr = a;
             }
@@ -490,10 +499,12 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const __grid_const
             for (int hlf = 0; hlf < 2; hlf++) {
 #pragma unroll
                 for (int i = hlf * 32; i < hlf * 32 + 32; i += 2) {
-                    const float e0 = ex2_approx(fmaf(__uint_as_float(sreg[2 * i]), scale, negM));
-                    const float e1 = ex2_approx(fmaf(__uint_as_float(sreg[2 * i + 1]), scale, negM));
-                    const float e2 = ex2_approx(fmaf(__uint_as_float(sreg[2 * i + 2]), scale, negM));
-                    const float e3 = ex2_fma(fmaf(__uint_as_float(sreg[2 * i + 3]), scale, negM));
+                    const float x0 = fmaf(__uint_as_float(sreg[2 * i]), scale, negM), x1 = fmaf(__uint_as_float(sreg[2 * i + 1]), scale, negM);
+                    const float x2 = fmaf(__uint_as_float(sreg[2 * i + 2]), scale, negM), x3 = fmaf(__uint_as_float(sreg[2 * i + 3]), scale, negM);
+                    const float e0 = ex2_approx(x0);
+                    const float e1 = (PF_EMU_PATTERN >= 2) ? ex2_fma(x1) : ex2_approx(x1);
+                    const float e2 = ex2_approx(x2);
+                    const float e3 = (PF_EMU_PATTERN >= 1) ? ex2_fma(x3) : ex2_approx(x3);
                     sum4[0] += e0; sum4[1] += e1; sum4[2] += e2; sum4[3] += e3;
                     sreg[i] = pack2<BF16>(e0, e1);
                     sreg[i + 1] = pack2<BF16>(e2, e3);
@@ -642,12 +653,10 @@ int launch_prefill(Context* ctx, int dt, const void* q, const void* k, const voi
     const void* kUse = k;
     if (ropeMode != 2) {
         if (!ropeTable) return fail(status, -2, "prefill attention: missing rope table");
-        // rotated K lives in the workspace right after the table (the caller sized the workspace for both)
-        const size_t tableBytes = (size_t)seqLen * 64 * 2 * sizeof(float);
+        // rotated K lives in the workspace (the caller sized it)
         const size_t kBytes = (size_t)batch * seqLen * kvHeads * 128 * 2;
-        if (ctx->workspaceBytes < tableBytes + kBytes + 1024 || (const char*)ropeTable != (const char*)ctx->workspace)
-            return fail(status, -7, "prefill attention: workspace not prepared");
-        uint16_t* kRot = (uint16_t*)((char*)ctx->workspace + ((tableBytes + 255) & ~(size_t)255));
+        if (ctx->workspaceBytes < kBytes) return fail(status, -7, "prefill attention: workspace not prepared");
+        uint16_t* kRot = (uint16_t*)ctx->workspace;
         const size_t items = (size_t)batch * seqLen * kvHeads * 16;
         size_t blocks = (items + 255) / 256, cap = (size_t)ctx->smCount * 16;
         if (blocks > cap) blocks = cap;

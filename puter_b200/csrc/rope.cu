@@ -184,6 +184,37 @@ int build_rope_table(Context* ctx, float* table, size_t seqLen, int headDim, dou
     return check_launch(ctx, status, "rope table");
 }
 
+// Returns the cos/sin table for this configuration from the context's cache, rebuilding it only when the configuration
+// (or the number of positions) changed.  A decoder applies the same RoPE to q and k of every layer, so the float64
+// angle evaluation runs once per configuration instead of once per call.
+const float* cached_rope_table(Context* ctx, size_t seqLen, int headDim, double base, long long startPos, int scaling, double factor,
+                               double low, double high, int origCtx, CUDAStatus* status) {
+    const double key[8] = {(double)seqLen, (double)headDim, base, (double)startPos, (double)scaling,
+                           scaling ? factor : 0.0, scaling ? low + 1e6 * high : 0.0, scaling ? (double)origCtx : 0.0};
+    const size_t need = seqLen * (size_t)(headDim / 2) * 2 * sizeof(float);
+    if (ctx->ropeKeyValid && memcmp(key, ctx->ropeKey, sizeof(key)) == 0 && ctx->ropeTable && ctx->ropeTableBytes >= need)
+        return ctx->ropeTable;
+    ctx->ropeKeyValid = 0;
+    if (ctx->ropeTableBytes < need) {
+        if (ctx->ropeTable) {
+            cudaStreamSynchronize(ctx->stream);  // earlier launches may still read the old table
+            cudaFree(ctx->ropeTable);
+            ctx->ropeTable = nullptr;
+            ctx->ropeTableBytes = 0;
+        }
+        if (cudaMalloc((void**)&ctx->ropeTable, need) != cudaSuccess) {
+            cudaGetLastError();
+            fail(status, -7, "rope: table allocation of %zu bytes failed", need);
+            return nullptr;
+        }
+        ctx->ropeTableBytes = need;
+    }
+    if (build_rope_table(ctx, ctx->ropeTable, seqLen, headDim, base, startPos, scaling, factor, low, high, origCtx, status) != 0) return nullptr;
+    memcpy(ctx->ropeKey, key, sizeof(key));
+    ctx->ropeKeyValid = 1;
+    return ctx->ropeTable;
+}
+
 }  // namespace puter
 
 using namespace puter;
@@ -205,11 +236,10 @@ extern "C" int cuda_dispatch_rope_f64(CUDADeviceRef contextRef, int elementDType
     PUTER_REQUIRE(inputRef, "input", elems * es);
     PUTER_REQUIRE(outRef, "out", elems * es);
     size_t half = headDim / 2;
-    float* table = (float*)ensure_workspace(ctx, (size_t)seqLen * half * 2 * sizeof(float), status);
+    if (half > 128) return fail(status, -6, "rope: head dimension %u exceeds the supported maximum of 256", headDim);
+    const float* table = cached_rope_table(ctx, seqLen, (int)headDim, baseFreq, (long long)startPosition, (int)scaling, scalingFactor,
+                                           lowFreqFactor, highFreqFactor, (int)originalContext, status);
     if (!table) return status ? status->code : -7;
-    rc = build_rope_table(ctx, table, seqLen, (int)headDim, baseFreq, (long long)startPosition, (int)scaling, scalingFactor,
-                          lowFreqFactor, highFreqFactor, (int)originalContext, status);
-    if (rc != 0) return rc;
     const float* cosT = table;
     const float* sinT = table + (size_t)seqLen * half;
     const void* in = dev_ptr(inputRef);

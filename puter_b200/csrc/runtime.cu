@@ -143,6 +143,7 @@ void cuda_close_device(CUDADeviceRef device) {
     for (int i = 0; i < 2; i++)
         if (ctx->pinned[i]) cudaFreeHost(ctx->pinned[i]);
     if (ctx->errorFlag) cudaFree(ctx->errorFlag);
+    if (ctx->ropeTable) cudaFree(ctx->ropeTable);
     for (int i = 0; i < 4; i++)
         if (ctx->stageEvents[i]) cudaEventDestroy(ctx->stageEvents[i]);
     cudaStreamDestroy(ctx->ownStream);
