@@ -57,7 +57,7 @@ class ClockSampler:
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100", "-i",
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "20", "-i",
                                           str(self.gpu)], stdout=self.file, stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
@@ -373,7 +373,7 @@ def main():
 
     line = {
         "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": per_step * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "ms_per_step": per_step * 1e3, "higher_is_better": True, "scaling": getattr(wl, "scaling", "weak"), "vs_baseline": None,
         "dtype": wl.dtype if hasattr(wl, "dtype") else "bf16", "data": "synthetic", "config": wl.config(), "clocks": clocks,
         "e2e": {"value": getattr(wl, "e2e_value", wl.value)(per_step_e2e, world), "unit": unit, "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h,
                 "ms_per_step": per_step_e2e * 1e3},

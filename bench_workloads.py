@@ -92,6 +92,7 @@ class ChainWorkload:
     """Config 5.  h = x + r; n = RMSNorm(h); g = GatedResidual(h, branch, mod); s = SwiGLU(gate, up)."""
 
     T, C, I, B = 16384, 4096, 14336, 4
+    scaling = "strong"  # the 16384 token rows are divided among the ranks
 
     def __init__(self, dev, rank, world):
         import torch

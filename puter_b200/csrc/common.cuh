@@ -182,6 +182,69 @@ __device__ __forceinline__ float fast_exp32(float x) {
     p = add(1.0f, p);
     return __uint_as_float(__float_as_uint(p) + ((uint32_t)k << 23));
 }
+// Packed f32x2 arithmetic (Blackwell): two float32 lanes per instruction.  The assembler contracts a packed multiply
+// followed by a packed add into one fused multiply-add, so these helpers are used only where one rounding more or less
+// is acceptable: the 16-bit gated activations, whose result is rounded to bf16/f16 anyway.  The float32 paths keep the
+// scalar, never-fused operations and stay bit-identical to the reference.
+__device__ __forceinline__ uint64_t pk2(float lo, float hi) {
+    uint64_t d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "f"(lo), "f"(hi));
+    return d;
+}
+__device__ __forceinline__ void un2(uint64_t v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+// Two FastExp32 (device/cpu/math/f32.go:21-47) with the polynomial in Horner form on fused packed multiply-adds: the same
+// polynomial and exponent splice as the reference, each step rounded once instead of twice (<= 1 float32 ulp apart).
+__device__ __forceinline__ void fast_exp32x2_fused(float x0, float x1, float& e0, float& e1) {
+    float z0, z1;
+    un2(mul2(pk2(x0, x1), pk2(1.4426950408889634f, 1.4426950408889634f)), z0, z1);
+    int k0 = (int)z0, k1 = (int)z1;
+    if (z0 < 0.0f) k0--;
+    if (z1 < 0.0f) k1--;
+    const uint64_t f = add2(pk2(z0, z1), pk2(-(float)k0, -(float)k1));
+    uint64_t p = fma2(f, pk2(0.00133389f, 0.00133389f), pk2(0.00961812f, 0.00961812f));
+    p = fma2(f, p, pk2(0.05550410f, 0.05550410f));
+    p = fma2(f, p, pk2(0.24022650f, 0.24022650f));
+    p = fma2(f, p, pk2(0.69314718f, 0.69314718f));
+    p = fma2(f, p, pk2(1.0f, 1.0f));
+    float p0, p1;
+    un2(p, p0, p1);
+    e0 = __uint_as_float(__float_as_uint(p0) + ((uint32_t)k0 << 23));
+    e1 = __uint_as_float(__float_as_uint(p1) + ((uint32_t)k1 << 23));
+    if (x0 < -87.33654f) e0 = 0.0f;
+    if (x1 < -87.33654f) e1 = 0.0f;
+    if (x0 > 88.72283f) e0 = 3.40282346638528859812e+38f;
+    if (x1 > 88.72283f) e1 = 3.40282346638528859812e+38f;
+}
+// two FastSwiGLU32 (silu(gate) * up) for 16-bit storage types
+__device__ __forceinline__ void fast_swiglu32x2_fused(float g0, float g1, float u0, float u1, float& r0, float& r1) {
+    float e0, e1, d0, d1;
+    fast_exp32x2_fused(-g0, -g1, e0, e1);
+    un2(add2(pk2(1.0f, 1.0f), pk2(e0, e1)), d0, d1);
+    un2(mul2(pk2(divf(g0, d0), divf(g1, d1)), pk2(u0, u1)), r0, r1);
+}
+// two f32 -> one word of two bf16 with the library's rounding rule (hardware RNE; NaN payload rule applied on the rare NaN)
+__device__ __forceinline__ uint32_t f32x2_to_bf16x2(float lo, float hi) {
+    uint32_t w;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(w) : "f"(hi), "f"(lo));
+    if (lo != lo || hi != hi) w = f32_to_bf16_bits(lo) | (f32_to_bf16_bits(hi) << 16);
+    return w;
+}
+
 __device__ __forceinline__ float fast_tanh32(float x) {  // f32.go:71-86
     if (x > 4.92f) return 1.0f;
     if (x < -4.92f) return -1.0f;

@@ -85,7 +85,10 @@ __global__ void __launch_bounds__(256) narrow_kernel(const float* __restrict__ s
             uint32_t b = narrow_bits<DT>(__uint_as_float(in[w].w[1]));
             uint32_t c = narrow_bits<DT>(__uint_as_float(in[w].w[2]));
             uint32_t d = narrow_bits<DT>(__uint_as_float(in[w].w[3]));
-            if (EB == 2) {
+            if (DT == DT_BF16) {
+                out.w[2 * w] = f32x2_to_bf16x2(__uint_as_float(in[w].w[0]), __uint_as_float(in[w].w[1]));
+                out.w[2 * w + 1] = f32x2_to_bf16x2(__uint_as_float(in[w].w[2]), __uint_as_float(in[w].w[3]));
+            } else if (EB == 2) {
                 out.w[2 * w] = a | (b << 16);
                 out.w[2 * w + 1] = c | (d << 16);
             } else {

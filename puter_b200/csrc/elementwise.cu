@@ -73,6 +73,9 @@ template <int DT> __device__ __forceinline__ Vec16 pack(const float* f) {
     if (DT == DT_F32) {
 #pragma unroll
         for (int i = 0; i < 4; i++) v.w[i] = __float_as_uint(f[i]);
+    } else if (DT == DT_BF16) {
+#pragma unroll
+        for (int i = 0; i < 4; i++) v.w[i] = f32x2_to_bf16x2(f[2 * i], f[2 * i + 1]);
     } else {
 #pragma unroll
         for (int i = 0; i < 4; i++)
@@ -85,6 +88,19 @@ template <int DT> __device__ __forceinline__ float load1(const void* p, size_t i
 }
 template <int DT> __device__ __forceinline__ void store1(void* p, size_t i, float v) {
     Storage<DT>::store((typename Storage<DT>::type*)p, i, v);
+}
+
+// applies a gated variant to PER lanes.  16-bit SwiGLU goes two lanes at a time through the packed, fused f32x2 path
+// (results agree with the reference except for a 1-ulp difference on roughly one element in a million); float32 keeps
+// the scalar unfused operations and is bit-identical.
+template <int OP, int PER> __device__ __forceinline__ void gated_lanes(float* fa, const float* fb) {
+    if (OP == G_SWIGLU && PER == 8) {
+#pragma unroll
+        for (int i = 0; i < PER; i += 2) fast_swiglu32x2_fused(fa[i], fa[i + 1], fb[i], fb[i + 1], fa[i], fa[i + 1]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < PER; i++) fa[i] = gated32<OP>(fa[i], fb[i]);
+    }
 }
 
 // ---- kernels ----
@@ -163,8 +179,7 @@ __global__ void __launch_bounds__(256) gated_tensors_kernel(void* __restrict__ d
         float fa[PER], fb[PER];
         unpack<DT>(a, fa);
         unpack<DT>(b, fb);
-#pragma unroll
-        for (int i = 0; i < PER; i++) fa[i] = gated32<OP>(fa[i], fb[i]);
+        gated_lanes<OP, PER>(fa, fb);
         st_stream((char*)dst + v * 16, pack<DT>(fa));
     }
     for (size_t i = vecs * PER + tid; i < n; i += stride) store1<DT>(dst, i, gated32<OP>(load1<DT>(gate, i), load1<DT>(up, i)));
@@ -188,8 +203,7 @@ __global__ void __launch_bounds__(256) gated_packed_kernel(void* __restrict__ ds
             float fa[PER], fb[PER];
             unpack<DT>(a, fa);
             unpack<DT>(b, fb);
-#pragma unroll
-            for (int i = 0; i < PER; i++) fa[i] = gated32<OP>(fa[i], fb[i]);
+            gated_lanes<OP, PER>(fa, fb);
             st_stream((char*)dst + (row * half + c) * ES, pack<DT>(fa));
         }
     } else {

@@ -34,6 +34,9 @@ template <int DT> __device__ __forceinline__ Vec16 pack(const float* f) {
     if (DT == DT_F32) {
 #pragma unroll
         for (int i = 0; i < 4; i++) v.w[i] = __float_as_uint(f[i]);
+    } else if (DT == DT_BF16) {
+#pragma unroll
+        for (int i = 0; i < 4; i++) v.w[i] = f32x2_to_bf16x2(f[2 * i], f[2 * i + 1]);
     } else {
 #pragma unroll
         for (int i = 0; i < 4; i++)

@@ -122,6 +122,10 @@ def test_gated_tensors(d, name, code, dt, n):
     got = host(out, want.dtype)
     if name == "GeGLU":
         assert rel_err(O.to_f32(got, dt), O.to_f32(want, dt)) <= (1e-6 if dt == O.F32 else 1e-2)
+    elif name == "SwiGLU" and dt != O.F32:
+        # 16-bit SwiGLU evaluates the reference polynomial with fused multiply-adds: at most one unit in the last place, rarely
+        diff = ulp16_diff(got, want)
+        assert diff.max() <= 1 and (diff > 0).mean() <= 1e-3
     else:
         assert np.array_equal(got.view(np.uint8), want.view(np.uint8))
 
@@ -134,7 +138,12 @@ def test_swiglu_packed(d, dt, batch, half):
     want = O.gated_packed(O.SWIGLU, dt, packed, batch, half)
     out = empty(batch * half * ES[dt])
     d.SwiGLU(out, dev(packed), batch, half, dt)
-    assert np.array_equal(host(out, want.dtype).reshape(batch, half).view(np.uint8), want.view(np.uint8))
+    got = host(out, want.dtype).reshape(batch, half)
+    if dt == O.F32 or half % 8:  # float32 and the element-at-a-time path are bit-identical to the reference
+        assert np.array_equal(got.view(np.uint8), want.view(np.uint8))
+    else:
+        diff = ulp16_diff(got, want)
+        assert diff.max() <= 1 and (diff > 0).mean() <= 1e-3
 
 
 @pytest.mark.parametrize("op,code", [("Add", O.ADD), ("Sub", O.SUB), ("Mul", O.MUL), ("Div", O.DIV), ("Max", O.MAX), ("Min", O.MIN)])
