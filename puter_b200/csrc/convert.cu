@@ -30,39 +30,59 @@ template <> __device__ __forceinline__ uint32_t narrow_bits<DT_E5M2>(float f) { 
 
 template <int DT> struct Narrow { static constexpr int kBytes = (DT == DT_BF16 || DT == DT_F16) ? 2 : 1; };
 
-// narrow -> f32.  One 16-byte vector of narrow elements per thread-iteration.
+// narrow -> f32.  Writes dominate (4 output bytes per 1-2 input bytes), so the work is laid out for the stores: a thread
+// produces ONE 16-byte output vector from 4 input elements (8 or 4 input bytes), which makes every warp-wide store a
+// contiguous 512-byte run; four independent vectors per iteration keep enough loads in flight.
 template <int DT>
 __global__ void __launch_bounds__(256) widen_kernel(const uint8_t* __restrict__ src, float* __restrict__ dst, size_t n) {
     constexpr int EB = Narrow<DT>::kBytes;
-    constexpr int PER = 16 / EB;  // elements per vector
-    size_t vecs = n / PER;
-    size_t stride = (size_t)gridDim.x * blockDim.x;
-    for (size_t v = (size_t)blockIdx.x * blockDim.x + threadIdx.x; v < vecs; v += stride) {
-        Vec16 in = ld_stream(src + v * 16);
-        float* o = dst + v * PER;
+    constexpr int UNROLL = 4;
+    const size_t quads = n / 4;  // groups of 4 elements
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    size_t q = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    for (; q + (UNROLL - 1) * stride < quads; q += UNROLL * stride) {
+        uint32_t lo[UNROLL], hi[UNROLL];
 #pragma unroll
-        for (int w = 0; w < 4; w++) {
+        for (int u = 0; u < UNROLL; u++) {
+            const size_t g = q + u * stride;
+            if (EB == 2) {
+                asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(lo[u]), "=r"(hi[u]) : "l"(src + g * 8));
+            } else {
+                asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(lo[u]) : "l"(src + g * 4));
+                hi[u] = 0;
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; u++) {
             Vec16 out;
             if (EB == 2) {
-                if (w >= 2) break;
-                out.w[0] = __float_as_uint(widen_bits<DT>(in.w[2 * w] & 0xFFFFu));
-                out.w[1] = __float_as_uint(widen_bits<DT>(in.w[2 * w] >> 16));
-                out.w[2] = __float_as_uint(widen_bits<DT>(in.w[2 * w + 1] & 0xFFFFu));
-                out.w[3] = __float_as_uint(widen_bits<DT>(in.w[2 * w + 1] >> 16));
+                out.w[0] = __float_as_uint(widen_bits<DT>(lo[u] & 0xFFFFu));
+                out.w[1] = __float_as_uint(widen_bits<DT>(lo[u] >> 16));
+                out.w[2] = __float_as_uint(widen_bits<DT>(hi[u] & 0xFFFFu));
+                out.w[3] = __float_as_uint(widen_bits<DT>(hi[u] >> 16));
             } else {
-                out.w[0] = __float_as_uint(widen_bits<DT>(in.w[w] & 0xFFu));
-                out.w[1] = __float_as_uint(widen_bits<DT>((in.w[w] >> 8) & 0xFFu));
-                out.w[2] = __float_as_uint(widen_bits<DT>((in.w[w] >> 16) & 0xFFu));
-                out.w[3] = __float_as_uint(widen_bits<DT>(in.w[w] >> 24));
+                out.w[0] = __float_as_uint(widen_bits<DT>(lo[u] & 0xFFu));
+                out.w[1] = __float_as_uint(widen_bits<DT>((lo[u] >> 8) & 0xFFu));
+                out.w[2] = __float_as_uint(widen_bits<DT>((lo[u] >> 16) & 0xFFu));
+                out.w[3] = __float_as_uint(widen_bits<DT>(lo[u] >> 24));
             }
-            st_stream(o + 4 * w, out);
+            st_stream(dst + (q + u * stride) * 4, out);
         }
     }
-    // ragged tail (< PER elements)
-    size_t tail = vecs * PER + (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    for (; q < quads; q += stride) {
+        Vec16 out;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const uint32_t bits = EB == 2 ? ((const uint16_t*)src)[q * 4 + i] : src[q * 4 + i];
+            out.w[i] = __float_as_uint(widen_bits<DT>(bits));
+        }
+        st_stream(dst + q * 4, out);
+    }
+    // ragged tail (< 4 elements)
+    size_t tail = quads * 4 + (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (tail < n) {
-        uint32_t b = EB == 2 ? ((const uint16_t*)src)[tail] : src[tail];
-        dst[tail] = widen_bits<DT>(b);
+        uint32_t bits = EB == 2 ? ((const uint16_t*)src)[tail] : src[tail];
+        dst[tail] = widen_bits<DT>(bits);
     }
 }
 
@@ -139,7 +159,7 @@ int launch_convert(Context* ctx, int srcDT, int dstDT, const void* src, void* ds
 #define WIDEN(DT)                                                                                                        \
     do {                                                                                                                 \
         if (aligned) {                                                                                                   \
-            int g = grid_for(ctx, n / (16 / Narrow<DT>::kBytes) + 256);                                                  \
+            int g = grid_for(ctx, n / 16 + 256);                                                                         \
             widen_kernel<DT><<<g, 256, 0, stream>>>((const uint8_t*)src, (float*)dst, n);                               \
         } else {                                                                                                         \
             widen_scalar_kernel<DT><<<grid_for(ctx, n), 256, 0, stream>>>((const uint8_t*)src, (float*)dst, n);         \
