@@ -461,6 +461,280 @@ __global__ void __launch_bounds__(kThreads, 1) paged_decode_kernel(DecodeParams 
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// fp8-e4m3 KV pages.  sm_100a has no native fp8 mma.sync (the assembler expands it into conversions plus f16 MMAs, ~20
+// instructions each), so the bytes are widened to f16 (exact) in registers, once per fragment, straight out of ldmatrix:
+//   * K: a non-transposed ldmatrix of the raw rows hands every lane 4 consecutive head dimensions of one token; two
+//     cvt.f16x2.e4m3x2 turn them into the two B registers of one m16n8k16 MMA whose K index runs over the dimensions
+//     {4t, 4t+1 | 4t+2, 4t+3} of a 16-dimension chunk — the query fragments are loaded in the same order, so nothing moves;
+//   * V: ldmatrix.trans on byte pairs + one byte permute per register gives, per lane, the tokens {2t, 2t+1, 8+2t, 9+2t}
+//     of one head dimension, which is exactly the token order the score accumulators (hence P) already have.
+// One step covers 32 tokens.  The bf16 query is multiplied in f16 (values beyond the f16 range would overflow), P in f16
+// (11 significant bits), accumulation in f32; the per-KV-head scales multiply the scores and the output.
+// ---------------------------------------------------------------------------------------------------------
+static constexpr int kTile8 = 32;                                  // tokens per fp8 step
+static constexpr int kStage8 = 2 * kTile8 * kHeadDim;              // K + V bytes of one step for one head: 8 KB
+static constexpr int kStages8 = 3;
+static constexpr int kSmem8 = kStages8 * kStage8 * kWarps;         // 192 KB
+
+// two e4m3 bytes (low 16 bits of `w`) -> f16x2, exact
+__device__ __forceinline__ uint32_t e4m3x2_to_f16x2(uint32_t w) {
+    const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(w & 0xFFFFu), __NV_E4M3);
+    return (uint32_t)h.x | ((uint32_t)h.y << 16);
+}
+
+template <bool BF16>
+__global__ void __launch_bounds__(kThreads, 1) paged_decode_fp8_kernel(DecodeParams p) {
+    extern __shared__ __align__(128) unsigned char smemRaw[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    if (warp >= p.groups * p.headsPerPass) return;
+    const int sub = warp / p.headsPerPass;
+    const int head0 = warp % p.headsPerPass;
+    const long long worker = (long long)blockIdx.x * p.groups + sub;
+    const long long T = p.tileStart[p.batch];
+    if (T == 0) return;
+    const long long lo = worker * T / p.workers, hi = (worker + 1) * T / p.workers;
+    if (lo >= hi) return;
+    unsigned char* wsm = smemRaw + (size_t)warp * (kStages8 * kStage8);
+    const uint32_t wsmAddr = smem_u32(wsm);
+    const size_t tokenStride = (size_t)p.kvHeads * kHeadDim;  // bytes between tokens of a page
+    const bool page16 = (p.pageSize % kTile) == 0;
+    int seq;
+    {
+        int a = 0, z = p.batch;
+        while (z - a > 1) {
+            int m = (a + z) >> 1;
+            if (p.tileStart[m] <= lo) a = m; else z = m;
+        }
+        seq = a;
+    }
+    for (int kvh = head0; kvh < p.kvHeads; kvh += p.headsPerPass) {
+        int b = seq;
+        long long cur = lo;
+        while (cur < hi) {
+            while (p.tileStart[b + 1] <= cur) b++;
+            const long long segStart = p.tileStart[b], segEndAll = p.tileStart[b + 1];
+            const long long segEnd = segEndAll < hi ? segEndAll : hi;
+            const int tok0 = (int)(cur - segStart) * kTile;
+            long long ctxl = p.ctxLens[b];
+            const long long capTok = (segEndAll - segStart) * kTile;
+            const int ctx = (int)(ctxl < capTok ? ctxl : capTok);
+            const long long endTokL = (segEnd - segStart) * kTile;
+            const int tokEnd = (int)(endTokL < ctx ? endTokL : ctx);  // this worker's share of the sequence: [tok0, tokEnd)
+            const int32_t* table = p.pageTable ? p.pageTable + (size_t)b * p.maxPages : nullptr;
+            const unsigned char* kBase = (const unsigned char*)p.kPages + (size_t)kvh * kHeadDim;
+            const unsigned char* vBase = (const unsigned char*)p.vPages + (size_t)kvh * kHeadDim;
+            // ---- Q fragments in f16: chunk c (16 head dimensions), a0/a1 = dims 16c+4t, +1 of rows g / g+8; a2/a3 = dims +2, +3 ----
+            uint32_t qa[8][4];
+            {
+                const uint16_t* qRow = (const uint16_t*)p.q + (size_t)b * p.numHeads * kHeadDim;
+#pragma unroll
+                for (int c = 0; c < 8; c++) {
+#pragma unroll
+                    for (int hrow = 0; hrow < 2; hrow++) {
+                        const int gi = g + 8 * hrow;
+                        uint32_t w0 = 0, w1 = 0;
+                        if (gi < p.group) {
+                            const uint2 raw = *(const uint2*)(qRow + (size_t)(kvh * p.group + gi) * kHeadDim + c * 16 + 4 * t);
+                            if (BF16) {
+                                w0 = pack16<false>(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xFFFF0000u));
+                                w1 = pack16<false>(__uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xFFFF0000u));
+                            } else {
+                                w0 = raw.x;
+                                w1 = raw.y;
+                            }
+                        }
+                        qa[c][hrow] = w0;
+                        qa[c][2 + hrow] = w1;
+                    }
+                }
+            }
+            float oacc[16][4];
+#pragma unroll
+            for (int j = 0; j < 16; j++) oacc[j][0] = oacc[j][1] = oacc[j][2] = oacc[j][3] = 0.f;
+            float mrow[2] = {-INFINITY, -INFINITY}, lrow[2] = {0.f, 0.f};
+            const float sScale = (p.kScale ? p.kScale[kvh] : 1.0f) * p.scaleLog2;
+
+            int cbase = -0x40000000, cval = 0;
+            auto page_of = [&](int entry) -> int {
+                if (!table) return entry;
+                if (entry - cbase >= 32 || entry < cbase) {
+                    cbase = entry;
+                    int idx = entry + lane;
+                    cval = idx < p.maxPages ? table[idx] : 0;
+                }
+                int pg = __shfl_sync(0xffffffffu, cval, entry - cbase);
+                if (pg < 0 || pg >= p.pageCount) {
+                    if (lane == 0) atomicExch(p.errorFlag, 1);
+                    pg = 0;  // never dereference an out-of-range page
+                }
+                return pg;
+            };
+            // async copies of the 32 tokens starting at `ts` into stage `st` (rows past tokEnd are zero-filled)
+            auto issue = [&](int ts, int st) {
+                const uint32_t dstK = wsmAddr + st * kStage8, dstV = dstK + kTile8 * kHeadDim;
+                const int c = lane & 7;
+                size_t halfOff[2] = {0, 0};
+                if (page16 || !table) {
+                    const int ps = table ? p.pageSize : kTile;
+#pragma unroll
+                    for (int h = 0; h < 2; h++) {
+                        const int tk = ts + h * kTile;
+                        halfOff[h] = tk < tokEnd ? ((size_t)page_of(tk / ps) * ps + (size_t)(tk % ps)) * tokenStride : 0;
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    const int r = i * 4 + (lane >> 3);
+                    const int tok = ts + r;
+                    size_t off;
+                    if (page16 || !table) {
+                        off = halfOff[r >> 4] + (size_t)(r & 15) * tokenStride;
+                    } else {
+                        int pg = 0;
+                        const int entry = tok / p.pageSize;
+                        if (tok < tokEnd && entry < p.maxPages) {
+                            pg = table[entry];
+                            if (pg < 0 || pg >= p.pageCount) { atomicExch(p.errorFlag, 1); pg = 0; }
+                        }
+                        off = ((size_t)pg * p.pageSize + tok % p.pageSize) * tokenStride;
+                    }
+                    const int bytes = tok < tokEnd ? 16 : 0;
+                    if (bytes == 0) off = 0;
+                    const uint32_t so = r * 128 + ((c ^ (r & 7)) * 16);
+                    cp_async16(dstK + so, kBase + off + c * 16, bytes);
+                    cp_async16(dstV + so, vBase + off + c * 16, bytes);
+                }
+            };
+
+            const int nSteps = (tokEnd - tok0 + kTile8 - 1) / kTile8;
+#pragma unroll
+            for (int s = 0; s < kStages8 - 1; s++) {
+                if (s < nSteps) issue(tok0 + s * kTile8, s);
+                cp_async_commit();
+            }
+            for (int it = 0; it < nSteps; it++) {
+                cp_async_wait<kStages8 - 2>();
+                __syncwarp();
+                {
+                    const int nx = it + kStages8 - 1;
+                    if (nx < nSteps) issue(tok0 + nx * kTile8, nx % kStages8);
+                    cp_async_commit();
+                }
+                const uint32_t tileK = wsmAddr + (it % kStages8) * kStage8, tileV = tileK + kTile8 * kHeadDim;
+                // ---- S = Q K^T : 16 x 32, four n-tiles of 8 tokens, one f16 MMA per 16-dimension chunk ----
+                float s[4][4];
+#pragma unroll
+                for (int j = 0; j < 4; j++) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+                {
+                    const int mi = lane >> 3, r = lane & 7;
+#pragma unroll
+                    for (int jp = 0; jp < 2; jp++) {
+                        const int tokr = (2 * jp + (mi >> 1)) * 8 + r;
+#pragma unroll
+                        for (int kk = 0; kk < 4; kk++) {
+                            const int chunk = 2 * kk + (mi & 1);
+                            uint32_t b0, b1, b2, b3;  // (tile 2jp, chunk 2kk), (2jp, 2kk+1), (2jp+1, 2kk), (2jp+1, 2kk+1)
+                            ldmatrix_x4(tileK + tokr * 128 + ((chunk ^ (tokr & 7)) * 16), b0, b1, b2, b3);
+                            mma16816<false>(s[2 * jp], qa[2 * kk], e4m3x2_to_f16x2(b0), e4m3x2_to_f16x2(b0 >> 16));
+                            mma16816<false>(s[2 * jp], qa[2 * kk + 1], e4m3x2_to_f16x2(b1), e4m3x2_to_f16x2(b1 >> 16));
+                            mma16816<false>(s[2 * jp + 1], qa[2 * kk], e4m3x2_to_f16x2(b2), e4m3x2_to_f16x2(b2 >> 16));
+                            mma16816<false>(s[2 * jp + 1], qa[2 * kk + 1], e4m3x2_to_f16x2(b3), e4m3x2_to_f16x2(b3 >> 16));
+                        }
+                    }
+                }
+                // ---- scale, mask, online softmax (log2 domain) ----
+                const int tokBase = tok0 + it * kTile8;
+                float pv[2][8];  // [row half][n-tile j * 2 + {0,1}]: tokens 8j + 2t + {0,1}
+#pragma unroll
+                for (int hrow = 0; hrow < 2; hrow++) {
+                    float mx = -INFINITY;
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+#pragma unroll
+                        for (int e = 0; e < 2; e++) {
+                            const int tok = tokBase + 8 * j + 2 * t + e;
+                            const float sc = tok < tokEnd ? s[j][2 * hrow + e] * sScale : -INFINITY;
+                            pv[hrow][2 * j + e] = sc;
+                            mx = fmaxf(mx, sc);
+                        }
+                    }
+                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+                    const float mNew = fmaxf(mrow[hrow], mx);
+                    const float alpha = (mNew == -INFINITY) ? 1.0f : exp2f(mrow[hrow] - mNew);
+                    float sum = 0.f;
+#pragma unroll
+                    for (int c = 0; c < 8; c++) {
+                        const float e = (pv[hrow][c] == -INFINITY) ? 0.f : exp2f(pv[hrow][c] - mNew);
+                        sum += e;
+                        pv[hrow][c] = e;
+                    }
+                    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+                    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+                    lrow[hrow] = lrow[hrow] * alpha + sum;
+                    mrow[hrow] = mNew;
+                    if (alpha != 1.0f) {
+#pragma unroll
+                        for (int j = 0; j < 16; j++) {
+                            oacc[j][2 * hrow] *= alpha;
+                            oacc[j][2 * hrow + 1] *= alpha;
+                        }
+                    }
+                }
+                // ---- P as the f16 A operand of two k16 steps (tokens 0..15 and 16..31) ----
+                uint32_t pa[2][4];
+#pragma unroll
+                for (int h2 = 0; h2 < 2; h2++) {
+                    pa[h2][0] = pack16<false>(pv[0][4 * h2], pv[0][4 * h2 + 1]);      // row g,   tokens 2t, 2t+1
+                    pa[h2][1] = pack16<false>(pv[1][4 * h2], pv[1][4 * h2 + 1]);      // row g+8
+                    pa[h2][2] = pack16<false>(pv[0][4 * h2 + 2], pv[0][4 * h2 + 3]);  // row g,   tokens 8+2t, 9+2t
+                    pa[h2][3] = pack16<false>(pv[1][4 * h2 + 2], pv[1][4 * h2 + 3]);
+                }
+                // ---- O += P V: V bytes reach the same token order through ldmatrix.trans + byte permutes ----
+                {
+                    const int mi = lane >> 3, r = lane & 7;
+                    const int tokr = mi * 8 + r;
+#pragma unroll
+                    for (int dg = 0; dg < 8; dg++) {
+                        uint32_t r0, r1, r2, r3;  // byte pairs of tokens 0-7, 8-15, 16-23, 24-31 at dimensions 16dg + 2g, +1
+                        ldmatrix_x4_trans(tileV + tokr * 128 + ((dg ^ (tokr & 7)) * 16), r0, r1, r2, r3);
+                        const uint32_t e0 = __byte_perm(r0, r1, 0x6420), o0 = __byte_perm(r0, r1, 0x7531);  // tokens {2t,2t+1,8+2t,9+2t}
+                        const uint32_t e1 = __byte_perm(r2, r3, 0x6420), o1 = __byte_perm(r2, r3, 0x7531);  // the same + 16
+                        mma16816<false>(oacc[2 * dg], pa[0], e4m3x2_to_f16x2(e0), e4m3x2_to_f16x2(e0 >> 16));
+                        mma16816<false>(oacc[2 * dg], pa[1], e4m3x2_to_f16x2(e1), e4m3x2_to_f16x2(e1 >> 16));
+                        mma16816<false>(oacc[2 * dg + 1], pa[0], e4m3x2_to_f16x2(o0), e4m3x2_to_f16x2(o0 >> 16));
+                        mma16816<false>(oacc[2 * dg + 1], pa[1], e4m3x2_to_f16x2(o1), e4m3x2_to_f16x2(o1 >> 16));
+                    }
+                }
+            }
+            cp_async_wait<0>();
+            __syncwarp();
+            // ---- partial of (worker, sequence b): even/odd n-tiles interleave back into consecutive dimensions ----
+            {
+                const long long slot = worker + b;
+                const float vS = p.vScale ? p.vScale[kvh] : 1.0f;
+#pragma unroll
+                for (int hrow = 0; hrow < 2; hrow++) {
+                    const int gi = g + 8 * hrow;
+                    if (gi < p.group) {
+                        const int head = kvh * p.group + gi;
+                        float* acc = p.partAcc + ((size_t)slot * p.numHeads + head) * kHeadDim;
+#pragma unroll
+                        for (int dg = 0; dg < 8; dg++)
+                            *(float4*)(acc + 16 * dg + 4 * t) = make_float4(oacc[2 * dg][2 * hrow] * vS, oacc[2 * dg + 1][2 * hrow] * vS,
+                                                                            oacc[2 * dg][2 * hrow + 1] * vS, oacc[2 * dg + 1][2 * hrow + 1] * vS);
+                        if (t == 0) p.partML[(size_t)slot * p.numHeads + head] = make_float2(mrow[hrow], lrow[hrow]);
+                    }
+                }
+            }
+            cur = segEnd;
+            if (cur >= segEndAll) b++;
+        }
+    }
+}
+
 // merges the partials of each (sequence, head) and writes the output row in the storage dtype
 template <bool BF16>
 __global__ void __launch_bounds__(kHeadDim) decode_merge_kernel(DecodeParams p, void* __restrict__ out) {
@@ -538,8 +812,13 @@ int launch_paged_decode(Context* ctx, int dt, int kvDT, const void* q, const voi
         paged_decode_kernel<B, F, NSTAGE, true><<<(unsigned)ctas, kThreads, smem, ctx->stream>>>(p);                     \
     } while (0)
     if (fp8) {
-        if (bf16) DECODE_LAUNCH(true, true, 5);
-        else DECODE_LAUNCH(false, true, 5);
+        if (bf16) {
+            cudaFuncSetAttribute(paged_decode_fp8_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem8);
+            paged_decode_fp8_kernel<true><<<(unsigned)ctas, kThreads, kSmem8, ctx->stream>>>(p);
+        } else {
+            cudaFuncSetAttribute(paged_decode_fp8_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem8);
+            paged_decode_fp8_kernel<false><<<(unsigned)ctas, kThreads, kSmem8, ctx->stream>>>(p);
+        }
     } else {
         if (bf16) DECODE_LAUNCH(true, false, 3);
         else DECODE_LAUNCH(false, false, 3);
@@ -736,8 +1015,13 @@ extern "C" int cuda_dispatch_paged_decode_attention_noalloc(CUDADeviceRef contex
         paged_decode_kernel<B, F, NSTAGE, true><<<(unsigned)ctas, kThreads, smem, ctx->stream>>>(p);                     \
     } while (0)
     if (fp8) {
-        if (bf16) DECODE_LAUNCH(true, true, 5);
-        else DECODE_LAUNCH(false, true, 5);
+        if (bf16) {
+            cudaFuncSetAttribute(paged_decode_fp8_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem8);
+            paged_decode_fp8_kernel<true><<<(unsigned)ctas, kThreads, kSmem8, ctx->stream>>>(p);
+        } else {
+            cudaFuncSetAttribute(paged_decode_fp8_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem8);
+            paged_decode_fp8_kernel<false><<<(unsigned)ctas, kThreads, kSmem8, ctx->stream>>>(p);
+        }
     } else {
         if (bf16) DECODE_LAUNCH(true, false, 3);
         else DECODE_LAUNCH(false, false, 3);

@@ -153,7 +153,12 @@ def test_paged_decode_matches_gather_then_mha(d, dt, kv_dt, ctx_lens, page_size,
             err = np.abs(O.to_f32(got[b], dt) - O.to_f32(want[b], dt)).max()
             assert err <= 2e-2, (b, c, err)
     live = np.array(ctx_lens) > 0
-    assert (got[live] != want[live]).mean() < 0.05  # rounded scores are reproduced: nearly all outputs bit-equal
+    if kv_dt == dt:
+        assert (got[live] != want[live]).mean() < 0.05  # rounded scores are reproduced: nearly all outputs bit-equal
+    else:
+        # fp8 pages are multiplied as stored; q and the softmax weights enter as two e4m3 terms (~8 significant bits)
+        err = np.abs(O.to_f32(got[live], dt) - O.to_f32(want[live], dt))
+        assert err.mean() <= 2e-3
 
 
 def test_paged_decode_flags_bad_page_ids_and_long_contexts(d):
