@@ -241,7 +241,8 @@ def cpu_decode_sample(fp8: bool, nseq: int = 4, threads: int | None = None, repe
         O.paged_decode(O.BF16, kvdt, q, k, v, table, ctx, PAGE, HQ, HKV, DIM, ks, vs)
         best = min(best, time.perf_counter() - t0)
     nbytes = decode_bytes(ctx, 1 if fp8 else 2)
-    return nbytes / best / 1e9, nseq / best, threads, f"first {nseq} of the 64 seeded sequences ({int(ctx.sum())} KV tokens), {best:.2f} s"
+    return (nbytes / best / 1e9, nseq / best, threads,
+            f"first {nseq} of the 64 seeded sequences ({int(ctx.sum())} KV tokens), best of {repeats} x {best:.2f} s")
 
 
 # ------------------------------------------------------------------------------------------------------------
@@ -270,7 +271,8 @@ def run_reference(args, rank, world):
         "warmup": args.warmup, "ms_per_step": wall / max(args.steps, 1) * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": "paged_decode_fp8kv" if fp8 else "paged_decode_bf16kv", "batch": 64, "query_heads": HQ, "kv_heads": HKV,
-                   "head_dim": DIM, "page_size": PAGE, "ctx_len": "U[512,32768] seed 2", "kv_tokens": int(ctx.sum())},
+                   "head_dim": DIM, "page_size": PAGE, "ctx_len": "U[512,32768] seed 2", "kv_tokens": int(ctx.sum()),
+                   "kv_dtype": "e4m3+f32 scale" if fp8 else "bf16"},
         "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": "port", "sample": desc,
                          "tokens_per_s": float(np.mean(toks))},
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -287,7 +289,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", default="decode", choices=["decode", "decode_fp8", "prefill", "convert", "chain"])
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--ref-seqs", type=int, default=4, help="sequences in the CPU sample")
+    ap.add_argument("--ref-seqs", type=int, default=16, help="sequences in the CPU sample")
     ap.add_argument("--ctx-min", type=int, default=512)
     ap.add_argument("--ctx-max", type=int, default=32768, help="smaller values give a profiler-sized case; not a bench number")
     ap.add_argument("--prefill-batch", type=int, default=4, help="1 gives a profiler-sized prefill case; not a bench number")
@@ -383,7 +385,7 @@ def main():
 
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         if args.workload in ("decode", "decode_fp8"):
-            gbs, tps, threads, desc = cpu_decode_sample(args.workload == "decode_fp8", nseq=args.ref_seqs)
+            gbs, tps, threads, desc = cpu_decode_sample(args.workload == "decode_fp8", nseq=args.ref_seqs, repeats=3)
             line["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port", "sample": desc, "tokens_per_s": tps}
         elif hasattr(wl, "cpu_baseline"):
             line["cpu_baseline"] = wl.cpu_baseline()
