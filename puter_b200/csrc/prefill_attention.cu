@@ -44,7 +44,7 @@ constexpr uint32_t kColS = 0, kColO = 256;  // S0 S1 O0 O1, 128 columns each
 constexpr long long kSpinLimit = 1ll << 24;
 
 struct Params {
-    CUtensorMap tmQ, tmK, tmV;
+    CUtensorMap tmQ, tmK, tmV, tmO;
     void* out;               // [B, S, Hq*D]
     const float* ropeTable;  // cos [S, D/2] then sin [S, D/2], or nullptr
     int* errorFlag;
@@ -88,6 +88,10 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     return false;
 }
 
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* tm, uint32_t src, int c0, int c1, int c2, int c3) {
+    asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+                 ::"l"(tm), "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* tm, uint32_t bar, int c0, int c1, int c2, int c3) {
     asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
                  ::"r"(dst), "l"(tm), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
@@ -204,51 +208,82 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
     return d;
 }
 
-// Rotates one raw Q row in shared memory (two swizzled 64-column blocks), float32 math with unfused multiplies,
-// results rounded to storage — the reference's RoPE on a 16-bit tensor (device/cpu/rope/compute.go:165-183).
+// rotate_q_fetch + rotate_q_tile: rotate the raw Q tile of one softmax group in shared memory (two swizzled 64-column blocks): the reference's RoPE on a
+// 16-bit tensor (device/cpu/rope/compute.go:165-183), float32 math, results rounded to storage.  The 128 threads of the
+// group walk the tile a few rows at a time with the lanes spread ALONG a row, so the cos/sin rows of the table (one per
+// position) are read as contiguous 256-byte runs; a thread-per-row mapping made every table load touch 32 cache lines and
+// cost ~5 us per CTA.  The products run two pairs at a time on the packed f32x2 pipe (second product fused into the sum).
+// Fetches this lane's share of the cos/sin rows (32 independent 16-byte loads); issued before the Q tile has landed so the
+// L2 round trips overlap the TMA load instead of queueing behind it.
+__device__ __forceinline__ void rotate_q_fetch(float4* tab, int warpInGroup, int lane, int ropeMode, const float* table, int seqLen, int pos0) {
+    const float* cosBase = table;
+    const float* sinBase = table + (size_t)seqLen * (kD / 2);
+    if (ropeMode == 1) {
+        const int c = lane & 7;
+#pragma unroll
+        for (int it = 0; it < 8; it++) {
+            const int pos = min(pos0 + warpInGroup * 32 + it * 4 + (lane >> 3), seqLen - 1);
+            tab[4 * it + 0] = __ldg((const float4*)(cosBase + (size_t)pos * 64 + c * 8));
+            tab[4 * it + 1] = __ldg((const float4*)(cosBase + (size_t)pos * 64 + c * 8 + 4));
+            tab[4 * it + 2] = __ldg((const float4*)(sinBase + (size_t)pos * 64 + c * 8));
+            tab[4 * it + 3] = __ldg((const float4*)(sinBase + (size_t)pos * 64 + c * 8 + 4));
+        }
+    } else {
+        const int cc = lane & 15;
+#pragma unroll
+        for (int it = 0; it < 16; it++) {
+            const int pos = min(pos0 + warpInGroup * 32 + it * 2 + (lane >> 4), seqLen - 1);
+            tab[2 * it + 0] = __ldg((const float4*)(cosBase + (size_t)pos * 64 + cc * 4));
+            tab[2 * it + 1] = __ldg((const float4*)(sinBase + (size_t)pos * 64 + cc * 4));
+        }
+    }
+}
+
 template <bool BF16>
-__device__ __forceinline__ void rotate_q_row(unsigned char* qRow0, int row, int ropeMode, const float* cosT, const float* sinT) {
-    unsigned char* qRow1 = qRow0 + kHalfTile;
-#pragma unroll 2
-    for (int c = 0; c < 8; c++) {
-        const int sw = (c ^ (row & 7)) * 16;
-        if (ropeMode == 1) {
-            // half mode: element i of block 0 pairs with element i of block 1; this chunk covers pairs 8c .. 8c+7
-            const float4 c0 = __ldg((const float4*)(cosT + c * 8)), c1 = __ldg((const float4*)(cosT + c * 8 + 4));
-            const float4 s0 = __ldg((const float4*)(sinT + c * 8)), s1 = __ldg((const float4*)(sinT + c * 8 + 4));
+__device__ __forceinline__ void rotate_q_tile(unsigned char* tile, int warpInGroup, int lane, int ropeMode, const float4* tab, int seqLen, int pos0) {
+    if (ropeMode == 1) {
+        // half mode: 8 lanes per row; lane c owns pairs 8c .. 8c+7 = chunk c of block 0 with chunk c of block 1
+        const int c = lane & 7;
+#pragma unroll
+        for (int it = 0; it < 8; it++) {
+            const int row = warpInGroup * 32 + it * 4 + (lane >> 3);
+            if (pos0 + row >= seqLen) continue;
+            const float4 c0 = tab[4 * it], c1 = tab[4 * it + 1], s0 = tab[4 * it + 2], s1 = tab[4 * it + 3];
             const float cs[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
             const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
-            Vec16 a = *(Vec16*)(qRow0 + sw), bq = *(Vec16*)(qRow1 + sw);
+            unsigned char* p0 = tile + row * 128 + ((c ^ (row & 7)) * 16);
+            Vec16 a = *(Vec16*)p0, bq = *(Vec16*)(p0 + kHalfTile);
 #pragma unroll
             for (int w = 0; w < 4; w++) {
-                float re[2], ro[2];
-#pragma unroll
-                for (int hsel = 0; hsel < 2; hsel++) {
-                    const int pi = w * 2 + hsel;
-                    const float e = widen16<BF16>((a.w[w] >> (16 * hsel)) & 0xFFFFu), o = widen16<BF16>((bq.w[w] >> (16 * hsel)) & 0xFFFFu);
-                    re[hsel] = sub(mul(e, cs[pi]), mul(o, sn[pi]));
-                    ro[hsel] = add(mul(e, sn[pi]), mul(o, cs[pi]));
-                }
-                a.w[w] = pack2<BF16>(re[0], re[1]);   // round-to-nearest-even to storage
-                bq.w[w] = pack2<BF16>(ro[0], ro[1]);
+                const uint64_t E = pk2(widen16<BF16>(a.w[w] & 0xFFFFu), widen16<BF16>(a.w[w] >> 16));
+                const uint64_t O = pk2(widen16<BF16>(bq.w[w] & 0xFFFFu), widen16<BF16>(bq.w[w] >> 16));
+                const uint64_t C = pk2(cs[2 * w], cs[2 * w + 1]), S = pk2(sn[2 * w], sn[2 * w + 1]), NS = pk2(-sn[2 * w], -sn[2 * w + 1]);
+                float r0, r1, q0f, q1f;
+                un2(fma2(O, NS, mul2(E, C)), r0, r1);   // e*c - o*s
+                un2(fma2(E, S, mul2(O, C)), q0f, q1f);  // e*s + o*c
+                a.w[w] = pack2<BF16>(r0, r1);
+                bq.w[w] = pack2<BF16>(q0f, q1f);
             }
-            *(Vec16*)(qRow0 + sw) = a;
-            *(Vec16*)(qRow1 + sw) = bq;
-        } else {
-            // interleaved mode: pairs (2i, 2i+1) sit in one 32-bit word; block blk, chunk c holds pairs 32*blk + 4c .. +3
+            *(Vec16*)p0 = a;
+            *(Vec16*)(p0 + kHalfTile) = bq;
+        }
+    } else {
+        // interleaved mode: 16 lanes per row; lane cc owns the 4 pairs of one 16-byte chunk (pairs 32*blk + 4c .. +3)
+        const int cc = lane & 15, blk = cc >> 3, c = cc & 7;
 #pragma unroll
-            for (int blk = 0; blk < 2; blk++) {
-                unsigned char* ptr = (blk ? qRow1 : qRow0) + sw;
-                const float4 c4 = __ldg((const float4*)(cosT + blk * 32 + c * 4)), s4 = __ldg((const float4*)(sinT + blk * 32 + c * 4));
-                const float cs[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
-                Vec16 a = *(Vec16*)ptr;
+        for (int it = 0; it < 16; it++) {
+            const int row = warpInGroup * 32 + it * 2 + (lane >> 4);
+            if (pos0 + row >= seqLen) continue;
+            const float4 c4 = tab[2 * it], s4 = tab[2 * it + 1];
+            unsigned char* ptr = tile + blk * kHalfTile + row * 128 + ((c ^ (row & 7)) * 16);
+            Vec16 a = *(Vec16*)ptr;
+            const float cs[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
 #pragma unroll
-                for (int w = 0; w < 4; w++) {
-                    const float e = widen16<BF16>(a.w[w] & 0xFFFFu), o = widen16<BF16>(a.w[w] >> 16);
-                    a.w[w] = pack2<BF16>(sub(mul(e, cs[w]), mul(o, sn[w])), add(mul(e, sn[w]), mul(o, cs[w])));
-                }
-                *(Vec16*)ptr = a;
+            for (int w = 0; w < 4; w++) {
+                const float e = widen16<BF16>(a.w[w] & 0xFFFFu), o = widen16<BF16>(a.w[w] >> 16);
+                a.w[w] = pack2<BF16>(sub(mul(e, cs[w]), mul(o, sn[w])), add(mul(e, sn[w]), mul(o, cs[w])));
             }
+            *(Vec16*)ptr = a;
         }
     }
 }
@@ -426,14 +461,19 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const __grid_const
         const int n = nT[t];
         bool okay = true;
         if (n > 0) {
+            const bool rotate = p.ropeMode != 2 && p.ropeTable != nullptr;
+            float4 tab[32];
+            if (rotate) rotate_q_fetch(tab, warp & 3, lane, p.ropeMode, p.ropeTable, p.seqLen, q0 + t * kBM);
             okay = __all_sync(0xffffffffu, mbar_wait(bar(BAR_Q + t), 0, abortFlag));
-            if (okay && p.ropeMode != 2 && p.ropeTable != nullptr && qPos < p.seqLen) {
-                const int half = kD / 2;
-                rotate_q_row<BF16>(smem + kSmemQ + t * kTileBytes + row * 128, row, p.ropeMode, p.ropeTable + (size_t)qPos * half,
-                                   p.ropeTable + (size_t)p.seqLen * half + (size_t)qPos * half);
+            if ((threadIdx.x & 127) == 0) PF_STAMP(3000 + 8 * t + 2);
+            if (okay && rotate) {
+                rotate_q_tile<BF16>(smem + kSmemQ + t * kTileBytes, warp & 3, lane, p.ropeMode, tab, p.seqLen, q0 + t * kBM);
+                __syncwarp();
             }
+            if ((threadIdx.x & 127) == 0) PF_STAMP(3000 + 8 * t + 3);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the tensor core
             mbar_arrive(bar(BAR_QREADY + t));
+            if ((threadIdx.x & 127) == 0) PF_STAMP(3000 + 8 * t + 4);
         }
         float mUsed = -INFINITY;   // the maximum the stored P and O are relative to (scaled, log2 domain)
         float lsum = 0.f;
@@ -524,22 +564,33 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const __grid_const
             if (okay) {
                 fence_after();
                 const float inv = lsum > 0.f ? 1.0f / lsum : 0.f;
-                uint16_t* orow = (uint16_t*)p.out + (((size_t)b * p.seqLen + qPos) * p.numHeads + head) * kD;
+                // The Q tile of this group is no longer read (all its MMAs have completed): stage the normalised rows there
+                // in the swizzled box layout and let TMA write them out as two 64-column boxes — coalesced, asynchronous,
+                // and clipped at the end of the sequence by the tensor map.
+                unsigned char* stage = smem + kSmemQ + t * kTileBytes + row * 128;
 #pragma unroll 1
                 for (int c = 0; c < 4; c++) {
                     uint32_t oreg[32];
                     tmem_ld32(laneBase + colO + c * 32, oreg);
                     tmem_wait_ld();
-                    if (qPos < p.seqLen) {
 #pragma unroll
-                        for (int v4 = 0; v4 < 4; v4++) {
-                            Vec16 o;
+                    for (int v4 = 0; v4 < 4; v4++) {
+                        Vec16 o;
 #pragma unroll
-                            for (int w = 0; w < 4; w++)
-                                o.w[w] = pack2<BF16>(__uint_as_float(oreg[v4 * 8 + 2 * w]) * inv, __uint_as_float(oreg[v4 * 8 + 2 * w + 1]) * inv);
-                            *(Vec16*)(orow + c * 32 + v4 * 8) = o;
-                        }
+                        for (int w = 0; w < 4; w++)
+                            o.w[w] = pack2<BF16>(__uint_as_float(oreg[v4 * 8 + 2 * w]) * inv, __uint_as_float(oreg[v4 * 8 + 2 * w + 1]) * inv);
+                        const int chunk = c * 4 + v4;  // 16-byte chunk of the 256-byte row
+                        *(Vec16*)(stage + (chunk >> 3) * kHalfTile + (((chunk & 7) ^ (row & 7)) * 16)) = o;
                     }
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                asm volatile("bar.sync %0, 128;" ::"r"(1 + t) : "memory");  // the 128 threads of this group
+                if (row == 0) {
+                    const uint32_t src = sBase + kSmemQ + t * kTileBytes;
+                    tma_store_4d(&p.tmO, src, 0, head, q0 + t * kBM, b);
+                    tma_store_4d(&p.tmO, src + kHalfTile, 64, head, q0 + t * kBM, b);
+                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // shared memory must outlive the read
                 }
             } else {
                 *abortFlag = 1;
@@ -614,30 +665,33 @@ __global__ void __launch_bounds__(256) rope_k_prepass_kernel(const uint16_t* __r
         uint16_t* dst = out + row * 128;
         if (halfMode) {
             Vec16 a = ld_stream(src + j * 8), bq = ld_stream(src + 64 + j * 8);
+            const float4 c0 = __ldg((const float4*)(cosT + s * half + j * 8)), c1 = __ldg((const float4*)(cosT + s * half + j * 8 + 4));
+            const float4 s0 = __ldg((const float4*)(sinT + s * half + j * 8)), s1 = __ldg((const float4*)(sinT + s * half + j * 8 + 4));
+            const float cs[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+            const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
 #pragma unroll
             for (int w = 0; w < 4; w++) {
-                uint32_t ra = 0, rb = 0;
+                float re[2], ro[2];
 #pragma unroll
                 for (int hsel = 0; hsel < 2; hsel++) {
-                    const size_t pi = j * 8 + w * 2 + hsel;
+                    const int pi = w * 2 + hsel;
                     const float e = pf::widen16<BF16>((a.w[w] >> (16 * hsel)) & 0xFFFFu), o = pf::widen16<BF16>((bq.w[w] >> (16 * hsel)) & 0xFFFFu);
-                    const float cs = __ldg(cosT + s * half + pi), sn = __ldg(sinT + s * half + pi);
-                    ra |= pf::narrow16<BF16>(sub(mul(e, cs), mul(o, sn))) << (16 * hsel);
-                    rb |= pf::narrow16<BF16>(add(mul(e, sn), mul(o, cs))) << (16 * hsel);
+                    re[hsel] = sub(mul(e, cs[pi]), mul(o, sn[pi]));
+                    ro[hsel] = add(mul(e, sn[pi]), mul(o, cs[pi]));
                 }
-                a.w[w] = ra;
-                bq.w[w] = rb;
+                a.w[w] = pf::pack2<BF16>(re[0], re[1]);
+                bq.w[w] = pf::pack2<BF16>(ro[0], ro[1]);
             }
             st_stream(dst + j * 8, a);
             st_stream(dst + 64 + j * 8, bq);
         } else {
             Vec16 a = ld_stream(src + j * 8);
+            const float4 c4 = __ldg((const float4*)(cosT + s * half + j * 4)), s4 = __ldg((const float4*)(sinT + s * half + j * 4));
+            const float cs[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
 #pragma unroll
             for (int w = 0; w < 4; w++) {
-                const size_t pi = j * 4 + w;
                 const float e = pf::widen16<BF16>(a.w[w] & 0xFFFFu), o = pf::widen16<BF16>(a.w[w] >> 16);
-                const float cs = __ldg(cosT + s * half + pi), sn = __ldg(sinT + s * half + pi);
-                a.w[w] = pf::narrow16<BF16>(sub(mul(e, cs), mul(o, sn))) | (pf::narrow16<BF16>(add(mul(e, sn), mul(o, cs))) << 16);
+                a.w[w] = pf::pack2<BF16>(sub(mul(e, cs[w]), mul(o, sn[w])), add(mul(e, sn[w]), mul(o, cs[w])));
             }
             st_stream(dst + j * 8, a);
         }
@@ -657,7 +711,7 @@ int launch_prefill(Context* ctx, int dt, const void* q, const void* k, const voi
         const size_t kBytes = (size_t)batch * seqLen * kvHeads * 128 * 2;
         if (ctx->workspaceBytes < kBytes) return fail(status, -7, "prefill attention: workspace not prepared");
         uint16_t* kRot = (uint16_t*)ctx->workspace;
-        const size_t items = (size_t)batch * seqLen * kvHeads * 16;
+        const size_t items = (size_t)batch * seqLen * kvHeads * (ropeMode == 1 ? 8 : 16);
         size_t blocks = (items + 255) / 256, cap = (size_t)ctx->smCount * 16;
         if (blocks > cap) blocks = cap;
         if (bf16) rope_k_prepass_kernel<true><<<(unsigned)blocks, 256, 0, ctx->stream>>>((const uint16_t*)k, kRot, ropeTable, batch, seqLen, kvHeads, ropeMode);
@@ -669,7 +723,7 @@ int launch_prefill(Context* ctx, int dt, const void* q, const void* k, const voi
     pf::Params p;
     memset(&p, 0, sizeof(p));
     if (!make_map(&p.tmQ, q, bf16, batch, seqLen, numHeads) || !make_map(&p.tmK, kUse, bf16, batch, seqLen, kvHeads) ||
-        !make_map(&p.tmV, v, bf16, batch, seqLen, kvHeads))
+        !make_map(&p.tmV, v, bf16, batch, seqLen, kvHeads) || !make_map(&p.tmO, out, bf16, batch, seqLen, numHeads))
         return fail(status, -7, "prefill attention: tensor map encoding failed");
     p.out = out;
     p.ropeTable = ropeMode != 2 ? ropeTable : nullptr;
