@@ -235,7 +235,11 @@ __device__ __forceinline__ void fast_swiglu32x2_fused(float g0, float g1, float 
     float e0, e1, d0, d1;
     fast_exp32x2_fused(-g0, -g1, e0, e1);
     un2(add2(pk2(1.0f, 1.0f), pk2(e0, e1)), d0, d1);
-    un2(mul2(pk2(divf(g0, d0), divf(g1, d1)), pk2(u0, u1)), r0, r1);
+    // reciprocal-multiply division (2 ulp) where the quotient is about to be rounded to 16 bits anyway; the IEEE divide
+    // only for denominators near the top of the float range, which the fast form would flush to zero
+    const float q0 = d0 > 8.0e37f ? divf(g0, d0) : __fdividef(g0, d0);
+    const float q1 = d1 > 8.0e37f ? divf(g1, d1) : __fdividef(g1, d1);
+    un2(mul2(pk2(q0, q1), pk2(u0, u1)), r0, r1);
 }
 // two f32 -> one word of two bf16 with the library's rounding rule (hardware RNE; NaN payload rule applied on the rare NaN)
 __device__ __forceinline__ uint32_t f32x2_to_bf16x2(float lo, float hi) {
@@ -243,6 +247,20 @@ __device__ __forceinline__ uint32_t f32x2_to_bf16x2(float lo, float hi) {
     asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(w) : "f"(hi), "f"(lo));
     if (lo != lo || hi != hi) w = f32_to_bf16_bits(lo) | (f32_to_bf16_bits(hi) << 16);
     return w;
+}
+
+// rounds two float32 to the 16-bit storage type: returns the packed word and replaces the inputs by the rounded values
+template <int DT> __device__ __forceinline__ uint32_t round_pair(float& a, float& b) {
+    if (DT == DT_BF16) {
+        const uint32_t w = f32x2_to_bf16x2(a, b);
+        a = __uint_as_float(w << 16);
+        b = __uint_as_float(w & 0xFFFF0000u);
+        return w;
+    }
+    const uint32_t lo = f32_to_f16_bits(a), hi = f32_to_f16_bits(b);
+    a = f16_bits_to_f32(lo);
+    b = f16_bits_to_f32(hi);
+    return lo | (hi << 16);
 }
 
 __device__ __forceinline__ float fast_tanh32(float x) {  // f32.go:71-86

@@ -114,9 +114,19 @@ __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(RowArgs a) {
                     Vec16 rin = ld_stream(rr + v * 16);
                     float g[PER];
                     unpack<DT>(rin, g);
+                    if (DT == DT_F32) {
 #pragma unroll
-                    for (int j = 0; j < PER; j++) f[j] = round_storage<DT>(add(f[j], g[j]));
-                    in = pack<DT>(f);
+                        for (int j = 0; j < PER; j++) f[j] = add(f[j], g[j]);
+                        in = pack<DT>(f);
+                    } else {
+                        // the unfused Add would store its result in the 16-bit type: round here, once, pair by pair
+#pragma unroll
+                        for (int j = 0; j < PER; j += 2) {
+                            f[j] = add(f[j], g[j]);
+                            f[j + 1] = add(f[j + 1], g[j + 1]);
+                            in.w[j / 2] = round_pair<DT>(f[j], f[j + 1]);
+                        }
+                    }
                     if (a.hOut) st_stream((char*)a.hOut + row * a.cols * ES + v * 16, in);
                 }
                 cache[i] = in;
