@@ -737,17 +737,16 @@ int launch_prefill(Context* ctx, int dt, const void* q, const void* k, const voi
     p.trace = nullptr;
     if (const char* e = getenv("PUTER_TRACE_PTR")) p.trace = (long long*)strtoull(e, nullptr, 0);
 #endif
-    if (const char* e = getenv("PUTER_PREFILL_V_LBO")) p.vLBO = (uint32_t)atoi(e);
-    if (const char* e = getenv("PUTER_PREFILL_V_SBO")) p.vSBO = (uint32_t)atoi(e);
     dim3 grid(((seqLen + 2 * pf::kBM - 1) / (2 * pf::kBM)) * numHeads * batch);
-    const bool roundScores = getenv("PUTER_PREFILL_ROUND") != nullptr;
 #define PF_LAUNCH(B, R)                                                                                                        \
     do {                                                                                                                       \
         cudaFuncSetAttribute(pf::prefill_kernel<B, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pf::kSmemTotal);      \
         pf::prefill_kernel<B, R><<<grid, pf::kThreads, pf::kSmemTotal, ctx->stream>>>(p);                                     \
     } while (0)
-    if (bf16) { if (roundScores) PF_LAUNCH(true, true); else PF_LAUNCH(true, false); }
-    else { if (roundScores) PF_LAUNCH(false, true); else PF_LAUNCH(false, false); }
+    // ROUND_SCORES (scores rounded to the storage type before the softmax, as the CPU path does) is kept in the kernel for
+    // study but not instantiated: contexts in exact mode take the scalar kernel instead.
+    if (bf16) PF_LAUNCH(true, false);
+    else PF_LAUNCH(false, false);
 #undef PF_LAUNCH
     return check_launch(ctx, status, "prefill attention");
 }
