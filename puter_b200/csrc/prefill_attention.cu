@@ -131,6 +131,12 @@ __device__ __forceinline__ void mma_ts(uint32_t dTmem, uint32_t aTmem, uint64_t 
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
+// one lane of a converged warp
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.b32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+    return pred != 0;
+}
 __device__ __forceinline__ void fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
@@ -179,6 +185,12 @@ template <bool BF16> __device__ __forceinline__ uint32_t narrow16(float f) {
 #ifndef PF_EMU_PATTERN
 #define PF_EMU_PATTERN 0
 #endif
+#ifndef PF_PACKED
+#define PF_PACKED 0
+#endif
+#ifndef PF_EMU_PAIRS
+#define PF_EMU_PAIRS 0
+#endif
 
 // barrier slots (8 bytes each) inside the barrier area; [2] = one per query tile of the CTA
 enum : uint32_t { BAR_Q = 0, BAR_QREADY = 2, BAR_K_FULL = 4, BAR_K_EMPTY = 6, BAR_V_FULL = 8, BAR_V_EMPTY = 10, BAR_S = 12, BAR_P = 14,
@@ -201,6 +213,23 @@ __device__ __forceinline__ float ex2_fma(float x) {
     r = fmaf(f, r, 0.6931471806f);
     r = fmaf(f, r, 1.0f);
     return __int_as_float(__float_as_int(r) + (__float_as_int(t) << 23));
+}
+// the same for a pair, on the packed f32x2 pipe (one instruction per step for both elements)
+__device__ __forceinline__ uint64_t ex2_fma2(uint64_t x) {
+    float x0, x1;
+    un2(x, x0, x1);
+    x = pk2(fmaxf(x0, -126.0f), fmaxf(x1, -126.0f));
+    const uint64_t magic = pk2(12582912.0f, 12582912.0f), negMagic = pk2(-12582912.0f, -12582912.0f);
+    const uint64_t t = add2(x, magic);
+    const uint64_t f = add2(x, mul2(add2(t, negMagic), pk2(-1.0f, -1.0f)));
+    uint64_t r = fma2(f, pk2(0.0096181291f, 0.0096181291f), pk2(0.0555041087f, 0.0555041087f));
+    r = fma2(f, r, pk2(0.2402265070f, 0.2402265070f));
+    r = fma2(f, r, pk2(0.6931471806f, 0.6931471806f));
+    r = fma2(f, r, pk2(1.0f, 1.0f));
+    float r0, r1, t0, t1;
+    un2(r, r0, r1);
+    un2(t, t0, t1);
+    return pk2(__int_as_float(__float_as_int(r0) + (__float_as_int(t0) << 23)), __int_as_float(__float_as_int(r1) + (__float_as_int(t1) << 23)));
 }
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
     float d;
@@ -304,7 +333,9 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const __grid_const
     __shared__ int abortShared;
     volatile int* abortFlag = &abortShared;
 
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // warp index through a shuffle: the compiler then knows it is warp-uniform (and with it everything the MMA warp derives
+    // from it), which lets the MMA descriptors live in uniform registers
+    const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
     // heavy (late) query tiles first; consecutive CTAs share a KV head so K/V tiles hit in L2
     const int numPairs = (p.seqLen + 2 * kBM - 1) / (2 * kBM);
     const int perPair = p.numHeads * p.batch;
@@ -348,7 +379,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const __grid_const
     fence_before();
     __syncthreads();
     fence_after();
-    const uint32_t tmem = tmemBaseShared;
+    const uint32_t tmem = __shfl_sync(0xffffffffu, tmemBaseShared, 0);
 
     if (warp == 9) {
         // ------------------------------------------------ TMA producer ------------------------------------------------
@@ -377,13 +408,21 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const __grid_const
         }
     } else if (warp == 8) {
         // ------------------------------------------------ MMA issuer --------------------------------------------------
-        if (lane == 0) {
+        // One elected thread issues every MMA.  tcgen05.mma issue blocks at the tensor core's own pace (the queue behind it is
+        // only a product or two deep), so the tensor core idles whenever this thread polls a barrier between products.  A
+        // turn of a tile therefore first collects every input it needs (V tile, next K tile, P) and then issues the P V
+        // product of the tile's current step and the score product of its next step as 16 MMAs back to back.  The tiles take
+        // turns, which keeps them half a period apart: one is on the tensor core while the other is in its softmax.
+        // The whole warp runs the loop converged and one elected lane issues: with a divergent "lane 0 only" branch the
+        // compiler has to build every descriptor in vector registers and move it to the uniform registers the MMA reads,
+        // ~10 instructions per product competing for issue slots with two softmax warps on the same scheduler.
+        {
+            const bool leader = elect_one();
             const uint32_t idescQK = make_idesc(BF16, false);
             const uint32_t idescPV = make_idesc(BF16, true);
             bool okay = true;
-            // One thread issues every MMA, and an M=128, N=128, K=16 product only lasts ~64 cycles on the tensor core, so
-            // the issue path is kept to an add per operand: descriptors are a constant high word plus a low word whose
-            // address field (bytes >> 4) is advanced by compile-time offsets and a per-stage delta.
+            // descriptors: a constant high word plus a low word whose address field (bytes >> 4) is advanced by
+            // compile-time offsets and a per-stage delta
             const uint64_t kmajorHi = make_desc(0, 16, 1024) >> 32, vHi = make_desc(0, p.vLBO, p.vSBO) >> 32;
             const uint32_t qLo = (uint32_t)make_desc(sBase + kSmemQ, 16, 1024), kLo = (uint32_t)make_desc(sBase + kSmemK, 16, 1024);
             const uint32_t vLo = (uint32_t)make_desc(sBase + kSmemV, p.vLBO, p.vSBO);
@@ -395,25 +434,25 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const __grid_const
 #pragma unroll
                 for (int kk = 0; kk < 8; kk++) {
                     const uint32_t off = ((kk >> 2) * kHalfTile + (kk & 3) * 32) >> 4;
-                    mma_ss(dS, desc(kmajorHi, qS + off), desc(kmajorHi, kS + off), idescQK, kk > 0);
+                    if (leader) mma_ss(dS, desc(kmajorHi, qS + off), desc(kmajorHi, kS + off), idescQK, kk > 0);
                 }
-                mma_commit(bar(BAR_S + t));
-                // last score product that reads this K stage (tile 1 while it is still running, else tile 0)
-                if (t == 1 || j >= nT[1]) mma_commit(bar(BAR_K_EMPTY + j % kStages));
+                if (leader) {
+                    mma_commit(bar(BAR_S + t));
+                    // last score product that reads this K stage (tile 1 while it is still running, else tile 0)
+                    if (t == 1 || j >= nT[1]) mma_commit(bar(BAR_K_EMPTY + j % kStages));
+                }
+                __syncwarp();
             };
             auto issue_pv = [&](int t, int j) {
                 const uint32_t vS = vLo + (uint32_t)(j % kStages) * (kTileBytes >> 4);
                 const uint32_t dO = tmem + kColO + t * 128, aP = tmem + kColS + t * 128;
-                mma_ts(dO, aP, desc(vHi, vS), idescPV, j > 0);
+                if (leader) mma_ts(dO, aP, desc(vHi, vS), idescPV, j > 0);
 #pragma unroll
-                for (int kk = 1; kk < 4; kk++) mma_ts(dO, aP + kk * 8, desc(vHi, vS + ((kk * 16 * 128) >> 4)), idescPV, 1);
-                if (!mbar_wait(bar(BAR_P2 + t), j & 1, abortFlag)) return false;  // second half of P
-                fence_after();
-#pragma unroll
-                for (int kk = 4; kk < 8; kk++) mma_ts(dO, aP + kk * 8, desc(vHi, vS + ((kk * 16 * 128) >> 4)), idescPV, 1);
-                return true;
+                for (int kk = 1; kk < 8; kk++)
+                    if (leader) mma_ts(dO, aP + kk * 8, desc(vHi, vS + ((kk * 16 * 128) >> 4)), idescPV, 1);
+                __syncwarp();
             };
-            // prologue: first scores of both tiles
+            // first scores of both tiles
             for (int t = 0; t < 2 && okay; t++) {
                 if (nT[t] == 0) continue;
                 okay = mbar_wait(bar(BAR_QREADY + t), 0, abortFlag);
@@ -427,26 +466,23 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const __grid_const
                 for (int t = 0; t < 2 && okay; t++) {
                     if (j >= nT[t]) continue;
                     PF_STAMP(2048 + 512 * t + j * 8 + 0);
-                    okay = mbar_wait(bar(BAR_V_FULL + st), (j / kStages) & 1, abortFlag);
+                    if (t == 0 || j >= nT[0]) {  // (tile 1 finds the stages its neighbour has already waited for)
+                        okay = mbar_wait(bar(BAR_V_FULL + st), (j / kStages) & 1, abortFlag);
+                        if (okay && j + 1 < nMax) okay = mbar_wait(bar(BAR_K_FULL + (j + 1) % kStages), ((j + 1) / kStages) & 1, abortFlag);
+                    }
                     PF_STAMP(2048 + 512 * t + j * 8 + 1);
                     if (okay) okay = mbar_wait(bar(BAR_P + t), j & 1, abortFlag);
                     if (!okay) break;
                     fence_after();
                     PF_STAMP(2048 + 512 * t + j * 8 + 2);
-                    okay = issue_pv(t, j);
-                    if (!okay) break;
+                    issue_pv(t, j);
                     PF_STAMP(2048 + 512 * t + j * 8 + 3);
-                    if (j + 1 == nT[t]) mma_commit(bar(BAR_O + t));
+                    if (j + 1 < nT[t]) issue_qk(t, j + 1);
+                    else if (leader) mma_commit(bar(BAR_O + t));
                     // last product that reads this V stage (tile 1 while it is still running, else tile 0)
-                    if (t == 1 || j >= nT[1]) mma_commit(bar(BAR_V_EMPTY + st));
-                    if (j + 1 < nT[t]) {
-                        okay = mbar_wait(bar(BAR_K_FULL + (j + 1) % kStages), ((j + 1) / kStages) & 1, abortFlag);
-                        if (!okay) break;
-                        fence_after();
-                        PF_STAMP(2048 + 512 * t + j * 8 + 4);
-                        issue_qk(t, j + 1);
-                        PF_STAMP(2048 + 512 * t + j * 8 + 5);
-                    }
+                    if (leader && (t == 1 || j >= nT[1])) mma_commit(bar(BAR_V_EMPTY + st));
+                    __syncwarp();
+                    PF_STAMP(2048 + 512 * t + j * 8 + 4);
                 }
             }
             if (!okay) *abortFlag = 1;
@@ -532,29 +568,67 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const __grid_const
             mUsed = mNew;
             const float negM = first && !grow ? 0.f : -mUsed;  // fully masked so far: every score is -inf and exp gives 0
             float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-            // P is packed in place (word i receives elements 2i and 2i+1, consumed by then) and handed to the MMA warp in two
-            // halves of 64 keys, so the first half of the P V product runs while the second half is still exponentiated.
-            // One exponential in four runs on the FMA pipe instead of the special-function unit.
+            // P is packed in place (word i receives elements 2i and 2i+1, consumed by then) and written over the first 64
+            // columns of S; the tile is handed to the MMA warp whole: it issues the P V product and the next score product
+            // back to back in one turn.
+#if PF_PACKED
+            // scale-and-shift and the row sums run two elements at a time on the packed f32x2 pipe (same roundings as the
+            // scalar fused multiply-add / add); PF_EMU_PAIRS of every four pairs take their exponentials from a packed
+            // polynomial on the FMA pipe instead of the special-function unit
+            const uint64_t SC = pk2(scale, scale), NM = pk2(negM, negM);
+            uint64_t sumA = pk2(0.f, 0.f), sumB = pk2(0.f, 0.f);
 #pragma unroll
-            for (int hlf = 0; hlf < 2; hlf++) {
-#pragma unroll
-                for (int i = hlf * 32; i < hlf * 32 + 32; i += 2) {
-                    const float x0 = fmaf(__uint_as_float(sreg[2 * i]), scale, negM), x1 = fmaf(__uint_as_float(sreg[2 * i + 1]), scale, negM);
-                    const float x2 = fmaf(__uint_as_float(sreg[2 * i + 2]), scale, negM), x3 = fmaf(__uint_as_float(sreg[2 * i + 3]), scale, negM);
-                    const float e0 = ex2_approx(x0);
-                    const float e1 = (PF_EMU_PATTERN >= 2) ? ex2_fma(x1) : ex2_approx(x1);
-                    const float e2 = ex2_approx(x2);
-                    const float e3 = (PF_EMU_PATTERN >= 1) ? ex2_fma(x3) : ex2_approx(x3);
-                    sum4[0] += e0; sum4[1] += e1; sum4[2] += e2; sum4[3] += e3;
-                    sreg[i] = pack2<BF16>(e0, e1);
-                    sreg[i + 1] = pack2<BF16>(e2, e3);
+            for (int i = 0; i < 64; i += 2) {
+                const uint64_t X01 = fma2(pk2(__uint_as_float(sreg[2 * i]), __uint_as_float(sreg[2 * i + 1])), SC, NM);
+                const uint64_t X23 = fma2(pk2(__uint_as_float(sreg[2 * i + 2]), __uint_as_float(sreg[2 * i + 3])), SC, NM);
+                uint64_t E01, E23;
+                {
+                    float x0, x1;
+                    un2(X01, x0, x1);
+                    E01 = pk2(ex2_approx(x0), ex2_approx(x1));
                 }
-                tmem_st32(laneBase + colS + hlf * 32, sreg + hlf * 32);  // P overwrites the first 64 columns of S
-                tmem_wait_st();
-                fence_before();
-                mbar_arrive(bar((hlf ? BAR_P2 : BAR_P) + t));
-                if (hlf == 0 && (threadIdx.x & 127) == 0) PF_STAMP(1024 * t + j * 8 + 4);
+                if (((i >> 1) & 3) < PF_EMU_PAIRS) {
+                    E23 = ex2_fma2(X23);
+                } else {
+                    float x2, x3;
+                    un2(X23, x2, x3);
+                    E23 = pk2(ex2_approx(x2), ex2_approx(x3));
+                }
+                sumA = add2(sumA, E01);
+                sumB = add2(sumB, E23);
+                float e0, e1, e2, e3;
+                un2(E01, e0, e1);
+                un2(E23, e2, e3);
+                sreg[i] = pack2<BF16>(e0, e1);
+                sreg[i + 1] = pack2<BF16>(e2, e3);
+                if (i == 30) tmem_st32(laneBase + colS, sreg);
             }
+            {
+                float a0, a1, b0, b1;
+                un2(sumA, a0, a1);
+                un2(sumB, b0, b1);
+                sum4[0] = a0; sum4[1] = a1; sum4[2] = b0; sum4[3] = b1;
+            }
+#else
+#pragma unroll
+            for (int i = 0; i < 64; i += 2) {
+                const float x0 = fmaf(__uint_as_float(sreg[2 * i]), scale, negM), x1 = fmaf(__uint_as_float(sreg[2 * i + 1]), scale, negM);
+                const float x2 = fmaf(__uint_as_float(sreg[2 * i + 2]), scale, negM), x3 = fmaf(__uint_as_float(sreg[2 * i + 3]), scale, negM);
+                const float e0 = ex2_approx(x0);
+                const float e1 = (PF_EMU_PATTERN >= 2) ? ex2_fma(x1) : ex2_approx(x1);
+                const float e2 = ex2_approx(x2);
+                const float e3 = (PF_EMU_PATTERN >= 1) ? ex2_fma(x3) : ex2_approx(x3);
+                sum4[0] += e0; sum4[1] += e1; sum4[2] += e2; sum4[3] += e3;
+                sreg[i] = pack2<BF16>(e0, e1);
+                sreg[i + 1] = pack2<BF16>(e2, e3);
+                if (i == 30) tmem_st32(laneBase + colS, sreg);
+            }
+#endif
+            tmem_st32(laneBase + colS + 32, sreg + 32);
+            tmem_wait_st();
+            fence_before();
+            mbar_arrive(bar(BAR_P + t));
+            if ((threadIdx.x & 127) == 0) PF_STAMP(1024 * t + j * 8 + 4);
             lsum += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
             if ((threadIdx.x & 127) == 0) PF_STAMP(1024 * t + j * 8 + 5);
         }
