@@ -8,9 +8,10 @@
 //   * one CTA owns two tiles of 128 query rows of one (batch, query head); heavy (late) tiles are scheduled first;
 //   * a TMA warp streams 128-key K and V tiles through a 2-stage shared-memory ring (SWIZZLE_128B boxes of 64 x 128),
 //     each tile serving both query tiles;
-//   * one elected thread of the MMA warp issues tcgen05.mma (kind::f16, M=128, N=128, K=16):  S = Q K^T into TMEM,
+//   * one elected lane of the MMA warp issues tcgen05.mma (kind::f16, M=128, N=128, K=16):  S = Q K^T into TMEM,
 //     then O += P V with P read back from TMEM as the A operand and V as an MN-major B operand; the two query tiles
-//     alternate so the tensor core works on one while the other is in its softmax;
+//     take turns (a turn = the P V product of the tile's step and the score product of its next step, 16 MMAs back to
+//     back), so the tensor core works on one tile while the other is in its softmax;
 //   * two groups of four softmax warps own one S row per thread (TMEM lane = row): tcgen05.ld, online softmax in the
 //     log2 domain, P packed to 16 bits and written over S with tcgen05.st; the O accumulator is rescaled lazily (only
 //     when a row maximum grew by more than 2^8), so most iterations never touch it;
@@ -180,18 +181,6 @@ template <bool BF16> __device__ __forceinline__ uint32_t narrow16(float f) {
     return f32_to_f16_bits(f);
 }
 
-// how many of every four exponentials run on the FMA pipe instead of the special-function unit (0, 1 or 2).
-// Measured on config 3: 0 -> 964 TFLOP/s, 1 -> 902, 2 -> 784 (the softmax warps are issue-bound, not MUFU-bound), so 0.
-#ifndef PF_EMU_PATTERN
-#define PF_EMU_PATTERN 0
-#endif
-#ifndef PF_PACKED
-#define PF_PACKED 0
-#endif
-#ifndef PF_EMU_PAIRS
-#define PF_EMU_PAIRS 0
-#endif
-
 // barrier slots (8 bytes each) inside the barrier area; [2] = one per query tile of the CTA
 enum : uint32_t { BAR_Q = 0, BAR_QREADY = 2, BAR_K_FULL = 4, BAR_K_EMPTY = 6, BAR_V_FULL = 8, BAR_V_EMPTY = 10, BAR_S = 12, BAR_P = 14,
                   BAR_O = 16, BAR_P2 = 18, BAR_COUNT = 20 };
@@ -200,36 +189,6 @@ __device__ __forceinline__ float ex2_approx(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
-}
-// 2^x for x <= 0 on the FMA pipe (the special-function unit does 16 exp2 per clock per SM and is the bottleneck of the
-// softmax): round x to the nearest integer n with the 1.5*2^23 trick, degree-4 polynomial for 2^f on f in [-0.5, 0.5]
-// (relative error 4e-5, far below the 16-bit rounding of P), then add n into the exponent field.
-__device__ __forceinline__ float ex2_fma(float x) {
-    x = fmaxf(x, -126.0f);
-    const float t = x + 12582912.0f;
-    const float f = x - (t - 12582912.0f);
-    float r = fmaf(f, 0.0096181291f, 0.0555041087f);
-    r = fmaf(f, r, 0.2402265070f);
-    r = fmaf(f, r, 0.6931471806f);
-    r = fmaf(f, r, 1.0f);
-    return __int_as_float(__float_as_int(r) + (__float_as_int(t) << 23));
-}
-// the same for a pair, on the packed f32x2 pipe (one instruction per step for both elements)
-__device__ __forceinline__ uint64_t ex2_fma2(uint64_t x) {
-    float x0, x1;
-    un2(x, x0, x1);
-    x = pk2(fmaxf(x0, -126.0f), fmaxf(x1, -126.0f));
-    const uint64_t magic = pk2(12582912.0f, 12582912.0f), negMagic = pk2(-12582912.0f, -12582912.0f);
-    const uint64_t t = add2(x, magic);
-    const uint64_t f = add2(x, mul2(add2(t, negMagic), pk2(-1.0f, -1.0f)));
-    uint64_t r = fma2(f, pk2(0.0096181291f, 0.0096181291f), pk2(0.0555041087f, 0.0555041087f));
-    r = fma2(f, r, pk2(0.2402265070f, 0.2402265070f));
-    r = fma2(f, r, pk2(0.6931471806f, 0.6931471806f));
-    r = fma2(f, r, pk2(1.0f, 1.0f));
-    float r0, r1, t0, t1;
-    un2(r, r0, r1);
-    un2(t, t0, t1);
-    return pk2(__int_as_float(__float_as_int(r0) + (__float_as_int(t0) << 23)), __int_as_float(__float_as_int(r1) + (__float_as_int(t1) << 23)));
 }
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
     float d;
@@ -448,9 +407,15 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const __grid_const
                 const uint32_t dO = tmem + kColO + t * 128, aP = tmem + kColS + t * 128;
                 if (leader) mma_ts(dO, aP, desc(vHi, vS), idescPV, j > 0);
 #pragma unroll
-                for (int kk = 1; kk < 8; kk++)
+                for (int kk = 1; kk < 4; kk++)
+                    if (leader) mma_ts(dO, aP + kk * 8, desc(vHi, vS + ((kk * 16 * 128) >> 4)), idescPV, 1);
+                if (!mbar_wait(bar(BAR_P2 + t), j & 1, abortFlag)) return false;  // second half of P (keys 64..127)
+                fence_after();
+#pragma unroll
+                for (int kk = 4; kk < 8; kk++)
                     if (leader) mma_ts(dO, aP + kk * 8, desc(vHi, vS + ((kk * 16 * 128) >> 4)), idescPV, 1);
                 __syncwarp();
+                return true;
             };
             // first scores of both tiles
             for (int t = 0; t < 2 && okay; t++) {
@@ -475,7 +440,8 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const __grid_const
                     if (!okay) break;
                     fence_after();
                     PF_STAMP(2048 + 512 * t + j * 8 + 2);
-                    issue_pv(t, j);
+                    okay = issue_pv(t, j);
+                    if (!okay) break;
                     PF_STAMP(2048 + 512 * t + j * 8 + 3);
                     if (j + 1 < nT[t]) issue_qk(t, j + 1);
                     else if (leader) mma_commit(bar(BAR_O + t));
@@ -568,32 +534,23 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const __grid_const
             mUsed = mNew;
             const float negM = first && !grow ? 0.f : -mUsed;  // fully masked so far: every score is -inf and exp gives 0
             float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-            // P is packed in place (word i receives elements 2i and 2i+1, consumed by then) and written over the first 64
-            // columns of S; the tile is handed to the MMA warp whole: it issues the P V product and the next score product
-            // back to back in one turn.
-#if PF_PACKED
             // scale-and-shift and the row sums run two elements at a time on the packed f32x2 pipe (same roundings as the
-            // scalar fused multiply-add / add); PF_EMU_PAIRS of every four pairs take their exponentials from a packed
-            // polynomial on the FMA pipe instead of the special-function unit
+            // scalar fused multiply-add / add); every exponential runs on the special-function unit (moving a quarter of
+            // them to a polynomial on the FMA pipe, packed or not, never paid: the softmax warps sit at the register limit
+            // and one warp per scheduler hides little latency, so extra instructions cost more than the unit's queue).
+            // P is packed in place (word i receives elements 2i and 2i+1, consumed by then) and written over the first 64
+            // columns of S in two halves of 64 keys, each handed to the MMA warp as soon as it is stored, so the first half
+            // of the P V product overlaps the second half of the exponentials.
             const uint64_t SC = pk2(scale, scale), NM = pk2(negM, negM);
             uint64_t sumA = pk2(0.f, 0.f), sumB = pk2(0.f, 0.f);
 #pragma unroll
             for (int i = 0; i < 64; i += 2) {
                 const uint64_t X01 = fma2(pk2(__uint_as_float(sreg[2 * i]), __uint_as_float(sreg[2 * i + 1])), SC, NM);
                 const uint64_t X23 = fma2(pk2(__uint_as_float(sreg[2 * i + 2]), __uint_as_float(sreg[2 * i + 3])), SC, NM);
-                uint64_t E01, E23;
-                {
-                    float x0, x1;
-                    un2(X01, x0, x1);
-                    E01 = pk2(ex2_approx(x0), ex2_approx(x1));
-                }
-                if (((i >> 1) & 3) < PF_EMU_PAIRS) {
-                    E23 = ex2_fma2(X23);
-                } else {
-                    float x2, x3;
-                    un2(X23, x2, x3);
-                    E23 = pk2(ex2_approx(x2), ex2_approx(x3));
-                }
+                float x0, x1, x2, x3;
+                un2(X01, x0, x1);
+                un2(X23, x2, x3);
+                const uint64_t E01 = pk2(ex2_approx(x0), ex2_approx(x1)), E23 = pk2(ex2_approx(x2), ex2_approx(x3));
                 sumA = add2(sumA, E01);
                 sumB = add2(sumB, E23);
                 float e0, e1, e2, e3;
@@ -601,7 +558,12 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const __grid_const
                 un2(E23, e2, e3);
                 sreg[i] = pack2<BF16>(e0, e1);
                 sreg[i + 1] = pack2<BF16>(e2, e3);
-                if (i == 30) tmem_st32(laneBase + colS, sreg);
+                if (i == 30) {
+                    tmem_st32(laneBase + colS, sreg);
+                    tmem_wait_st();
+                    fence_before();
+                    mbar_arrive(bar(BAR_P + t));
+                }
             }
             {
                 float a0, a1, b0, b1;
@@ -609,25 +571,10 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const __grid_const
                 un2(sumB, b0, b1);
                 sum4[0] = a0; sum4[1] = a1; sum4[2] = b0; sum4[3] = b1;
             }
-#else
-#pragma unroll
-            for (int i = 0; i < 64; i += 2) {
-                const float x0 = fmaf(__uint_as_float(sreg[2 * i]), scale, negM), x1 = fmaf(__uint_as_float(sreg[2 * i + 1]), scale, negM);
-                const float x2 = fmaf(__uint_as_float(sreg[2 * i + 2]), scale, negM), x3 = fmaf(__uint_as_float(sreg[2 * i + 3]), scale, negM);
-                const float e0 = ex2_approx(x0);
-                const float e1 = (PF_EMU_PATTERN >= 2) ? ex2_fma(x1) : ex2_approx(x1);
-                const float e2 = ex2_approx(x2);
-                const float e3 = (PF_EMU_PATTERN >= 1) ? ex2_fma(x3) : ex2_approx(x3);
-                sum4[0] += e0; sum4[1] += e1; sum4[2] += e2; sum4[3] += e3;
-                sreg[i] = pack2<BF16>(e0, e1);
-                sreg[i + 1] = pack2<BF16>(e2, e3);
-                if (i == 30) tmem_st32(laneBase + colS, sreg);
-            }
-#endif
             tmem_st32(laneBase + colS + 32, sreg + 32);
             tmem_wait_st();
             fence_before();
-            mbar_arrive(bar(BAR_P + t));
+            mbar_arrive(bar(BAR_P2 + t));
             if ((threadIdx.x & 127) == 0) PF_STAMP(1024 * t + j * 8 + 4);
             lsum += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
             if ((threadIdx.x & 127) == 0) PF_STAMP(1024 * t + j * 8 + 5);
