@@ -170,6 +170,9 @@ class DecodeWorkload:
         self.out_host = torch.zeros(self.batch, HQ * DIM, dtype=torch.bfloat16).pin_memory()
         self.cfg = MultiHeadAttentionConfig(NumHeads=HQ, HeadDim=DIM, Causal=True, KVHeadCount=HKV)
         self.bytes_per_step = decode_bytes(self.ctx, self.esize)
+        # DRAM traffic (ncu dram__bytes_read + write) over algorithmic bytes, from the small-case captures summarised in
+        # profiles/paged_decode_bf16.md and profiles/paged_decode_fp8.md; traffic grows in proportion to the tokens read
+        self.traffic_ratio = (317.9 + 4.6) / 316.8 if fp8 else (634.7 + 5.7) / 633.6
         self.units_per_step = self.batch  # tokens
         self.h2d = self.q_host.numel() * 2 + self.table_host.numel() * 4 + self.ctx_host.numel() * 4
         self.d2h = self.out_host.numel() * 2
@@ -370,7 +373,9 @@ def main():
     if roof is None:
         achieved = wl.bytes_per_step / per_step / 1e9
         roof = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
-                "traffic": None, "peak_source": peaks["source"],
+                "traffic": (wl.bytes_per_step * wl.traffic_ratio) if getattr(wl, "traffic_ratio", None) else None,
+                "traffic_note": "bytes per step: ncu dram read+write of a captured case scaled by algorithmic bytes (see profiles/)",
+                "peak_source": peaks["source"],
                 "note": "achieved = algorithmic bytes / CUDA-event time of the whole step (all launches of the step); rank-local"}
 
     line = {

@@ -212,6 +212,21 @@ int cuda_dispatch_kv_page_write(CUDADeviceRef contextRef, int elementDType, CUDA
 int cuda_dispatch_kv_page_gather(CUDADeviceRef contextRef, int elementDType, CUDABufferRef storageRef, CUDABufferRef pageTableRef,
                                  CUDABufferRef outputRef, uint32_t pageCount, uint32_t pageSize, uint32_t inner, uint32_t outRows,
                                  uint64_t storageOffset, uint64_t completionToken, CUDAStatus* status);
+/* NEW, no single counterpart in the reference: the KV-cache producer step of a decoder layer in one launch.  Equals
+   RoPE(k) (device/interface.go RoPE; device/cpu/rope/compute.go:55-193) at the per-row position positions[row], the result
+   rounded to elementDType, then, when kvDType is e4m3, the cast of value / scale[kv head] (convert package rules), then
+   KVPageWrite (execution/page_intrinsic.go:361-438) of K and of V into pools [pageCount, pageSize, kvHeads * headDim] updated
+   in place.  positions, pageIDs and offsets are int32 device arrays of `rows` entries, so placing a new token needs no host
+   read (the reference reads the RoPE start position on the host: execution/bind_resolver.go:108-121).  Rows whose page, offset
+   or position (>= maxPositions) is out of range are skipped and raise the context's error flag.  kvDType is elementDType
+   (f16/bf16) or 4 (e4m3, with kScaleRef / vScaleRef f32 per KV head; otherwise they may be NULL). */
+int cuda_dispatch_rope_kv_page_write(CUDADeviceRef contextRef, int elementDType, int kvDType, CUDABufferRef kRef, CUDABufferRef vRef,
+                                     CUDABufferRef positionsRef, CUDABufferRef pageIDsRef, CUDABufferRef offsetsRef,
+                                     CUDABufferRef kPagesRef, CUDABufferRef vPagesRef, CUDABufferRef kScaleRef, CUDABufferRef vScaleRef,
+                                     uint32_t rows, uint32_t kvHeads, uint32_t headDim, uint32_t pageCount, uint32_t pageSize,
+                                     uint32_t maxPositions, double baseFreq, uint32_t halfMode, uint32_t scaling, double scalingFactor,
+                                     double lowFreqFactor, double highFreqFactor, uint32_t originalContext, uint64_t completionToken,
+                                     CUDAStatus* status);
 
 /* ---- attention ---- */
 /* device/cuda/attention/multihead.h:10-27 (device.Attention.MultiHeadAttention, device/interface.go:98-103).

@@ -63,6 +63,8 @@ SIGNATURES = {
     "cuda_dispatch_rope_pairs": (cint, [vp, cint, vp, vp, vp, vp, u32, u64, SP]),
     "cuda_dispatch_kv_page_write": (cint, [vp, cint, vp, vp, vp, vp, vp, u32, u32, u32, u32, u64, u64, SP]),
     "cuda_dispatch_kv_page_gather": (cint, [vp, cint, vp, vp, vp, u32, u32, u32, u32, u64, u64, SP]),
+    "cuda_dispatch_rope_kv_page_write": (cint, [vp, cint, cint, vp, vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, u32, dbl, u32, u32,
+                                                dbl, dbl, dbl, u32, u64, SP]),
     "cuda_dispatch_multi_head_attention": (cint, [vp, cint, cint, vp, vp, vp, vp, u32, u32, u32, u32, u32, u32, u32, u64, SP]),
     "cuda_dispatch_flash_attention": (cint, [vp, cint, vp, vp, vp, vp, u32, u32, u32, u32, u64, SP]),
     "cuda_dispatch_flash_attention_causal": (cint, [vp, cint, vp, vp, vp, vp, u32, u32, u32, u32, u32, u64, SP]),

@@ -107,6 +107,84 @@ __global__ void __launch_bounds__(256) rope_rotate_kernel(const void* __restrict
     }
 }
 
+// KV-cache producer: RoPE(k) at a per-row position, optional e4m3 quantisation with a per-head scale, and the paged write of K
+// and V, in one pass (no reference counterpart as one op: it equals RoPE -> [convert] -> KVPageWrite for K and
+// [convert] -> KVPageWrite for V; device/cpu/rope/compute.go:55-193, execution/page_intrinsic.go:361-438).  Positions, page
+// ids and offsets are device arrays, so a decode step needs no host read to place its new token.  A work item is 8
+// elements of V, or of K in interleaved mode, or 8 + 8 elements (a vector and its partner `half` further on) of K in half mode.
+template <int DT, bool HALF, bool FP8>
+__global__ void __launch_bounds__(256) rope_kv_page_write_kernel(const uint16_t* __restrict__ k, const uint16_t* __restrict__ v,
+                                                                const int32_t* __restrict__ positions, const int32_t* __restrict__ pageIDs,
+                                                                const int32_t* __restrict__ offsets, void* __restrict__ kPages,
+                                                                void* __restrict__ vPages, const float* __restrict__ kScale,
+                                                                const float* __restrict__ vScale, const float* __restrict__ cosT,
+                                                                const float* __restrict__ sinT, size_t rows, size_t heads, size_t headDim,
+                                                                size_t pageCount, size_t pageSize, size_t maxPositions,
+                                                                int* __restrict__ errorFlag) {
+    const size_t half = headDim / 2;
+    const size_t kItemsPerHead = HALF ? half / 8 : headDim / 8, vItemsPerHead = headDim / 8;
+    const size_t kItems = rows * heads * kItemsPerHead, total = kItems + rows * heads * vItemsPerHead;
+    const size_t inner = heads * headDim;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    auto store8 = [&](void* pool, size_t elem, const float* f, float scale) {
+        if (FP8) {
+            uint32_t w0 = 0, w1 = 0;
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                w0 |= f32_to_e4m3_bits(__fdiv_rn(f[i], scale)) << (8 * i);
+                w1 |= f32_to_e4m3_bits(__fdiv_rn(f[4 + i], scale)) << (8 * i);
+            }
+            *(uint2*)((char*)pool + elem) = make_uint2(w0, w1);
+        } else {
+            *(Vec16*)((char*)pool + elem * 2) = pack<DT>(f);
+        }
+    };
+    for (size_t it = (size_t)blockIdx.x * blockDim.x + threadIdx.x; it < total; it += stride) {
+        const bool isK = it < kItems;
+        const size_t local = isK ? it : it - kItems;
+        const size_t perHead = isK ? kItemsPerHead : vItemsPerHead;
+        const size_t j = local % perHead, rh = local / perHead, h = rh % heads, row = rh / heads;
+        const long long page = pageIDs[row], off = offsets[row], pos = positions[row];
+        if (page < 0 || page >= (long long)pageCount || off < 0 || off >= (long long)pageSize || pos < 0 || pos >= (long long)maxPositions) {
+            if (j == 0 && h == 0) atomicExch(errorFlag, 1);
+            continue;
+        }
+        const size_t src = row * inner + h * headDim;
+        const size_t dst = ((size_t)page * pageSize + (size_t)off) * inner + h * headDim;
+        if (!isK) {
+            float f[8];
+            unpack<DT>(ld_stream((const char*)v + (src + j * 8) * 2), f);
+            if (FP8) store8(vPages, dst + j * 8, f, vScale[h]);
+            else *(Vec16*)((char*)vPages + (dst + j * 8) * 2) = ld_stream((const char*)v + (src + j * 8) * 2);
+        } else if (HALF) {
+            const size_t p0 = j * 8;
+            float e[8], o[8], re[8], ro[8];
+            unpack<DT>(ld_stream((const char*)k + (src + p0) * 2), e);
+            unpack<DT>(ld_stream((const char*)k + (src + half + p0) * 2), o);
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const float c = __ldg(cosT + (size_t)pos * half + p0 + i), sn = __ldg(sinT + (size_t)pos * half + p0 + i);
+                // rounded to the storage type first, as the separate RoPE op would have stored it
+                re[i] = Storage<DT>::widen(Storage<DT>::narrow(sub(mul(e[i], c), mul(o[i], sn))));
+                ro[i] = Storage<DT>::widen(Storage<DT>::narrow(add(mul(e[i], sn), mul(o[i], c))));
+            }
+            store8(kPages, dst + p0, re, FP8 ? kScale[h] : 1.f);
+            store8(kPages, dst + half + p0, ro, FP8 ? kScale[h] : 1.f);
+        } else {
+            const size_t p0 = j * 4;
+            float f[8], r[8];
+            unpack<DT>(ld_stream((const char*)k + (src + 2 * p0) * 2), f);
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const float c = __ldg(cosT + (size_t)pos * half + p0 + i), sn = __ldg(sinT + (size_t)pos * half + p0 + i);
+                r[2 * i] = Storage<DT>::widen(Storage<DT>::narrow(sub(mul(f[2 * i], c), mul(f[2 * i + 1], sn))));
+                r[2 * i + 1] = Storage<DT>::widen(Storage<DT>::narrow(add(mul(f[2 * i], sn), mul(f[2 * i + 1], c))));
+            }
+            store8(kPages, dst + 2 * p0, r, FP8 ? kScale[h] : 1.f);
+        }
+    }
+}
+
 // scalar path: one thread per pair
 template <int DT>
 __global__ void __launch_bounds__(256) rope_rotate_scalar_kernel(const void* __restrict__ in, void* __restrict__ out,
@@ -287,4 +365,68 @@ extern "C" int cuda_dispatch_rope_pairs(CUDADeviceRef contextRef, int elementDTy
     rope_pairs_kernel<<<(halfDim + 255) / 256, 256, 0, ctx->stream>>>((const float*)dev_ptr(inputRef), (float*)dev_ptr(outRef),
                                                                       (const float*)dev_ptr(cosRef), (const float*)dev_ptr(sinRef), halfDim);
     return check_launch(ctx, status, "rope pairs");
+}
+
+extern "C" int cuda_dispatch_rope_kv_page_write(CUDADeviceRef contextRef, int elementDType, int kvDType, CUDABufferRef kRef, CUDABufferRef vRef,
+                                                CUDABufferRef positionsRef, CUDABufferRef pageIDsRef, CUDABufferRef offsetsRef,
+                                                CUDABufferRef kPagesRef, CUDABufferRef vPagesRef, CUDABufferRef kScaleRef,
+                                                CUDABufferRef vScaleRef, uint32_t rows, uint32_t kvHeads, uint32_t headDim,
+                                                uint32_t pageCount, uint32_t pageSize, uint32_t maxPositions, double baseFreq,
+                                                uint32_t halfMode, uint32_t scaling, double scalingFactor, double lowFreqFactor,
+                                                double highFreqFactor, uint32_t originalContext, uint64_t completionToken,
+                                                CUDAStatus* status) {
+    (void)completionToken;
+    PUTER_ENTER(ctx);
+    if (rows == 0 || kvHeads == 0 || pageCount == 0 || pageSize == 0) return ok(status);
+    if (elementDType != DT_F16 && elementDType != DT_BF16) return fail(status, -6, "rope kv page write: unsupported dtype %d", elementDType);
+    const bool fp8 = kvDType == DT_E4M3;
+    if (!fp8 && kvDType != elementDType) return fail(status, -6, "rope kv page write: unsupported cache dtype %d", kvDType);
+    if (headDim == 0 || headDim % 16 != 0 || headDim > 256) return fail(status, -6, "rope kv page write: unsupported head dimension %u", headDim);
+    if (maxPositions == 0) return fail(status, -2, "rope kv page write: maxPositions must be positive");
+    int rc = validate_rope(status, baseFreq, halfMode, scaling, scalingFactor, lowFreqFactor, highFreqFactor, originalContext);
+    if (rc != 0) return rc;
+    const size_t inner = (size_t)kvHeads * headDim, kvEs = fp8 ? 1 : 2;
+    PUTER_REQUIRE(kRef, "k", (size_t)rows * inner * 2);
+    PUTER_REQUIRE(vRef, "v", (size_t)rows * inner * 2);
+    PUTER_REQUIRE(positionsRef, "positions", (size_t)rows * 4);
+    PUTER_REQUIRE(pageIDsRef, "pageIDs", (size_t)rows * 4);
+    PUTER_REQUIRE(offsetsRef, "offsets", (size_t)rows * 4);
+    PUTER_REQUIRE(kPagesRef, "kPages", (size_t)pageCount * pageSize * inner * kvEs);
+    PUTER_REQUIRE(vPagesRef, "vPages", (size_t)pageCount * pageSize * inner * kvEs);
+    if (fp8) {
+        PUTER_REQUIRE(kScaleRef, "kScale", (size_t)kvHeads * 4);
+        PUTER_REQUIRE(vScaleRef, "vScale", (size_t)kvHeads * 4);
+    }
+    const void* kp = dev_ptr(kRef);
+    const void* vp = dev_ptr(vRef);
+    void* kPool = dev_ptr(kPagesRef);
+    void* vPool = dev_ptr(vPagesRef);
+    if ((((uintptr_t)kp | (uintptr_t)vp | (uintptr_t)kPool | (uintptr_t)vPool) & 15u) != 0)
+        return fail(status, -2, "rope kv page write: buffers must be 16-byte aligned");
+    const float* table = cached_rope_table(ctx, maxPositions, (int)headDim, baseFreq, 0, (int)scaling, scalingFactor, lowFreqFactor,
+                                           highFreqFactor, (int)originalContext, status);
+    if (!table) return status ? status->code : -7;
+    const size_t half = headDim / 2;
+    const float* cosT = table;
+    const float* sinT = table + (size_t)maxPositions * half;
+    const size_t items = (size_t)rows * kvHeads * ((halfMode ? half : headDim) / 8 + headDim / 8);
+    size_t blocks = (items + 255) / 256, cap = (size_t)ctx->smCount * 16;
+    const int grid = (int)(blocks < cap ? (blocks ? blocks : 1) : cap);
+    const float* ks = fp8 ? (const float*)dev_ptr(kScaleRef) : nullptr;
+    const float* vs = fp8 ? (const float*)dev_ptr(vScaleRef) : nullptr;
+#define PRODUCER_LAUNCH(DT, HALF, FP8)                                                                                              \
+    rope_kv_page_write_kernel<DT, HALF, FP8><<<grid, 256, 0, ctx->stream>>>(                                                        \
+        (const uint16_t*)kp, (const uint16_t*)vp, (const int32_t*)dev_ptr(positionsRef), (const int32_t*)dev_ptr(pageIDsRef),        \
+        (const int32_t*)dev_ptr(offsetsRef), kPool, vPool, ks, vs, cosT, sinT, rows, kvHeads, headDim, pageCount, pageSize,          \
+        maxPositions, ctx->errorFlag)
+#define PRODUCER_PICK(DT)                                                  \
+    do {                                                                   \
+        if (halfMode) { if (fp8) PRODUCER_LAUNCH(DT, true, true); else PRODUCER_LAUNCH(DT, true, false); }   \
+        else { if (fp8) PRODUCER_LAUNCH(DT, false, true); else PRODUCER_LAUNCH(DT, false, false); }          \
+    } while (0)
+    if (elementDType == DT_BF16) PRODUCER_PICK(DT_BF16);
+    else PRODUCER_PICK(DT_F16);
+#undef PRODUCER_PICK
+#undef PRODUCER_LAUNCH
+    return check_launch(ctx, status, "rope kv page write");
 }

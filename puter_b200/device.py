@@ -287,6 +287,16 @@ class Device:
         self._call("cuda_dispatch_kv_page_gather", [storage, pageTable, output],
                    lambda r: (format, r[0], r[1], r[2], pageCount, pageSize, inner, outRows, storageOffset, 0))
 
+    def RoPEKVPageWrite(self, rope: RoPEConfig, k, v, positions, pageIDs, offsets, kPages, vPages, rows, kvHeads, headDim, pageCount,
+                        pageSize, maxPositions, format, kvFormat=None, kScale=None, vScale=None):
+        """KV-cache producer of a decode layer in one launch: RoPE(k) at positions[row] -> [e4m3 of value / scale] -> KVPageWrite of K
+        and V (in place).  No single reference counterpart; equals RoPE + Convert + KVPageWrite run one after the other."""
+        kvf = format if kvFormat is None else kvFormat
+        self._call("cuda_dispatch_rope_kv_page_write", [k, v, positions, pageIDs, offsets, kPages, vPages, kScale, vScale],
+                   lambda r: (format, kvf, r[0], r[1], r[2], r[3], r[4], r[5], r[6], r[7], r[8], rows, kvHeads, headDim, pageCount,
+                              pageSize, maxPositions, float(rope.BaseFreq), int(rope.Mode), int(rope.Scaling), float(rope.ScalingFactor),
+                              float(rope.LowFreqFactor), float(rope.HighFreqFactor), int(rope.OriginalContext), 0))
+
     # ---- Attention ------------------------------------------------------------------------------------
     def MultiHeadAttention(self, config: MultiHeadAttentionConfig, query, key, value, output, seqQ, seqK, format):
         if config.ALiBiSlope != 0:
