@@ -140,6 +140,38 @@ def rmsnorm(dt: int, x: np.ndarray, scale: np.ndarray, eps: float) -> np.ndarray
     return out
 
 
+def layernorm(dt: int, x: np.ndarray, scale: np.ndarray, bias: np.ndarray) -> np.ndarray:
+    """device.LayerNorm.LayerNorm (epsilon fixed at 1e-5 by the reference)."""
+    x = np.ascontiguousarray(x, dtype=_NP[dt])
+    scale = np.ascontiguousarray(scale, dtype=_NP[dt])
+    bias = np.ascontiguousarray(bias, dtype=_NP[dt])
+    rows, cols = x.shape
+    out = np.empty_like(x)
+    _check(lib().oracle_layernorm(dt, _p(x), _p(scale), _p(bias), _p(out), _ll(rows), _ll(cols)), "layernorm")
+    return out
+
+
+def adaptive_rmsnorm(dt: int, x: np.ndarray, modulation: np.ndarray, rows_per_batch: int, mod_cols: int, eps: float) -> np.ndarray:
+    x = np.ascontiguousarray(x, dtype=_NP[dt])
+    modulation = np.ascontiguousarray(modulation, dtype=_NP[dt])
+    rows, cols = x.shape
+    out = np.empty_like(x)
+    _check(lib().oracle_adaptive_rmsnorm(dt, _p(x), _p(modulation), _p(out), _ll(rows), _ll(cols), _ll(rows_per_batch), _ll(mod_cols),
+                                         ctypes.c_double(eps)), "adaptive_rmsnorm")
+    return out
+
+
+def modulated_layernorm(dt: int, x: np.ndarray, modulation: np.ndarray, rows_per_batch: int, mod_cols: int, eps: float,
+                        set_index: int) -> np.ndarray:
+    x = np.ascontiguousarray(x, dtype=_NP[dt])
+    modulation = np.ascontiguousarray(modulation, dtype=_NP[dt])
+    rows, cols = x.shape
+    out = np.empty_like(x)
+    _check(lib().oracle_modulated_layernorm(dt, _p(x), _p(modulation), _p(out), _ll(rows), _ll(cols), _ll(rows_per_batch), _ll(mod_cols),
+                                            ctypes.c_double(eps), _ll(set_index)), "modulated_layernorm")
+    return out
+
+
 def gated_residual(dt, residual, branch, modulation, rows, last_dim, rows_per_batch, mod_cols, set_index):
     residual = np.ascontiguousarray(residual, dtype=_NP[dt])
     branch = np.ascontiguousarray(branch, dtype=_NP[dt])

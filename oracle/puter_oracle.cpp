@@ -180,6 +180,11 @@ inline void store_typed(void* p, size_t i, float v, int dt) {
         case E5M2: ((uint8_t*)p)[i] = f32_to_e5m2(v); break;
     }
 }
+inline float round_typed(float v, int dt) {
+    if (dt == BF16) return bf16_to_f32(f32_to_bf16(v));
+    if (dt == F16) return f16_to_f32(f32_to_f16(v));
+    return v;
+}
 inline size_t esize(int dt) {
     switch (dt) { case F32: return 4; case F16: case BF16: return 2; case F64: return 8; default: return 1; }
 }
@@ -581,6 +586,143 @@ ORACLE_API int oracle_rmsnorm(int dt, const void* in, const void* scale, void* o
         return 0;
     }
     return -1;
+}
+
+// device.LayerNorm.LayerNorm: device/cpu/layernorm/compute.go:109-127 (f32: row sum in float32, mean and variance carried in
+// float64, 1/sqrt in float64; apply = ((x - mean) * inv) * scale + bias with every product rounded, f32_generic.go:14-24),
+// :484-511 (16-bit: bf16 mean from the float32 row sum rounded to bf16, reduction/bf16_kernels.go:41-51; f16 mean from the plain
+// float32 sum, :572-580; float32 variance :582-602; epsilon 1e-5 added in float32).
+static const float kLayerNormEps = 1e-5f;
+ORACLE_API int oracle_layernorm(int dt, const void* in, const void* scale, const void* bias, void* out, long long rows, long long cols) {
+    if (rows == 0 || cols == 0) return 0;
+    if (dt == F32) {
+        const float* x = (const float*)in;
+        const float* g = (const float*)scale;
+        const float* b = (const float*)bias;
+        float* o = (float*)out;
+#pragma omp parallel for schedule(static)
+        for (long long r = 0; r < rows; r++) {
+            const float* row = x + r * cols;
+            float sum = 0.f;
+            for (long long i = 0; i < cols; i++) sum += row[i];
+            const double mean = (double)sum / (double)cols;
+            const float mean32 = (float)mean;
+            float sq = 0.f;
+            for (long long i = 0; i < cols; i++) {
+                const float d = row[i] - mean32;
+                sq += d * d;
+            }
+            const double var = (double)sq / (double)cols;
+            const float inv = (float)(1.0 / std::sqrt(var + 1e-5));
+            for (long long i = 0; i < cols; i++) {
+                float d = row[i] - mean32;
+                d *= inv;
+                d *= g[i];
+                o[r * cols + i] = d + b[i];
+            }
+        }
+        return 0;
+    }
+    if (dt == BF16 || dt == F16) {
+#pragma omp parallel for schedule(static)
+        for (long long r = 0; r < rows; r++) {
+            const size_t base = (size_t)r * cols;
+            float sum = 0.f;
+            for (long long i = 0; i < cols; i++) sum += load_typed(in, base + i, dt);
+            if (dt == BF16) sum = round_typed(sum, dt);  // SumBFloat16Native returns a bf16
+            const float mean = sum / (float)cols;
+            float var = 0.f;
+            for (long long i = 0; i < cols; i++) {
+                const float d = load_typed(in, base + i, dt) - mean;
+                var += d * d;
+            }
+            var = var / (float)cols;
+            const float inv = (float)(1.0 / std::sqrt((double)(var + kLayerNormEps)));
+            for (long long i = 0; i < cols; i++) {
+                const float nrm = (load_typed(in, base + i, dt) - mean) * inv;
+                store_typed(out, base + i, nrm * load_typed(scale, i, dt) + load_typed(bias, i, dt), dt);
+            }
+        }
+        return 0;
+    }
+    return -1;
+}
+
+// device.LayerNorm.AdaptiveRMSNorm: device/cpu/layernorm/compute.go:209-264,387-482 (mean square from 256 strided float32
+// partial sums folded pairwise; out = (x * inv) * (1 + scale) + shift with modulation row [scale | shift] of the row's batch).
+ORACLE_API int oracle_adaptive_rmsnorm(int dt, const void* in, const void* mod, void* out, long long rows, long long cols,
+                                       long long rowsPerBatch, long long modCols, double eps) {
+    if (!(eps > 0) || rowsPerBatch <= 0 || rows % rowsPerBatch != 0 || modCols < 2 * cols) return -2;  // :625-644
+    if (dt != F32 && dt != BF16 && dt != F16) return -1;
+    if (rows == 0 || cols == 0) return 0;
+#pragma omp parallel for schedule(static)
+    for (long long r = 0; r < rows; r++) {
+        const size_t base = (size_t)r * cols, mbase = (size_t)(r / rowsPerBatch) * modCols;
+        float partial[256];
+        for (int l = 0; l < 256; l++) {
+            partial[l] = 0.f;
+            for (long long i = l; i < cols; i += 256) {
+                const float v = load_typed(in, base + i, dt);
+                partial[l] += v * v;
+            }
+        }
+        for (int stride = 128; stride > 0; stride >>= 1)
+            for (int l = 0; l < stride; l++) partial[l] += partial[l + stride];
+        const float ms = partial[0] / (float)cols;
+        const float inv = (float)(1.0 / std::sqrt((double)ms + eps));
+        for (long long i = 0; i < cols; i++) {
+            const float nrm = load_typed(in, base + i, dt) * inv;
+            const float sc = load_typed(mod, mbase + i, dt), sh = load_typed(mod, mbase + cols + i, dt);
+            store_typed(out, base + i, nrm * (1.0f + sc) + sh, dt);
+        }
+    }
+    return 0;
+}
+
+// device.LayerNorm.ModulatedLayerNorm: device/cpu/layernorm/compute.go:266-333,513-570 (statistics as LayerNorm but with the
+// configured epsilon added in float64; modulation row of the batch at offset set*3*cols holds [shift | scale];
+// out = ((x - mean) * inv) * (1 + scale) + shift).
+ORACLE_API int oracle_modulated_layernorm(int dt, const void* in, const void* mod, void* out, long long rows, long long cols,
+                                          long long rowsPerBatch, long long modCols, double eps, long long set) {
+    if (!(eps > 0) || set < 0 || rowsPerBatch <= 0 || rows % rowsPerBatch != 0 || modCols < (set * 3 + 2) * cols) return -2;  // :604-648
+    if (dt != F32 && dt != BF16 && dt != F16) return -1;
+    if (rows == 0 || cols == 0) return 0;
+#pragma omp parallel for schedule(static)
+    for (long long r = 0; r < rows; r++) {
+        const size_t base = (size_t)r * cols, mbase = (size_t)(r / rowsPerBatch) * modCols + (size_t)set * cols * 3;
+        float mean, inv;
+        if (dt == F32) {
+            const float* row = (const float*)in + base;
+            float sum = 0.f;
+            for (long long i = 0; i < cols; i++) sum += row[i];
+            const double mean64 = (double)sum / (double)cols;
+            mean = (float)mean64;
+            float sq = 0.f;
+            for (long long i = 0; i < cols; i++) {
+                const float d = row[i] - mean;
+                sq += d * d;
+            }
+            inv = (float)(1.0 / std::sqrt((double)sq / (double)cols + eps));
+        } else {
+            float sum = 0.f;
+            for (long long i = 0; i < cols; i++) sum += load_typed(in, base + i, dt);
+            if (dt == BF16) sum = round_typed(sum, dt);
+            mean = sum / (float)cols;
+            float var = 0.f;
+            for (long long i = 0; i < cols; i++) {
+                const float d = load_typed(in, base + i, dt) - mean;
+                var += d * d;
+            }
+            var = var / (float)cols;
+            inv = (float)(1.0 / std::sqrt((double)var + eps));
+        }
+        for (long long i = 0; i < cols; i++) {
+            const float nrm = (load_typed(in, base + i, dt) - mean) * inv;
+            const float sh = load_typed(mod, mbase + i, dt), sc = load_typed(mod, mbase + cols + i, dt);
+            store_typed(out, base + i, nrm * (1.0f + sc) + sh, dt);
+        }
+    }
+    return 0;
 }
 
 // gated residual: execution/math_gated_residual_intrinsic.go:206-223 (f32);

@@ -281,7 +281,7 @@ __device__ __forceinline__ void rotate_q_tile(unsigned char* tile, int warpInGro
 // O1 384-511; P_t overwrites the first 64 columns of S_t (each thread rewrites only the row it has already read).
 // MMA order in steady state: PV0(j), QK0(j+1), PV1(j), QK1(j+1): each softmax group works while the tensor core
 // runs the other tile's two products.
-template <bool BF16, bool ROUND_SCORES>
+template <bool BF16>
 __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const __grid_constant__ Params p) {
     extern __shared__ unsigned char smemRaw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)smemRaw + 1023) & ~(uintptr_t)1023);  // swizzled boxes: 1024-byte aligned
@@ -492,11 +492,6 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const __grid_const
             tmem_wait_ld();
             if ((threadIdx.x & 127) == 0) PF_STAMP(1024 * t + j * 8 + 2);
             const int key0 = j * kBN;
-            if (ROUND_SCORES) {
-                // the reference rounds every dot product to the storage type before scaling
-#pragma unroll
-                for (int i = 0; i < 128; i++) sreg[i] = __float_as_uint(widen16<BF16>(narrow16<BF16>(__uint_as_float(sreg[i]))));
-            }
             if ((p.causal && key0 + kBN - 1 > q0 + t * kBM) || (key0 + kBN > p.seqLen)) {
                 // diagonal or ragged tile: mask keys beyond the row position / the sequence end
 #pragma unroll
@@ -759,15 +754,15 @@ int launch_prefill(Context* ctx, int dt, const void* q, const void* k, const voi
     if (const char* e = getenv("PUTER_TRACE_PTR")) p.trace = (long long*)strtoull(e, nullptr, 0);
 #endif
     dim3 grid(((seqLen + 2 * pf::kBM - 1) / (2 * pf::kBM)) * numHeads * batch);
-#define PF_LAUNCH(B, R)                                                                                                        \
+#define PF_LAUNCH(B)                                                                                                           \
     do {                                                                                                                       \
-        cudaFuncSetAttribute(pf::prefill_kernel<B, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pf::kSmemTotal);      \
-        pf::prefill_kernel<B, R><<<grid, pf::kThreads, pf::kSmemTotal, ctx->stream>>>(p);                                     \
+        cudaFuncSetAttribute(pf::prefill_kernel<B>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pf::kSmemTotal);      \
+        pf::prefill_kernel<B><<<grid, pf::kThreads, pf::kSmemTotal, ctx->stream>>>(p);                                     \
     } while (0)
-    // ROUND_SCORES (scores rounded to the storage type before the softmax, as the CPU path does) is kept in the kernel for
-    // study but not instantiated: contexts in exact mode take the scalar kernel instead.
-    if (bf16) PF_LAUNCH(true, false);
-    else PF_LAUNCH(false, false);
+    // (scores are not re-rounded to the storage type before the softmax as the CPU path does: contexts in exact mode take the
+    // scalar kernel, which does)
+    if (bf16) PF_LAUNCH(true);
+    else PF_LAUNCH(false);
 #undef PF_LAUNCH
     return check_launch(ctx, status, "prefill attention");
 }
