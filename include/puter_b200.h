@@ -174,6 +174,24 @@ int cuda_dispatch_rmsnorm(CUDADeviceRef contextRef, int elementDType, CUDABuffer
 int cuda_dispatch_rmsnorm_f64(CUDADeviceRef contextRef, int elementDType, CUDABufferRef inputRef, CUDABufferRef scaleRef,
                               CUDABufferRef outputRef, uint32_t rows, uint32_t cols, double epsilon, uint64_t completionToken,
                               CUDAStatus* status);
+/* device/cuda/layernorm/native/layer.h:14-25, called with a float epsilon by device/cuda/layernorm/dispatch_cuda.go:100-112
+   (device.LayerNorm.LayerNorm, device/interface.go:362-366).  The CPU op has no epsilon argument and uses 1e-5
+   (device/cpu/layernorm/compute.go:11); epsilon <= 0 selects that value. */
+int cuda_dispatch_layernorm(CUDADeviceRef contextRef, int elementDType, CUDABufferRef inputRef, CUDABufferRef scaleRef,
+                            CUDABufferRef biasRef, CUDABufferRef outputRef, uint32_t rows, uint32_t cols, float epsilon,
+                            uint64_t completionToken, CUDAStatus* status);
+/* NEW (CPU-only in the reference): device.LayerNorm.AdaptiveRMSNorm, device/interface.go:356-361;
+   device/cpu/layernorm/compute.go:209-264,387-482.  modulation is [rows / rowsPerBatch, modulationCols] = [scale | shift | ...]. */
+int cuda_dispatch_adaptive_rmsnorm(CUDADeviceRef contextRef, int elementDType, CUDABufferRef inputRef, CUDABufferRef modulationRef,
+                                   CUDABufferRef outputRef, uint32_t rows, uint32_t cols, uint32_t rowsPerBatch,
+                                   uint32_t modulationCols, double epsilon, uint64_t completionToken, CUDAStatus* status);
+/* NEW (CPU-only in the reference): device.LayerNorm.ModulatedLayerNorm, device/interface.go:367-372;
+   device/cpu/layernorm/compute.go:266-333,513-570.  The [shift | scale] pair of modulation set `set` starts at column
+   set * 3 * cols of the batch's modulation row (device.ModulatedLayerNormConfig, device/config.go:94-109). */
+int cuda_dispatch_modulated_layernorm(CUDADeviceRef contextRef, int elementDType, CUDABufferRef inputRef, CUDABufferRef modulationRef,
+                                      CUDABufferRef outputRef, uint32_t rows, uint32_t cols, uint32_t rowsPerBatch,
+                                      uint32_t modulationCols, uint32_t set, double epsilon, uint64_t completionToken,
+                                      CUDAStatus* status);
 /* NEW: fused residual add + RMSNorm (+ gated residual), one pass over the rows:
      h = x + residual;  normOut = RMSNorm(h, scale);  hOut = h (may be NULL);
      gatedOut = h + modulation[...] * branch   (skipped when branchRef == NULL)

@@ -6,6 +6,8 @@ method names and argument order of ``device/interface.go`` over torch tensors (t
 memory, streams and process groups).
 """
 from . import dtypes
-from .device import Device, DeviceError, FlashAttentionConfig, MultiHeadAttentionConfig, RMSNormConfig, RoPEConfig
+from .device import (Device, DeviceError, FlashAttentionConfig, ModulatedLayerNormConfig, MultiHeadAttentionConfig, RMSNormConfig,
+                     RoPEConfig)
 
-__all__ = ["Device", "DeviceError", "RMSNormConfig", "RoPEConfig", "MultiHeadAttentionConfig", "FlashAttentionConfig", "dtypes"]
+__all__ = ["Device", "DeviceError", "RMSNormConfig", "RoPEConfig", "MultiHeadAttentionConfig", "FlashAttentionConfig", "ModulatedLayerNormConfig",
+           "dtypes"]

@@ -56,6 +56,9 @@ SIGNATURES = {
     "cuda_dispatch_binary_elementwise": (cint, [vp, cint, cint, vp, vp, vp, u32, u64, SP]),
     "cuda_dispatch_gated_residual": (cint, [vp, cint, vp, vp, vp, vp, u32, u32, u32, u32, u32, u64, SP]),
     "cuda_dispatch_rmsnorm": (cint, [vp, cint, vp, vp, vp, u32, u32, flt, u64, SP]),
+    "cuda_dispatch_layernorm": (cint, [vp, cint, vp, vp, vp, vp, u32, u32, flt, u64, SP]),
+    "cuda_dispatch_adaptive_rmsnorm": (cint, [vp, cint, vp, vp, vp, u32, u32, u32, u32, dbl, u64, SP]),
+    "cuda_dispatch_modulated_layernorm": (cint, [vp, cint, vp, vp, vp, u32, u32, u32, u32, u32, dbl, u64, SP]),
     "cuda_dispatch_rmsnorm_f64": (cint, [vp, cint, vp, vp, vp, u32, u32, dbl, u64, SP]),
     "cuda_dispatch_add_rmsnorm_gated_residual": (cint, [vp, cint, vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, dbl, u32, u32, u32, u64, SP]),
     "cuda_dispatch_rope": (cint, [vp, cint, vp, vp, u32, u32, u32, u32, flt, flt, flt, flt, u32, u32, u32, u64, SP]),

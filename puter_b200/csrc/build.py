@@ -22,6 +22,7 @@ SOURCES = [
     "convert.cu",
     "elementwise.cu",
     "norm.cu",
+    "layernorm.cu",
     "rope.cu",
     "pages.cu",
     "attention_exact.cu",

@@ -1,0 +1,210 @@
+// Sibling row normalisations of RMSNorm: device.LayerNorm.LayerNorm, AdaptiveRMSNorm and ModulatedLayerNorm
+// (device/interface.go:355-379).
+//
+// Reference semantics (device/cpu/layernorm/compute.go):
+//   LayerNorm          :109-127, 484-511   mean and variance per row, epsilon 1e-5,
+//                                           out = ((x - mean) * inv) * scale + bias
+//   AdaptiveRMSNorm    :209-264, 387-482   mean square of the row, out = (x * inv) * (1 + scale) + shift with the
+//                                           modulation row [scale | shift] of the row's batch
+//   ModulatedLayerNorm :266-333, 513-570   LayerNorm statistics with the configured epsilon,
+//                                           out = ((x - mean) * inv) * (1 + scale) + shift with [shift | scale] at
+//                                           offset set * 3 * cols of the batch's modulation row
+// Float32 rows carry the statistics in float64 as the CPU code does (float32 row sum -> float64 mean; float32 sum of squared
+// differences -> float64 variance; 1/sqrt in float64); 16-bit rows use float32 statistics, the bf16 row sum being rounded to
+// bf16 first (reduction/bf16_kernels.go:41-51).  Products and sums of the apply step are rounded one by one (no fused
+// multiply-add), results are rounded to the storage type once.
+//
+// One CTA per row at a time (grid-stride over rows): the row is read from HBM once, widened into shared memory, reduced twice
+// (sum, then squared differences against the mean) and written once: 2 x the row in traffic, the HBM minimum.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace puter {
+
+namespace {
+
+enum : int { OP_LAYERNORM = 0, OP_ADAPTIVE_RMS = 1, OP_MODULATED_LN = 2 };
+
+__device__ __forceinline__ float block_sum_f32(float v, float* scratch) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    __syncthreads();  // scratch may still be read from the previous reduction
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float t = lane < nw ? scratch[lane] : 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    return t;
+}
+
+struct RowNormParams {
+    const void* in;
+    const void* p0;   // LayerNorm: scale; the other two: modulation
+    const void* p1;   // LayerNorm: bias
+    void* out;
+    size_t rows, cols, rowsPerBatch, modCols, set;
+    double eps;
+};
+
+template <int DT, int OP>
+__global__ void __launch_bounds__(256) row_norm_kernel(RowNormParams p) {
+    using T = typename Storage<DT>::type;
+    extern __shared__ float rowBuf[];  // the widened row
+    __shared__ float scratch[8];
+    const size_t cols = p.cols;
+    for (size_t row = blockIdx.x; row < p.rows; row += gridDim.x) {
+        const T* x = (const T*)p.in + row * cols;
+        T* o = (T*)p.out + row * cols;
+        // ---- load once, first reduction ----
+        float acc = 0.f;
+        for (size_t i = threadIdx.x; i < cols; i += blockDim.x) {
+            const float v = Storage<DT>::load(x, i);
+            rowBuf[i] = v;
+            acc += OP == OP_ADAPTIVE_RMS ? v * v : v;
+        }
+        float total = block_sum_f32(acc, scratch);
+        float mean = 0.f, inv;
+        if (OP == OP_ADAPTIVE_RMS) {
+            const float ms = __fdiv_rn(total, (float)cols);
+            inv = (float)(1.0 / sqrt((double)ms + p.eps));
+        } else {
+            double var64;
+            if (DT == DT_F32) {
+                mean = (float)((double)total / (double)cols);
+            } else {
+                if (DT == DT_BF16) total = Storage<DT>::widen(Storage<DT>::narrow(total));
+                mean = __fdiv_rn(total, (float)cols);
+            }
+            float sq = 0.f;
+            for (size_t i = threadIdx.x; i < cols; i += blockDim.x) {
+                const float d = sub(rowBuf[i], mean);
+                sq = add(sq, mul(d, d));
+            }
+            sq = block_sum_f32(sq, scratch);
+            if (DT == DT_F32) {
+                var64 = (double)sq / (double)cols;
+                inv = (float)(1.0 / sqrt(var64 + p.eps));
+            } else if (OP == OP_LAYERNORM) {
+                inv = (float)(1.0 / sqrt((double)add(__fdiv_rn(sq, (float)cols), (float)p.eps)));  // epsilon added in float32
+            } else {
+                inv = (float)(1.0 / sqrt((double)__fdiv_rn(sq, (float)cols) + p.eps));
+            }
+        }
+        // ---- apply ----
+        if (OP == OP_LAYERNORM) {
+            const T* g = (const T*)p.p0;
+            const T* b = (const T*)p.p1;
+            for (size_t i = threadIdx.x; i < cols; i += blockDim.x) {
+                const float d = mul(mul(sub(rowBuf[i], mean), inv), Storage<DT>::load(g, i));
+                Storage<DT>::store(o, i, add(d, Storage<DT>::load(b, i)));
+            }
+        } else {
+            const size_t batch = row / p.rowsPerBatch;
+            const T* m = (const T*)p.p0 + batch * p.modCols + (OP == OP_MODULATED_LN ? p.set * cols * 3 : 0);
+            for (size_t i = threadIdx.x; i < cols; i += blockDim.x) {
+                // AdaptiveRMSNorm: [scale | shift]; ModulatedLayerNorm: [shift | scale]
+                const float first = Storage<DT>::load(m, i), second = Storage<DT>::load(m, cols + i);
+                const float scale = OP == OP_ADAPTIVE_RMS ? first : second, shift = OP == OP_ADAPTIVE_RMS ? second : first;
+                const float nrm = mul(OP == OP_ADAPTIVE_RMS ? rowBuf[i] : sub(rowBuf[i], mean), inv);
+                Storage<DT>::store(o, i, add(mul(nrm, add(1.0f, scale)), shift));
+            }
+        }
+        __syncthreads();  // rowBuf is overwritten by the next row
+    }
+}
+
+constexpr size_t kMaxCols = 16384;  // 64 KB of shared memory for the widened row
+
+template <int OP>
+int launch_row_norm(Context* ctx, int dt, const RowNormParams& p, CUDAStatus* status, const char* what) {
+    if (p.cols > kMaxCols) return fail(status, -6, "%s: last dimension %zu exceeds the supported maximum of %zu", what, p.cols, kMaxCols);
+    const size_t smem = p.cols * sizeof(float);
+    size_t blocks = p.rows, cap = (size_t)ctx->smCount * 8;
+    if (blocks > cap) blocks = cap;
+#define ROWNORM_LAUNCH(DT)                                                                                          \
+    do {                                                                                                            \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(row_norm_kernel<DT, OP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        row_norm_kernel<DT, OP><<<(unsigned)blocks, 256, smem, ctx->stream>>>(p);                                    \
+    } while (0)
+    if (dt == DT_F32) ROWNORM_LAUNCH(DT_F32);
+    else if (dt == DT_BF16) ROWNORM_LAUNCH(DT_BF16);
+    else if (dt == DT_F16) ROWNORM_LAUNCH(DT_F16);
+    else return fail(status, -6, "%s: unsupported dtype %d", what, dt);
+#undef ROWNORM_LAUNCH
+    return check_launch(ctx, status, what);
+}
+
+}  // namespace
+
+}  // namespace puter
+
+using namespace puter;
+
+extern "C" int cuda_dispatch_layernorm(CUDADeviceRef contextRef, int elementDType, CUDABufferRef inputRef, CUDABufferRef scaleRef,
+                                       CUDABufferRef biasRef, CUDABufferRef outputRef, uint32_t rows, uint32_t cols, float epsilon,
+                                       uint64_t completionToken, CUDAStatus* status) {
+    (void)completionToken;
+    PUTER_ENTER(ctx);
+    if (rows == 0 || cols == 0) return ok(status);
+    const size_t es = dtype_size(elementDType);
+    if (es == 0) return fail(status, -6, "layernorm: unsupported dtype %d", elementDType);
+    PUTER_REQUIRE(inputRef, "input", (size_t)rows * cols * es);
+    PUTER_REQUIRE(outputRef, "output", (size_t)rows * cols * es);
+    PUTER_REQUIRE(scaleRef, "scale", (size_t)cols * es);
+    PUTER_REQUIRE(biasRef, "bias", (size_t)cols * es);
+    RowNormParams p = {};
+    p.in = dev_ptr(inputRef); p.p0 = dev_ptr(scaleRef); p.p1 = dev_ptr(biasRef); p.out = dev_ptr(outputRef);
+    p.rows = rows; p.cols = cols; p.rowsPerBatch = 1;
+    p.eps = epsilon > 0.f ? (double)epsilon : 1e-5;  // the CPU op has no epsilon argument: 1e-5 (compute.go:11)
+    return launch_row_norm<OP_LAYERNORM>(ctx, elementDType, p, status, "layernorm");
+}
+
+static int check_modulated(CUDAStatus* status, const char* what, double eps, uint32_t rows, uint32_t rowsPerBatch, uint64_t modCols,
+                           uint64_t needCols) {
+    if (!(eps > 0)) return fail(status, -2, "%s: epsilon must be positive, got %g", what, eps);
+    if (rowsPerBatch == 0) return fail(status, -2, "%s: rowsPerBatch must be positive", what);
+    if (rows % rowsPerBatch != 0) return fail(status, -2, "%s: rows must be divisible by rowsPerBatch", what);
+    if (modCols < needCols) return fail(status, -2, "%s: modulation width too small", what);
+    return 0;
+}
+
+extern "C" int cuda_dispatch_adaptive_rmsnorm(CUDADeviceRef contextRef, int elementDType, CUDABufferRef inputRef, CUDABufferRef modulationRef,
+                                              CUDABufferRef outputRef, uint32_t rows, uint32_t cols, uint32_t rowsPerBatch,
+                                              uint32_t modulationCols, double epsilon, uint64_t completionToken, CUDAStatus* status) {
+    (void)completionToken;
+    PUTER_ENTER(ctx);
+    int rc = check_modulated(status, "adaptive rmsnorm", epsilon, rows, rowsPerBatch, modulationCols, 2ull * cols);
+    if (rc != 0) return rc;
+    if (rows == 0 || cols == 0) return ok(status);
+    const size_t es = dtype_size(elementDType);
+    if (es == 0) return fail(status, -6, "adaptive rmsnorm: unsupported dtype %d", elementDType);
+    PUTER_REQUIRE(inputRef, "input", (size_t)rows * cols * es);
+    PUTER_REQUIRE(outputRef, "output", (size_t)rows * cols * es);
+    PUTER_REQUIRE(modulationRef, "modulation", (size_t)(rows / rowsPerBatch) * modulationCols * es);
+    RowNormParams p = {};
+    p.in = dev_ptr(inputRef); p.p0 = dev_ptr(modulationRef); p.out = dev_ptr(outputRef);
+    p.rows = rows; p.cols = cols; p.rowsPerBatch = rowsPerBatch; p.modCols = modulationCols; p.eps = epsilon;
+    return launch_row_norm<OP_ADAPTIVE_RMS>(ctx, elementDType, p, status, "adaptive rmsnorm");
+}
+
+extern "C" int cuda_dispatch_modulated_layernorm(CUDADeviceRef contextRef, int elementDType, CUDABufferRef inputRef,
+                                                 CUDABufferRef modulationRef, CUDABufferRef outputRef, uint32_t rows, uint32_t cols,
+                                                 uint32_t rowsPerBatch, uint32_t modulationCols, uint32_t set, double epsilon,
+                                                 uint64_t completionToken, CUDAStatus* status) {
+    (void)completionToken;
+    PUTER_ENTER(ctx);
+    int rc = check_modulated(status, "modulated layernorm", epsilon, rows, rowsPerBatch, modulationCols, ((uint64_t)set * 3 + 2) * cols);
+    if (rc != 0) return rc;
+    if (rows == 0 || cols == 0) return ok(status);
+    const size_t es = dtype_size(elementDType);
+    if (es == 0) return fail(status, -6, "modulated layernorm: unsupported dtype %d", elementDType);
+    PUTER_REQUIRE(inputRef, "input", (size_t)rows * cols * es);
+    PUTER_REQUIRE(outputRef, "output", (size_t)rows * cols * es);
+    PUTER_REQUIRE(modulationRef, "modulation", (size_t)(rows / rowsPerBatch) * modulationCols * es);
+    RowNormParams p = {};
+    p.in = dev_ptr(inputRef); p.p0 = dev_ptr(modulationRef); p.out = dev_ptr(outputRef);
+    p.rows = rows; p.cols = cols; p.rowsPerBatch = rowsPerBatch; p.modCols = modulationCols; p.set = set; p.eps = epsilon;
+    return launch_row_norm<OP_MODULATED_LN>(ctx, elementDType, p, status, "modulated layernorm");
+}

@@ -35,6 +35,12 @@ class RMSNormConfig:  # device/config.go:82-92
 
 
 @dataclass
+class ModulatedLayerNormConfig:  # device/config.go:94-109
+    Epsilon: float = 1e-6
+    Set: int = 0
+
+
+@dataclass
 class RoPEConfig:  # device/config.go:123-134; defaults device/cpu/rope/config.go:7-15
     BaseFreq: float = 10000.0
     StartPosition: int = 0
@@ -251,6 +257,21 @@ class Device:
     def RMSNorm(self, config: RMSNormConfig, input, scale, output, rows, lastDim, format):
         self._call("cuda_dispatch_rmsnorm_f64", [input, scale, output],
                    lambda r: (format, r[0], r[1], r[2], rows, lastDim, float(config.Epsilon), 0))
+
+    def LayerNorm(self, input, scale, bias, output, rows, lastDim, format):
+        """device.LayerNorm.LayerNorm (device/interface.go:362-366); epsilon 1e-5 as on the CPU."""
+        self._call("cuda_dispatch_layernorm", [input, scale, bias, output], lambda r: (format, r[0], r[1], r[2], r[3], rows, lastDim, 0.0, 0))
+
+    def AdaptiveRMSNorm(self, config: RMSNormConfig, input, modulation, output, rows, lastDim, rowsPerBatch, modulationCols, format):
+        """device.LayerNorm.AdaptiveRMSNorm (device/interface.go:356-361)."""
+        self._call("cuda_dispatch_adaptive_rmsnorm", [input, modulation, output],
+                   lambda r: (format, r[0], r[1], r[2], rows, lastDim, rowsPerBatch, modulationCols, float(config.Epsilon), 0))
+
+    def ModulatedLayerNorm(self, config: "ModulatedLayerNormConfig", input, modulation, output, rows, lastDim, rowsPerBatch, modulationCols,
+                           format):
+        """device.LayerNorm.ModulatedLayerNorm (device/interface.go:367-372)."""
+        self._call("cuda_dispatch_modulated_layernorm", [input, modulation, output],
+                   lambda r: (format, r[0], r[1], r[2], rows, lastDim, rowsPerBatch, modulationCols, int(config.Set), float(config.Epsilon), 0))
 
     def GatedResidual(self, residual, branch, modulation, output, rows, lastDim, rowsPerBatch, modulationCols, set, format):
         """execution/math_gated_residual_intrinsic.go:11-17 (gatedResidualDevice)."""

@@ -227,3 +227,24 @@ def test_bf16_dot_result_is_rounded_to_storage():
     g = O.from_f32(np.ones(300, np.float32), O.BF16)
     out = O.to_f32(O.rmsnorm(O.BF16, x, g, 1e-6), O.BF16)
     assert np.all(out == out[0, 0])
+
+
+def test_layernorm_family_against_float64_numpy():
+    """No literal known answers exist for these ops in the reference's tests (they compare against Go helper references), so the
+    restatements are checked against the defining formulas in float64."""
+    rng = np.random.default_rng(11)
+    x = (rng.standard_normal((5, 300)) * 2 + 0.5).astype(np.float32)
+    g = rng.uniform(0.5, 1.5, 300).astype(np.float32)
+    b = rng.standard_normal(300).astype(np.float32)
+    xd = x.astype(np.float64)
+    norm = (xd - xd.mean(1, keepdims=True)) / np.sqrt(xd.var(1, keepdims=True) + 1e-5)
+    assert np.abs(O.layernorm(O.F32, x, g, b) - (norm * g + b)).max() < 5e-6
+    got16 = O.to_f32(O.layernorm(O.BF16, O.from_f32(x, O.BF16), O.from_f32(g, O.BF16), O.from_f32(b, O.BF16)), O.BF16)
+    assert np.abs(got16 - (norm * g + b)).max() < 6e-2
+    mod = (rng.standard_normal((1, 900)) * 0.1).astype(np.float32)
+    want = xd / np.sqrt((xd ** 2).mean(1, keepdims=True) + 1e-6) * (1 + mod[0, :300]) + mod[0, 300:600]
+    assert np.abs(O.adaptive_rmsnorm(O.F32, x, mod, 5, 900, 1e-6) - want).max() < 5e-6
+    mod2 = (rng.standard_normal((1, 1500)) * 0.1).astype(np.float32)
+    norm6 = (xd - xd.mean(1, keepdims=True)) / np.sqrt(xd.var(1, keepdims=True) + 1e-6)
+    want = norm6 * (1 + mod2[0, 1200:1500]) + mod2[0, 900:1200]
+    assert np.abs(O.modulated_layernorm(O.F32, x, mod2, 5, 1500, 1e-6, 1) - want).max() < 5e-6
