@@ -39,6 +39,33 @@ __device__ __forceinline__ float block_sum_f32(float v, float* scratch) {
     return t;
 }
 
+// 16 bytes of storage <-> PER floats (4 for f32, 8 for the 16-bit types)
+template <int DT> struct Per { static constexpr int kPer = DT == DT_F32 ? 4 : 8; };
+template <int DT> __device__ __forceinline__ void unpack_row(const Vec16& v, float* f) {
+    if (DT == DT_F32) {
+#pragma unroll
+        for (int i = 0; i < 4; i++) f[i] = __uint_as_float(v.w[i]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            f[2 * i] = Storage<DT>::widen((uint16_t)(v.w[i] & 0xFFFFu));
+            f[2 * i + 1] = Storage<DT>::widen((uint16_t)(v.w[i] >> 16));
+        }
+    }
+}
+template <int DT> __device__ __forceinline__ Vec16 pack_row(const float* f) {
+    Vec16 v;
+    if (DT == DT_F32) {
+#pragma unroll
+        for (int i = 0; i < 4; i++) v.w[i] = __float_as_uint(f[i]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 4; i++)
+            v.w[i] = (uint32_t)Storage<DT>::narrow(f[2 * i]) | ((uint32_t)Storage<DT>::narrow(f[2 * i + 1]) << 16);
+    }
+    return v;
+}
+
 struct RowNormParams {
     const void* in;
     const void* p0;   // LayerNorm: scale; the other two: modulation
@@ -48,21 +75,63 @@ struct RowNormParams {
     double eps;
 };
 
-template <int DT, int OP>
+// VEC: cols is a multiple of the vector width and every buffer is 16-byte aligned (rows then stay aligned too)
+template <int DT, int OP, bool VEC>
 __global__ void __launch_bounds__(256) row_norm_kernel(RowNormParams p) {
     using T = typename Storage<DT>::type;
+    constexpr int PER = Per<DT>::kPer;
     extern __shared__ float rowBuf[];  // the widened row
     __shared__ float scratch[8];
     const size_t cols = p.cols;
+    // Rows of up to kAhead vectors per thread are fetched one row ahead into registers, so the loads of the next row are in
+    // flight while this row is reduced and written (a CTA otherwise alternates between waiting for memory and computing).
+    constexpr int kAhead = 4;
+    const size_t nvec = cols / PER;
+    const bool ahead = VEC && nvec <= (size_t)kAhead * 256;
+    Vec16 nxt[kAhead];
+    auto fetch = [&](size_t row) {
+        const char* src = (const char*)((const T*)p.in + row * cols);
+#pragma unroll
+        for (int k = 0; k < kAhead; k++) {
+            const size_t v = threadIdx.x + (size_t)k * 256;
+            if (v < nvec) nxt[k] = ld_stream(src + v * 16);
+        }
+    };
+    if (ahead && blockIdx.x < p.rows) fetch(blockIdx.x);
     for (size_t row = blockIdx.x; row < p.rows; row += gridDim.x) {
         const T* x = (const T*)p.in + row * cols;
         T* o = (T*)p.out + row * cols;
         // ---- load once, first reduction ----
         float acc = 0.f;
-        for (size_t i = threadIdx.x; i < cols; i += blockDim.x) {
-            const float v = Storage<DT>::load(x, i);
-            rowBuf[i] = v;
-            acc += OP == OP_ADAPTIVE_RMS ? v * v : v;
+        if (ahead) {
+#pragma unroll
+            for (int k = 0; k < kAhead; k++) {
+                const size_t v = threadIdx.x + (size_t)k * 256;
+                if (v < nvec) {
+                    float f[PER];
+                    unpack_row<DT>(nxt[k], f);
+#pragma unroll
+                    for (int i = 0; i < PER; i += 4) *(float4*)(rowBuf + v * PER + i) = make_float4(f[i], f[i + 1], f[i + 2], f[i + 3]);
+#pragma unroll
+                    for (int i = 0; i < PER; i++) acc += OP == OP_ADAPTIVE_RMS ? f[i] * f[i] : f[i];
+                }
+            }
+            if (row + gridDim.x < p.rows) fetch(row + gridDim.x);
+        } else if (VEC) {
+            for (size_t v = threadIdx.x; v < cols / PER; v += blockDim.x) {
+                float f[PER];
+                unpack_row<DT>(ld_stream((const char*)x + v * 16), f);
+#pragma unroll
+                for (int i = 0; i < PER; i += 4) *(float4*)(rowBuf + v * PER + i) = make_float4(f[i], f[i + 1], f[i + 2], f[i + 3]);
+#pragma unroll
+                for (int i = 0; i < PER; i++) acc += OP == OP_ADAPTIVE_RMS ? f[i] * f[i] : f[i];
+            }
+        } else {
+            for (size_t i = threadIdx.x; i < cols; i += blockDim.x) {
+                const float v = Storage<DT>::load(x, i);
+                rowBuf[i] = v;
+                acc += OP == OP_ADAPTIVE_RMS ? v * v : v;
+            }
         }
         float total = block_sum_f32(acc, scratch);
         float mean = 0.f, inv;
@@ -78,9 +147,17 @@ __global__ void __launch_bounds__(256) row_norm_kernel(RowNormParams p) {
                 mean = __fdiv_rn(total, (float)cols);
             }
             float sq = 0.f;
-            for (size_t i = threadIdx.x; i < cols; i += blockDim.x) {
-                const float d = sub(rowBuf[i], mean);
-                sq = add(sq, mul(d, d));
+            if (VEC) {
+                for (size_t v = threadIdx.x; v < cols / 4; v += blockDim.x) {
+                    const float4 f = *(const float4*)(rowBuf + v * 4);
+                    const float d0 = sub(f.x, mean), d1 = sub(f.y, mean), d2 = sub(f.z, mean), d3 = sub(f.w, mean);
+                    sq = add(add(add(add(sq, mul(d0, d0)), mul(d1, d1)), mul(d2, d2)), mul(d3, d3));
+                }
+            } else {
+                for (size_t i = threadIdx.x; i < cols; i += blockDim.x) {
+                    const float d = sub(rowBuf[i], mean);
+                    sq = add(sq, mul(d, d));
+                }
             }
             sq = block_sum_f32(sq, scratch);
             if (DT == DT_F32) {
@@ -96,19 +173,46 @@ __global__ void __launch_bounds__(256) row_norm_kernel(RowNormParams p) {
         if (OP == OP_LAYERNORM) {
             const T* g = (const T*)p.p0;
             const T* b = (const T*)p.p1;
-            for (size_t i = threadIdx.x; i < cols; i += blockDim.x) {
-                const float d = mul(mul(sub(rowBuf[i], mean), inv), Storage<DT>::load(g, i));
-                Storage<DT>::store(o, i, add(d, Storage<DT>::load(b, i)));
+            if (VEC) {
+                for (size_t v = threadIdx.x; v < cols / PER; v += blockDim.x) {
+                    float gs[PER], bs[PER], r[PER];
+                    unpack_row<DT>(*(const Vec16*)((const char*)g + v * 16), gs);
+                    unpack_row<DT>(*(const Vec16*)((const char*)b + v * 16), bs);
+#pragma unroll
+                    for (int i = 0; i < PER; i++) r[i] = add(mul(mul(sub(rowBuf[v * PER + i], mean), inv), gs[i]), bs[i]);
+                    st_stream((char*)o + v * 16, pack_row<DT>(r));
+                }
+            } else {
+                for (size_t i = threadIdx.x; i < cols; i += blockDim.x) {
+                    const float d = mul(mul(sub(rowBuf[i], mean), inv), Storage<DT>::load(g, i));
+                    Storage<DT>::store(o, i, add(d, Storage<DT>::load(b, i)));
+                }
             }
         } else {
             const size_t batch = row / p.rowsPerBatch;
             const T* m = (const T*)p.p0 + batch * p.modCols + (OP == OP_MODULATED_LN ? p.set * cols * 3 : 0);
-            for (size_t i = threadIdx.x; i < cols; i += blockDim.x) {
-                // AdaptiveRMSNorm: [scale | shift]; ModulatedLayerNorm: [shift | scale]
-                const float first = Storage<DT>::load(m, i), second = Storage<DT>::load(m, cols + i);
-                const float scale = OP == OP_ADAPTIVE_RMS ? first : second, shift = OP == OP_ADAPTIVE_RMS ? second : first;
-                const float nrm = mul(OP == OP_ADAPTIVE_RMS ? rowBuf[i] : sub(rowBuf[i], mean), inv);
-                Storage<DT>::store(o, i, add(mul(nrm, add(1.0f, scale)), shift));
+            // AdaptiveRMSNorm: [scale | shift]; ModulatedLayerNorm: [shift | scale]
+            if (VEC) {
+                for (size_t v = threadIdx.x; v < cols / PER; v += blockDim.x) {
+                    float first[PER], second[PER], r[PER];
+                    unpack_row<DT>(*(const Vec16*)((const char*)m + v * 16), first);
+                    unpack_row<DT>(*(const Vec16*)((const char*)(m + cols) + v * 16), second);
+#pragma unroll
+                    for (int i = 0; i < PER; i++) {
+                        const float scale = OP == OP_ADAPTIVE_RMS ? first[i] : second[i], shift = OP == OP_ADAPTIVE_RMS ? second[i] : first[i];
+                        const float x0 = rowBuf[v * PER + i];
+                        const float nrm = mul(OP == OP_ADAPTIVE_RMS ? x0 : sub(x0, mean), inv);
+                        r[i] = add(mul(nrm, add(1.0f, scale)), shift);
+                    }
+                    st_stream((char*)o + v * 16, pack_row<DT>(r));
+                }
+            } else {
+                for (size_t i = threadIdx.x; i < cols; i += blockDim.x) {
+                    const float first = Storage<DT>::load(m, i), second = Storage<DT>::load(m, cols + i);
+                    const float scale = OP == OP_ADAPTIVE_RMS ? first : second, shift = OP == OP_ADAPTIVE_RMS ? second : first;
+                    const float nrm = mul(OP == OP_ADAPTIVE_RMS ? rowBuf[i] : sub(rowBuf[i], mean), inv);
+                    Storage<DT>::store(o, i, add(mul(nrm, add(1.0f, scale)), shift));
+                }
             }
         }
         __syncthreads();  // rowBuf is overwritten by the next row
@@ -120,13 +224,22 @@ constexpr size_t kMaxCols = 16384;  // 64 KB of shared memory for the widened ro
 template <int OP>
 int launch_row_norm(Context* ctx, int dt, const RowNormParams& p, CUDAStatus* status, const char* what) {
     if (p.cols > kMaxCols) return fail(status, -6, "%s: last dimension %zu exceeds the supported maximum of %zu", what, p.cols, kMaxCols);
-    const size_t smem = p.cols * sizeof(float);
+    const size_t smem = (p.cols * sizeof(float) + 15) & ~(size_t)15;
     size_t blocks = p.rows, cap = (size_t)ctx->smCount * 8;
     if (blocks > cap) blocks = cap;
+    const size_t es = dt == DT_F32 ? 4 : 2, per = 16 / es;
+    // the modulation row of a batch starts at batch * modCols (+ set * 3 * cols) elements and its second half cols further on
+    const bool vec = p.cols % per == 0 && (((uintptr_t)p.in | (uintptr_t)p.out | (uintptr_t)p.p0 | (uintptr_t)p.p1) & 15u) == 0 &&
+                     (OP == OP_LAYERNORM || p.modCols % per == 0);
 #define ROWNORM_LAUNCH(DT)                                                                                          \
     do {                                                                                                            \
-        if (smem > 48 * 1024) cudaFuncSetAttribute(row_norm_kernel<DT, OP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-        row_norm_kernel<DT, OP><<<(unsigned)blocks, 256, smem, ctx->stream>>>(p);                                    \
+        if (vec) {                                                                                                  \
+            if (smem > 48 * 1024) cudaFuncSetAttribute(row_norm_kernel<DT, OP, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            row_norm_kernel<DT, OP, true><<<(unsigned)blocks, 256, smem, ctx->stream>>>(p);                          \
+        } else {                                                                                                    \
+            if (smem > 48 * 1024) cudaFuncSetAttribute(row_norm_kernel<DT, OP, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            row_norm_kernel<DT, OP, false><<<(unsigned)blocks, 256, smem, ctx->stream>>>(p);                         \
+        }                                                                                                           \
     } while (0)
     if (dt == DT_F32) ROWNORM_LAUNCH(DT_F32);
     else if (dt == DT_BF16) ROWNORM_LAUNCH(DT_BF16);

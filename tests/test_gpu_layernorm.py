@@ -41,13 +41,14 @@ def test_layernorm(dt, rows, cols):
 
 
 @pytest.mark.parametrize("dt", [O.F32, O.BF16, O.F16])
+@pytest.mark.parametrize("pad", [0, 5])  # 0: 16-byte vector path, 5: modulation rows unaligned -> scalar path
 @pytest.mark.parametrize("rows,cols,rpb", [(4, 64, 2), (12, 1536, 4), (6, 4096, 6)])
-def test_adaptive_rmsnorm(dt, rows, cols, rpb):
+def test_adaptive_rmsnorm(dt, rows, cols, rpb, pad):
     import puter_b200
 
     d = puter_b200.Device()
     rng = np.random.default_rng(rows + cols)
-    mod_cols = 2 * cols + 5
+    mod_cols = 2 * cols + pad
     x = O.from_f32(rng.standard_normal((rows, cols)).astype(np.float32), dt)
     mod = O.from_f32((rng.standard_normal((rows // rpb, mod_cols)) * 0.2).astype(np.float32), dt)
     want = O.adaptive_rmsnorm(dt, x, mod, rpb, mod_cols, 1e-6)
@@ -57,13 +58,14 @@ def test_adaptive_rmsnorm(dt, rows, cols, rpb):
 
 
 @pytest.mark.parametrize("dt", [O.F32, O.BF16, O.F16])
+@pytest.mark.parametrize("pad", [0, 3])
 @pytest.mark.parametrize("rows,cols,rpb,set_index", [(4, 64, 2, 0), (12, 1536, 4, 1), (6, 4096, 3, 2)])
-def test_modulated_layernorm(dt, rows, cols, rpb, set_index):
+def test_modulated_layernorm(dt, rows, cols, rpb, set_index, pad):
     import puter_b200
 
     d = puter_b200.Device()
     rng = np.random.default_rng(rows + cols + set_index)
-    mod_cols = (set_index * 3 + 2) * cols + 3
+    mod_cols = (set_index * 3 + 2) * cols + pad
     x = O.from_f32((rng.standard_normal((rows, cols)) + 0.5).astype(np.float32), dt)
     mod = O.from_f32((rng.standard_normal((rows // rpb, mod_cols)) * 0.2).astype(np.float32), dt)
     want = O.modulated_layernorm(dt, x, mod, rpb, mod_cols, 1e-6, set_index)
