@@ -27,6 +27,11 @@ enum class DType : int { Float32 = 0, Float16 = 1, BFloat16 = 2, Float64 = 3, Fl
 struct RMSNormConfig {
     double Epsilon = 1e-5;
 };
+// device/config.go:94-109
+struct ModulatedLayerNormConfig {
+    double Epsilon = 1e-6;
+    int Set = 0;
+};
 // device/config.go:111-134
 enum class RoPEMode : int { Interleaved = 0, Half = 1 };
 enum class RoPEScaling : int { None = 0, Llama3 = 1 };
@@ -128,6 +133,25 @@ class Backend {
         check(cuda_dispatch_rmsnorm_f64(ctx_, (int)f, ref(input), ref(scale), ref(output), (uint32_t)rows, (uint32_t)lastDim,
                                         config.Epsilon, 0, &st), st);
     }
+    // device.LayerNorm.LayerNorm / AdaptiveRMSNorm / ModulatedLayerNorm (device/interface.go:355-372)
+    void LayerNorm(void* input, void* scale, void* bias, void* output, int rows, int lastDim, DType f) {
+        CUDAStatus st;
+        check(cuda_dispatch_layernorm(ctx_, (int)f, ref(input), ref(scale), ref(bias), ref(output), (uint32_t)rows, (uint32_t)lastDim, 0.0f, 0,
+                                      &st), st);
+    }
+    void AdaptiveRMSNorm(RMSNormConfig config, void* input, void* modulation, void* output, int rows, int lastDim, int rowsPerBatch,
+                         int modulationCols, DType f) {
+        CUDAStatus st;
+        check(cuda_dispatch_adaptive_rmsnorm(ctx_, (int)f, ref(input), ref(modulation), ref(output), (uint32_t)rows, (uint32_t)lastDim,
+                                             (uint32_t)rowsPerBatch, (uint32_t)modulationCols, config.Epsilon, 0, &st), st);
+    }
+    void ModulatedLayerNorm(ModulatedLayerNormConfig config, void* input, void* modulation, void* output, int rows, int lastDim,
+                            int rowsPerBatch, int modulationCols, DType f) {
+        CUDAStatus st;
+        check(cuda_dispatch_modulated_layernorm(ctx_, (int)f, ref(input), ref(modulation), ref(output), (uint32_t)rows, (uint32_t)lastDim,
+                                                (uint32_t)rowsPerBatch, (uint32_t)modulationCols, (uint32_t)config.Set, config.Epsilon, 0,
+                                                &st), st);
+    }
     // gatedResidualDevice (execution/math_gated_residual_intrinsic.go:11-17)
     void GatedResidual(void* residual, void* branch, void* modulation, void* output, int rows, int lastDim, int rowsPerBatch,
                        int modulationCols, int set, DType f) {
@@ -153,6 +177,19 @@ class Backend {
         check(cuda_dispatch_kv_page_write(ctx_, (int)f, ref(storage), ref(values), ref(pageIDs), ref(offsets), ref(output),
                                           (uint32_t)pageCount, (uint32_t)pageSize, (uint32_t)inner, (uint32_t)valueRows,
                                           (uint64_t)storageOffset, 0, &st), st);
+    }
+    // KV-cache producer: RoPE(k) at positions[row] -> [e4m3 of value / scale] -> KVPageWrite of K and V, one launch (no single
+    // reference counterpart; kScale / vScale may be null unless kvFormat is Float8E4M3)
+    void RoPEKVPageWrite(RoPEConfig c, void* k, void* v, void* positions, void* pageIDs, void* offsets, void* kPages, void* vPages,
+                         void* kScale, void* vScale, int rows, int kvHeads, int headDim, int pageCount, int pageSize, int maxPositions,
+                         DType f, DType kvFormat) {
+        CUDAStatus st;
+        check(cuda_dispatch_rope_kv_page_write(ctx_, (int)f, (int)kvFormat, ref(k), ref(v), ref(positions), ref(pageIDs), ref(offsets),
+                                               ref(kPages), ref(vPages), kScale ? ref(kScale) : nullptr, vScale ? ref(vScale) : nullptr, (uint32_t)rows,
+                                               (uint32_t)kvHeads,
+                                               (uint32_t)headDim, (uint32_t)pageCount, (uint32_t)pageSize, (uint32_t)maxPositions,
+                                               c.BaseFreq, (uint32_t)c.Mode, (uint32_t)c.Scaling, c.ScalingFactor, c.LowFreqFactor,
+                                               c.HighFreqFactor, (uint32_t)c.OriginalContext, 0, &st), st);
     }
     void KVPageGather(void* storage, void* pageTable, void* output, int pageCount, int pageSize, int inner, int outRows,
                       int storageOffset, DType f) {
