@@ -122,39 +122,45 @@ class ChainWorkload:
         assert self.row_in_batch_offset == 0 or self.rows <= self.rpb - self.row_in_batch_offset
         self.gate = torch.randn(self.rows, self.I, device="cuda", dtype=bf, generator=g)
         self.up = torch.randn(self.rows, self.I, device="cuda", dtype=bf, generator=g)
-        self.n_out = torch.empty(self.rows, self.C, device="cuda", dtype=bf)
-        self.g_out = torch.empty(self.rows, self.C, device="cuda", dtype=bf)
-        self.s_out = torch.empty(self.rows, self.I, device="cuda", dtype=bf)
+        if world > 1:
+            # the kernels write this rank's rows straight into their place in the gathered tensors, so the all-gathers run in
+            # place (no local copy) and the first two overlap the SwiGLU kernel
+            self.n_all = torch.empty(self.T, self.C, device="cuda", dtype=bf)
+            self.g_all = torch.empty(self.T, self.C, device="cuda", dtype=bf)
+            self.s_all = torch.empty(self.T, self.I, device="cuda", dtype=bf)
+            self.n_out, self.g_out, self.s_out = (t[r0:r0 + self.rows] for t in (self.n_all, self.g_all, self.s_all))
+        else:
+            self.n_out = torch.empty(self.rows, self.C, device="cuda", dtype=bf)
+            self.g_out = torch.empty(self.rows, self.C, device="cuda", dtype=bf)
+            self.s_out = torch.empty(self.rows, self.I, device="cuda", dtype=bf)
         self.cfg = RMSNormConfig(1e-6)
         self.bytes_per_step_global = 2 * (3 * self.T * self.C + 2 * self.T * self.C) + 2 * (3 * self.T * self.I)
         self.bytes_per_step = self.bytes_per_step_global // world
         # profiles/norm_swiglu_chain.md: (402.7 + 225.0 + 939.6 + 435.9) MB measured for 671.1 + 1409.3 MB algorithmic (the
         # write counters lag the cache flush)
         self.traffic_ratio = (402.7 + 225.0 + 939.6 + 435.9) / (671.1 + 1409.3)
-        if world > 1:
-            self.n_all = torch.empty(self.T, self.C, device="cuda", dtype=bf)
-            self.g_all = torch.empty(self.T, self.C, device="cuda", dtype=bf)
-            self.s_all = torch.empty(self.T, self.I, device="cuda", dtype=bf)
         self.x_host = self.x.cpu().pin_memory()
         self.n_host = torch.empty(self.rows, self.C, dtype=bf).pin_memory()
         self.h2d, self.d2h = self.x_host.numel() * 2, self.n_host.numel() * 2
 
-    def _kernels(self):
+    def step(self):
         D = self.D
         # rowsPerBatch: with sharded rows every rank's rows fall inside whole batch items or a fraction of one
         rpb = min(self.rpb, self.rows) if self.rows < self.rpb else self.rpb
         self.dev.AddRMSNormGatedResidual(self.cfg, self.x, self.r, self.gamma, self.branch, self.mod, None, self.n_out, self.g_out,
                                          self.rows, self.C, rpb, 3 * self.C, 0, D.BFloat16)
-        self.dev.SwiGLUTensors(self.s_out, self.gate, self.up, self.rows * self.I, D.BFloat16)
-
-    def step(self):
-        self._kernels()
+        works = []
         if self.world > 1:
             import torch.distributed as dist
 
-            dist.all_gather_into_tensor(self.n_all, self.n_out)
-            dist.all_gather_into_tensor(self.g_all, self.g_out)
-            dist.all_gather_into_tensor(self.s_all, self.s_out)
+            # in place (input = this rank's slice of the output); asynchronous, so they travel while SwiGLU computes
+            works.append(dist.all_gather_into_tensor(self.n_all, self.n_out, async_op=True))
+            works.append(dist.all_gather_into_tensor(self.g_all, self.g_out, async_op=True))
+        self.dev.SwiGLUTensors(self.s_out, self.gate, self.up, self.rows * self.I, D.BFloat16)
+        if self.world > 1:
+            works.append(dist.all_gather_into_tensor(self.s_all, self.s_out, async_op=True))
+            for w in works:
+                w.wait()  # orders the current stream after the collective; no host block
 
     def step_e2e(self):
         self.x.copy_(self.x_host, non_blocking=True)
@@ -163,7 +169,7 @@ class ChainWorkload:
 
     def config(self):
         return {"workload": self.name, "tokens": self.T, "hidden": self.C, "intermediate": self.I, "rows_per_rank": self.rows,
-                "collective": "nccl all_gather of n,g,s" if self.world > 1 else "none",
+                "collective": "nccl all_gather of n,g,s, in place, n and g overlapped with the SwiGLU kernel" if self.world > 1 else "none",
                 "l2": "inputs larger than L2 (2.08 GB per step)"}
 
     def metric(self):
