@@ -219,6 +219,102 @@ __global__ void __launch_bounds__(256) row_norm_kernel(RowNormParams p) {
     }
 }
 
+// Rows of up to 32 * VPL vectors: one warp per row, the raw 16-byte vectors of the row held in registers (VPL per lane, lane l
+// owns vectors l, l + 32, ...), reductions by shuffles: no shared memory, no CTA-wide barrier between the passes.
+__device__ __forceinline__ float warp_sum_f32(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+template <int DT, int OP, int VPL>
+__global__ void __launch_bounds__(256) row_norm_warp_kernel(RowNormParams p) {
+    using T = typename Storage<DT>::type;
+    constexpr int PER = Per<DT>::kPer;
+    const size_t cols = p.cols, nvec = cols / PER;
+    const int lane = threadIdx.x & 31;
+    const size_t warpsTotal = (size_t)gridDim.x * (blockDim.x >> 5);
+    for (size_t row = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < p.rows; row += warpsTotal) {
+        const char* x = (const char*)((const T*)p.in + row * cols);
+        char* o = (char*)((T*)p.out + row * cols);
+        Vec16 raw[VPL];
+#pragma unroll
+        for (int k = 0; k < VPL; k++) {
+            const size_t v = lane + (size_t)k * 32;
+            if (v < nvec) raw[k] = ld_stream(x + v * 16);
+        }
+        float acc = 0.f;
+#pragma unroll
+        for (int k = 0; k < VPL; k++) {
+            if (lane + (size_t)k * 32 < nvec) {
+                float f[PER];
+                unpack_row<DT>(raw[k], f);
+#pragma unroll
+                for (int i = 0; i < PER; i++) acc += OP == OP_ADAPTIVE_RMS ? f[i] * f[i] : f[i];
+            }
+        }
+        float total = warp_sum_f32(acc);
+        float mean = 0.f, inv;
+        if (OP == OP_ADAPTIVE_RMS) {
+            inv = (float)(1.0 / sqrt((double)__fdiv_rn(total, (float)cols) + p.eps));
+        } else {
+            if (DT == DT_F32) {
+                mean = (float)((double)total / (double)cols);
+            } else {
+                if (DT == DT_BF16) total = Storage<DT>::widen(Storage<DT>::narrow(total));
+                mean = __fdiv_rn(total, (float)cols);
+            }
+            float sq = 0.f;
+#pragma unroll
+            for (int k = 0; k < VPL; k++) {
+                if (lane + (size_t)k * 32 < nvec) {
+                    float f[PER];
+                    unpack_row<DT>(raw[k], f);
+#pragma unroll
+                    for (int i = 0; i < PER; i++) {
+                        const float d = sub(f[i], mean);
+                        sq = add(sq, mul(d, d));
+                    }
+                }
+            }
+            sq = warp_sum_f32(sq);
+            if (DT == DT_F32) inv = (float)(1.0 / sqrt((double)sq / (double)cols + p.eps));
+            else if (OP == OP_LAYERNORM) inv = (float)(1.0 / sqrt((double)add(__fdiv_rn(sq, (float)cols), (float)p.eps)));
+            else inv = (float)(1.0 / sqrt((double)__fdiv_rn(sq, (float)cols) + p.eps));
+        }
+        const char* a0;
+        const char* a1;
+        if (OP == OP_LAYERNORM) {
+            a0 = (const char*)p.p0;  // scale
+            a1 = (const char*)p.p1;  // bias
+        } else {
+            const T* m = (const T*)p.p0 + (row / p.rowsPerBatch) * p.modCols + (OP == OP_MODULATED_LN ? p.set * cols * 3 : 0);
+            a0 = (const char*)m;            // AdaptiveRMSNorm: scale; ModulatedLayerNorm: shift
+            a1 = (const char*)(m + cols);   // AdaptiveRMSNorm: shift; ModulatedLayerNorm: scale
+        }
+#pragma unroll
+        for (int k = 0; k < VPL; k++) {
+            const size_t v = lane + (size_t)k * 32;
+            if (v < nvec) {
+                float f[PER], c0[PER], c1[PER], r[PER];
+                unpack_row<DT>(raw[k], f);
+                unpack_row<DT>(*(const Vec16*)(a0 + v * 16), c0);
+                unpack_row<DT>(*(const Vec16*)(a1 + v * 16), c1);
+#pragma unroll
+                for (int i = 0; i < PER; i++) {
+                    if (OP == OP_LAYERNORM) {
+                        r[i] = add(mul(mul(sub(f[i], mean), inv), c0[i]), c1[i]);
+                    } else {
+                        const float scale = OP == OP_ADAPTIVE_RMS ? c0[i] : c1[i], shift = OP == OP_ADAPTIVE_RMS ? c1[i] : c0[i];
+                        const float nrm = mul(OP == OP_ADAPTIVE_RMS ? f[i] : sub(f[i], mean), inv);
+                        r[i] = add(mul(nrm, add(1.0f, scale)), shift);
+                    }
+                }
+                st_stream(o + v * 16, pack_row<DT>(r));
+            }
+        }
+    }
+}
+
 constexpr size_t kMaxCols = 16384;  // 64 KB of shared memory for the widened row
 
 template <int OP>
@@ -231,9 +327,17 @@ int launch_row_norm(Context* ctx, int dt, const RowNormParams& p, CUDAStatus* st
     // the modulation row of a batch starts at batch * modCols (+ set * 3 * cols) elements and its second half cols further on
     const bool vec = p.cols % per == 0 && (((uintptr_t)p.in | (uintptr_t)p.out | (uintptr_t)p.p0 | (uintptr_t)p.p1) & 15u) == 0 &&
                      (OP == OP_LAYERNORM || p.modCols % per == 0);
+    // vector rows of up to 512 vectors (4096 16-bit or 2048 float32 elements) take the warp-per-row kernel
+    const size_t nvec = vec ? p.cols / per : 0;
+    const int vpl = nvec == 0 || nvec > 512 ? 0 : nvec <= 128 ? 4 : nvec <= 256 ? 8 : 16;
+    size_t warpBlocks = (p.rows + 7) / 8;
+    if (warpBlocks > cap) warpBlocks = cap;
 #define ROWNORM_LAUNCH(DT)                                                                                          \
     do {                                                                                                            \
-        if (vec) {                                                                                                  \
+        if (vpl == 4) row_norm_warp_kernel<DT, OP, 4><<<(unsigned)warpBlocks, 256, 0, ctx->stream>>>(p);             \
+        else if (vpl == 8) row_norm_warp_kernel<DT, OP, 8><<<(unsigned)warpBlocks, 256, 0, ctx->stream>>>(p);        \
+        else if (vpl == 16) row_norm_warp_kernel<DT, OP, 16><<<(unsigned)warpBlocks, 256, 0, ctx->stream>>>(p);      \
+        else if (vec) {                                                                                                  \
             if (smem > 48 * 1024) cudaFuncSetAttribute(row_norm_kernel<DT, OP, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
             row_norm_kernel<DT, OP, true><<<(unsigned)blocks, 256, smem, ctx->stream>>>(p);                          \
         } else {                                                                                                    \
