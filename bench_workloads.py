@@ -252,6 +252,30 @@ class PrefillWorkload:
                 "head_dim": self.D_, "rope": "theta 5e5, half mode, fused", "flops": "causal 4*B*Hq*D*S(S+1)/2",
                 "l2": "inputs larger than L2 (q,k,v,out = %d MB per step)" % ((2 * self.q.numel() + 2 * self.k.numel()) * 2 >> 20)}
 
+    def cpu_baseline(self):
+        """The CPU path on a bounded sample of config 3: RoPE of q and k of one batch item, then MultiHeadAttention on every 16th
+        query row of every head (the causal FLOPs of those rows are what is counted)."""
+        import oracle as O
+
+        O.build()
+        threads = os.cpu_count() or 1
+        O.set_threads(threads)
+        rng = np.random.default_rng(1)
+        S, HQ, HKV, Dh = self.S, self.HQ, self.HKV, self.D_
+        q = O.from_f32(rng.standard_normal((S, HQ * Dh), dtype=np.float32), O.BF16)
+        k = O.from_f32(rng.standard_normal((S, HKV * Dh), dtype=np.float32), O.BF16)
+        v = O.from_f32(rng.standard_normal((S, HKV * Dh), dtype=np.float32), O.BF16)
+        rows = np.repeat(np.arange(7, S, 16, dtype=np.int32), HQ)
+        heads = np.tile(np.arange(HQ, dtype=np.int32), S // 16)
+        flops = 4.0 * Dh * float((rows.astype(np.int64) + 1).sum())
+        t0 = time.perf_counter()
+        qr = O.rope(O.BF16, q, S, HQ, Dh, base=500000.0, mode=1)
+        kr = O.rope(O.BF16, k, S, HKV, Dh, base=500000.0, mode=1)
+        O.mha_rows(O.BF16, qr, kr, v, S, S, HQ, HKV, Dh, rows, heads, True)
+        dt = time.perf_counter() - t0
+        return {"value": flops / dt / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                "sample": f"one batch item: RoPE(q), RoPE(k), then every 16th query row of all {HQ} heads ({flops:.3g} causal FLOPs) in {dt:.2f} s"}
+
     def metric(self):
         return "prefill_attn_tflops", "TFLOP/s"
 
