@@ -171,7 +171,7 @@ class DecodeWorkload:
         self.cfg = MultiHeadAttentionConfig(NumHeads=HQ, HeadDim=DIM, Causal=True, KVHeadCount=HKV)
         self.bytes_per_step = decode_bytes(self.ctx, self.esize)
         # DRAM traffic (ncu dram__bytes_read + write) over algorithmic bytes, from the small-case captures summarised in
-        # profiles/paged_decode_bf16.md and profiles/paged_decode_fp8.md; traffic grows in proportion to the tokens read
+        # the profiles folder (bf16 and fp8 decode captures); traffic grows in proportion to the tokens read
         self.traffic_ratio = (317.9 + 4.6) / 316.8 if fp8 else (634.7 + 5.7) / 633.6
         self.units_per_step = self.batch  # tokens
         self.h2d = self.q_host.numel() * 2 + self.table_host.numel() * 4 + self.ctx_host.numel() * 4

@@ -34,7 +34,7 @@ class ConvertWorkload:
         self.directions = [(D.BFloat16, D.Float32), (D.Float16, D.Float32), (D.Float8E4M3, D.Float32), (D.Float8E5M2, D.Float32),
                            (D.Float32, D.BFloat16), (D.Float32, D.Float16)]
         self.bytes_per_step = sum(n * (D.SIZE[s] + D.SIZE[d]) for s, d in self.directions)
-        self.traffic_ratio = 1.0  # profiles/convert.md: every direction's DRAM bytes equal its algorithmic bytes
+        self.traffic_ratio = 1.0  # ncu launch list of the sweep: every direction's DRAM bytes equal its algorithmic bytes
         # end to end = the convert package's own call shape: host slices in, host slices out (f32 -> bf16, 2^26 elements)
         self.e2e_n = 1 << 26
         self.src_host = torch.empty(self.e2e_n, dtype=torch.float32).pin_memory()
@@ -136,7 +136,7 @@ class ChainWorkload:
         self.cfg = RMSNormConfig(1e-6)
         self.bytes_per_step_global = 2 * (3 * self.T * self.C + 2 * self.T * self.C) + 2 * (3 * self.T * self.I)
         self.bytes_per_step = self.bytes_per_step_global // world
-        # profiles/norm_swiglu_chain.md: (402.7 + 225.0 + 939.6 + 435.9) MB measured for 671.1 + 1409.3 MB algorithmic (the
+        # ncu captures of the two kernels: (402.7 + 225.0 + 939.6 + 435.9) MB measured for 671.1 + 1409.3 MB algorithmic (the
         # write counters lag the cache flush)
         self.traffic_ratio = (402.7 + 225.0 + 939.6 + 435.9) / (671.1 + 1409.3)
         self.x_host = self.x.cpu().pin_memory()
@@ -288,7 +288,7 @@ class PrefillWorkload:
     def roofline(self, sec, peaks):
         ach = self.flops / sec / 1e12
         return {"bound": "tensor", "achieved": ach, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": ach / peaks["bf16_tflops"],
-                # profiles/prefill_attention_tcgen05.md: 52.5 MB read + 4.5 MB written per batch item (K/V re-reads hit in L2)
+                # ncu capture of the batch-1 case: 52.5 MB read + 4.5 MB written per batch item (K/V re-reads hit in L2)
                 "traffic": 57.0e6 * self.B, "traffic_note": "bytes per step, scaled from the batch-1 ncu capture",
                 "peak_source": peaks["source"],
                 "note": "causal FLOPs / CUDA-event time of the step (K rotation pre-pass + attention kernel)"}
