@@ -255,7 +255,28 @@ def run_reference(args, rank, world):
         return
     fp8 = args.workload == "decode_fp8"
     if args.workload not in ("decode", "decode_fp8"):
-        print(json.dumps({"impl": "reference", "unavailable": f"reference arm implemented for the decode workloads, not {args.workload}"}))
+        # the other workloads time their own bounded CPU sample (the oracle's restatement of the same ops); the classes are
+        # not constructed (their constructors allocate on the GPU), only their constants and cpu_baseline() are used
+        import bench_workloads as W
+
+        cls, name = {"convert": (W.ConvertWorkload, "dtype_convert_sweep"), "chain": (W.ChainWorkload, "add_rmsnorm_gated_residual_swiglu"),
+                     "prefill": (W.PrefillWorkload, "prefill_causal_gqa_rope")}[args.workload]
+        wl = object.__new__(cls)
+        metric, unit = wl.metric()
+        samples = []
+        t0 = time.perf_counter()
+        for _ in range(max(args.steps, 1)):
+            samples.append(wl.cpu_baseline())
+        wall = time.perf_counter() - t0
+        value = float(np.mean([x["value"] for x in samples]))
+        base = dict(samples[-1], value=value)
+        print(json.dumps({
+            "impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": wall / max(args.steps, 1) * 1e3, "higher_is_better": True, "scaling": getattr(cls, "scaling", "weak"),
+            "vs_baseline": None, "dtype": "bf16" if args.workload != "convert" else "u8/u16/f32 bit patterns", "data": "synthetic",
+            "config": {"workload": name, "sample": base["sample"]}, "cpu_baseline": base,
+            "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0,
+            "note": "C++ restatement of puter device/cpu, not the Go binary: no Go toolchain here"}))
         return
     threads = os.cpu_count() or 1
     for _ in range(max(args.warmup, 0)):

@@ -22,9 +22,10 @@ def test_reference_arm_prints_one_contract_line():
     assert line["config"]["workload"] == "paged_decode_bf16kv"
 
 
-def test_reference_arm_declines_other_workloads_cleanly():
-    out = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--workload", "convert"],
-                         capture_output=True, text=True, timeout=600, cwd=ROOT)
-    assert out.returncode == 0
+def test_reference_arm_times_the_cpu_sample_of_the_other_workloads():
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--workload", "prefill", "--steps", "1",
+                          "--warmup", "0"], capture_output=True, text=True, timeout=900, cwd=ROOT)
+    assert out.returncode == 0, out.stderr[-2000:]
     line = json.loads([l for l in out.stdout.splitlines() if l.startswith("{")][-1])
-    assert line["impl"] == "reference" and "unavailable" in line
+    assert line["impl"] == "reference" and line["metric"] == "prefill_attn_tflops" and line["unit"] == "TFLOP/s"
+    assert line["value"] > 0 and line["cpu_baseline"]["kind"] == "port" and line["gpu_launches"] == 0
