@@ -377,6 +377,8 @@ def main():
 
     for _ in range(args.warmup):
         wl.step()
+    if hasattr(wl, "verify"):
+        wl.verify()  # untimed self-check of the multi-GPU exchange
     launches0 = dev.launch_count()
     sec, clocks = timed(wl.step, args.steps, sample_clocks=True)
     launches = dev.launch_count() - launches0

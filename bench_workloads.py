@@ -162,6 +162,19 @@ class ChainWorkload:
             for w in works:
                 w.wait()  # orders the current stream after the collective; no host block
 
+    def verify(self):
+        """Every rank draws the same seeded shard, so after the all-gathers each rank's slice of a gathered tensor must equal
+        this rank's own: checks that the in-place, overlapped gathers delivered complete data."""
+        if self.world == 1:
+            return
+        self.step()
+        self.torch.cuda.synchronize()
+        # (the gated residual depends on the modulation row of the batch item a rank's rows belong to, so only n and s compare)
+        for full, mine in ((self.n_all, self.n_out), (self.s_all, self.s_out)):
+            for r in range(self.world):
+                if not self.torch.equal(full[r * self.rows:(r + 1) * self.rows], mine):
+                    raise RuntimeError("chain workload: gathered rows of rank %d differ from the local result" % r)
+
     def step_e2e(self):
         self.x.copy_(self.x_host, non_blocking=True)
         self.step()
