@@ -190,28 +190,6 @@ __device__ __forceinline__ float ex2_approx(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
-#ifndef PF_EMU_PAIRS
-#define PF_EMU_PAIRS 0
-#endif
-// 2^x for a pair of x <= 0 on the packed f32x2 FMA pipe: round x to the nearest integer n with the 1.5 * 2^23 trick, a
-// degree-4 polynomial for 2^f on f in [-0.5, 0.5] (relative error 4e-5, far below the 16-bit rounding of P), then n is added
-// into the exponent field
-__device__ __forceinline__ uint64_t ex2_fma2(uint64_t x) {
-    float x0, x1;
-    un2(x, x0, x1);
-    x = pk2(fmaxf(x0, -126.0f), fmaxf(x1, -126.0f));
-    const uint64_t magic = pk2(12582912.0f, 12582912.0f), negMagic = pk2(-12582912.0f, -12582912.0f);
-    const uint64_t t = add2(x, magic);
-    const uint64_t f = add2(x, mul2(add2(t, negMagic), pk2(-1.0f, -1.0f)));
-    uint64_t r = fma2(f, pk2(0.0096181291f, 0.0096181291f), pk2(0.0555041087f, 0.0555041087f));
-    r = fma2(f, r, pk2(0.2402265070f, 0.2402265070f));
-    r = fma2(f, r, pk2(0.6931471806f, 0.6931471806f));
-    r = fma2(f, r, pk2(1.0f, 1.0f));
-    float r0, r1, t0, t1;
-    un2(r, r0, r1);
-    un2(t, t0, t1);
-    return pk2(__int_as_float(__float_as_int(r0) + (__float_as_int(t0) << 23)), __int_as_float(__float_as_int(r1) + (__float_as_int(t1) << 23)));
-}
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
     float d;
     asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
@@ -562,8 +540,8 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const __grid_const
             float sum4[4] = {0.f, 0.f, 0.f, 0.f};
             // scale-and-shift and the row sums run two elements at a time on the packed f32x2 pipe (same roundings as the
             // scalar fused multiply-add / add); every exponential runs on the special-function unit (moving a quarter of
-            // them to a polynomial on the FMA pipe, packed or not, never paid: the softmax warps sit at the register limit
-            // and one warp per scheduler hides little latency, so extra instructions cost more than the unit's queue).
+            // them to a polynomial on the FMA pipe, packed or not, never paid, with 168 or with 200 registers per thread:
+            // one warp per scheduler hides little latency, so the extra instructions cost more than the unit's queue).
             // P is packed in place (word i receives elements 2i and 2i+1, consumed by then) and written over the first 64
             // columns of S in two halves of 64 keys, each handed to the MMA warp as soon as it is stored, so the first half
             // of the P V product overlaps the second half of the exponentials.
@@ -576,8 +554,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const __grid_const
                 float x0, x1, x2, x3;
                 un2(X01, x0, x1);
                 un2(X23, x2, x3);
-                const uint64_t E01 = pk2(ex2_approx(x0), ex2_approx(x1));
-                const uint64_t E23 = (((i >> 1) & 3) < PF_EMU_PAIRS) ? ex2_fma2(X23) : pk2(ex2_approx(x2), ex2_approx(x3));
+                const uint64_t E01 = pk2(ex2_approx(x0), ex2_approx(x1)), E23 = pk2(ex2_approx(x2), ex2_approx(x3));
                 sumA = add2(sumA, E01);
                 sumB = add2(sumB, E23);
                 float e0, e1, e2, e3;
