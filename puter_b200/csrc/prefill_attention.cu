@@ -5,9 +5,11 @@
 // score = dot(q,k) * 1/sqrt(D), softmax over the visible keys, out = sum_k p[k] v[k], stored with round-to-nearest-even.
 //
 // Shape of the kernel (head_dim 128, 16-bit inputs):
-//   * one CTA owns two tiles of 128 query rows of one (batch, query head); heavy (late) tiles are scheduled first;
-//   * a TMA warp streams 128-key K and V tiles through a 2-stage shared-memory ring (SWIZZLE_128B boxes of 64 x 128),
-//     each tile serving both query tiles;
+//   * a work item is two tiles of 128 query rows of one (batch, query head); the grid is persistent (one CTA per SM), items
+//     are numbered heavy (late rows) first and dealt to the CTAs in serpentine order, so a CTA pays launch, TMEM allocation
+//     and barrier set-up once and the next item's Q tiles are loaded while the current item finishes;
+//   * a TMA warp streams 128-key K and V tiles through a 2-stage shared-memory ring (SWIZZLE_128B boxes of 64 x 128) that
+//     runs on across items, each tile serving both query tiles;
 //   * one elected lane of the MMA warp issues tcgen05.mma (kind::f16, M=128, N=128, K=16):  S = Q K^T into TMEM,
 //     then O += P V with P read back from TMEM as the A operand and V as an MN-major B operand; the two query tiles
 //     take turns (a turn = the P V product of the tile's step and the score product of its next step, 16 MMAs back to
@@ -38,7 +40,8 @@ constexpr uint32_t kHalfTile = kTileBytes / 2;         // one 64-column swizzled
 constexpr uint32_t kSmemQ = 0;
 constexpr uint32_t kSmemK = kSmemQ + 2 * kTileBytes;  // two query tiles
 constexpr uint32_t kSmemV = kSmemK + kStages * kTileBytes;
-constexpr uint32_t kSmemBar = kSmemV + kStages * kTileBytes;
+constexpr uint32_t kSmemStage = kSmemV + kStages * kTileBytes;  // output staging tile (shared by the two query tiles in turn)
+constexpr uint32_t kSmemBar = kSmemStage + kTileBytes;
 constexpr uint32_t kSmemTotal = kSmemBar + 256 + 1024;  // + alignment slack
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColS = 0, kColO = 256;  // S0 S1 O0 O1, 128 columns each
@@ -183,7 +186,7 @@ template <bool BF16> __device__ __forceinline__ uint32_t narrow16(float f) {
 
 // barrier slots (8 bytes each) inside the barrier area; [2] = one per query tile of the CTA
 enum : uint32_t { BAR_Q = 0, BAR_QREADY = 2, BAR_K_FULL = 4, BAR_K_EMPTY = 6, BAR_V_FULL = 8, BAR_V_EMPTY = 10, BAR_S = 12, BAR_P = 14,
-                  BAR_O = 16, BAR_P2 = 18, BAR_COUNT = 20 };
+                  BAR_O = 16, BAR_P2 = 18, BAR_QFREE = 20, BAR_STAGED = 22, BAR_STGFREE = 24, BAR_COUNT = 25 };
 
 __device__ __forceinline__ float ex2_approx(float x) {
     float y;
@@ -276,8 +279,23 @@ __device__ __forceinline__ void rotate_q_tile(unsigned char* tile, int warpInGro
     }
 }
 
-// One CTA = two 128-row query tiles (rows q0 .. q0+255) of one (batch, head).  Warps 0-3 / 4-7 are the softmax
-// groups of tile 0 / 1, warp 8 issues the MMAs, warp 9 drives TMA.  TMEM columns: S0 0-127, S1 128-255, O0 256-383,
+// Fetch the table rows, wait for the Q tile, rotate it.  Its own function (not inlined) so that the 128 table registers are
+// allocated apart from the softmax loop of the caller (128 live scores per thread).
+template <bool BF16>
+__device__ __noinline__ bool rotate_q_when_loaded(unsigned char* tile, int warpInGroup, int lane, int ropeMode, const float* table, int seqLen,
+                                                   int pos0, uint32_t barQ, uint32_t parity, volatile int* abortFlag) {
+    float4 tab[32];
+    rotate_q_fetch(tab, warpInGroup, lane, ropeMode, table, seqLen, pos0);
+    const bool okay = __all_sync(0xffffffffu, mbar_wait(barQ, parity, abortFlag));
+    if (okay) {
+        rotate_q_tile<BF16>(tile, warpInGroup, lane, ropeMode, tab, seqLen, pos0);
+        __syncwarp();
+    }
+    return okay;
+}
+
+// A work item = two 128-row query tiles (rows q0 .. q0+255) of one (batch, head); a CTA works through its share of the
+// items.  Warps 0-3 / 4-7 are the softmax groups of tile 0 / 1, warp 8 issues the MMAs, warp 9 drives TMA.  TMEM columns: S0 0-127, S1 128-255, O0 256-383,
 // O1 384-511; P_t overwrites the first 64 columns of S_t (each thread rewrites only the row it has already read).
 // MMA order in steady state: PV0(j), QK0(j+1), PV1(j), QK1(j+1): each softmax group works while the tensor core
 // runs the other tile's two products.
@@ -295,23 +313,34 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const __grid_const
     // warp index through a shuffle: the compiler then knows it is warp-uniform (and with it everything the MMA warp derives
     // from it), which lets the MMA descriptors live in uniform registers
     const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
-    // heavy (late) query tiles first; consecutive CTAs share a KV head so K/V tiles hit in L2
-    const int numPairs = (p.seqLen + 2 * kBM - 1) / (2 * kBM);
-    const int perPair = p.numHeads * p.batch;
-    const int pairIdx = numPairs - 1 - (int)(blockIdx.x / perPair);
-    const int rem = (int)(blockIdx.x % perPair);
-    const int head = rem % p.numHeads, b = rem / p.numHeads;
-    const int kvHead = head / (p.numHeads / p.kvHeads);
-    const int q0 = pairIdx * 2 * kBM;
-    // number of key tiles each query tile needs
-    int nT[2];
-#pragma unroll
-    for (int t = 0; t < 2; t++) {
-        const int qs = q0 + t * kBM;
-        const int lastKey = p.causal ? min(p.seqLen, qs + kBM) : p.seqLen;
-        nT[t] = qs < p.seqLen ? (lastKey + kBN - 1) / kBN : 0;
-    }
-    const int nMax = max(nT[0], nT[1]);
+    // Work items (the two query tiles of one (batch, head, 256-row block)) are numbered heavy (late rows) first, consecutive
+    // items sharing a KV head so K/V tiles hit in L2.  The grid is persistent: the resident CTAs are dealt items in serpentine
+    // order (0..G-1, G-1..0, ...), which gives every CTA the same mix of long and short items; TMEM, the barriers and the K/V
+    // ring live across items, and a CTA pays launch, allocation and barrier set-up once.
+    struct Item { int head, b, kvHead, q0, nMax, nT0, nT1; };  // nT0 / nT1: key tiles query tile 0 / 1 needs
+    // Decoded from the launch parameters on every call, behind an opaque copy of the item number: the softmax threads sit
+    // at the register limit, and anything precomputed here would stay live across their main loop.
+    auto get_item = [&](int it, Item& w) -> bool {
+        asm volatile("" : "+r"(it));
+        const int numPairs = (p.seqLen + 2 * kBM - 1) / (2 * kBM);
+        const int perPair = p.numHeads * p.batch;
+        const int G = (int)gridDim.x;
+        const int idx = it * G + ((it & 1) ? G - 1 - (int)blockIdx.x : (int)blockIdx.x);
+        if (idx >= numPairs * perPair) return false;
+        const int rem = idx % perPair;
+        w.head = rem % p.numHeads;
+        w.b = rem / p.numHeads;
+        w.kvHead = w.head / (p.numHeads / p.kvHeads);
+        w.q0 = (numPairs - 1 - idx / perPair) * 2 * kBM;
+        auto tiles_for = [&](int qs) {
+            const int lastKey = p.causal ? min(p.seqLen, qs + kBM) : p.seqLen;
+            return qs < p.seqLen ? (lastKey + kBN - 1) / kBN : 0;
+        };
+        w.nT0 = tiles_for(w.q0);
+        w.nT1 = tiles_for(w.q0 + kBM);
+        w.nMax = max(w.nT0, w.nT1);
+        return true;
+    };
 
     if (threadIdx.x == 0) {
         abortShared = 0;
@@ -322,7 +351,10 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const __grid_const
             mbar_init(bar(BAR_P + t), 128);
             mbar_init(bar(BAR_P2 + t), 128);
             mbar_init(bar(BAR_O + t), 1);
+            mbar_init(bar(BAR_QFREE + t), 1);
+            mbar_init(bar(BAR_STAGED + t), 128);
         }
+        mbar_init(bar(BAR_STGFREE), 1);
         for (int s = 0; s < kStages; s++) {
             mbar_init(bar(BAR_K_FULL + s), 1);
             mbar_init(bar(BAR_K_EMPTY + s), 1);
@@ -351,27 +383,53 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const __grid_const
     } else if (warp == 9) {
         // ------------------------------------------------ TMA producer ------------------------------------------------
         if (lane == 0) {
-            for (int t = 0; t < 2; t++) {
-                if (nT[t] == 0) continue;
-                mbar_expect_tx(bar(BAR_Q + t), kTileBytes);
-                tma_load_4d(sBase + kSmemQ + t * kTileBytes, &p.tmQ, bar(BAR_Q + t), 0, head, q0 + t * kBM, b);
-                tma_load_4d(sBase + kSmemQ + t * kTileBytes + kHalfTile, &p.tmQ, bar(BAR_Q + t), 64, head, q0 + t * kBM, b);
-            }
-            // K and V rings are released separately: a K stage is free as soon as both score products of its tile
-            // have run, a V stage after both P V products, so the next K tile is in flight a whole period early
-            for (int j = 0; j < nMax; j++) {
-                const int st = j % kStages;
-                const uint32_t par = ((j / kStages) - 1) & 1;
-                if (j >= kStages && !mbar_wait(bar(BAR_K_EMPTY + st), par, abortFlag)) { *abortFlag = 1; break; }
+            uint32_t lc = 0;        // ring position of key tile 0 of the current item: the K/V ring runs on across items
+            uint32_t uc[2] = {};    // items each query tile took part in so far
+            bool okay = true;
+            Item w = {};
+            auto load_k = [&](int j) {
+                const uint32_t ring = lc + (uint32_t)j;
+                const int st = ring % kStages;
+                if (ring >= kStages && !mbar_wait(bar(BAR_K_EMPTY + st), ((ring / kStages) - 1) & 1, abortFlag)) return false;
                 mbar_expect_tx(bar(BAR_K_FULL + st), kTileBytes);
-                const uint32_t kDst = sBase + kSmemK + st * kTileBytes, vDst = sBase + kSmemV + st * kTileBytes;
-                tma_load_4d(kDst, &p.tmK, bar(BAR_K_FULL + st), 0, kvHead, j * kBN, b);
-                tma_load_4d(kDst + kHalfTile, &p.tmK, bar(BAR_K_FULL + st), 64, kvHead, j * kBN, b);
-                if (j >= kStages && !mbar_wait(bar(BAR_V_EMPTY + st), par, abortFlag)) { *abortFlag = 1; break; }
+                const uint32_t kDst = sBase + kSmemK + st * kTileBytes;
+                tma_load_4d(kDst, &p.tmK, bar(BAR_K_FULL + st), 0, w.kvHead, j * kBN, w.b);
+                tma_load_4d(kDst + kHalfTile, &p.tmK, bar(BAR_K_FULL + st), 64, w.kvHead, j * kBN, w.b);
+                return true;
+            };
+            auto load_v = [&](int j) {
+                const uint32_t ring = lc + (uint32_t)j;
+                const int st = ring % kStages;
+                if (ring >= kStages && !mbar_wait(bar(BAR_V_EMPTY + st), ((ring / kStages) - 1) & 1, abortFlag)) return false;
                 mbar_expect_tx(bar(BAR_V_FULL + st), kTileBytes);
-                tma_load_4d(vDst, &p.tmV, bar(BAR_V_FULL + st), 0, kvHead, j * kBN, b);
-                tma_load_4d(vDst + kHalfTile, &p.tmV, bar(BAR_V_FULL + st), 64, kvHead, j * kBN, b);
+                const uint32_t vDst = sBase + kSmemV + st * kTileBytes;
+                tma_load_4d(vDst, &p.tmV, bar(BAR_V_FULL + st), 0, w.kvHead, j * kBN, w.b);
+                tma_load_4d(vDst + kHalfTile, &p.tmV, bar(BAR_V_FULL + st), 64, w.kvHead, j * kBN, w.b);
+                return true;
+            };
+            auto load_q = [&](int t) {
+                if ((t == 0 ? w.nT0 : w.nT1) == 0) return true;
+                // the buffer is free once the last score product of the tile's previous item has run
+                if (uc[t] > 0 && !mbar_wait(bar(BAR_QFREE + t), (uc[t] - 1) & 1, abortFlag)) return false;
+                uc[t]++;
+                mbar_expect_tx(bar(BAR_Q + t), kTileBytes);
+                tma_load_4d(sBase + kSmemQ + t * kTileBytes, &p.tmQ, bar(BAR_Q + t), 0, w.head, w.q0 + t * kBM, w.b);
+                tma_load_4d(sBase + kSmemQ + t * kTileBytes + kHalfTile, &p.tmQ, bar(BAR_Q + t), 64, w.head, w.q0 + t * kBM, w.b);
+                return true;
+            };
+            // K and V rings are released separately: a K stage is free as soon as both score products of its tile have run,
+            // a V stage after both P V products, so the next K tile is in flight a whole period early.  One thread issues
+            // every load and each wait blocks it, so the loads of an item are ordered by the time their buffers come free
+            // at the end of the previous item: K stage of key tile 0, Q buffer 0 (after tile 0's last score product), V stage
+            // of key tile 0, Q buffer 1, then the rest of the ring.  The very first item has nothing to wait for and starts
+            // with Q.
+            for (int it = 0; okay && get_item(it, w); it++) {
+                if (it == 0) okay = load_q(0) && load_k(0) && load_q(1) && load_v(0);
+                else okay = load_k(0) && load_q(0) && load_v(0) && load_q(1);
+                for (int j = 1; j < w.nMax && okay; j++) okay = load_k(j) && load_v(j);
+                lc += (uint32_t)w.nMax;
             }
+            if (!okay) *abortFlag = 1;
         }
     } else if (warp == 8) {
         // ------------------------------------------------ MMA issuer --------------------------------------------------
@@ -394,8 +452,12 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const __grid_const
             const uint32_t qLo = (uint32_t)make_desc(sBase + kSmemQ, 16, 1024), kLo = (uint32_t)make_desc(sBase + kSmemK, 16, 1024);
             const uint32_t vLo = (uint32_t)make_desc(sBase + kSmemV, p.vLBO, p.vSBO);
             auto desc = [](uint64_t hi, uint32_t lo) { return (hi << 32) | (uint64_t)lo; };
+            uint32_t lc = 0;        // ring position of key tile 0 of the current item
+            uint32_t sc[2] = {};    // key-tile steps each query tile has run so far (parity of its S / P barriers)
+            uint32_t uc[2] = {};    // items each query tile took part in so far (parity of its Q / O barriers)
+            int nT[2] = {};
             auto issue_qk = [&](int t, int j) {
-                const uint32_t kS = kLo + (uint32_t)(j % kStages) * (kTileBytes >> 4);
+                const uint32_t kS = kLo + ((lc + (uint32_t)j) % kStages) * (kTileBytes >> 4);
                 const uint32_t qS = qLo + (uint32_t)t * (kTileBytes >> 4);
                 const uint32_t dS = tmem + kColS + t * 128;
 #pragma unroll
@@ -405,19 +467,20 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const __grid_const
                 }
                 if (leader) {
                     mma_commit(bar(BAR_S + t));
+                    if (j + 1 == nT[t]) mma_commit(bar(BAR_QFREE + t));  // the Q tile is no longer read
                     // last score product that reads this K stage (tile 1 while it is still running, else tile 0)
-                    if (t == 1 || j >= nT[1]) mma_commit(bar(BAR_K_EMPTY + j % kStages));
+                    if (t == 1 || j >= nT[1]) mma_commit(bar(BAR_K_EMPTY + (lc + (uint32_t)j) % kStages));
                 }
                 __syncwarp();
             };
             auto issue_pv = [&](int t, int j) {
-                const uint32_t vS = vLo + (uint32_t)(j % kStages) * (kTileBytes >> 4);
+                const uint32_t vS = vLo + ((lc + (uint32_t)j) % kStages) * (kTileBytes >> 4);
                 const uint32_t dO = tmem + kColO + t * 128, aP = tmem + kColS + t * 128;
                 if (leader) mma_ts(dO, aP, desc(vHi, vS), idescPV, j > 0);
 #pragma unroll
                 for (int kk = 1; kk < 4; kk++)
                     if (leader) mma_ts(dO, aP + kk * 8, desc(vHi, vS + ((kk * 16 * 128) >> 4)), idescPV, 1);
-                if (!mbar_wait(bar(BAR_P2 + t), j & 1, abortFlag)) return false;  // second half of P (keys 64..127)
+                if (!mbar_wait(bar(BAR_P2 + t), (sc[t] + (uint32_t)j) & 1, abortFlag)) return false;  // second half of P (keys 64..127)
                 fence_after();
 #pragma unroll
                 for (int kk = 4; kk < 8; kk++)
@@ -425,38 +488,51 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const __grid_const
                 __syncwarp();
                 return true;
             };
-            // first scores of both tiles
-            for (int t = 0; t < 2 && okay; t++) {
-                if (nT[t] == 0) continue;
-                okay = mbar_wait(bar(BAR_QREADY + t), 0, abortFlag);
-                if (okay) okay = mbar_wait(bar(BAR_K_FULL + 0), 0, abortFlag);
-                if (!okay) break;
-                fence_after();
-                issue_qk(t, 0);
-            }
-            for (int j = 0; j < nMax && okay; j++) {
-                const int st = j % kStages;
+            Item w = {};
+            for (int it = 0; okay && get_item(it, w); it++) {
+                nT[0] = w.nT0;
+                nT[1] = w.nT1;
+                const int nMax = w.nMax;
+                // first scores of both tiles (a tile's softmax group is past the previous item's epilogue when it hands
+                // over the first P, which is what the first P V product waits for before it overwrites O)
                 for (int t = 0; t < 2 && okay; t++) {
-                    if (j >= nT[t]) continue;
-                    PF_STAMP(2048 + 512 * t + j * 8 + 0);
-                    if (t == 0 || j >= nT[0]) {  // (tile 1 finds the stages its neighbour has already waited for)
-                        okay = mbar_wait(bar(BAR_V_FULL + st), (j / kStages) & 1, abortFlag);
-                        if (okay && j + 1 < nMax) okay = mbar_wait(bar(BAR_K_FULL + (j + 1) % kStages), ((j + 1) / kStages) & 1, abortFlag);
-                    }
-                    PF_STAMP(2048 + 512 * t + j * 8 + 1);
-                    if (okay) okay = mbar_wait(bar(BAR_P + t), j & 1, abortFlag);
+                    if (nT[t] == 0) continue;
+                    okay = mbar_wait(bar(BAR_QREADY + t), uc[t] & 1, abortFlag);
+                    if (okay) okay = mbar_wait(bar(BAR_K_FULL + lc % kStages), (lc / kStages) & 1, abortFlag);
                     if (!okay) break;
                     fence_after();
-                    PF_STAMP(2048 + 512 * t + j * 8 + 2);
-                    okay = issue_pv(t, j);
-                    if (!okay) break;
-                    PF_STAMP(2048 + 512 * t + j * 8 + 3);
-                    if (j + 1 < nT[t]) issue_qk(t, j + 1);
-                    else if (leader) mma_commit(bar(BAR_O + t));
-                    // last product that reads this V stage (tile 1 while it is still running, else tile 0)
-                    if (leader && (t == 1 || j >= nT[1])) mma_commit(bar(BAR_V_EMPTY + st));
-                    __syncwarp();
-                    PF_STAMP(2048 + 512 * t + j * 8 + 4);
+                    issue_qk(t, 0);
+                }
+                for (int j = 0; j < nMax && okay; j++) {
+                    const uint32_t ring = lc + (uint32_t)j;
+                    const int st = ring % kStages;
+                    for (int t = 0; t < 2 && okay; t++) {
+                        if (j >= nT[t]) continue;
+                        PF_STAMP(2048 + 512 * t + j * 8 + 0);
+                        if (t == 0 || j >= nT[0]) {  // (tile 1 finds the stages its neighbour has already waited for)
+                            okay = mbar_wait(bar(BAR_V_FULL + st), (ring / kStages) & 1, abortFlag);
+                            if (okay && j + 1 < nMax) okay = mbar_wait(bar(BAR_K_FULL + (ring + 1) % kStages), ((ring + 1) / kStages) & 1, abortFlag);
+                        }
+                        PF_STAMP(2048 + 512 * t + j * 8 + 1);
+                        if (okay) okay = mbar_wait(bar(BAR_P + t), (sc[t] + (uint32_t)j) & 1, abortFlag);
+                        if (!okay) break;
+                        fence_after();
+                        PF_STAMP(2048 + 512 * t + j * 8 + 2);
+                        okay = issue_pv(t, j);
+                        if (!okay) break;
+                        PF_STAMP(2048 + 512 * t + j * 8 + 3);
+                        if (j + 1 < nT[t]) issue_qk(t, j + 1);
+                        else if (leader) mma_commit(bar(BAR_O + t));
+                        // last product that reads this V stage (tile 1 while it is still running, else tile 0)
+                        if (leader && (t == 1 || j >= nT[1])) mma_commit(bar(BAR_V_EMPTY + st));
+                        __syncwarp();
+                        PF_STAMP(2048 + 512 * t + j * 8 + 4);
+                    }
+                }
+                lc += (uint32_t)nMax;
+                for (int t = 0; t < 2; t++) {
+                    sc[t] += (uint32_t)nT[t];
+                    uc[t] += nT[t] > 0 ? 1u : 0u;
                 }
             }
             if (!okay) *abortFlag = 1;
@@ -466,32 +542,36 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const __grid_const
         asm volatile("setmaxnreg.inc.sync.aligned.u32 200;");
         const int t = warp >> 2;                  // query tile of this group
         const int row = threadIdx.x & 127;        // TMEM lane = query row within the tile
-        const int qPos = q0 + t * kBM + row;
         const uint32_t laneBase = tmem + ((uint32_t)((warp & 3) * 32) << 16);
         const uint32_t colS = kColS + t * 128, colO = kColO + t * 128;
-        const int n = nT[t];
+        const float scale = p.scaleLog2;
         bool okay = true;
-        if (n > 0) {
-            const bool rotate = p.ropeMode != 2 && p.ropeTable != nullptr;
-            float4 tab[32];
-            if (rotate) rotate_q_fetch(tab, warp & 3, lane, p.ropeMode, p.ropeTable, p.seqLen, q0 + t * kBM);
-            okay = __all_sync(0xffffffffu, mbar_wait(bar(BAR_Q + t), 0, abortFlag));
-            if ((threadIdx.x & 127) == 0) PF_STAMP(3000 + 8 * t + 2);
-            if (okay && rotate) {
-                rotate_q_tile<BF16>(smem + kSmemQ + t * kTileBytes, warp & 3, lane, p.ropeMode, tab, p.seqLen, q0 + t * kBM);
-                __syncwarp();
-            }
-            if ((threadIdx.x & 127) == 0) PF_STAMP(3000 + 8 * t + 3);
+        uint32_t sc = 0, uc = 0;  // parities of the key-tile steps / items this group has run so far (barrier phases)
+#pragma unroll 1
+        for (int it = 0; okay; it++) {
+        int n, q0;
+        {
+            Item w;
+            if (!get_item(it, w)) break;
+            n = t == 0 ? w.nT0 : w.nT1;
+            q0 = w.q0;
+        }
+        if (n == 0) continue;
+        const int qPos = q0 + t * kBM + row;
+        {
+            if (p.ropeMode != 2 && p.ropeTable != nullptr)
+                okay = rotate_q_when_loaded<BF16>(smem + kSmemQ + t * kTileBytes, warp & 3, lane, p.ropeMode, p.ropeTable, p.seqLen,
+                                                  q0 + t * kBM, bar(BAR_Q + t), uc & 1, abortFlag);
+            else
+                okay = __all_sync(0xffffffffu, mbar_wait(bar(BAR_Q + t), uc & 1, abortFlag));
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the tensor core
             mbar_arrive(bar(BAR_QREADY + t));
-            if ((threadIdx.x & 127) == 0) PF_STAMP(3000 + 8 * t + 4);
         }
         float mUsed = -INFINITY;   // the maximum the stored P and O are relative to (scaled, log2 domain)
         float lsum = 0.f;
-        const float scale = p.scaleLog2;
         for (int j = 0; j < n && okay; j++) {
             if ((threadIdx.x & 127) == 0) PF_STAMP(1024 * t + j * 8 + 0);
-            okay = __all_sync(0xffffffffu, mbar_wait(bar(BAR_S + t), j & 1, abortFlag));  // keeps the warp convergent
+            okay = __all_sync(0xffffffffu, mbar_wait(bar(BAR_S + t), (sc ^ (uint32_t)j) & 1, abortFlag));  // keeps the warp convergent
             if (!okay) break;
             fence_after();
             if ((threadIdx.x & 127) == 0) PF_STAMP(1024 * t + j * 8 + 1);
@@ -584,15 +664,17 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const __grid_const
             if ((threadIdx.x & 127) == 0) PF_STAMP(1024 * t + j * 8 + 5);
         }
         // epilogue: wait for the last P V product of this tile, normalise and store
-        if (n > 0) {
-            if (okay) okay = __all_sync(0xffffffffu, mbar_wait(bar(BAR_O + t), 0, abortFlag));
+        {
+            if (okay) okay = __all_sync(0xffffffffu, mbar_wait(bar(BAR_O + t), uc & 1, abortFlag));
+            // Stage the normalised rows in the swizzled box layout and let TMA write them out as two 64-column boxes:
+            // coalesced, asynchronous, and clipped at the end of the sequence by the tensor map.  The staging tile is shared
+            // by the groups in turn (tile 0, tile 1, tile 0 of the next item, ...): STGFREE completes one phase per release,
+            // so tile 0 waits for an odd phase (none before its first item) and tile 1 for an even one.
+            if (okay && (t == 1 || it > 0)) okay = __all_sync(0xffffffffu, mbar_wait(bar(BAR_STGFREE), t == 0 ? 1u : 0u, abortFlag));
             if (okay) {
                 fence_after();
                 const float inv = lsum > 0.f ? 1.0f / lsum : 0.f;
-                // The Q tile of this group is no longer read (all its MMAs have completed): stage the normalised rows there
-                // in the swizzled box layout and let TMA write them out as two 64-column boxes — coalesced, asynchronous,
-                // and clipped at the end of the sequence by the tensor map.
-                unsigned char* stage = smem + kSmemQ + t * kTileBytes + row * 128;
+                unsigned char* stage = smem + kSmemStage + row * 128;
 #pragma unroll 1
                 for (int c = 0; c < 4; c++) {
                     uint32_t oreg[32];
@@ -609,18 +691,32 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const __grid_const
                     }
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                asm volatile("bar.sync %0, 128;" ::"r"(1 + t) : "memory");  // the 128 threads of this group
+                // every row of the group is staged (a counted barrier with a bounded wait, not bar.sync, so that a group that
+                // lost a warp to an expired wait cannot hang); then one thread stores the tile and, once the store has read
+                // shared memory, passes the staging tile on
+                mbar_arrive(bar(BAR_STAGED + t));
                 if (row == 0) {
-                    const uint32_t src = sBase + kSmemQ + t * kTileBytes;
-                    tma_store_4d(&p.tmO, src, 0, head, q0 + t * kBM, b);
-                    tma_store_4d(&p.tmO, src + kHalfTile, 64, head, q0 + t * kBM, b);
-                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-                    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // shared memory must outlive the read
+                    if (mbar_wait(bar(BAR_STAGED + t), uc & 1, abortFlag)) {
+                        Item w;
+                        get_item(it, w);
+                        const uint32_t src = sBase + kSmemStage;
+                        tma_store_4d(&p.tmO, src, 0, w.head, w.q0 + t * kBM, w.b);
+                        tma_store_4d(&p.tmO, src + kHalfTile, 64, w.head, w.q0 + t * kBM, w.b);
+                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // shared memory must outlive the read
+                        mbar_arrive(bar(BAR_STGFREE));
+                        if (t == 0 && w.nT1 == 0) mbar_arrive(bar(BAR_STGFREE));  // no second tile in this item: its turn too
+                    } else {
+                        *abortFlag = 1;
+                    }
                 }
             } else {
                 *abortFlag = 1;
             }
         }
+        sc ^= (uint32_t)n;
+        uc ^= 1u;
+        }  // items
     }
     // ---------------------------------------------------- teardown ----------------------------------------------------
     fence_before();
@@ -762,7 +858,8 @@ int launch_prefill(Context* ctx, int dt, const void* q, const void* k, const voi
     p.trace = nullptr;
     if (const char* e = getenv("PUTER_TRACE_PTR")) p.trace = (long long*)strtoull(e, nullptr, 0);
 #endif
-    dim3 grid(((seqLen + 2 * pf::kBM - 1) / (2 * pf::kBM)) * numHeads * batch);
+    unsigned items = ((seqLen + 2 * pf::kBM - 1) / (2 * pf::kBM)) * numHeads * batch;
+    dim3 grid(items < (unsigned)ctx->smCount ? items : (unsigned)ctx->smCount);  // persistent: one CTA per SM (shared memory allows no more)
 #define PF_LAUNCH(B)                                                                                                           \
     do {                                                                                                                       \
         cudaFuncSetAttribute(pf::prefill_kernel<B>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pf::kSmemTotal);      \
