@@ -34,7 +34,7 @@ constexpr int kD = 128;          // head dimension
 constexpr int kBM = 128;         // query rows per CTA
 constexpr int kBN = 128;         // keys per tile
 constexpr int kStages = 2;
-constexpr int kThreads = 384;     // warps 0-3 / 4-7 softmax of query tile 0 / 1, warp 8 MMA, warp 9 TMA, warps 10-11 idle    // warps 0-3 / 4-7 softmax of query tile 0 / 1, warp 8 MMA, warp 9 TMA
+constexpr int kThreads = 384;     // warps 0-3 / 4-7 softmax of query tile 0 / 1, warp 8 MMA, warp 9 TMA loads, warps 10 / 11 output stores    // warps 0-3 / 4-7 softmax of query tile 0 / 1, warp 8 MMA, warp 9 TMA
 constexpr uint32_t kTileBytes = kBN * kD * 2;          // one K or V tile: 32 KB
 constexpr uint32_t kHalfTile = kTileBytes / 2;         // one 64-column swizzled block: 16 KB
 constexpr uint32_t kSmemQ = 0;
@@ -375,11 +375,34 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const __grid_const
     // Register reallocation between warpgroups (first thing inside each group's branch, so that the compiler sees which code
     // runs under which budget): a CTA of 3 warps per scheduler is limited to 168 registers per thread, which left the softmax
     // threads (128 scores live per thread) no room to overlap the FMA -> exp2 -> add chains of different elements.  The MMA /
-    // TMA warpgroup (warps 8-11; 10 and 11 exist only to complete the group) drops to 96 registers, the two softmax warpgroups
+    // TMA warpgroup (warps 8-11) drops to 96 registers, the two softmax warpgroups
     // rise to 200: 6 % more throughput and no spills.
     if (warp >= 8) asm volatile("setmaxnreg.dec.sync.aligned.u32 96;");
     if (warp >= 10) {
-        // (idle)
+        // ------------------------------------------------ output stores -----------------------------------------------
+        // Warp 10 / 11 writes the staged output tile of query tile 0 / 1 with TMA and, once the store has read shared memory,
+        // passes the staging tile on.  A softmax thread doing this made its whole warp (and, through the QREADY barrier, its
+        // whole group) wait ~1.5 us per item for the store before it could start on the next item.
+        const int t = warp - 10;
+        if (lane == 0) {
+            uint32_t uc = 0;  // parity of the items this tile took part in so far
+            bool okay = true;
+            Item w = {};
+            for (int it = 0; okay && get_item(it, w); it++) {
+                if ((t == 0 ? w.nT0 : w.nT1) == 0) continue;
+                okay = mbar_wait(bar(BAR_STAGED + t), uc & 1, abortFlag);  // every row staged, made visible to the async proxy
+                if (!okay) break;
+                const uint32_t src = sBase + kSmemStage;
+                tma_store_4d(&p.tmO, src, 0, w.head, w.q0 + t * kBM, w.b);
+                tma_store_4d(&p.tmO, src + kHalfTile, 64, w.head, w.q0 + t * kBM, w.b);
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // shared memory must outlive the read
+                mbar_arrive(bar(BAR_STGFREE));
+                if (t == 0 && w.nT1 == 0) mbar_arrive(bar(BAR_STGFREE));  // no second tile in this item: its turn too
+                uc ^= 1u;
+            }
+            if (!okay) *abortFlag = 1;
+        }
     } else if (warp == 9) {
         // ------------------------------------------------ TMA producer ------------------------------------------------
         if (lane == 0) {
@@ -691,25 +714,8 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const __grid_const
                     }
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                // every row of the group is staged (a counted barrier with a bounded wait, not bar.sync, so that a group that
-                // lost a warp to an expired wait cannot hang); then one thread stores the tile and, once the store has read
-                // shared memory, passes the staging tile on
+                // every row of the group is staged: the store warp of this tile (counted barrier, bounded wait) takes it from here
                 mbar_arrive(bar(BAR_STAGED + t));
-                if (row == 0) {
-                    if (mbar_wait(bar(BAR_STAGED + t), uc & 1, abortFlag)) {
-                        Item w;
-                        get_item(it, w);
-                        const uint32_t src = sBase + kSmemStage;
-                        tma_store_4d(&p.tmO, src, 0, w.head, w.q0 + t * kBM, w.b);
-                        tma_store_4d(&p.tmO, src + kHalfTile, 64, w.head, w.q0 + t * kBM, w.b);
-                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-                        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // shared memory must outlive the read
-                        mbar_arrive(bar(BAR_STGFREE));
-                        if (t == 0 && w.nT1 == 0) mbar_arrive(bar(BAR_STGFREE));  // no second tile in this item: its turn too
-                    } else {
-                        *abortFlag = 1;
-                    }
-                }
             } else {
                 *abortFlag = 1;
             }
