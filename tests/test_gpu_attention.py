@@ -268,3 +268,34 @@ def test_prefill_config3_full_size_on_a_row_sample(d):
     # size-independent property: row 0 attends only to key 0, so out[0] == v[0] of its KV head, exactly
     v0 = v[:, 0, :].reshape(B, HKV, D_)
     assert np.array_equal(got[:, 0, :].reshape(B, HQ, D_), np.repeat(v0, HQ // HKV, axis=1))
+
+
+@pytest.mark.parametrize("batch,seq,hq,hkv,causal,mode", [(3, 1000, 16, 4, True, 1), (3, 1000, 16, 4, True, 0), (2, 640, 32, 8, False, None),
+                                                        (5, 520, 32, 8, True, 1)])
+def test_prefill_persistent_grid_many_items_per_cta(d, batch, seq, hq, hkv, causal, mode):
+    """More (batch, head, row block) items than SMs, ragged last tiles, with and without fused RoPE: every CTA of the persistent
+    grid runs several items back to back (barrier phases, K/V ring and staging tile carried across items).  Checked on a row
+    sample of every batch item against the CPU semantics."""
+    import puter_b200
+
+    dim, dt = 128, O.BF16
+    rng = np.random.default_rng(seq + hq + (mode or 7))
+    q = O.from_f32(rng.standard_normal((batch, seq, hq * dim), dtype=np.float32), dt)
+    k = O.from_f32(rng.standard_normal((batch, seq, hkv * dim), dtype=np.float32), dt)
+    v = O.from_f32(rng.standard_normal((batch, seq, hkv * dim), dtype=np.float32), dt)
+    out = empty(q.nbytes)
+    rope = None if mode is None else puter_b200.RoPEConfig(BaseFreq=500000.0, Mode=mode)
+    cfg = puter_b200.MultiHeadAttentionConfig(NumHeads=hq, HeadDim=dim, Causal=causal, KVHeadCount=hkv)
+    d.RoPEAttentionPrefill(rope, cfg, dev(q), dev(k), dev(v), out, batch, seq, dt)
+    got = O.to_f32(host(out, np.uint16, (batch, seq, hq, dim)), dt)
+    assert d.take_error() == 0
+    rows = np.array([0, 1, 127, 128, 255, 256, 300, seq // 2, seq - 129, seq - 2, seq - 1], np.int32)
+    for b in range(batch):
+        qb, kb = q[b], k[b]
+        if mode is not None:
+            qb = O.rope(dt, qb, seq, hq, dim, base=500000.0, mode=mode).reshape(seq, hq * dim)
+            kb = O.rope(dt, kb, seq, hkv, dim, base=500000.0, mode=mode).reshape(seq, hkv * dim)
+        r = np.repeat(rows, hq)
+        h = np.tile(np.arange(hq, dtype=np.int32), rows.size)
+        want = O.to_f32(O.mha_rows(dt, qb, kb, v[b], seq, seq, hq, hkv, dim, r, h, causal), dt)
+        assert np.abs(got[b, r, h] - want).max() <= 2e-2
