@@ -7,8 +7,11 @@
 Default workload = paged decode attention (batch 64, 32 query heads, 8 KV heads, head_dim 128, contexts
 ~U[512, 32768], page 16, bf16 KV, a random permutation of physical pages): the configuration the headline
 metric "decode-attn HBM GB/s" is quoted on.  One step = one decode step over the whole batch.  Prints ONE
-JSON line (rank 0).  For N > 1 launch with torchrun: every rank owns its own batch of sequences and page pool
-(sequences are independent: no data-path collective; weak scaling).
+JSON line (rank 0).
+
+For N > 1 launch with torchrun.  The ONE seeded batch is divided among the ranks: whole sequences, assigned
+longest first to the least loaded rank; each rank holds only the KV pages of its own sequences and there is no
+data-path collective (strong scaling: value = bytes of the whole batch / slowest rank's time).
 
 `--impl reference` times the CPU restatement of the reference's device/cpu path (the Go reference cannot be
 built here: no Go toolchain, and its `manifesto` dependency is absent) on a bounded sample of the same
@@ -18,7 +21,6 @@ from __future__ import annotations
 
 import argparse
 import json
-import math
 import os
 import subprocess
 import sys
@@ -31,7 +33,10 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-HQ, HKV, DIM, PAGE = 32, 8, 128, 16
+import bench_inputs as BI  # noqa: E402
+
+HQ, HKV, DIM, PAGE = BI.HQ, BI.HKV, BI.DIM, BI.PAGE
+CTX_RANGE = [512, 32768]  # --ctx-min / --ctx-max shrink the workload for profiler captures only
 
 
 def measured_peaks():
@@ -63,7 +68,7 @@ class ClockSampler:
             self.proc = None
 
     def stop(self):
-        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0, "power_w_max": None}
         if self.proc is None:
             return out
         self.proc.terminate()
@@ -74,7 +79,7 @@ class ClockSampler:
         self.file.flush()
         rows = [r.strip().split(",") for r in open(self.file.name) if r.strip()]
         os.unlink(self.file.name)
-        sm, mx, reasons = [], [], set()
+        sm, mx, pw, reasons = [], [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for r in rows:
             if len(r) < 9:
@@ -82,170 +87,190 @@ class ClockSampler:
             try:
                 sm.append(float(r[1]))
                 mx.append(float(r[2]))
+                pw.append(float(r[3]))
             except ValueError:
                 continue
             for name, val in zip(names, r[5:9]):
                 if val.strip().lower() == "active":
                     reasons.add(name)
         if sm:
-            out.update(sm_mhz=float(np.median(sm)), sm_max_mhz=float(max(mx)), reasons=sorted(reasons), samples=len(sm))
+            out.update(sm_mhz=float(np.median(sm)), sm_max_mhz=float(max(mx)), reasons=sorted(reasons), samples=len(sm),
+                       power_w_max=float(max(pw)))
         return out
 
 
 # ------------------------------------------------------------------------------------------------------------
-# workloads
+# config 4: paged decode attention
 # ------------------------------------------------------------------------------------------------------------
-CTX_RANGE = [512, 32768]  # --ctx-min / --ctx-max shrink the workload for profiler captures only
+def decode_batch() -> BI.DecodeBatch:
+    return BI.DecodeBatch(seed=2, batch=64, ctx_min=CTX_RANGE[0], ctx_max=CTX_RANGE[1])
 
 
-def decode_context_lengths(seed: int, batch: int = 64):
-    rng = np.random.default_rng(seed)
-    return rng.integers(CTX_RANGE[0], CTX_RANGE[1], batch, endpoint=True).astype(np.int32)
-
-
-def decode_bytes(ctx, esize):
-    """Algorithmic bytes of one decode step: K and V of every live token once, q and out rows, page-table entries."""
-    pages = int(((ctx.astype(np.int64) + PAGE - 1) // PAGE).sum())
-    kv = int(ctx.astype(np.int64).sum()) * HKV * DIM * 2 * esize
-    qo = len(ctx) * HQ * DIM * (2 + 2)
-    scales = 2 * HKV * 4 if esize == 1 else 0
-    return kv + qo + 4 * pages + scales
+def decode_config(batch: BI.DecodeBatch, fp8: bool, world: int) -> dict:
+    """The config dict both arms print (identical for a given N)."""
+    esize = 1 if fp8 else 2
+    return {"workload": "paged_decode_fp8kv" if fp8 else "paged_decode_bf16kv", "batch": batch.batch, "query_heads": HQ, "kv_heads": HKV,
+            "head_dim": DIM, "page_size": PAGE, "ctx_len": "U[%d,%d] seed 2" % tuple(CTX_RANGE), "kv_tokens": int(batch.ctx.sum()),
+            "kv_dtype": "e4m3+f32 scale" if fp8 else "bf16",
+            "parallelism": "whole sequences over %d GPU(s), longest first to the least loaded; no collective" % world,
+            "l2": "inputs larger than L2 (KV pools %.2f GB)" % (2 * int(batch.pages_per.sum()) * PAGE * BI.INNER * esize / 1e9)}
 
 
 class DecodeWorkload:
-    """Config 4: paged decode attention, one new token per sequence."""
+    """Config 4: paged decode attention, one new token per sequence; this rank's share of the seeded batch."""
 
-    def __init__(self, dev, rank: int, fp8: bool):
+    scaling = "strong"
+
+    def __init__(self, dev, rank: int, world: int, fp8: bool):
         import torch
 
-        from puter_b200 import MultiHeadAttentionConfig, dtypes
+        from puter_b200 import MultiHeadAttentionConfig, dtypes, sharding
 
-        self.torch = torch
-        self.dev = dev
-        self.fp8 = fp8
-        self.name = "paged_decode_fp8kv" if fp8 else "paged_decode_bf16kv"
-        self.ctx = decode_context_lengths(2 + 1000 * rank)
-        self.batch = len(self.ctx)
-        rng = np.random.default_rng(2 + 1000 * rank)
-        pages_per = (self.ctx.astype(np.int64) + PAGE - 1) // PAGE
-        self.total_pages = int(pages_per.sum())
-        self.max_pages = int(pages_per.max())
-        perm = rng.permutation(self.total_pages).astype(np.int32)  # page table = a random permutation of the pool
-        table = np.zeros((self.batch, self.max_pages), np.int32)
-        at = 0
-        for b, n in enumerate(pages_per):
-            table[b, :n] = perm[at:at + n]
-            at += n
-        self.table_host = torch.from_numpy(table).pin_memory()
-        self.ctx_host = torch.from_numpy(self.ctx.copy()).pin_memory()
-        g = torch.Generator(device="cuda")
-        g.manual_seed(2 + 1000 * rank)
-        elems = self.total_pages * PAGE * HKV * DIM
+        self.torch, self.dev, self.fp8, self.world, self.rank = torch, dev, fp8, world, rank
+        self.data = decode_batch()
+        self.owned_all = sharding.lpt_assign(self.data.ctx, world)
+        self.owned = self.owned_all[rank]
         self.esize = 1 if fp8 else 2
+        st = BI.upload_decode(dev, self.data, self.owned, fp8)
+        self.st = st
+        self.batch = len(self.owned)
         self.fmt = dtypes.BFloat16
         self.kvfmt = dtypes.Float8E4M3 if fp8 else dtypes.BFloat16
-        if fp8:
-            self.kscale = torch.empty(HKV, device="cuda").uniform_(0.01, 0.1, generator=g)
-            self.vscale = torch.empty(HKV, device="cuda").uniform_(0.01, 0.1, generator=g)
-            # stored byte = e4m3(x / s): generate in chunks to bound the float32 temporaries
-            self.k = torch.empty(elems, dtype=torch.float8_e4m3fn, device="cuda")
-            self.v = torch.empty(elems, dtype=torch.float8_e4m3fn, device="cuda")
-            chunk = PAGE * HKV * DIM * 4096
-            srep_k = (1.0 / self.kscale).repeat_interleave(DIM)
-            srep_v = (1.0 / self.vscale).repeat_interleave(DIM)
-            for dst, srep in ((self.k, srep_k), (self.v, srep_v)):
-                for s in range(0, elems, chunk):
-                    n = min(chunk, elems - s)
-                    x = torch.randn(n, device="cuda", generator=g).view(-1, HKV * DIM) * srep
-                    dst[s:s + n] = x.clamp_(-448, 448).to(torch.float8_e4m3fn).view(-1)
-        else:
-            self.kscale = self.vscale = None
-            self.k = torch.randn(elems, device="cuda", dtype=torch.bfloat16, generator=g)
-            self.v = torch.randn(elems, device="cuda", dtype=torch.bfloat16, generator=g)
-        self.q_host = torch.randn(self.batch, HQ * DIM, dtype=torch.float32).to(torch.bfloat16).pin_memory()
-        self.q = self.q_host.cuda()
-        self.table = self.table_host.cuda()
-        self.ctx_dev = self.ctx_host.cuda()
-        self.out = torch.zeros(self.batch, HQ * DIM, dtype=torch.bfloat16, device="cuda")
-        self.out_host = torch.zeros(self.batch, HQ * DIM, dtype=torch.bfloat16).pin_memory()
+        self.k, self.v = st["k"], st["v"]
+        self.kscale, self.vscale = st.get("k_scale"), st.get("v_scale")
+        self.total_pages, self.max_pages = st["total_pages"], st["max_pages"]
+        # this step's host inputs (query rows, page tables, lengths) live in ONE pinned buffer and reach the device in one copy
+        qb, tb, cb = st["q_host"].numel() * 2, st["table_host"].numel() * 4, st["ctx_host"].numel() * 4
+        off_t = (qb + 255) & ~255
+        off_c = (off_t + tb + 255) & ~255
+        total = off_c + max(cb, 4)
+        self.stage_host = torch.zeros(total, dtype=torch.uint8).pin_memory()
+        self.stage_dev = torch.zeros(total, dtype=torch.uint8, device="cuda")
+        self.stage_host[:qb].copy_(st["q_host"].view(torch.uint8).view(-1))
+        self.stage_host[off_t:off_t + tb].copy_(st["table_host"].view(torch.uint8).view(-1))
+        self.stage_host[off_c:off_c + cb].copy_(st["ctx_host"].view(torch.uint8).view(-1))
+        self.stage_dev.copy_(self.stage_host)
+        self.q = self.stage_dev[:qb].view(torch.int16).view(self.batch, HQ * DIM)
+        self.table = self.stage_dev[off_t:off_t + tb].view(torch.int32).view(self.batch, self.max_pages)
+        self.ctx_dev = self.stage_dev[off_c:off_c + cb].view(torch.int32)
+        self.out = torch.zeros(self.batch, HQ * DIM, dtype=torch.int16, device="cuda")
+        self.out_host = torch.zeros(self.batch, HQ * DIM, dtype=torch.int16).pin_memory()
         self.cfg = MultiHeadAttentionConfig(NumHeads=HQ, HeadDim=DIM, Causal=True, KVHeadCount=HKV)
-        self.bytes_per_step = decode_bytes(self.ctx, self.esize)
+        self.bytes_per_step = self.data.algorithmic_bytes(self.owned, self.esize)       # this rank
+        self.bytes_per_step_global = self.data.algorithmic_bytes(None, self.esize)      # the whole batch
         # DRAM traffic (ncu dram__bytes_read + write) over algorithmic bytes, from the small-case captures summarised in
         # the profiles folder (bf16 and fp8 decode captures); traffic grows in proportion to the tokens read
         self.traffic_ratio = (317.9 + 4.6) / 316.8 if fp8 else (634.7 + 5.7) / 633.6
-        self.units_per_step = self.batch  # tokens
-        self.h2d = self.q_host.numel() * 2 + self.table_host.numel() * 4 + self.ctx_host.numel() * 4
+        self.h2d = qb + tb + cb
         self.d2h = self.out_host.numel() * 2
-        self.working_set = 2 * elems * self.esize
+        torch.cuda.synchronize()
 
     def step(self):
         self.dev.PagedDecodeAttention(self.cfg, self.q, self.k, self.v, self.table, self.ctx_dev, self.out, self.batch, self.max_pages,
                                       self.total_pages, PAGE, self.fmt, kvFormat=self.kvfmt, kScale=self.kscale, vScale=self.vscale)
 
     def step_e2e(self):
-        # a decode step as the caller sees it: this step's query rows, page tables and lengths arrive from the host,
-        # the attention rows go back; the KV cache is device-resident state, as in the reference's paged-KV design
-        self.q.copy_(self.q_host, non_blocking=True)
-        self.table.copy_(self.table_host, non_blocking=True)
-        self.ctx_dev.copy_(self.ctx_host, non_blocking=True)
+        # a decode step as the caller sees it: this step's query rows, page tables and lengths arrive from the host (one
+        # copy), the attention rows go back; the KV cache is device-resident state, as in the reference's paged-KV design
+        self.stage_dev.copy_(self.stage_host, non_blocking=True)
         self.step()
         self.out_host.copy_(self.out, non_blocking=True)
 
     def config(self):
-        return {"workload": self.name, "batch": self.batch, "query_heads": HQ, "kv_heads": HKV, "head_dim": DIM, "page_size": PAGE,
-                "ctx_len": "U[%d,%d] seed 2" % tuple(CTX_RANGE), "kv_tokens": int(self.ctx.sum()), "kv_dtype": "e4m3+f32 scale" if self.fp8 else "bf16",
-                "l2": "inputs larger than L2 (KV pool %.2f GB)" % (self.working_set / 1e9)}
+        return decode_config(self.data, self.fp8, self.world)
 
     def metric(self):
         return "decode_attn_hbm_gbps", "GB/s"
 
     def value(self, seconds_per_step, world):
-        return self.bytes_per_step * world / seconds_per_step / 1e9
+        return self.bytes_per_step_global / seconds_per_step / 1e9
+
+    def bytes_per_rank(self):
+        return [self.data.algorithmic_bytes(o, self.esize) for o in self.owned_all]
 
     def extra(self, seconds_per_step, world):
-        return {"tokens_per_s": self.units_per_step * world / seconds_per_step}
+        loads = [int(self.data.ctx[o].sum()) for o in self.owned_all]
+        return {"tokens_per_s": self.data.batch / seconds_per_step,
+                "partition": {"sequences_per_rank": [len(o) for o in self.owned_all], "kv_tokens_per_rank": loads,
+                              "imbalance_max_over_mean": max(loads) / (sum(loads) / len(loads))}}
 
 
-def cpu_decode_sample(fp8: bool, nseq: int = 4, threads: int | None = None, repeats: int = 1):
+class ReplicaDecodeWorkload:
+    """The earlier weak-scaling measurement, kept as a labelled secondary: every rank runs its own full-size batch
+    (device-generated data; nothing is shared or divided)."""
+
+    scaling = "weak"
+
+    def __init__(self, dev, rank: int, world: int):
+        import torch
+
+        from puter_b200 import MultiHeadAttentionConfig, dtypes
+
+        self.dev = dev
+        data = BI.DecodeBatch(seed=2 + 1000 * rank)
+        table, count = data.shard_tables(range(data.batch))
+        g = torch.Generator(device="cuda")
+        g.manual_seed(2 + 1000 * rank)
+        elems = count * PAGE * BI.INNER
+        self.k = torch.randn(elems, device="cuda", dtype=torch.bfloat16, generator=g)
+        self.v = torch.randn(elems, device="cuda", dtype=torch.bfloat16, generator=g)
+        self.q = torch.randn(data.batch, HQ * DIM, device="cuda", dtype=torch.bfloat16, generator=g)
+        self.table = torch.from_numpy(table).cuda()
+        self.ctx = torch.from_numpy(data.ctx.copy()).cuda()
+        self.out = torch.zeros_like(self.q)
+        self.cfg = MultiHeadAttentionConfig(NumHeads=HQ, HeadDim=DIM, Causal=True, KVHeadCount=HKV)
+        self.args = (data.batch, table.shape[1], count, PAGE, dtypes.BFloat16)
+        self.bytes_per_step = data.algorithmic_bytes(None, 2)
+
+    def step(self):
+        self.dev.PagedDecodeAttention(self.cfg, self.q, self.k, self.v, self.table, self.ctx, self.out, *self.args)
+
+
+def cpu_decode_sample(fp8: bool, nseq: int = 16, threads: int | None = None, repeats: int = 1, prepared=None):
     """Times the CPU oracle (restatement of device/cpu: page_gather + MultiHeadAttention) on the first `nseq`
-    sequences of the seeded batch, all host threads.  Returns (GB/s, tokens/s, threads, description)."""
+    sequences of the seeded batch.  Returns (GB/s, tokens/s, threads, description, prepared inputs)."""
     import oracle as O
 
     O.build()
     threads = threads or (os.cpu_count() or 1)
     O.set_threads(threads)
-    ctx = decode_context_lengths(2)[:nseq]
-    rng = np.random.default_rng(2)
-    pages_per = (ctx.astype(np.int64) + PAGE - 1) // PAGE
-    total = int(pages_per.sum())
-    table = np.zeros((nseq, int(pages_per.max())), np.int32)
-    perm = rng.permutation(total).astype(np.int32)
-    at = 0
-    for b, n in enumerate(pages_per):
-        table[b, :n] = perm[at:at + n]
-        at += n
-    shape = (total, PAGE, HKV * DIM)
-    kf = rng.standard_normal(shape, dtype=np.float32)
-    vf = rng.standard_normal(shape, dtype=np.float32)
-    q = O.from_f32(rng.standard_normal((nseq, HQ * DIM), dtype=np.float32), O.BF16)
-    ks = vs = None
-    if fp8:
-        ks = rng.uniform(0.01, 0.1, HKV).astype(np.float32)
-        vs = rng.uniform(0.01, 0.1, HKV).astype(np.float32)
-        k = O.from_f32((kf.reshape(total, PAGE, HKV, DIM) / ks[None, None, :, None]).reshape(shape), O.E4M3)
-        v = O.from_f32((vf.reshape(total, PAGE, HKV, DIM) / vs[None, None, :, None]).reshape(shape), O.E4M3)
-        kvdt = O.E4M3
-    else:
-        k, v = O.from_f32(kf, O.BF16), O.from_f32(vf, O.BF16)
-        kvdt = O.BF16
+    data = decode_batch()
+    if prepared is None:
+        seqs = list(range(nseq))
+        qs, ks, vs = [], [], []
+        for i in seqs:
+            q, k, v = data.sequence(i)
+            if fp8:
+                k, v = data.scaled_for_fp8(k, v)
+            qs.append(O.from_f32(q, O.BF16))
+            ks.append(O.from_f32(k, O.E4M3 if fp8 else O.BF16))
+            vs.append(O.from_f32(v, O.E4M3 if fp8 else O.BF16))
+        table, count = data.shard_tables(seqs)
+        kp = np.zeros((count, PAGE, BI.INNER), ks[0].dtype)
+        vp = np.zeros((count, PAGE, BI.INNER), ks[0].dtype)
+        for row, i in enumerate(seqs):
+            n = int(data.pages_per[i])
+            kp[table[row, :n]] = ks[row].reshape(n, PAGE, BI.INNER)
+            vp[table[row, :n]] = vs[row].reshape(n, PAGE, BI.INNER)
+        prepared = (np.stack(qs), kp, vp, table, data.ctx[seqs].copy(), seqs)
+    q, kp, vp, table, ctx, seqs = prepared
+    kvdt = O.E4M3 if fp8 else O.BF16
     best = float("inf")
     for _ in range(repeats):
         t0 = time.perf_counter()
-        O.paged_decode(O.BF16, kvdt, q, k, v, table, ctx, PAGE, HQ, HKV, DIM, ks, vs)
+        O.paged_decode(O.BF16, kvdt, q, kp, vp, table, ctx, PAGE, HQ, HKV, DIM, data.k_scale if fp8 else None, data.v_scale if fp8 else None)
         best = min(best, time.perf_counter() - t0)
-    nbytes = decode_bytes(ctx, 1 if fp8 else 2)
-    return (nbytes / best / 1e9, nseq / best, threads,
-            f"first {nseq} of the 64 seeded sequences ({int(ctx.sum())} KV tokens), best of {repeats} x {best:.2f} s")
+    nbytes = data.algorithmic_bytes(seqs, 1 if fp8 else 2)
+    return (nbytes / best / 1e9, len(seqs) / best, threads,
+            f"first {len(seqs)} of the 64 seeded sequences ({int(ctx.sum())} KV tokens), best of {repeats} x {best:.2f} s", prepared)
+
+
+def cpu_decode_baseline(fp8: bool, nseq: int):
+    """All host threads on `nseq` sequences, and one thread (the reference ops are single-goroutine loops) on two of them."""
+    gbs, tps, threads, desc, _ = cpu_decode_sample(fp8, nseq=nseq, repeats=3)
+    gbs1, tps1, _, desc1, _ = cpu_decode_sample(fp8, nseq=min(2, nseq), threads=1, repeats=1)
+    return {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port", "sample": desc, "tokens_per_s": tps,
+            "value_1thread": gbs1, "tokens_per_s_1thread": tps1, "sample_1thread": desc1}
 
 
 # ------------------------------------------------------------------------------------------------------------
@@ -259,9 +284,9 @@ def run_reference(args, rank, world):
         # not constructed (their constructors allocate on the GPU), only their constants and cpu_baseline() are used
         import bench_workloads as W
 
-        cls, name = {"convert": (W.ConvertWorkload, "dtype_convert_sweep"), "chain": (W.ChainWorkload, "add_rmsnorm_gated_residual_swiglu"),
-                     "prefill": (W.PrefillWorkload, "prefill_causal_gqa_rope")}[args.workload]
+        cls = {"convert": W.ConvertWorkload, "chain": W.ChainWorkload, "prefill": W.PrefillWorkload}[args.workload]
         wl = object.__new__(cls)
+        wl.world = args.gpus
         metric, unit = wl.metric()
         samples = []
         t0 = time.perf_counter()
@@ -272,36 +297,38 @@ def run_reference(args, rank, world):
         base = dict(samples[-1], value=value)
         print(json.dumps({
             "impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": wall / max(args.steps, 1) * 1e3, "higher_is_better": True, "scaling": getattr(cls, "scaling", "weak"),
-            "vs_baseline": None, "dtype": "bf16" if args.workload != "convert" else "u8/u16/f32 bit patterns", "data": "synthetic",
-            "config": {"workload": name, "sample": base["sample"]}, "cpu_baseline": base,
+            "ms_per_step": wall / max(args.steps, 1) * 1e3, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": cls.dtype, "data": "synthetic",
+            "config": cls.static_config(args.gpus), "cpu_baseline": base,
             "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0,
             "note": "C++ restatement of puter device/cpu, not the Go binary: no Go toolchain here"}))
         return
     threads = os.cpu_count() or 1
-    for _ in range(max(args.warmup, 0)):
-        cpu_decode_sample(fp8, nseq=1, threads=threads)
+    prepared = None
     vals, toks, desc = [], [], ""
+    for _ in range(max(args.warmup, 0)):
+        *_, prepared = cpu_decode_sample(fp8, nseq=args.ref_seqs, threads=threads, prepared=prepared)
+    if prepared is None:
+        *_, prepared = cpu_decode_sample(fp8, nseq=args.ref_seqs, threads=threads)
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        gbs, tps, threads, desc = cpu_decode_sample(fp8, nseq=args.ref_seqs, threads=threads)
+        gbs, tps, threads, desc, prepared = cpu_decode_sample(fp8, nseq=args.ref_seqs, threads=threads, prepared=prepared)
         vals.append(gbs)
         toks.append(tps)
     wall = time.perf_counter() - t0
     value = float(np.mean(vals))
-    ctx = decode_context_lengths(2)
+    gbs1, tps1, _, desc1, _ = cpu_decode_sample(fp8, nseq=min(2, args.ref_seqs), threads=1)
     line = {
         "impl": "reference", "metric": "decode_attn_hbm_gbps", "value": value, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": wall / max(args.steps, 1) * 1e3, "higher_is_better": True, "scaling": "weak",
+        "warmup": args.warmup, "ms_per_step": wall / max(args.steps, 1) * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "paged_decode_fp8kv" if fp8 else "paged_decode_bf16kv", "batch": 64, "query_heads": HQ, "kv_heads": HKV,
-                   "head_dim": DIM, "page_size": PAGE, "ctx_len": "U[512,32768] seed 2", "kv_tokens": int(ctx.sum()),
-                   "kv_dtype": "e4m3+f32 scale" if fp8 else "bf16"},
+        "config": decode_config(decode_batch(), fp8, args.gpus),
         "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": "port", "sample": desc,
-                         "tokens_per_s": float(np.mean(toks))},
+                         "tokens_per_s": float(np.mean(toks)), "value_1thread": gbs1, "tokens_per_s_1thread": tps1, "sample_1thread": desc1},
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
-        "note": "C++ restatement of puter device/cpu (page_gather + MultiHeadAttention), not the Go binary: no Go toolchain here",
+        "note": "C++ restatement of puter device/cpu (page_gather + MultiHeadAttention), not the Go binary: no Go toolchain here; "
+                "a step is one pass over the sample named in cpu_baseline.sample (a rate, so comparable with the whole batch)",
     }
     print(json.dumps(line))
 
@@ -317,12 +344,15 @@ def main():
     ap.add_argument("--ctx-min", type=int, default=512)
     ap.add_argument("--ctx-max", type=int, default=32768, help="smaller values give a profiler-sized case; not a bench number")
     ap.add_argument("--prefill-batch", type=int, default=4, help="1 gives a profiler-sized prefill case; not a bench number")
+    ap.add_argument("--chain-tokens", type=int, default=16384, help="fewer token rows give a profiler-sized chain case; not a bench number")
+    ap.add_argument("--sustained-seconds", type=float, default=2.0, help="length of the sustained loop of the headline step (0 = skip)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-secondary", action="store_true")
     args = ap.parse_args()
     CTX_RANGE[0], CTX_RANGE[1] = args.ctx_min, args.ctx_max
     os.environ["PUTER_BENCH_PREFILL_BATCH"] = str(args.prefill_batch)
-    profiling = (args.ctx_min, args.ctx_max) != (512, 32768) or args.prefill_batch != 4
+    os.environ["PUTER_BENCH_CHAIN_TOKENS"] = str(args.chain_tokens)
+    profiling = (args.ctx_min, args.ctx_max) != (512, 32768) or args.prefill_batch != 4 or args.chain_tokens != 16384
     args.warmup = max(args.warmup, 3) if args.impl == "ours" and not profiling else args.warmup
 
     rank = int(os.environ.get("RANK", "0"))
@@ -347,7 +377,7 @@ def main():
     from bench_workloads import make_workload  # noqa: E402  (secondary workloads live beside this file)
 
     dev = puter_b200.Device(local_rank)
-    wl = make_workload(args.workload, dev, rank, DecodeWorkload)
+    wl = make_workload(args.workload, dev, rank, world, DecodeWorkload)
 
     def barrier():
         if world > 1:
@@ -355,7 +385,8 @@ def main():
         torch.cuda.synchronize()
 
     def timed(fn, steps, sample_clocks=False):
-        """Times `steps` calls of fn with CUDA events on the launching stream; returns (max-over-ranks seconds, clocks)."""
+        """Times `steps` calls of fn with CUDA events on the launching stream; returns (max-over-ranks seconds, clocks,
+        per-rank seconds)."""
         sampler = ClockSampler(local_rank) if sample_clocks else None
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
@@ -369,24 +400,27 @@ def main():
         barrier()
         clocks = sampler.stop() if sampler else None
         sec = start.elapsed_time(stop) / 1e3
+        per_rank = [sec]
         if world > 1:
             t = torch.tensor([sec], device="cuda", dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            sec = float(t.item())
-        return sec, clocks
+            allt = torch.empty(world, device="cuda", dtype=torch.float64)
+            dist.all_gather_into_tensor(allt, t)
+            per_rank = [float(x) for x in allt.tolist()]
+            sec = max(per_rank)
+        return sec, clocks, per_rank
 
     for _ in range(args.warmup):
         wl.step()
     if hasattr(wl, "verify"):
         wl.verify()  # untimed self-check of the multi-GPU exchange
     launches0 = dev.launch_count()
-    sec, clocks = timed(wl.step, args.steps, sample_clocks=True)
+    sec, clocks, per_rank = timed(wl.step, args.steps, sample_clocks=True)
     launches = dev.launch_count() - launches0
     per_step = sec / args.steps
 
     for _ in range(2):
         wl.step_e2e()
-    sec_e2e, _ = timed(wl.step_e2e, args.steps)
+    sec_e2e, _, _ = timed(wl.step_e2e, args.steps)
     per_step_e2e = sec_e2e / args.steps
 
     peaks = measured_peaks()
@@ -394,40 +428,52 @@ def main():
     value = wl.value(per_step, world)
     roof = wl.roofline(per_step, peaks) if hasattr(wl, "roofline") else None
     if roof is None:
-        achieved = wl.bytes_per_step / per_step / 1e9
+        # rank-local: this rank's algorithmic bytes over this rank's own time
+        mine = per_rank[rank] / args.steps
+        achieved = wl.bytes_per_step / mine / 1e9
         roof = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
                 "traffic": (wl.bytes_per_step * wl.traffic_ratio) if getattr(wl, "traffic_ratio", None) else None,
-                "traffic_note": "bytes per step: ncu dram read+write of a captured case scaled by algorithmic bytes (see profiles/)",
+                "traffic_note": "bytes per step: ncu dram read+write of a captured case scaled by algorithmic bytes",
                 "peak_source": peaks["source"],
-                "note": "achieved = algorithmic bytes / CUDA-event time of the whole step (all launches of the step); rank-local"}
+                "note": "achieved = this rank's algorithmic bytes / CUDA-event time of its whole step (all launches of the step)"}
+        if world > 1 and hasattr(wl, "bytes_per_rank"):
+            roof["per_rank_frac"] = [b / (t / args.steps) / 1e9 / peaks["hbm_gbs"] for b, t in zip(wl.bytes_per_rank(), per_rank)]
 
     line = {
         "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": per_step * 1e3, "higher_is_better": True, "scaling": getattr(wl, "scaling", "weak"), "vs_baseline": None,
+        "ms_per_step": per_step * 1e3, "higher_is_better": True, "scaling": getattr(wl, "scaling", "strong"), "vs_baseline": None,
         "dtype": wl.dtype if hasattr(wl, "dtype") else "bf16", "data": "synthetic", "config": wl.config(), "clocks": clocks,
         "e2e": {"value": getattr(wl, "e2e_value", wl.value)(per_step_e2e, world), "unit": unit, "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h,
                 "ms_per_step": per_step_e2e * 1e3},
-        "gpu_launches": int(launches), "roofline": roof,
+        "gpu_launches": int(launches), "roofline": roof, "ms_per_step_per_rank": [t / args.steps * 1e3 for t in per_rank],
     }
     line.update(wl.extra(per_step, world))
 
+    if args.sustained_seconds > 0 and not profiling:
+        # the same step looped for seconds of device time, clocks sampled: what a serving loop sees once the part is warm
+        n = max(args.steps, int(args.sustained_seconds / per_step) + 1)
+        sec_s, clocks_s, _ = timed(wl.step, n, sample_clocks=True)
+        line["sustained"] = {"value": wl.value(sec_s / n, world), "unit": unit, "ms_per_step": sec_s / n * 1e3, "steps": n,
+                             "seconds": sec_s, "sm_mhz_median": clocks_s["sm_mhz"], "power_w_max": clocks_s["power_w_max"],
+                             "reasons": clocks_s["reasons"], "ms_x_mhz": (sec_s / n * 1e3 * clocks_s["sm_mhz"]) if clocks_s["sm_mhz"] else None}
+
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         if args.workload in ("decode", "decode_fp8"):
-            gbs, tps, threads, desc = cpu_decode_sample(args.workload == "decode_fp8", nseq=args.ref_seqs, repeats=3)
-            line["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port", "sample": desc, "tokens_per_s": tps}
+            line["cpu_baseline"] = cpu_decode_baseline(args.workload == "decode_fp8", args.ref_seqs)
         elif hasattr(wl, "cpu_baseline"):
             line["cpu_baseline"] = wl.cpu_baseline()
 
-    if not args.no_secondary and args.workload == "decode":
+    if not args.no_secondary and args.workload == "decode" and not profiling:
         from bench_workloads import secondary_lines
 
-        sec_lines = secondary_lines(dev, rank, world, timed, peaks, DecodeWorkload, free=[wl])
+        sec_lines = secondary_lines(dev, rank, world, timed, peaks, DecodeWorkload, ReplicaDecodeWorkload, free=[wl])
         if sec_lines:
             line["secondary"] = sec_lines
 
     if rank == 0:
         print(json.dumps(line))
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
 
 

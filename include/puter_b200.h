@@ -196,7 +196,10 @@ int cuda_dispatch_modulated_layernorm(CUDADeviceRef contextRef, int elementDType
      h = x + residual;  normOut = RMSNorm(h, scale);  hOut = h (may be NULL);
      gatedOut = h + modulation[...] * branch   (skipped when branchRef == NULL)
    each result rounded to the storage dtype where the unfused ops would round (catalog-style fusion,
-   fusion/catalog.go:183-205). */
+   fusion/catalog.go:183-205).
+   Aliasing (also for cuda_dispatch_rmsnorm*): an output may be exactly the buffer of x or of residual (an in-place
+   residual stream); an output that overlaps them only partly, that overlaps scale, branch or modulation, or that
+   overlaps another output is refused with -2. */
 int cuda_dispatch_add_rmsnorm_gated_residual(CUDADeviceRef contextRef, int elementDType, CUDABufferRef xRef, CUDABufferRef residualRef,
                                              CUDABufferRef scaleRef, CUDABufferRef branchRef, CUDABufferRef modulationRef,
                                              CUDABufferRef hOutRef, CUDABufferRef normOutRef, CUDABufferRef gatedOutRef, uint32_t rows,
@@ -222,7 +225,8 @@ int cuda_dispatch_rope_pairs(CUDADeviceRef contextRef, int elementDType, CUDABuf
 
 /* ---- paged KV (device.Shape.PageWrite/PageGather, device/interface.go:625-635;
         execution/page_intrinsic.go:13-24; no CUDA kernel in the reference) ---- */
-/* NEW: storageOffset in elements (layer_index * layer elements).  outputRef == storageRef updates in place. */
+/* NEW: storageOffset in elements (layer_index * layer elements).  outputRef == storageRef updates in place.
+   Value rows aimed at the same (page, offset) within one call race (the CPU loop keeps the last one). */
 int cuda_dispatch_kv_page_write(CUDADeviceRef contextRef, int elementDType, CUDABufferRef storageRef, CUDABufferRef valuesRef,
                                 CUDABufferRef pageIDsRef, CUDABufferRef offsetsRef, CUDABufferRef outputRef, uint32_t pageCount,
                                 uint32_t pageSize, uint32_t inner, uint32_t valueRows, uint64_t storageOffset,
@@ -277,8 +281,10 @@ int cuda_dispatch_rope_attention_prefill(CUDADeviceRef contextRef, int elementDT
      k/v pages   [pageCount, pageSize, kvHeads*headDim]         kvDType: elementDType, or Float8E4M3 with
                                                                  per-KV-head f32 scales kScale/vScale [kvHeads]
      pageTable   [batch, maxPagesPerSeq] int32, ctxLens [batch] int32
-   ctxLens[i] == 0 leaves row i of out untouched.  A page id outside [0,pageCount) or ctx > maxPages*pageSize
-   is never dereferenced: the sequence is skipped and *errorFlag (device int32, may be NULL) is set to 1. */
+   ctxLens[i] == 0 leaves row i of out untouched.  A page id outside [0,pageCount) is never dereferenced (page 0 is
+   read in its place) and a context longer than maxPages*pageSize is cut to that length; either way *errorFlag
+   (device int32; NULL = the context's own flag, read with cuda_context_take_error) is set to 1 and the output
+   row of that sequence is not valid. */
 int cuda_dispatch_paged_decode_attention(CUDADeviceRef contextRef, int elementDType, int kvDType, CUDABufferRef queryRef,
                                          CUDABufferRef kPagesRef, CUDABufferRef vPagesRef, CUDABufferRef pageTableRef,
                                          CUDABufferRef ctxLensRef, CUDABufferRef kScaleRef, CUDABufferRef vScaleRef,

@@ -13,10 +13,11 @@
 namespace puter {
 int launch_mha_exact(Context* ctx, int dt, const void* q, const void* k, const void* v, void* out, uint32_t seqQ, uint32_t seqK,
                      uint32_t numHeads, uint32_t kvHeads, uint32_t headDim, uint32_t causal, uint32_t window, CUDAStatus* status);
+struct DecodeScratch;
 int launch_paged_decode(Context* ctx, int dt, int kvDT, const void* q, const void* kPages, const void* vPages, const int32_t* pageTable,
-                        const int32_t* ctxLens, const float* kScale, const float* vScale, void* out, int* errorFlag, uint32_t batch,
-                        uint32_t maxPages, uint32_t pageCount, uint32_t pageSize, uint32_t numHeads, uint32_t kvHeads,
-                        long long seqStrideKV, long long totalTilesHint, CUDAStatus* status);
+                        const int32_t* ctxLens, int uniformCtx, const float* kScale, const float* vScale, void* out, int* errorFlag,
+                        uint32_t batch, uint32_t maxPages, uint32_t pageCount, uint32_t pageSize, uint32_t numHeads, uint32_t kvHeads,
+                        long long seqStrideKV, long long totalTilesHint, const DecodeScratch* fixed, CUDAStatus* status);
 bool decode_supported(int dt, int kvDT, uint32_t numHeads, uint32_t kvHeads, uint32_t headDim);
 bool prefill_supported(int dt, uint32_t seqQ, uint32_t seqK, uint32_t numHeads, uint32_t kvHeads, uint32_t headDim, uint32_t causal);
 int launch_prefill(Context* ctx, int dt, const void* q, const void* k, const void* v, void* out, uint32_t batch, uint32_t seqLen,
@@ -26,11 +27,6 @@ int validate_rope(CUDAStatus* status, double base, uint32_t halfMode, uint32_t s
                   uint32_t origCtx);
 const float* cached_rope_table(Context* ctx, size_t seqLen, int headDim, double base, long long startPos, int scaling, double factor,
                                double low, double high, int origCtx, CUDAStatus* status);
-
-__global__ void fill_i32_kernel(int32_t* p, int32_t v, int n) {
-    int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) p[i] = v;
-}
 }  // namespace puter
 
 using namespace puter;
@@ -59,13 +55,9 @@ extern "C" int cuda_dispatch_multi_head_attention(CUDADeviceRef contextRef, int 
     const bool aligned = (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)o) & 15u) == 0;
     if (!ctx->exact && windowSize == 0 && aligned) {
         if (seqQ == 1 && decode_supported(elementDType, elementDType, numHeads, kvHeads, headDim)) {
-            // one sequence, contiguous K/V: the context length travels through the context's scratch word
-            int32_t* len = (int32_t*)((char*)ctx->errorFlag + 64);
-            fill_i32_kernel<<<1, 32, 0, ctx->stream>>>(len, (int32_t)seqK, 1);
-            int rc = check_launch(ctx, status, "decode length");
-            if (rc != 0) return rc;
-            return launch_paged_decode(ctx, elementDType, elementDType, q, k, v, nullptr, len, nullptr, nullptr, o, nullptr, 1, 0,
-                                       (seqK + 15) / 16, 16, numHeads, kvHeads, 0, (long long)((seqK + 15) / 16), status);
+            // one sequence, contiguous K/V: the context length travels as a kernel argument
+            return launch_paged_decode(ctx, elementDType, elementDType, q, k, v, nullptr, nullptr, (int)seqK, nullptr, nullptr, o, nullptr, 1,
+                                       0, (seqK + 15) / 16, 16, numHeads, kvHeads, 0, (long long)((seqK + 15) / 16), nullptr, status);
         }
         if (prefill_supported(elementDType, seqQ, seqK, numHeads, kvHeads, headDim, causal))
             return launch_prefill(ctx, elementDType, q, k, v, o, 1, seqQ, numHeads, kvHeads, headDim, causal, 2, nullptr, status);

@@ -41,6 +41,9 @@ struct Context {
     size_t pinnedBytes;
     cudaEvent_t stageEvents[4];
     int* errorFlag;  // device int32 owned by the context
+    // arrival counters of the split-KV decode kernels: zeroed once here, every launch returns them to zero
+    int* decodeCounters;
+    size_t decodeCounterBytes;
     // cos/sin table of the last RoPE configuration (positions x headDim/2, cos then sin), reused while the config repeats
     float* ropeTable;
     size_t ropeTableBytes;

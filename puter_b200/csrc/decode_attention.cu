@@ -18,8 +18,10 @@
 //     contiguous ranges, one per worker (a CTA, or a fraction of one when there are fewer than 8 KV
 //     heads), so every SM reads the same number of bytes whatever the context-length mix; a range may
 //     span several sequences and a sequence several ranges;
-//   * each (worker, sequence) pair leaves an un-normalised partial (max, sum, accumulator) in scratch
-//     memory; a second small kernel merges the partials of a sequence and writes the rounded output;
+//   * each (worker, sequence, KV head) triple leaves an un-normalised partial (max, sum, accumulator) in scratch
+//     memory and bumps a counter; the warp that finds itself last for a (sequence, KV head) merges the partials
+//     in worker order and writes the rounded output rows, so a decode step is ONE launch: the tile prefix sums
+//     are recomputed by every CTA in shared memory (a separate one-block kernel only beyond 1024 sequences);
 //   * the GQA group (<= 16 query heads per KV head) forms the M=16 rows of mma.sync m16n8k16 tiles fed by
 //     ldmatrix from XOR-swizzled shared memory; tensor-core throughput is irrelevant here, the point is to
 //     keep the instruction count per byte far below the issue limit.
@@ -37,20 +39,24 @@ static constexpr int kTile = 16;       // tokens per tile
 static constexpr int kWarps = 8;
 static constexpr int kThreads = kWarps * 32;
 
+static constexpr int kPrefixSmem = 1024;  // sequences whose tile prefix sums fit the in-kernel scan
+
 struct DecodeParams {
     const void* q;            // [batch, numHeads*128]
     const void* kPages;       // [pageCount, pageSize, kvHeads*128]
     const void* vPages;
     const int32_t* pageTable; // [batch, maxPages] or nullptr: pages are consecutive (contiguous K/V per sequence)
-    const int32_t* ctxLens;   // [batch]
+    const int32_t* ctxLens;   // [batch], or nullptr: every sequence has uniformCtx tokens
     const float* kScale;      // [kvHeads] or nullptr (fp8 only)
     const float* vScale;
-    const long long* tileStart;  // [batch+1] exclusive prefix of tiles per sequence
+    const int* tileStart;     // [batch+1] exclusive prefix of tiles per sequence, or nullptr: scanned in shared memory
     float* partAcc;           // [slots, numHeads, 128]
     float2* partML;           // [slots, numHeads]  (max in log2 domain, sum)
+    int* counters;            // [batch, kvHeads] arrivals per (sequence, KV head); zero on entry, zero again on exit
+    void* out;                // [batch, numHeads*128]
     int* errorFlag;
     long long seqStrideKV;    // contiguous mode: elements between consecutive sequences' K (and V)
-    int batch, maxPages, pageCount, pageSize, numHeads, kvHeads, group;
+    int batch, maxPages, pageCount, pageSize, numHeads, kvHeads, group, uniformCtx;
     int headsPerPass, groups, workers;  // warps-as-heads per pass, sub-ranges per CTA, total workers
     float scaleLog2;          // (1/sqrt(headDim)) * log2(e)
     float scale;
@@ -107,44 +113,119 @@ template <bool BF16> __device__ __forceinline__ float round16(float v) {
     return __half2float(__float2half_rn(v));
 }
 
-// exclusive prefix sum of tiles per sequence (one block); clamps over-long contexts and flags them
-__global__ void decode_prefix_kernel(const int32_t* __restrict__ ctxLens, long long* __restrict__ tileStart, int batch, int maxPages,
-                                     int pageSize, int* __restrict__ errorFlag) {
-    __shared__ long long warpSums[32];
-    __shared__ long long carry;
+// tiles of sequence b; clamps negative and over-long contexts and flags them
+__device__ __forceinline__ int seq_tiles(const DecodeParams& p, int b) {
+    long long ctx = p.ctxLens ? (long long)p.ctxLens[b] : (long long)p.uniformCtx;
+    if (ctx < 0) { ctx = 0; atomicExch(p.errorFlag, 1); }
+    if (p.pageTable) {
+        const long long cap = (long long)p.maxPages * p.pageSize;
+        if (ctx > cap) { ctx = cap; atomicExch(p.errorFlag, 1); }
+    }
+    return (int)((ctx + kTile - 1) / kTile);
+}
+
+// context length of sequence b as the kernels use it: never beyond the tiles counted for it
+__device__ __forceinline__ int seq_ctx(const DecodeParams& p, int b, int tiles) {
+    const long long ctx = p.ctxLens ? (long long)p.ctxLens[b] : (long long)p.uniformCtx;
+    const long long cap = (long long)tiles * kTile;
+    return (int)(ctx < cap ? ctx : cap);
+}
+
+// Exclusive prefix sum of tiles per sequence over the whole block: out[0..batch].  Every thread of the block must call it.
+__device__ void block_tile_prefix(const DecodeParams& p, int* out) {
+    __shared__ int warpSums[32];
+    __shared__ int carry;
     if (threadIdx.x == 0) carry = 0;
     __syncthreads();
-    const long long cap = (long long)maxPages * pageSize;
-    for (int base = 0; base < batch; base += blockDim.x) {
-        int b = base + threadIdx.x;
-        long long t = 0;
-        if (b < batch) {
-            long long ctx = ctxLens[b];
-            if (ctx < 0) { ctx = 0; atomicExch(errorFlag, 1); }
-            if (maxPages > 0 && ctx > cap) { ctx = cap; atomicExch(errorFlag, 1); }
-            t = (ctx + kTile - 1) / kTile;
-        }
-        long long incl = t;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nWarps = (blockDim.x + 31) >> 5;
+    for (int base = 0; base < p.batch; base += blockDim.x) {
+        const int b = base + threadIdx.x;
+        const int tiles = b < p.batch ? seq_tiles(p, b) : 0;
+        int incl = tiles;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
-            long long n = __shfl_up_sync(0xffffffffu, incl, o);
-            if ((threadIdx.x & 31) >= o) incl += n;
+            const int n = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += n;
         }
-        int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
         if (lane == 31) warpSums[warp] = incl;
         __syncthreads();
-        long long before = carry;
+        int before = carry;
         for (int w = 0; w < warp; w++) before += warpSums[w];
-        if (b < batch) tileStart[b] = before + incl - t;
+        if (b < p.batch) out[b] = before + incl - tiles;
         __syncthreads();
         if (threadIdx.x == blockDim.x - 1) carry = before + incl;
         __syncthreads();
+        (void)nWarps;
     }
-    if (threadIdx.x == 0) tileStart[batch] = carry;
+    if (threadIdx.x == 0) out[p.batch] = carry;
+    __syncthreads();
 }
+
+// the same scan as a kernel of its own, for batches beyond the in-kernel limit
+__global__ void __launch_bounds__(1024) decode_prefix_kernel(DecodeParams p, int* __restrict__ tileStart) { block_tile_prefix(p, tileStart); }
 
 // worker index that owns global tile g when T tiles are cut into NV equal contiguous ranges [v*T/NV, (v+1)*T/NV)
 __device__ __forceinline__ long long worker_of_tile(long long g, long long T, long long NV) { return ((g + 1) * NV - 1) / T; }
+
+__device__ __forceinline__ float4 ldcg4(const float* p) { return __ldcg((const float4*)p); }
+
+// Called by a whole warp once its partial of (worker, sequence b, KV head kvh) is in scratch.  Counts the arrival; the warp
+// that arrives last for (b, kvh) merges the partials of all owning workers in worker order (so the result does not depend on
+// which warp happens to be last), normalises, rounds and writes the group's output rows, and returns the counter to zero.
+// A sequence that lies inside one worker's range needs no counter at all.
+template <bool BF16>
+__device__ __forceinline__ void merge_if_last(const DecodeParams& p, const int* ts, int b, int kvh, int lane) {
+    const long long T = ts[p.batch];
+    const long long s0 = ts[b], s1 = ts[b + 1];
+    const long long W = p.workers;
+    const long long v0 = worker_of_tile(s0, T, W), v1 = worker_of_tile(s1 - 1, T, W);
+    // workers whose own range is empty (fewer tiles than workers) never write a partial
+    auto owns = [&](long long v) { return (v + 1) * T / W > v * T / W; };
+    int owners = (int)(v1 - v0 + 1);
+    if (T < W) {
+        owners = 0;
+        for (long long v = v0; v <= v1; v++) owners += owns(v) ? 1 : 0;
+    }
+    __threadfence();  // this lane's partial stores are visible device-wide before the arrival is counted
+    __syncwarp();
+    if (owners > 1) {
+        int last = 0;
+        if (lane == 0) {
+            int* c = p.counters + (size_t)b * p.kvHeads + kvh;
+            last = atomicAdd(c, 1) == owners - 1;
+            if (last) *c = 0;  // nobody else touches this counter again in this launch
+        }
+        last = __shfl_sync(0xffffffffu, last, 0);
+        if (!last) return;
+        __threadfence();
+    }
+    uint16_t* orow = (uint16_t*)p.out + (size_t)b * p.numHeads * kHeadDim;
+    for (int gi = 0; gi < p.group; gi++) {
+        const int head = kvh * p.group + gi;
+        float M = -INFINITY;
+        for (long long v = v0; v <= v1; v++)
+            if (owns(v)) M = fmaxf(M, __ldcg(&p.partML[(size_t)(v + b) * p.numHeads + head]).x);
+        float den = 0.f;
+        float4 num = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (long long v = v0; v <= v1; v++) {
+            if (!owns(v)) continue;
+            const float2 ml = __ldcg(&p.partML[(size_t)(v + b) * p.numHeads + head]);
+            const float w = (ml.x == -INFINITY) ? 0.f : exp2f(ml.x - M);
+            const float4 a = ldcg4(p.partAcc + ((size_t)(v + b) * p.numHeads + head) * kHeadDim + 4 * lane);
+            den += ml.y * w;
+            num.x += a.x * w; num.y += a.y * w; num.z += a.z * w; num.w += a.w * w;
+        }
+        float o[4] = {num.x, num.y, num.z, num.w};
+        uint32_t w2[2];
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            const float a = den > 0.f ? o[2 * i] / den : 0.f, c = den > 0.f ? o[2 * i + 1] / den : 0.f;
+            const uint32_t lo = BF16 ? f32_to_bf16_bits(a) : f32_to_f16_bits(a), hi = BF16 ? f32_to_bf16_bits(c) : f32_to_f16_bits(c);
+            w2[i] = lo | (hi << 16);
+        }
+        *(uint2*)(orow + (size_t)head * kHeadDim + 4 * lane) = make_uint2(w2[0], w2[1]);
+    }
+}
 
 template <bool BF16, bool FP8KV, int NS>
 struct DecodeSmem {
@@ -159,13 +240,19 @@ __global__ void __launch_bounds__(kThreads, 1) paged_decode_kernel(DecodeParams 
     extern __shared__ __align__(128) unsigned char smemRaw[];
     using SM = DecodeSmem<BF16, FP8KV, NS>;
     constexpr bool MMA_BF16 = BF16 && !FP8KV;  // fp8 pages are widened to f16, so that path multiplies in f16
+    __shared__ int sTileStart[kPrefixSmem + 1];
+    const int* ts = p.tileStart;
+    if (!ts) {
+        block_tile_prefix(p, sTileStart);
+        ts = sTileStart;
+    }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     if (warp >= p.groups * p.headsPerPass) return;
     const int sub = warp / p.headsPerPass;
     const int head0 = warp % p.headsPerPass;
     const long long worker = (long long)blockIdx.x * p.groups + sub;
-    const long long T = p.tileStart[p.batch];
+    const long long T = ts[p.batch];
     if (T == 0) return;
     const long long lo = worker * T / p.workers, hi = (worker + 1) * T / p.workers;
     if (lo >= hi) return;
@@ -182,7 +269,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_decode_kernel(DecodeParams 
         int a = 0, z = p.batch;
         while (z - a > 1) {
             int m = (a + z) >> 1;
-            if (p.tileStart[m] <= lo) a = m; else z = m;
+            if (ts[m] <= lo) a = m; else z = m;
         }
         seq = a;
     }
@@ -191,14 +278,12 @@ __global__ void __launch_bounds__(kThreads, 1) paged_decode_kernel(DecodeParams 
         int b = seq;
         long long cur = lo;
         while (cur < hi) {
-            while (p.tileStart[b + 1] <= cur) b++;  // skip empty sequences
-            const long long segStart = p.tileStart[b];
-            const long long segEndAll = p.tileStart[b + 1];
+            while (ts[b + 1] <= cur) b++;  // skip empty sequences
+            const long long segStart = ts[b];
+            const long long segEndAll = ts[b + 1];
             const long long segEnd = segEndAll < hi ? segEndAll : hi;
             const int tile0 = (int)(cur - segStart), tile1 = (int)(segEnd - segStart);  // local tile range [tile0, tile1)
-            long long ctxl = p.ctxLens[b];
-            const long long capTok = (long long)(segEndAll - segStart) * kTile;
-            const int ctx = (int)(ctxl < capTok ? ctxl : capTok);
+            const int ctx = seq_ctx(p, b, (int)(segEndAll - segStart));
             const int32_t* table = p.pageTable ? p.pageTable + (size_t)b * p.maxPages : nullptr;
             const unsigned char* kBase = (const unsigned char*)p.kPages + (size_t)kvh * kHeadDim * es;
             const unsigned char* vBase = (const unsigned char*)p.vPages + (size_t)kvh * kHeadDim * es;
@@ -455,6 +540,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_decode_kernel(DecodeParams 
                     }
                 }
             }
+            merge_if_last<BF16>(p, ts, b, kvh, lane);
             cur = segEnd;
             if (cur >= segEndAll) b++;
         }
@@ -463,36 +549,71 @@ __global__ void __launch_bounds__(kThreads, 1) paged_decode_kernel(DecodeParams 
 
 // ---------------------------------------------------------------------------------------------------------
 // fp8-e4m3 KV pages.  sm_100a has no native fp8 mma.sync (the assembler expands it into conversions plus f16 MMAs, ~20
-// instructions each), so the bytes are widened to f16 (exact) in registers, once per fragment, straight out of ldmatrix:
+// instructions each), so the bytes are widened to f16 (exact) in registers, straight out of ldmatrix, and the kernel is
+// built to spend as few instructions per byte as it can:
+//   * the TOKENS are the M = 16 rows of every m16n8k16 MMA and the (<= 8) query heads of the KV head's group its N = 8
+//     columns: S^T = K Q^T and O^T += V^T P^T.  With the heads as rows (as in the 16-bit kernel) 12 of 16 rows would
+//     multiply zeros for a group of 4; this way a 32-token step costs 16 + 16 MMAs and the output accumulator 32 registers;
 //   * K: a non-transposed ldmatrix of the raw rows hands every lane 4 consecutive head dimensions of one token; two
-//     cvt.f16x2.e4m3x2 turn them into the two B registers of one m16n8k16 MMA whose K index runs over the dimensions
-//     {4t, 4t+1 | 4t+2, 4t+3} of a 16-dimension chunk — the query fragments are loaded in the same order, so nothing moves;
-//   * V: ldmatrix.trans on byte pairs + one byte permute per register gives, per lane, the tokens {2t, 2t+1, 8+2t, 9+2t}
-//     of one head dimension, which is exactly the token order the score accumulators (hence P) already have.
-// One step covers 32 tokens.  The bf16 query is multiplied in f16 (values beyond the f16 range would overflow), P in f16
-// (11 significant bits), accumulation in f32; the per-KV-head scales multiply the scores and the output.
+//     cvt.f16x2.e4m3x2 turn them into A registers of an MMA whose K index runs over the dimensions
+//     {4t, 4t+1 | 4t+2, 4t+3} of a 16-dimension chunk — the query fragments (B operand) are loaded in the same order;
+//   * V: ldmatrix.trans on byte pairs + one byte permute per register gives, per lane, the tokens {2t, 2t+1} of the
+//     dimensions 2g and 2g+1: the A registers of V^T with the rows of a 16-dimension tile ordered {0,2,..,14,1,3,..,15};
+//   * P^T: the score accumulator holds (token g, heads 2t, 2t+1); movmatrix transposes the packed f16 pairs into the
+//     B-operand layout (head g, tokens 2t, 2t+1);
+//   * the softmax maximum is reduced over the 8 lanes that share a head column; the row sums stay per lane until the end.
+// The bf16 query is multiplied in f16 (values beyond the f16 range would overflow), P in f16 (11 significant bits),
+// accumulation in f32; the per-KV-head scales multiply the scores and the output.
 // ---------------------------------------------------------------------------------------------------------
 static constexpr int kTile8 = 32;                                  // tokens per fp8 step
 static constexpr int kStage8 = 2 * kTile8 * kHeadDim;              // K + V bytes of one step for one head: 8 KB
 static constexpr int kStages8 = 3;
 static constexpr int kSmem8 = kStages8 * kStage8 * kWarps;         // 192 KB
 
-// two e4m3 bytes (low 16 bits of `w`) -> f16x2, exact
-__device__ __forceinline__ uint32_t e4m3x2_to_f16x2(uint32_t w) {
-    const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(w & 0xFFFFu), __NV_E4M3);
-    return (uint32_t)h.x | ((uint32_t)h.y << 16);
+// two e4m3 bytes (low / high 16 bits of `w`) -> f16x2, exact
+__device__ __forceinline__ uint32_t e4m3x2_lo(uint32_t w) {
+    uint32_t d;
+    asm("{ .reg .b16 lo, hi; mov.b32 {lo, hi}, %1; cvt.rn.f16x2.e4m3x2 %0, lo; }" : "=r"(d) : "r"(w));
+    return d;
+}
+__device__ __forceinline__ uint32_t e4m3x2_hi(uint32_t w) {
+    uint32_t d;
+    asm("{ .reg .b16 lo, hi; mov.b32 {lo, hi}, %1; cvt.rn.f16x2.e4m3x2 %0, hi; }" : "=r"(d) : "r"(w));
+    return d;
+}
+__device__ __forceinline__ float ex2_approx(float x) {  // 2^x, flush-to-zero, 2 ulp: ex2(-inf) = 0
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+    return d;
+}
+__device__ __forceinline__ void mma16816_f16(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-template <bool BF16>
+// NT = n-tiles of 8 query heads per KV head (1: group <= 8, 2: group <= 16)
+template <bool BF16, int NT>
 __global__ void __launch_bounds__(kThreads, 1) paged_decode_fp8_kernel(DecodeParams p) {
     extern __shared__ __align__(128) unsigned char smemRaw[];
+    __shared__ int sTileStart[kPrefixSmem + 1];
+    const int* ts = p.tileStart;
+    if (!ts) {
+        block_tile_prefix(p, sTileStart);
+        ts = sTileStart;
+    }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     if (warp >= p.groups * p.headsPerPass) return;
     const int sub = warp / p.headsPerPass;
     const int head0 = warp % p.headsPerPass;
     const long long worker = (long long)blockIdx.x * p.groups + sub;
-    const long long T = p.tileStart[p.batch];
+    const long long T = ts[p.batch];
     if (T == 0) return;
     const long long lo = worker * T / p.workers, hi = (worker + 1) * T / p.workers;
     if (lo >= hi) return;
@@ -505,35 +626,47 @@ __global__ void __launch_bounds__(kThreads, 1) paged_decode_fp8_kernel(DecodePar
         int a = 0, z = p.batch;
         while (z - a > 1) {
             int m = (a + z) >> 1;
-            if (p.tileStart[m] <= lo) a = m; else z = m;
+            if (ts[m] <= lo) a = m; else z = m;
         }
         seq = a;
     }
+    // per-lane constants of the copy pattern: lane = (row in a group of 4 tokens, 16-byte chunk of the 128-byte row)
+    const int cpRow = lane >> 3, cpChunk = lane & 7;
+    const size_t cpSrc = (size_t)cpRow * tokenStride + (size_t)cpChunk * 16;
+    const uint32_t cpDstEven = (uint32_t)(cpRow * 128 + ((cpChunk ^ cpRow) * 16));        // rows 8j + cpRow
+    const uint32_t cpDstOdd = (uint32_t)((cpRow + 4) * 128 + ((cpChunk ^ (cpRow + 4)) * 16));  // rows 8j + 4 + cpRow
+    // per-lane ldmatrix addresses inside a stage (swizzle: 16-byte chunk ^ (token & 7))
+    const int lmRow = lane & 7, lmMat = lane >> 3;
+    const uint32_t kLm = (uint32_t)(((lmMat & 1) * 8 + lmRow) * 128);  // + 16*mt*128, chunk (2cp + (lmMat >> 1)) ^ lmRow
+    const uint32_t vLm = (uint32_t)(lane * 128);                       // matrix j = tokens 8j..8j+7, chunk dt ^ lmRow
+
     for (int kvh = head0; kvh < p.kvHeads; kvh += p.headsPerPass) {
         int b = seq;
         long long cur = lo;
         while (cur < hi) {
-            while (p.tileStart[b + 1] <= cur) b++;
-            const long long segStart = p.tileStart[b], segEndAll = p.tileStart[b + 1];
+            while (ts[b + 1] <= cur) b++;
+            const long long segStart = ts[b], segEndAll = ts[b + 1];
             const long long segEnd = segEndAll < hi ? segEndAll : hi;
             const int tok0 = (int)(cur - segStart) * kTile;
-            long long ctxl = p.ctxLens[b];
-            const long long capTok = (segEndAll - segStart) * kTile;
-            const int ctx = (int)(ctxl < capTok ? ctxl : capTok);
+            const int ctx = seq_ctx(p, b, (int)(segEndAll - segStart));
             const long long endTokL = (segEnd - segStart) * kTile;
             const int tokEnd = (int)(endTokL < ctx ? endTokL : ctx);  // this worker's share of the sequence: [tok0, tokEnd)
             const int32_t* table = p.pageTable ? p.pageTable + (size_t)b * p.maxPages : nullptr;
             const unsigned char* kBase = (const unsigned char*)p.kPages + (size_t)kvh * kHeadDim;
             const unsigned char* vBase = (const unsigned char*)p.vPages + (size_t)kvh * kHeadDim;
-            // ---- Q fragments in f16: chunk c (16 head dimensions), a0/a1 = dims 16c+4t, +1 of rows g / g+8; a2/a3 = dims +2, +3 ----
-            uint32_t qa[8][4];
+            if (!table) {
+                kBase += (size_t)b * p.seqStrideKV;
+                vBase += (size_t)b * p.seqStrideKV;
+            }
+            // ---- Q as the B operand, f16: chunk c (16 head dimensions): b0 = dims 16c+4t, +1 of head g; b1 = dims +2, +3 ----
+            uint32_t qb[8][NT][2];
             {
                 const uint16_t* qRow = (const uint16_t*)p.q + (size_t)b * p.numHeads * kHeadDim;
 #pragma unroll
-                for (int c = 0; c < 8; c++) {
+                for (int nt = 0; nt < NT; nt++) {
+                    const int gi = nt * 8 + g;
 #pragma unroll
-                    for (int hrow = 0; hrow < 2; hrow++) {
-                        const int gi = g + 8 * hrow;
+                    for (int c = 0; c < 8; c++) {
                         uint32_t w0 = 0, w1 = 0;
                         if (gi < p.group) {
                             const uint2 raw = *(const uint2*)(qRow + (size_t)(kvh * p.group + gi) * kHeadDim + c * 16 + 4 * t);
@@ -545,15 +678,21 @@ __global__ void __launch_bounds__(kThreads, 1) paged_decode_fp8_kernel(DecodePar
                                 w1 = raw.y;
                             }
                         }
-                        qa[c][hrow] = w0;
-                        qa[c][2 + hrow] = w1;
+                        qb[c][nt][0] = w0;
+                        qb[c][nt][1] = w1;
                     }
                 }
             }
-            float oacc[16][4];
+            // O^T: tile dt = dims 16dt .. 16dt+15 in the row order {0,2,..,14,1,3,..,15}; [0],[1] = (dim 16dt+2g, heads 2t, 2t+1),
+            // [2],[3] = (dim 16dt+2g+1, heads 2t, 2t+1)
+            float oacc[8][NT][4];
 #pragma unroll
-            for (int j = 0; j < 16; j++) oacc[j][0] = oacc[j][1] = oacc[j][2] = oacc[j][3] = 0.f;
-            float mrow[2] = {-INFINITY, -INFINITY}, lrow[2] = {0.f, 0.f};
+            for (int dt = 0; dt < 8; dt++)
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++) oacc[dt][nt][0] = oacc[dt][nt][1] = oacc[dt][nt][2] = oacc[dt][nt][3] = 0.f;
+            float mcol[NT][2], lcol[NT][2];  // per head column (heads 8nt + 2t, + 1): running maximum (shared by the warp), this lane's sum
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) { mcol[nt][0] = mcol[nt][1] = -INFINITY; lcol[nt][0] = lcol[nt][1] = 0.f; }
             const float sScale = (p.kScale ? p.kScale[kvh] : 1.0f) * p.scaleLog2;
 
             int cbase = -0x40000000, cval = 0;
@@ -571,40 +710,51 @@ __global__ void __launch_bounds__(kThreads, 1) paged_decode_fp8_kernel(DecodePar
                 }
                 return pg;
             };
-            // async copies of the 32 tokens starting at `ts` into stage `st` (rows past tokEnd are zero-filled)
-            auto issue = [&](int ts, int st) {
+            // async copies of the 32 tokens starting at `tsk` into stage `st` (rows past tokEnd are zero-filled)
+            auto issue = [&](int tsk, int st) {
                 const uint32_t dstK = wsmAddr + st * kStage8, dstV = dstK + kTile8 * kHeadDim;
-                const int c = lane & 7;
-                size_t halfOff[2] = {0, 0};
                 if (page16 || !table) {
                     const int ps = table ? p.pageSize : kTile;
+                    const bool full = tsk + kTile8 <= tokEnd;
 #pragma unroll
                     for (int h = 0; h < 2; h++) {
-                        const int tk = ts + h * kTile;
-                        halfOff[h] = tk < tokEnd ? ((size_t)page_of(tk / ps) * ps + (size_t)(tk % ps)) * tokenStride : 0;
-                    }
-                }
+                        const int tk = tsk + h * kTile;
+                        size_t halfOff = 0;
+                        if (tk < tokEnd) halfOff = ((size_t)page_of(tk / ps) * ps + (size_t)(tk % ps)) * tokenStride;
+                        const unsigned char* ks = kBase + halfOff + cpSrc;
+                        const unsigned char* vs = vBase + halfOff + cpSrc;
 #pragma unroll
-                for (int i = 0; i < 8; i++) {
-                    const int r = i * 4 + (lane >> 3);
-                    const int tok = ts + r;
-                    size_t off;
-                    if (page16 || !table) {
-                        off = halfOff[r >> 4] + (size_t)(r & 15) * tokenStride;
-                    } else {
+                        for (int i = 0; i < 4; i++) {
+                            const uint32_t so = (uint32_t)((h * 16 + (i >> 1) * 8) * 128) + ((i & 1) ? cpDstOdd : cpDstEven);
+                            const size_t rowOff = (size_t)(4 * i) * tokenStride;
+                            if (full) {
+                                cp_async16(dstK + so, ks + rowOff, 16);
+                                cp_async16(dstV + so, vs + rowOff, 16);
+                            } else {
+                                const bool live = tk + 4 * i + cpRow < tokEnd;
+                                cp_async16(dstK + so, live ? ks + rowOff : kBase, live ? 16 : 0);
+                                cp_async16(dstV + so, live ? vs + rowOff : vBase, live ? 16 : 0);
+                            }
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 8; i++) {
+                        const int r = i * 4 + cpRow;
+                        const int tok = tsk + r;
                         int pg = 0;
                         const int entry = tok / p.pageSize;
                         if (tok < tokEnd && entry < p.maxPages) {
                             pg = table[entry];
                             if (pg < 0 || pg >= p.pageCount) { atomicExch(p.errorFlag, 1); pg = 0; }
                         }
-                        off = ((size_t)pg * p.pageSize + tok % p.pageSize) * tokenStride;
+                        size_t off = ((size_t)pg * p.pageSize + tok % p.pageSize) * tokenStride;
+                        const int bytes = tok < tokEnd ? 16 : 0;
+                        if (bytes == 0) off = 0;
+                        const uint32_t so = r * 128 + ((cpChunk ^ (r & 7)) * 16);
+                        cp_async16(dstK + so, kBase + off + cpChunk * 16, bytes);
+                        cp_async16(dstV + so, vBase + off + cpChunk * 16, bytes);
                     }
-                    const int bytes = tok < tokEnd ? 16 : 0;
-                    if (bytes == 0) off = 0;
-                    const uint32_t so = r * 128 + ((c ^ (r & 7)) * 16);
-                    cp_async16(dstK + so, kBase + off + c * 16, bytes);
-                    cp_async16(dstV + so, vBase + off + c * 16, bytes);
                 }
             };
 
@@ -614,163 +764,179 @@ __global__ void __launch_bounds__(kThreads, 1) paged_decode_fp8_kernel(DecodePar
                 if (s < nSteps) issue(tok0 + s * kTile8, s);
                 cp_async_commit();
             }
+            int stage = 0;
             for (int it = 0; it < nSteps; it++) {
                 cp_async_wait<kStages8 - 2>();
                 __syncwarp();
                 {
                     const int nx = it + kStages8 - 1;
-                    if (nx < nSteps) issue(tok0 + nx * kTile8, nx % kStages8);
+                    int nst = stage + kStages8 - 1;
+                    if (nst >= kStages8) nst -= kStages8;
+                    if (nx < nSteps) issue(tok0 + nx * kTile8, nst);
                     cp_async_commit();
                 }
-                const uint32_t tileK = wsmAddr + (it % kStages8) * kStage8, tileV = tileK + kTile8 * kHeadDim;
-                // ---- S = Q K^T : 16 x 32, four n-tiles of 8 tokens, one f16 MMA per 16-dimension chunk ----
-                float s[4][4];
+                const uint32_t tileK = wsmAddr + stage * kStage8, tileV = tileK + kTile8 * kHeadDim;
+                if (++stage == kStages8) stage = 0;
+                // ---- S^T = K Q^T : 32 tokens x 8 heads per n-tile; two m-tiles of 16 tokens ----
+                float sacc[2][NT][4];
 #pragma unroll
-                for (int j = 0; j < 4; j++) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
-                {
-                    const int mi = lane >> 3, r = lane & 7;
+                for (int mt = 0; mt < 2; mt++)
 #pragma unroll
-                    for (int jp = 0; jp < 2; jp++) {
-                        const int tokr = (2 * jp + (mi >> 1)) * 8 + r;
+                    for (int nt = 0; nt < NT; nt++) sacc[mt][nt][0] = sacc[mt][nt][1] = sacc[mt][nt][2] = sacc[mt][nt][3] = 0.f;
 #pragma unroll
-                        for (int kk = 0; kk < 4; kk++) {
-                            const int chunk = 2 * kk + (mi & 1);
-                            uint32_t b0, b1, b2, b3;  // (tile 2jp, chunk 2kk), (2jp, 2kk+1), (2jp+1, 2kk), (2jp+1, 2kk+1)
-                            ldmatrix_x4(tileK + tokr * 128 + ((chunk ^ (tokr & 7)) * 16), b0, b1, b2, b3);
-                            mma16816<false>(s[2 * jp], qa[2 * kk], e4m3x2_to_f16x2(b0), e4m3x2_to_f16x2(b0 >> 16));
-                            mma16816<false>(s[2 * jp], qa[2 * kk + 1], e4m3x2_to_f16x2(b1), e4m3x2_to_f16x2(b1 >> 16));
-                            mma16816<false>(s[2 * jp + 1], qa[2 * kk], e4m3x2_to_f16x2(b2), e4m3x2_to_f16x2(b2 >> 16));
-                            mma16816<false>(s[2 * jp + 1], qa[2 * kk + 1], e4m3x2_to_f16x2(b3), e4m3x2_to_f16x2(b3 >> 16));
+                for (int mt = 0; mt < 2; mt++) {
+#pragma unroll
+                    for (int cp = 0; cp < 4; cp++) {
+                        uint32_t r0, r1, r2, r3;  // (tokens 0-7, chunk 2cp), (8-15, 2cp), (0-7, 2cp+1), (8-15, 2cp+1) of m-tile mt
+                        ldmatrix_x4(tileK + kLm + mt * (16 * 128) + (((2 * cp + (lmMat >> 1)) ^ lmRow) * 16), r0, r1, r2, r3);
+                        const uint32_t a0 = e4m3x2_lo(r0), a1 = e4m3x2_lo(r1), a2 = e4m3x2_hi(r0), a3 = e4m3x2_hi(r1);
+                        const uint32_t c0 = e4m3x2_lo(r2), c1 = e4m3x2_lo(r3), c2 = e4m3x2_hi(r2), c3 = e4m3x2_hi(r3);
+#pragma unroll
+                        for (int nt = 0; nt < NT; nt++) {
+                            mma16816_f16(sacc[mt][nt], a0, a1, a2, a3, qb[2 * cp][nt][0], qb[2 * cp][nt][1]);
+                            mma16816_f16(sacc[mt][nt], c0, c1, c2, c3, qb[2 * cp + 1][nt][0], qb[2 * cp + 1][nt][1]);
                         }
                     }
                 }
-                // ---- scale, mask, online softmax (log2 domain) ----
+                // ---- scale, mask, online softmax (log2 domain); sacc[mt][nt] = (token 16mt+g, heads 2t, 2t+1), (token 16mt+g+8, ...) ----
                 const int tokBase = tok0 + it * kTile8;
-                float pv[2][8];  // [row half][n-tile j * 2 + {0,1}]: tokens 8j + 2t + {0,1}
+                const bool tail = tokBase + kTile8 > tokEnd;
+                bool rescale = false;
+                float alpha[NT][2];
 #pragma unroll
-                for (int hrow = 0; hrow < 2; hrow++) {
-                    float mx = -INFINITY;
+                for (int nt = 0; nt < NT; nt++) {
 #pragma unroll
-                    for (int j = 0; j < 4; j++) {
+                    for (int j = 0; j < 2; j++) {
+                        float x[4];
 #pragma unroll
-                        for (int e = 0; e < 2; e++) {
-                            const int tok = tokBase + 8 * j + 2 * t + e;
-                            const float sc = tok < tokEnd ? s[j][2 * hrow + e] * sScale : -INFINITY;
-                            pv[hrow][2 * j + e] = sc;
-                            mx = fmaxf(mx, sc);
+                        for (int mt = 0; mt < 2; mt++) {
+#pragma unroll
+                            for (int r = 0; r < 2; r++) {
+                                float sc = sacc[mt][nt][2 * r + j] * sScale;
+                                if (tail && tokBase + 16 * mt + 8 * r + g >= tokEnd) sc = -INFINITY;
+                                x[2 * mt + r] = sc;
+                            }
                         }
-                    }
-                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-                    const float mNew = fmaxf(mrow[hrow], mx);
-                    const float alpha = (mNew == -INFINITY) ? 1.0f : exp2f(mrow[hrow] - mNew);
-                    float sum = 0.f;
+                        float mx = fmaxf(fmaxf(x[0], x[1]), fmaxf(x[2], x[3]));
+                        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+                        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+                        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+                        const float mNew = fmaxf(mcol[nt][j], mx);
+                        const float a = (mNew == -INFINITY) ? 1.0f : ex2_approx(mcol[nt][j] - mNew);
+                        const float base = (mNew == -INFINITY) ? 0.f : mNew;
+                        float sum = 0.f;
 #pragma unroll
-                    for (int c = 0; c < 8; c++) {
-                        const float e = (pv[hrow][c] == -INFINITY) ? 0.f : exp2f(pv[hrow][c] - mNew);
-                        sum += e;
-                        pv[hrow][c] = e;
-                    }
-                    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-                    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-                    lrow[hrow] = lrow[hrow] * alpha + sum;
-                    mrow[hrow] = mNew;
-                    if (alpha != 1.0f) {
-#pragma unroll
-                        for (int j = 0; j < 16; j++) {
-                            oacc[j][2 * hrow] *= alpha;
-                            oacc[j][2 * hrow + 1] *= alpha;
+                        for (int i = 0; i < 4; i++) {
+                            const float e = ex2_approx(x[i] - base);  // 2^-inf = 0 for masked tokens
+                            sum += e;
+                            sacc[i >> 1][nt][2 * (i & 1) + j] = e;
                         }
+                        lcol[nt][j] = lcol[nt][j] * a + sum;
+                        mcol[nt][j] = mNew;
+                        alpha[nt][j] = a;
+                        rescale |= a != 1.0f;
                     }
                 }
-                // ---- P as the f16 A operand of two k16 steps (tokens 0..15 and 16..31) ----
-                uint32_t pa[2][4];
+                if (__any_sync(0xffffffffu, rescale)) {
 #pragma unroll
-                for (int h2 = 0; h2 < 2; h2++) {
-                    pa[h2][0] = pack16<false>(pv[0][4 * h2], pv[0][4 * h2 + 1]);      // row g,   tokens 2t, 2t+1
-                    pa[h2][1] = pack16<false>(pv[1][4 * h2], pv[1][4 * h2 + 1]);      // row g+8
-                    pa[h2][2] = pack16<false>(pv[0][4 * h2 + 2], pv[0][4 * h2 + 3]);  // row g,   tokens 8+2t, 9+2t
-                    pa[h2][3] = pack16<false>(pv[1][4 * h2 + 2], pv[1][4 * h2 + 3]);
+                    for (int dt = 0; dt < 8; dt++)
+#pragma unroll
+                        for (int nt = 0; nt < NT; nt++) {
+                            oacc[dt][nt][0] *= alpha[nt][0];
+                            oacc[dt][nt][1] *= alpha[nt][1];
+                            oacc[dt][nt][2] *= alpha[nt][0];
+                            oacc[dt][nt][3] *= alpha[nt][1];
+                        }
                 }
-                // ---- O += P V: V bytes reach the same token order through ldmatrix.trans + byte permutes ----
-                {
-                    const int mi = lane >> 3, r = lane & 7;
-                    const int tokr = mi * 8 + r;
+                // ---- P^T as the f16 B operand: (token g, heads 2t, 2t+1) -> movmatrix -> (head g, tokens 2t, 2t+1) ----
+                uint32_t pb[2][NT][2];
 #pragma unroll
-                    for (int dg = 0; dg < 8; dg++) {
-                        uint32_t r0, r1, r2, r3;  // byte pairs of tokens 0-7, 8-15, 16-23, 24-31 at dimensions 16dg + 2g, +1
-                        ldmatrix_x4_trans(tileV + tokr * 128 + ((dg ^ (tokr & 7)) * 16), r0, r1, r2, r3);
-                        const uint32_t e0 = __byte_perm(r0, r1, 0x6420), o0 = __byte_perm(r0, r1, 0x7531);  // tokens {2t,2t+1,8+2t,9+2t}
-                        const uint32_t e1 = __byte_perm(r2, r3, 0x6420), o1 = __byte_perm(r2, r3, 0x7531);  // the same + 16
-                        mma16816<false>(oacc[2 * dg], pa[0], e4m3x2_to_f16x2(e0), e4m3x2_to_f16x2(e0 >> 16));
-                        mma16816<false>(oacc[2 * dg], pa[1], e4m3x2_to_f16x2(e1), e4m3x2_to_f16x2(e1 >> 16));
-                        mma16816<false>(oacc[2 * dg + 1], pa[0], e4m3x2_to_f16x2(o0), e4m3x2_to_f16x2(o0 >> 16));
-                        mma16816<false>(oacc[2 * dg + 1], pa[1], e4m3x2_to_f16x2(o1), e4m3x2_to_f16x2(o1 >> 16));
+                for (int mt = 0; mt < 2; mt++)
+#pragma unroll
+                    for (int nt = 0; nt < NT; nt++) {
+                        pb[mt][nt][0] = movmatrix_trans(pack16<false>(sacc[mt][nt][0], sacc[mt][nt][1]));  // tokens 16mt + 0..7
+                        pb[mt][nt][1] = movmatrix_trans(pack16<false>(sacc[mt][nt][2], sacc[mt][nt][3]));  // tokens 16mt + 8..15
+                    }
+                // ---- O^T += V^T P^T ----
+#pragma unroll
+                for (int dt = 0; dt < 8; dt++) {
+                    uint32_t r0, r1, r2, r3;  // byte pairs (dims 16dt + 2g, +1) of tokens 8j + 2t (low half) and 8j + 2t + 1 (high half)
+                    ldmatrix_x4_trans(tileV + vLm + ((dt ^ lmRow) * 16), r0, r1, r2, r3);
+                    {
+                        const uint32_t ev = __byte_perm(r0, r1, 0x6420), od = __byte_perm(r0, r1, 0x7531);
+                        const uint32_t a0 = e4m3x2_lo(ev), a1 = e4m3x2_lo(od), a2 = e4m3x2_hi(ev), a3 = e4m3x2_hi(od);
+#pragma unroll
+                        for (int nt = 0; nt < NT; nt++) mma16816_f16(oacc[dt][nt], a0, a1, a2, a3, pb[0][nt][0], pb[0][nt][1]);
+                    }
+                    {
+                        const uint32_t ev = __byte_perm(r2, r3, 0x6420), od = __byte_perm(r2, r3, 0x7531);
+                        const uint32_t a0 = e4m3x2_lo(ev), a1 = e4m3x2_lo(od), a2 = e4m3x2_hi(ev), a3 = e4m3x2_hi(od);
+#pragma unroll
+                        for (int nt = 0; nt < NT; nt++) mma16816_f16(oacc[dt][nt], a0, a1, a2, a3, pb[1][nt][0], pb[1][nt][1]);
                     }
                 }
             }
             cp_async_wait<0>();
             __syncwarp();
-            // ---- partial of (worker, sequence b): even/odd n-tiles interleave back into consecutive dimensions ----
+            // ---- partial of (worker, sequence b, KV head): row sums reduced over the lanes of a head column ----
             {
                 const long long slot = worker + b;
                 const float vS = p.vScale ? p.vScale[kvh] : 1.0f;
 #pragma unroll
-                for (int hrow = 0; hrow < 2; hrow++) {
-                    const int gi = g + 8 * hrow;
-                    if (gi < p.group) {
-                        const int head = kvh * p.group + gi;
-                        float* acc = p.partAcc + ((size_t)slot * p.numHeads + head) * kHeadDim;
+                for (int nt = 0; nt < NT; nt++) {
 #pragma unroll
-                        for (int dg = 0; dg < 8; dg++)
-                            *(float4*)(acc + 16 * dg + 4 * t) = make_float4(oacc[2 * dg][2 * hrow] * vS, oacc[2 * dg + 1][2 * hrow] * vS,
-                                                                            oacc[2 * dg][2 * hrow + 1] * vS, oacc[2 * dg + 1][2 * hrow + 1] * vS);
-                        if (t == 0) p.partML[(size_t)slot * p.numHeads + head] = make_float2(mrow[hrow], lrow[hrow]);
+                    for (int j = 0; j < 2; j++) {
+                        float l = lcol[nt][j];
+                        l += __shfl_xor_sync(0xffffffffu, l, 4);
+                        l += __shfl_xor_sync(0xffffffffu, l, 8);
+                        l += __shfl_xor_sync(0xffffffffu, l, 16);
+                        const int gi = nt * 8 + 2 * t + j;
+                        if (gi < p.group) {
+                            const int head = kvh * p.group + gi;
+                            float* acc = p.partAcc + ((size_t)slot * p.numHeads + head) * kHeadDim;
+#pragma unroll
+                            for (int dt = 0; dt < 8; dt++)
+                                *(float2*)(acc + 16 * dt + 2 * g) = make_float2(oacc[dt][nt][j] * vS, oacc[dt][nt][2 + j] * vS);
+                            if (g == 0) p.partML[(size_t)slot * p.numHeads + head] = make_float2(mcol[nt][j], l);
+                        }
                     }
                 }
             }
+            merge_if_last<BF16>(p, ts, b, kvh, lane);
             cur = segEnd;
             if (cur >= segEndAll) b++;
         }
     }
 }
 
-// merges the partials of each (sequence, head) and writes the output row in the storage dtype
-template <bool BF16>
-__global__ void __launch_bounds__(kHeadDim) decode_merge_kernel(DecodeParams p, void* __restrict__ out) {
-    const int b = blockIdx.x, head = blockIdx.y, d = threadIdx.x;
-    const long long T = p.tileStart[p.batch];
-    const long long s0 = p.tileStart[b], s1 = p.tileStart[b + 1];
-    if (s1 <= s0 || T == 0) return;  // empty context: row left untouched
-    const long long v0 = worker_of_tile(s0, T, p.workers), v1 = worker_of_tile(s1 - 1, T, p.workers);
-    float M = -INFINITY;
-    // workers whose own range is empty (fewer tiles than workers) never wrote a partial
-    auto owns = [&](long long v) { return (v + 1) * T / p.workers > v * T / p.workers; };
-    for (long long v = v0; v <= v1; v++)
-        if (owns(v)) M = fmaxf(M, p.partML[(size_t)(v + b) * p.numHeads + head].x);
-    float num = 0.f, den = 0.f;
-    for (long long v = v0; v <= v1; v++) {
-        if (!owns(v)) continue;
-        const float2 ml = p.partML[(size_t)(v + b) * p.numHeads + head];
-        const float w = (ml.x == -INFINITY) ? 0.f : exp2f(ml.x - M);
-        den += ml.y * w;
-        num += p.partAcc[((size_t)(v + b) * p.numHeads + head) * kHeadDim + d] * w;
-    }
-    const float o = den > 0.f ? num / den : 0.f;
-    uint16_t* orow = (uint16_t*)out + ((size_t)b * p.numHeads + head) * kHeadDim;
-    orow[d] = BF16 ? (uint16_t)f32_to_bf16_bits(o) : (uint16_t)f32_to_f16_bits(o);
+struct DecodeScratch {
+    char* base;        // partial accumulators, (max, sum) pairs [, tile prefix sums for large batches]
+    size_t bytes;      // capacity of `base`
+    int* counters;     // arrival counters
+    size_t counterBytes;
+    bool clearCounters;  // the counters are not known to be zero: clear them on the stream first
+};
+
+size_t decode_scratch_bytes(uint32_t batch, uint32_t numHeads, int workers) {
+    const size_t slots = (size_t)workers + batch;
+    const size_t accBytes = slots * numHeads * kHeadDim * sizeof(float);
+    const size_t mlBytes = ((slots * numHeads * sizeof(float2)) + 255) & ~(size_t)255;
+    const size_t prefBytes = batch > (uint32_t)kPrefixSmem ? (((size_t)batch + 1) * sizeof(int) + 255) & ~(size_t)255 : 0;
+    return accBytes + mlBytes + prefBytes;
 }
 
-// Host launcher shared by the paged entry point and the seqQ == 1 fast path of MultiHeadAttention.
-// pageTable == nullptr selects contiguous K/V ([ctx, kvHeads*128] per sequence, sequences seqStrideKV apart).
+// Host launcher shared by both paged entry points and the seqQ == 1 fast path of MultiHeadAttention.
+// pageTable == nullptr selects contiguous K/V ([ctx, kvHeads*128] per sequence, sequences seqStrideKV apart);
+// ctxLens == nullptr gives every sequence uniformCtx tokens.  `fixed` != nullptr supplies the scratch (nothing is
+// allocated); otherwise it comes from the context's grow-only workspace and counter block.
 int launch_paged_decode(Context* ctx, int dt, int kvDT, const void* q, const void* kPages, const void* vPages, const int32_t* pageTable,
-                        const int32_t* ctxLens, const float* kScale, const float* vScale, void* out, int* errorFlag, uint32_t batch,
-                        uint32_t maxPages, uint32_t pageCount, uint32_t pageSize, uint32_t numHeads, uint32_t kvHeads,
-                        long long seqStrideKV, long long totalTilesHint, CUDAStatus* status) {
+                        const int32_t* ctxLens, int uniformCtx, const float* kScale, const float* vScale, void* out, int* errorFlag,
+                        uint32_t batch, uint32_t maxPages, uint32_t pageCount, uint32_t pageSize, uint32_t numHeads, uint32_t kvHeads,
+                        long long seqStrideKV, long long totalTilesHint, const DecodeScratch* fixed, CUDAStatus* status) {
     const int group = (int)(numHeads / kvHeads);
     DecodeParams p{};
-    p.q = q; p.kPages = kPages; p.vPages = vPages; p.pageTable = pageTable; p.ctxLens = ctxLens;
-    p.kScale = kScale; p.vScale = vScale;
+    p.q = q; p.kPages = kPages; p.vPages = vPages; p.pageTable = pageTable; p.ctxLens = ctxLens; p.uniformCtx = uniformCtx;
+    p.kScale = kScale; p.vScale = vScale; p.out = out;
     p.errorFlag = errorFlag ? errorFlag : ctx->errorFlag;
     p.seqStrideKV = seqStrideKV;
     p.batch = (int)batch; p.maxPages = (int)maxPages; p.pageCount = (int)pageCount; p.pageSize = (int)pageSize;
@@ -790,46 +956,64 @@ int launch_paged_decode(Context* ctx, int dt, int kvDT, const void* q, const voi
 
     const size_t slots = (size_t)p.workers + batch;
     const size_t accBytes = slots * numHeads * kHeadDim * sizeof(float);
-    const size_t mlBytes = slots * numHeads * sizeof(float2);
-    const size_t prefBytes = ((size_t)batch + 1) * sizeof(long long);
-    char* ws = (char*)ensure_workspace(ctx, accBytes + mlBytes + prefBytes + 512, status);
-    if (!ws) return status ? status->code : -7;
+    const size_t mlBytes = ((slots * numHeads * sizeof(float2)) + 255) & ~(size_t)255;
+    const size_t need = decode_scratch_bytes(batch, numHeads, p.workers);
+    const size_t counterBytes = (size_t)batch * kvHeads * sizeof(int);
+    char* ws;
+    bool clear;
+    if (fixed) {
+        if (need > fixed->bytes || counterBytes > fixed->counterBytes)
+            return fail(status, -2, "paged decode attention: scratch of %zu + %zu bytes exceeds the %zu + %zu supplied", need, counterBytes,
+                        fixed->bytes, fixed->counterBytes);
+        ws = fixed->base;
+        p.counters = fixed->counters;
+        clear = fixed->clearCounters;
+    } else if (counterBytes <= ctx->decodeCounterBytes) {
+        ws = (char*)ensure_workspace(ctx, need + 512, status);
+        if (!ws) return status ? status->code : -7;
+        p.counters = ctx->decodeCounters;  // zero since the context was opened; every launch leaves them zero
+        clear = false;
+    } else {
+        const size_t cOff = (need + 255) & ~(size_t)255;
+        ws = (char*)ensure_workspace(ctx, cOff + counterBytes + 512, status);
+        if (!ws) return status ? status->code : -7;
+        p.counters = (int*)(ws + cOff);  // the workspace is shared with other ops: not known to be zero
+        clear = true;
+    }
     p.partAcc = (float*)ws;
     p.partML = (float2*)(ws + accBytes);
-    p.tileStart = (long long*)(ws + accBytes + ((mlBytes + 255) & ~(size_t)255));
-
-    decode_prefix_kernel<<<1, 1024, 0, ctx->stream>>>(ctxLens, (long long*)p.tileStart, (int)batch, pageTable ? (int)maxPages : 0,
-                                                       (int)pageSize, p.errorFlag);
-    int rc = check_launch(ctx, status, "decode prefix");
-    if (rc != 0) return rc;
+    if (clear && cudaMemsetAsync(p.counters, 0, counterBytes, ctx->stream) != cudaSuccess)
+        return fail(status, -7, "paged decode attention: clearing the arrival counters failed");
+    if (batch > (uint32_t)kPrefixSmem) {
+        int* tsG = (int*)(ws + accBytes + mlBytes);
+        decode_prefix_kernel<<<1, 1024, 0, ctx->stream>>>(p, tsG);
+        int rc = check_launch(ctx, status, "decode prefix");
+        if (rc != 0) return rc;
+        p.tileStart = tsG;
+    }
 
     const bool bf16 = dt == DT_BF16;
     const bool fp8 = kvDT == DT_E4M3;
-#define DECODE_LAUNCH(B, F, NSTAGE)                                                                                      \
-    do {                                                                                                                 \
-        constexpr int smem = DecodeSmem<B, F, NSTAGE>::kTotal;                                                           \
-        cudaFuncSetAttribute(paged_decode_kernel<B, F, NSTAGE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); \
-        paged_decode_kernel<B, F, NSTAGE, true><<<(unsigned)ctas, kThreads, smem, ctx->stream>>>(p);                     \
+#define DECODE_LAUNCH(KERNEL, SMEM)                                                             \
+    do {                                                                                        \
+        cudaFuncSetAttribute(KERNEL, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(SMEM)); \
+        KERNEL<<<(unsigned)ctas, kThreads, SMEM, ctx->stream>>>(p);                             \
     } while (0)
     if (fp8) {
-        if (bf16) {
-            cudaFuncSetAttribute(paged_decode_fp8_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem8);
-            paged_decode_fp8_kernel<true><<<(unsigned)ctas, kThreads, kSmem8, ctx->stream>>>(p);
+        if (group <= 8) {
+            if (bf16) DECODE_LAUNCH((paged_decode_fp8_kernel<true, 1>), kSmem8);
+            else DECODE_LAUNCH((paged_decode_fp8_kernel<false, 1>), kSmem8);
         } else {
-            cudaFuncSetAttribute(paged_decode_fp8_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem8);
-            paged_decode_fp8_kernel<false><<<(unsigned)ctas, kThreads, kSmem8, ctx->stream>>>(p);
+            if (bf16) DECODE_LAUNCH((paged_decode_fp8_kernel<true, 2>), kSmem8);
+            else DECODE_LAUNCH((paged_decode_fp8_kernel<false, 2>), kSmem8);
         }
     } else {
-        if (bf16) DECODE_LAUNCH(true, false, 3);
-        else DECODE_LAUNCH(false, false, 3);
+        constexpr int smem16 = DecodeSmem<true, false, 3>::kTotal;
+        if (bf16) DECODE_LAUNCH((paged_decode_kernel<true, false, 3, true>), smem16);
+        else DECODE_LAUNCH((paged_decode_kernel<false, false, 3, true>), smem16);
     }
 #undef DECODE_LAUNCH
-    rc = check_launch(ctx, status, "paged decode attention");
-    if (rc != 0) return rc;
-    dim3 mgrid(batch, numHeads);
-    if (bf16) decode_merge_kernel<true><<<mgrid, kHeadDim, 0, ctx->stream>>>(p, out);
-    else decode_merge_kernel<false><<<mgrid, kHeadDim, 0, ctx->stream>>>(p, out);
-    return check_launch(ctx, status, "decode merge");
+    return check_launch(ctx, status, "paged decode attention");
 }
 
 bool decode_supported(int dt, int kvDT, uint32_t numHeads, uint32_t kvHeads, uint32_t headDim) {
@@ -839,66 +1023,22 @@ bool decode_supported(int dt, int kvDT, uint32_t numHeads, uint32_t kvHeads, uin
     return numHeads / kvHeads <= 16;
 }
 
-}  // namespace puter
-
-using namespace puter;
-
-extern "C" int cuda_dispatch_paged_decode_attention(CUDADeviceRef contextRef, int elementDType, int kvDType, CUDABufferRef queryRef,
-                                                    CUDABufferRef kPagesRef, CUDABufferRef vPagesRef, CUDABufferRef pageTableRef,
-                                                    CUDABufferRef ctxLensRef, CUDABufferRef kScaleRef, CUDABufferRef vScaleRef,
-                                                    CUDABufferRef outRef, CUDABufferRef errorFlagRef, uint32_t batch, uint32_t maxPagesPerSeq,
-                                                    uint32_t pageCount, uint32_t pageSize, uint32_t numHeads, uint32_t kvHeads,
-                                                    uint32_t headDim, uint64_t completionToken, CUDAStatus* status) {
-    (void)completionToken;
-    PUTER_ENTER(ctx);
-    if (batch == 0 || numHeads == 0) return ok(status);
-    if (kvHeads == 0) kvHeads = numHeads;
-    if (!decode_supported(elementDType, kvDType, numHeads, kvHeads, headDim))
-        return fail(status, -6,
-                    "paged decode attention: supported are bf16/f16 queries, KV pages of the same type or fp8-e4m3, head_dim 128, "
-                    "<= 16 query heads per KV head (got dtype %d, kv dtype %d, heads %u/%u, head_dim %u)",
-                    elementDType, kvDType, numHeads, kvHeads, headDim);
-    if (pageSize == 0 || pageCount == 0 || maxPagesPerSeq == 0) return fail(status, -2, "paged decode attention: empty page geometry");
-    const size_t kvEs = dtype_size(kvDType);
-    const size_t poolBytes = (size_t)pageCount * pageSize * kvHeads * headDim * kvEs;
-    PUTER_REQUIRE(queryRef, "query", (size_t)batch * numHeads * headDim * 2);
-    PUTER_REQUIRE(outRef, "out", (size_t)batch * numHeads * headDim * 2);
-    PUTER_REQUIRE(kPagesRef, "kPages", poolBytes);
-    PUTER_REQUIRE(vPagesRef, "vPages", poolBytes);
-    PUTER_REQUIRE(pageTableRef, "pageTable", (size_t)batch * maxPagesPerSeq * 4);
-    PUTER_REQUIRE(ctxLensRef, "ctxLens", (size_t)batch * 4);
-    const float* ks = nullptr;
-    const float* vs = nullptr;
-    if (kvDType == DT_E4M3 && kvDType != elementDType) {
-        if (kScaleRef) { PUTER_REQUIRE(kScaleRef, "kScale", (size_t)kvHeads * 4); ks = (const float*)dev_ptr(kScaleRef); }
-        if (vScaleRef) { PUTER_REQUIRE(vScaleRef, "vScale", (size_t)kvHeads * 4); vs = (const float*)dev_ptr(vScaleRef); }
-    }
-    int* flag = nullptr;
-    if (errorFlagRef) { PUTER_REQUIRE(errorFlagRef, "errorFlag", 4); flag = (int*)dev_ptr(errorFlagRef); }
-    if ((((uintptr_t)dev_ptr(kPagesRef) | (uintptr_t)dev_ptr(vPagesRef)) & 15u) != 0 || ((uintptr_t)dev_ptr(queryRef) & 3u) != 0)
-        return fail(status, -2, "paged decode attention: K/V pools must be 16-byte aligned");
-    return launch_paged_decode(ctx, elementDType, kvDType, dev_ptr(queryRef), dev_ptr(kPagesRef), dev_ptr(vPagesRef),
-                               (const int32_t*)dev_ptr(pageTableRef), (const int32_t*)dev_ptr(ctxLensRef), ks, vs, dev_ptr(outRef), flag,
-                               batch, maxPagesPerSeq, pageCount, pageSize, numHeads, kvHeads, 0, -1, status);
-}
-
 // ---------------------------------------------------------------------------------------------------------
-// Allocation-free variant of paged decode attention.
+// Fixed scratch of the allocation-free entry point.
 //
 // Some hosts may not allocate device memory at the moment they need to run a decode step: a serving loop
 // whose memory is fully pre-planned and handed out by its own arena (so a hidden cudaMalloc would either
 // fail or fragment the plan), a caller inside a latency-critical section where the implicit device
 // synchronisation of cudaMalloc/cudaFree is not acceptable, or an embedding runtime that forbids driver
 // allocations after start-up.  The regular entry point keeps its split-KV partials in a grow-only workspace
-// that it allocates on demand; this one keeps them in a fixed array that is part of the library image.
+// that it allocates on demand; the allocation-free one keeps them in a fixed array that is part of the
+// library image.
 //
 // The array lives in device memory of every GPU that loads the library, for the life of the process
 // (kStaticScratchBytes per GPU).  In host code the symbol below is only a stand-in: its device address is
 // obtained once per device with cudaGetSymbolAddress, with that device current, and that pointer is what
 // the kernels receive.
 // ---------------------------------------------------------------------------------------------------------
-namespace puter {
-
 static constexpr size_t kStaticScratchBytes = 8u << 20;  // 8 MiB per GPU
 static __device__ __align__(256) unsigned char g_decodeStaticScratch[kStaticScratchBytes];
 
@@ -926,34 +1066,22 @@ static void* static_scratch_for(Context* ctx, CUDAStatus* status) {
     return g_staticScratchPtr[ctx->device];
 }
 
-}  // namespace puter
-
-// Same operation and arguments as cuda_dispatch_paged_decode_attention, with the split-KV scratch in the
-// library's fixed per-GPU array instead of an allocated workspace.  Calls no cudaMalloc / cudaFree and no
-// allocating library routine.  Problems whose partials do not fit kStaticScratchBytes are refused with -2
-// (with 32 query heads on a 148-SM GPU the limit is a batch of 355 sequences).
-//
-// The first call on a device resolves the array's device address (cudaGetSymbolAddress); make that first
-// call outside of any stream capture.  Every call on a GPU shares the one array: two calls whose kernels
-// can overlap on that GPU (different streams, or different contexts of the same device) race on it, so
-// keep them stream-ordered.  Nothing has to start at zero: every scratch word a call reads is written
-// earlier in the same call, so the previous call's contents are simply overwritten.
-extern "C" int cuda_dispatch_paged_decode_attention_noalloc(CUDADeviceRef contextRef, int elementDType, int kvDType, CUDABufferRef queryRef,
-                                                            CUDABufferRef kPagesRef, CUDABufferRef vPagesRef, CUDABufferRef pageTableRef,
-                                                            CUDABufferRef ctxLensRef, CUDABufferRef kScaleRef, CUDABufferRef vScaleRef,
-                                                            CUDABufferRef outRef, CUDABufferRef errorFlagRef, uint32_t batch,
-                                                            uint32_t maxPagesPerSeq, uint32_t pageCount, uint32_t pageSize, uint32_t numHeads,
-                                                            uint32_t kvHeads, uint32_t headDim, uint64_t completionToken, CUDAStatus* status) {
-    (void)completionToken;
+// Both paged entry points: validation, then the shared launcher (with the fixed array when noalloc).
+static int paged_decode_entry(bool noalloc, CUDADeviceRef contextRef, int elementDType, int kvDType, CUDABufferRef queryRef,
+                              CUDABufferRef kPagesRef, CUDABufferRef vPagesRef, CUDABufferRef pageTableRef, CUDABufferRef ctxLensRef,
+                              CUDABufferRef kScaleRef, CUDABufferRef vScaleRef, CUDABufferRef outRef, CUDABufferRef errorFlagRef,
+                              uint32_t batch, uint32_t maxPagesPerSeq, uint32_t pageCount, uint32_t pageSize, uint32_t numHeads,
+                              uint32_t kvHeads, uint32_t headDim, CUDAStatus* status) {
     PUTER_ENTER(ctx);
+    const char* what = noalloc ? "paged decode attention (no-alloc)" : "paged decode attention";
     if (batch == 0 || numHeads == 0) return ok(status);
     if (kvHeads == 0) kvHeads = numHeads;
     if (!decode_supported(elementDType, kvDType, numHeads, kvHeads, headDim))
         return fail(status, -6,
-                    "paged decode attention (no-alloc): supported are bf16/f16 queries, KV pages of the same type or fp8-e4m3, head_dim 128, "
+                    "%s: supported are bf16/f16 queries, KV pages of the same type or fp8-e4m3, head_dim 128, "
                     "<= 16 query heads per KV head (got dtype %d, kv dtype %d, heads %u/%u, head_dim %u)",
-                    elementDType, kvDType, numHeads, kvHeads, headDim);
-    if (pageSize == 0 || pageCount == 0 || maxPagesPerSeq == 0) return fail(status, -2, "paged decode attention (no-alloc): empty page geometry");
+                    what, elementDType, kvDType, numHeads, kvHeads, headDim);
+    if (pageSize == 0 || pageCount == 0 || maxPagesPerSeq == 0) return fail(status, -2, "%s: empty page geometry", what);
     const size_t kvEs = dtype_size(kvDType);
     const size_t poolBytes = (size_t)pageCount * pageSize * kvHeads * headDim * kvEs;
     PUTER_REQUIRE(queryRef, "query", (size_t)batch * numHeads * headDim * 2);
@@ -968,69 +1096,69 @@ extern "C" int cuda_dispatch_paged_decode_attention_noalloc(CUDADeviceRef contex
         if (kScaleRef) { PUTER_REQUIRE(kScaleRef, "kScale", (size_t)kvHeads * 4); ks = (const float*)dev_ptr(kScaleRef); }
         if (vScaleRef) { PUTER_REQUIRE(vScaleRef, "vScale", (size_t)kvHeads * 4); vs = (const float*)dev_ptr(vScaleRef); }
     }
-    int* flag = ctx->errorFlag;
+    int* flag = nullptr;
     if (errorFlagRef) { PUTER_REQUIRE(errorFlagRef, "errorFlag", 4); flag = (int*)dev_ptr(errorFlagRef); }
-    if ((((uintptr_t)dev_ptr(kPagesRef) | (uintptr_t)dev_ptr(vPagesRef)) & 15u) != 0 || ((uintptr_t)dev_ptr(queryRef) & 3u) != 0)
-        return fail(status, -2, "paged decode attention (no-alloc): K/V pools must be 16-byte aligned");
-
-    DecodeParams p{};
-    p.q = dev_ptr(queryRef); p.kPages = dev_ptr(kPagesRef); p.vPages = dev_ptr(vPagesRef);
-    p.pageTable = (const int32_t*)dev_ptr(pageTableRef); p.ctxLens = (const int32_t*)dev_ptr(ctxLensRef);
-    p.kScale = ks; p.vScale = vs; p.errorFlag = flag; p.seqStrideKV = 0;
-    p.batch = (int)batch; p.maxPages = (int)maxPagesPerSeq; p.pageCount = (int)pageCount; p.pageSize = (int)pageSize;
-    p.numHeads = (int)numHeads; p.kvHeads = (int)kvHeads; p.group = (int)(numHeads / kvHeads);
-    p.headsPerPass = kvHeads < (uint32_t)kWarps ? (int)kvHeads : kWarps;
-    p.groups = kWarps / p.headsPerPass;
-    const long long ctas = ctx->smCount;
-    p.workers = (int)(ctas * p.groups);
-    p.scale = (float)(1.0 / sqrt((double)kHeadDim));
-    p.scaleLog2 = p.scale * 1.4426950408889634f;
-
-    // carve the fixed array: accumulators, (max, sum) pairs, tile prefix sums
-    const size_t slots = (size_t)p.workers + batch;
-    const size_t accBytes = slots * numHeads * kHeadDim * sizeof(float);
-    const size_t mlBytes = ((slots * numHeads * sizeof(float2)) + 255) & ~(size_t)255;
-    const size_t prefBytes = ((size_t)batch + 1) * sizeof(long long);
-    const size_t need = accBytes + mlBytes + prefBytes;
-    if (need > kStaticScratchBytes)
-        return fail(status, -2,
-                    "paged decode attention (no-alloc): batch %u with %u query heads needs %zu bytes of split-KV scratch, the fixed "
-                    "per-GPU array holds %zu; use cuda_dispatch_paged_decode_attention or a smaller batch",
-                    batch, numHeads, need, kStaticScratchBytes);
-    char* ws = (char*)static_scratch_for(ctx, status);
-    if (!ws) return status ? status->code : -7;
-    p.partAcc = (float*)ws;
-    p.partML = (float2*)(ws + accBytes);
-    p.tileStart = (long long*)(ws + accBytes + mlBytes);
-
-    decode_prefix_kernel<<<1, 1024, 0, ctx->stream>>>(p.ctxLens, (long long*)p.tileStart, (int)batch, (int)maxPagesPerSeq, (int)pageSize, p.errorFlag);
-    int rc = check_launch(ctx, status, "decode prefix");
-    if (rc != 0) return rc;
-    const bool bf16 = elementDType == DT_BF16;
-    const bool fp8 = kvDType == DT_E4M3;
-#define DECODE_LAUNCH(B, F, NSTAGE)                                                                                      \
-    do {                                                                                                                 \
-        constexpr int smem = DecodeSmem<B, F, NSTAGE>::kTotal;                                                           \
-        cudaFuncSetAttribute(paged_decode_kernel<B, F, NSTAGE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); \
-        paged_decode_kernel<B, F, NSTAGE, true><<<(unsigned)ctas, kThreads, smem, ctx->stream>>>(p);                     \
-    } while (0)
-    if (fp8) {
-        if (bf16) {
-            cudaFuncSetAttribute(paged_decode_fp8_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem8);
-            paged_decode_fp8_kernel<true><<<(unsigned)ctas, kThreads, kSmem8, ctx->stream>>>(p);
-        } else {
-            cudaFuncSetAttribute(paged_decode_fp8_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem8);
-            paged_decode_fp8_kernel<false><<<(unsigned)ctas, kThreads, kSmem8, ctx->stream>>>(p);
-        }
-    } else {
-        if (bf16) DECODE_LAUNCH(true, false, 3);
-        else DECODE_LAUNCH(false, false, 3);
+    if ((((uintptr_t)dev_ptr(kPagesRef) | (uintptr_t)dev_ptr(vPagesRef)) & 15u) != 0 || ((uintptr_t)dev_ptr(queryRef) & 7u) != 0 ||
+        ((uintptr_t)dev_ptr(outRef) & 7u) != 0)
+        return fail(status, -2, "%s: K/V pools must be 16-byte aligned, query and output rows 8-byte aligned", what);
+    DecodeScratch fixed{};
+    if (noalloc) {
+        // carve the fixed array: arrival counters at its end (cleared on the stream before every launch: an earlier call with
+        // another geometry may have left partials there), everything else from its start
+        const int workers = ctx->smCount * (kWarps / (kvHeads < (uint32_t)kWarps ? (int)kvHeads : kWarps));
+        const size_t need = decode_scratch_bytes(batch, numHeads, workers);
+        const size_t counterBytes = (((size_t)batch * kvHeads * sizeof(int)) + 255) & ~(size_t)255;
+        if (need + counterBytes > kStaticScratchBytes)
+            return fail(status, -2,
+                        "%s: batch %u with %u query heads needs %zu bytes of split-KV scratch, the fixed per-GPU array holds %zu; "
+                        "use cuda_dispatch_paged_decode_attention or a smaller batch",
+                        what, batch, numHeads, need + counterBytes, kStaticScratchBytes);
+        char* base = (char*)static_scratch_for(ctx, status);
+        if (!base) return status ? status->code : -7;
+        fixed.base = base;
+        fixed.bytes = kStaticScratchBytes - counterBytes;
+        fixed.counters = (int*)(base + kStaticScratchBytes - counterBytes);
+        fixed.counterBytes = counterBytes;
+        fixed.clearCounters = true;
     }
-#undef DECODE_LAUNCH
-    rc = check_launch(ctx, status, "paged decode attention (no-alloc)");
-    if (rc != 0) return rc;
-    dim3 mgrid(batch, numHeads);
-    if (bf16) decode_merge_kernel<true><<<mgrid, kHeadDim, 0, ctx->stream>>>(p, dev_ptr(outRef));
-    else decode_merge_kernel<false><<<mgrid, kHeadDim, 0, ctx->stream>>>(p, dev_ptr(outRef));
-    return check_launch(ctx, status, "decode merge");
+    return launch_paged_decode(ctx, elementDType, kvDType, dev_ptr(queryRef), dev_ptr(kPagesRef), dev_ptr(vPagesRef),
+                               (const int32_t*)dev_ptr(pageTableRef), (const int32_t*)dev_ptr(ctxLensRef), 0, ks, vs, dev_ptr(outRef), flag,
+                               batch, maxPagesPerSeq, pageCount, pageSize, numHeads, kvHeads, 0, -1, noalloc ? &fixed : nullptr, status);
+}
+
+}  // namespace puter
+
+using namespace puter;
+
+extern "C" int cuda_dispatch_paged_decode_attention(CUDADeviceRef contextRef, int elementDType, int kvDType, CUDABufferRef queryRef,
+                                                    CUDABufferRef kPagesRef, CUDABufferRef vPagesRef, CUDABufferRef pageTableRef,
+                                                    CUDABufferRef ctxLensRef, CUDABufferRef kScaleRef, CUDABufferRef vScaleRef,
+                                                    CUDABufferRef outRef, CUDABufferRef errorFlagRef, uint32_t batch, uint32_t maxPagesPerSeq,
+                                                    uint32_t pageCount, uint32_t pageSize, uint32_t numHeads, uint32_t kvHeads,
+                                                    uint32_t headDim, uint64_t completionToken, CUDAStatus* status) {
+    (void)completionToken;
+    return paged_decode_entry(false, contextRef, elementDType, kvDType, queryRef, kPagesRef, vPagesRef, pageTableRef, ctxLensRef, kScaleRef,
+                              vScaleRef, outRef, errorFlagRef, batch, maxPagesPerSeq, pageCount, pageSize, numHeads, kvHeads, headDim, status);
+}
+
+// Same operation and arguments as cuda_dispatch_paged_decode_attention, with the split-KV scratch in the
+// library's fixed per-GPU array instead of an allocated workspace.  Calls no cudaMalloc / cudaFree and no
+// allocating library routine.  Problems whose partials do not fit kStaticScratchBytes are refused with -2
+// (with 32 query heads over 8 KV heads on a 148-SM GPU the limit is a batch of 355 sequences).
+//
+// The first call on a device resolves the array's device address (cudaGetSymbolAddress); make that first
+// call outside of any stream capture.  Every call on a GPU shares the one array: two calls whose kernels
+// can overlap on that GPU (different streams, or different contexts of the same device) race on it, so
+// keep them stream-ordered.  The array keeps the previous call's contents; the only words that must start
+// at zero, the arrival counters, are cleared on the stream at the start of every call, and every other
+// scratch word a call reads is written earlier in the same call.
+extern "C" int cuda_dispatch_paged_decode_attention_noalloc(CUDADeviceRef contextRef, int elementDType, int kvDType, CUDABufferRef queryRef,
+                                                            CUDABufferRef kPagesRef, CUDABufferRef vPagesRef, CUDABufferRef pageTableRef,
+                                                            CUDABufferRef ctxLensRef, CUDABufferRef kScaleRef, CUDABufferRef vScaleRef,
+                                                            CUDABufferRef outRef, CUDABufferRef errorFlagRef, uint32_t batch,
+                                                            uint32_t maxPagesPerSeq, uint32_t pageCount, uint32_t pageSize, uint32_t numHeads,
+                                                            uint32_t kvHeads, uint32_t headDim, uint64_t completionToken, CUDAStatus* status) {
+    (void)completionToken;
+    return paged_decode_entry(true, contextRef, elementDType, kvDType, queryRef, kPagesRef, vPagesRef, pageTableRef, ctxLensRef, kScaleRef,
+                              vScaleRef, outRef, errorFlagRef, batch, maxPagesPerSeq, pageCount, pageSize, numHeads, kvHeads, headDim, status);
 }

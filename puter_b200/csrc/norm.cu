@@ -86,8 +86,14 @@ struct RowArgs {
     double eps;
 };
 
+// read-once input: through the non-coherent path, unless an output of the same launch aliases an input (in-place use)
+template <bool INPLACE> __device__ __forceinline__ Vec16 ld_in(const void* p) { return INPLACE ? *(const Vec16*)p : ld_stream(p); }
+
 // MAXV 16-byte vectors per thread are cached in registers; rows longer than MAXV*blockDim vectors re-read.
-template <int DT, int MAXV, bool FUSED>
+// INPLACE: an output is the same buffer as x or residual (an in-place residual stream).  Every element is then read by
+// the one thread that later writes it, before it writes it; inputs are read with plain loads, and the second pass over
+// the vectors beyond the register cache takes x + residual from hOut (already stored) instead of adding again.
+template <int DT, int MAXV, bool FUSED, bool INPLACE>
 __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(RowArgs a) {
     constexpr int PER = Lanes<DT>::kPer;
     constexpr size_t ES = DT == DT_F32 ? 4 : 2;
@@ -106,12 +112,12 @@ __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(RowArgs a) {
         for (int i = 0; i < MAXV; i++) {
             size_t v = threadIdx.x + (size_t)i * blockDim.x;
             if (v < nvec) {
-                Vec16 in = ld_stream(xr + v * 16);
-                if (gated) cacheB[i] = ld_stream((const char*)a.branch + row * a.cols * ES + v * 16);
+                Vec16 in = ld_in<INPLACE>(xr + v * 16);
+                if (gated) cacheB[i] = ld_stream((const char*)a.branch + row * a.cols * ES + v * 16);  // never aliased (checked by the host)
                 float f[PER];
                 unpack<DT>(in, f);
                 if (FUSED) {
-                    Vec16 rin = ld_stream(rr + v * 16);
+                    Vec16 rin = ld_in<INPLACE>(rr + v * 16);
                     float g[PER];
                     unpack<DT>(rin, g);
                     if (DT == DT_F32) {
@@ -186,7 +192,9 @@ __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(RowArgs a) {
         }
         for (size_t v = threadIdx.x + (size_t)MAXV * blockDim.x; v < nvec; v += blockDim.x) {
             Vec16 hv;
-            if (FUSED) {
+            if (FUSED && INPLACE && a.hOut) {
+                hv = *(const Vec16*)((const char*)a.hOut + row * a.cols * ES + v * 16);  // stored by this thread in the first pass
+            } else if (FUSED) {
                 float f[PER], g[PER];
                 unpack<DT>(*(const Vec16*)(xr + v * 16), f);
                 unpack<DT>(*(const Vec16*)(rr + v * 16), g);
@@ -343,19 +351,49 @@ static int launch_rows(Context* ctx, const RowArgs& a, CUDAStatus* status) {
     size_t cap = (size_t)ctx->smCount * 16;
     int grid = (int)(a.rows < cap ? a.rows : cap);
     const size_t nvec = a.cols / PER;
+    const void* outs[3] = {a.hOut, a.normOut, a.gatedOut};
+    bool inplace = false;
+    for (const void* o : outs) inplace |= o && (o == a.x || o == a.residual);
     // measured at 16384 x 4096 bf16: plain RMSNorm 4.49 TB/s warp-per-row vs 4.05 block-per-row; the fused form needs twice the
     // registers per lane, fits one block per SM and is faster block-per-row (4.49 vs 3.27 TB/s)
-    if (!FUSED && vec && nvec <= 512 && nvec >= 128 && a.rows >= 64) {
+    if (inplace && vec) rmsnorm_rows_kernel<DT, 4, FUSED, true><<<grid, 256, 0, ctx->stream>>>(a);
+    else if (!FUSED && vec && nvec <= 512 && nvec >= 128 && a.rows >= 64) {
         size_t blocks = (a.rows + 7) / 8, capW = (size_t)ctx->smCount * 4;
         rmsnorm_warp_rows_kernel<DT, FUSED><<<(unsigned)(blocks < capW ? blocks : capW), 256, 0, ctx->stream>>>(a);
-    } else if (vec && nvec <= 2 * 256) rmsnorm_rows_kernel<DT, 2, FUSED><<<grid, 256, 0, ctx->stream>>>(a);  // fewer registers, more rows in flight
-    else if (vec) rmsnorm_rows_kernel<DT, 4, FUSED><<<grid, 256, 0, ctx->stream>>>(a);
-    else rmsnorm_rows_scalar_kernel<DT, FUSED><<<grid, 256, 0, ctx->stream>>>(a);
+    } else if (vec && nvec <= 2 * 256) rmsnorm_rows_kernel<DT, 2, FUSED, false><<<grid, 256, 0, ctx->stream>>>(a);  // fewer registers, more rows in flight
+    else if (vec) rmsnorm_rows_kernel<DT, 4, FUSED, false><<<grid, 256, 0, ctx->stream>>>(a);
+    else rmsnorm_rows_scalar_kernel<DT, FUSED><<<grid, 256, 0, ctx->stream>>>(a);  // plain loads, element by element: in-place safe
     return check_launch(ctx, status, FUSED ? "add+rmsnorm+gated residual" : "rmsnorm");
+}
+
+// Aliasing rules of the row kernels: an output may be exactly the buffer of x or of residual (in-place); it may not
+// overlap them partially, may not overlap scale, branch or modulation at all, and two outputs may not overlap each other.
+static int check_row_aliasing(CUDAStatus* status, const RowArgs& a, size_t es) {
+    const size_t bytes = a.rows * a.cols * es;
+    auto overlap = [](const void* p, size_t pn, const void* q, size_t qn) {
+        return p && q && (const char*)p < (const char*)q + qn && (const char*)q < (const char*)p + pn;
+    };
+    const void* outs[3] = {a.hOut, a.normOut, a.gatedOut};
+    const char* names[3] = {"hOut", "normOut", "gatedOut"};
+    const size_t batches = a.rowsPerBatch ? (a.rows + a.rowsPerBatch - 1) / a.rowsPerBatch : 0;
+    for (int i = 0; i < 3; i++) {
+        if (!outs[i]) continue;
+        for (const void* in : {a.x, a.residual})
+            if (in != outs[i] && overlap(outs[i], bytes, in, bytes))
+                return fail(status, -2, "rmsnorm: %s partially overlaps an input (only the exact same buffer may be reused in place)", names[i]);
+        if (overlap(outs[i], bytes, a.scale, a.cols * es) || overlap(outs[i], bytes, a.branch, bytes) ||
+            overlap(outs[i], bytes, a.mod, batches * a.modCols * es))
+            return fail(status, -2, "rmsnorm: %s overlaps scale, branch or modulation", names[i]);
+        for (int j = i + 1; j < 3; j++)
+            if (overlap(outs[i], bytes, outs[j], bytes)) return fail(status, -2, "rmsnorm: %s and %s overlap", names[i], names[j]);
+    }
+    return 0;
 }
 
 template <bool FUSED>
 static int dispatch_rows(Context* ctx, int dt, const RowArgs& a, CUDAStatus* status) {
+    int rc = check_row_aliasing(status, a, dtype_size(dt));
+    if (rc != 0) return rc;
     if (dt == DT_F32) return launch_rows<DT_F32, FUSED>(ctx, a, status);
     if (dt == DT_BF16) return launch_rows<DT_BF16, FUSED>(ctx, a, status);
     if (dt == DT_F16) return launch_rows<DT_F16, FUSED>(ctx, a, status);

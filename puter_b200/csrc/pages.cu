@@ -8,6 +8,8 @@
 // Page ids / offsets outside the valid range make the CPU op fail before touching memory; on the device such
 // rows are never dereferenced: they are skipped and a device-side error flag is raised, which the host reads
 // at the next synchronisation.  Pure byte movement: 16-byte vectors when rows allow, any dtype by element size.
+// Two value rows aimed at the same (page, offset) in one write race with each other (the CPU loop keeps the
+// last one); a KV cache never does that, and callers that might must split the write.
 #include "common.cuh"
 
 namespace puter {

@@ -125,6 +125,13 @@ int cuda_open_device_index(int ordinal, CUDADeviceRef* outDevice, CUDAStatus* st
         return fail(status, -7, "cuda: context allocation failed");
     }
     cudaMemset(ctx->errorFlag, 0, 256);
+    ctx->decodeCounterBytes = 64 << 10;
+    if (cudaMalloc((void**)&ctx->decodeCounters, ctx->decodeCounterBytes) != cudaSuccess) {
+        cudaFree(ctx->errorFlag);
+        delete ctx;
+        return fail(status, -7, "cuda: context allocation failed");
+    }
+    cudaMemset(ctx->decodeCounters, 0, ctx->decodeCounterBytes);
     *outDevice = ctx;
     std::lock_guard<std::mutex> lock(g_mu);
     if (!g_default) g_default = ctx;
@@ -143,6 +150,7 @@ void cuda_close_device(CUDADeviceRef device) {
     for (int i = 0; i < 2; i++)
         if (ctx->pinned[i]) cudaFreeHost(ctx->pinned[i]);
     if (ctx->errorFlag) cudaFree(ctx->errorFlag);
+    if (ctx->decodeCounters) cudaFree(ctx->decodeCounters);
     if (ctx->ropeTable) cudaFree(ctx->ropeTable);
     for (int i = 0; i < 4; i++)
         if (ctx->stageEvents[i]) cudaEventDestroy(ctx->stageEvents[i]);
@@ -218,6 +226,8 @@ int cuda_memcpy_async_d2d(CUDABufferRef dst, CUDABufferRef src, long long bytes,
     if (!dst || !src) return fail(status, -2, "cuda: nil buffer in d2d copy");
     Buffer* d = (Buffer*)dst;
     Buffer* s = (Buffer*)src;
+    if (d->bytes >= 0 && bytes > d->bytes) return fail(status, -2, "cuda: d2d copy of %lld bytes exceeds the destination (%lld)", bytes, d->bytes);
+    if (s->bytes >= 0 && bytes > s->bytes) return fail(status, -2, "cuda: d2d copy of %lld bytes exceeds the source (%lld)", bytes, s->bytes);
     cudaSetDevice(d->device);
     cudaError_t err = cudaMemcpyAsync(d->ptr, s->ptr, (size_t)bytes, cudaMemcpyDeviceToDevice, (cudaStream_t)stream);
     if (err != cudaSuccess) return fail(status, -7, "cuda: d2d copy failed: %s", cudaGetErrorString(err));

@@ -86,10 +86,15 @@ class Device:
             raise DeviceError(rc, self._status.message.decode(errors="replace"))
         self.ref = ref
         self.follow_torch_stream = follow_torch_stream
+        self._stream = None  # stream last handed to the library
+        self._refs = {}      # (address, bytes) -> CUDABufferRef
 
     # ---- plumbing -------------------------------------------------------------------------------------
     def close(self):
         if getattr(self, "ref", None):
+            for r in self._refs.values():
+                self.lib.cuda_buffer_release(r)
+            self._refs.clear()
             self.lib.cuda_close_device(self.ref)
             self.ref = None
 
@@ -106,34 +111,32 @@ class Device:
     def _enter(self):
         if self.follow_torch_stream:
             s = self._torch.cuda.current_stream(self.ordinal).cuda_stream
-            self.lib.cuda_context_set_stream(self.ref, ctypes.c_void_p(s), ctypes.byref(self._status))
+            if s != self._stream:  # the library keeps the stream until told otherwise: only a change costs a call
+                self.lib.cuda_context_set_stream(self.ref, ctypes.c_void_p(s), ctypes.byref(self._status))
+                self._stream = s
 
-    class _Bufs:
-        def __init__(self, dev, tensors):
-            self.dev = dev
-            self.refs = []
-            for t in tensors:
-                if t is None:
-                    self.refs.append(None)
-                    continue
-                assert t.is_cuda and t.is_contiguous(), "device tensors must be contiguous CUDA memory"
-                r = dev.lib.cuda_buffer_wrap(dev.ref, ctypes.c_void_p(t.data_ptr()), t.numel() * t.element_size())
-                self.refs.append(ctypes.c_void_p(r))
-
-        def __enter__(self):
-            return self.refs
-
-        def __exit__(self, *exc):
-            for r in self.refs:
-                if r is not None:
-                    self.dev.lib.cuda_buffer_release(r)
-            return False
+    def _ref(self, t):
+        """Non-owning CUDABufferRef of a tensor's memory.  Handles are cached by (address, size): a serving loop passes the
+        same buffers every step, and a handle is only a (pointer, size) record, so reuse is safe for as long as the
+        address range stays valid for the call that uses it."""
+        if t is None:
+            return None
+        assert t.is_cuda and t.is_contiguous(), "device tensors must be contiguous CUDA memory"
+        key = (t.data_ptr(), t.numel() * t.element_size())
+        r = self._refs.get(key)
+        if r is None:
+            r = ctypes.c_void_p(self.lib.cuda_buffer_wrap(self.ref, ctypes.c_void_p(key[0]), key[1]))
+            self._refs[key] = r
+        return r
 
     def _call(self, name, tensors, build_args):
         self._enter()
-        with Device._Bufs(self, tensors) as refs:
-            args = build_args(refs)
-            rc = getattr(self.lib, name)(self.ref, *args, ctypes.byref(self._status))
+        if len(self._refs) >= 4096:  # bound the cache (between calls only): handles are cheap to rebuild
+            for old in self._refs.values():
+                self.lib.cuda_buffer_release(old)
+            self._refs.clear()
+        args = build_args([self._ref(t) for t in tensors])
+        rc = getattr(self.lib, name)(self.ref, *args, ctypes.byref(self._status))
         self._check(rc)
 
     def set_exact(self, exact: bool):

@@ -253,6 +253,62 @@ def test_fused_add_rmsnorm_gated_residual_equals_unfused_ops(d, dt):
         assert ulp16_diff(host(no, np.uint16), n.ravel()).max() <= 1
 
 
+@pytest.mark.parametrize("dt,cols", [(O.BF16, 16384), (O.F32, 8192), (O.BF16, 1024), (O.F16, 4100)])
+@pytest.mark.parametrize("inplace", [False, True])
+def test_fused_and_plain_rmsnorm_long_rows_in_place_and_out_of_place(d, dt, cols, inplace):
+    """Rows longer than the register cache of the row kernel (more than 8192 16-bit / 4096 float32 columns) take its second
+    pass over memory; with the residual stream updated in place (hOut = x) that pass must not add the residual twice."""
+    import puter_b200
+
+    rows, rpb = 12, 4
+    rng = np.random.default_rng(cols)
+    x = O.from_f32(rng.standard_normal((rows, cols)).astype(np.float32), dt)
+    r = O.from_f32(rng.standard_normal((rows, cols)).astype(np.float32), dt)
+    br = O.from_f32(rng.standard_normal((rows, cols)).astype(np.float32), dt)
+    g = O.from_f32(rng.uniform(0.5, 1.5, cols).astype(np.float32), dt)
+    mod = O.from_f32(rng.uniform(0, 1, (rows // rpb) * 3 * cols).astype(np.float32), dt)
+    h = O.binary(O.ADD, dt, x, r)
+    n = O.rmsnorm(dt, h.reshape(rows, cols), g, 1e-6)
+    gr = O.gated_residual(dt, h, br, mod, rows, cols, rpb, 3 * cols, 0)
+    xd, rd = dev(x), dev(r)
+    ho = xd if inplace else empty(x.nbytes)
+    go = rd if inplace else empty(x.nbytes)   # the gated output reuses the residual's buffer
+    no = empty(x.nbytes)
+    d.AddRMSNormGatedResidual(puter_b200.RMSNormConfig(1e-6), xd, rd, dev(g), dev(br), dev(mod), ho, no, go, rows, cols, rpb, 3 * cols, 0, dt)
+    assert np.array_equal(host(ho, h.dtype).view(np.uint8), h.ravel().view(np.uint8))
+    assert np.array_equal(host(go, gr.dtype).view(np.uint8), gr.ravel().view(np.uint8))
+    if dt == O.F32:
+        assert rel_err(host(no, np.float32), n) <= 1e-6
+    else:
+        assert ulp16_diff(host(no, np.uint16), n.ravel()).max() <= 1
+    # plain RMSNorm, output over its input
+    xd = dev(h)
+    out = xd if inplace else empty(x.nbytes)
+    d.RMSNorm(puter_b200.RMSNormConfig(1e-6), xd, dev(g), out, rows, cols, dt)
+    if dt == O.F32:
+        assert rel_err(host(out, np.float32), n) <= 1e-6
+    else:
+        assert ulp16_diff(host(out, np.uint16), n.ravel()).max() <= 1
+
+
+def test_rmsnorm_refuses_overlaps_it_cannot_run_in_place(d):
+    import puter_b200
+
+    rows, cols = 4, 256
+    buf = dev(np.zeros(rows * cols * 2 + 64, np.float32))
+    x, shifted = buf[:rows * cols * 4], buf[64:64 + rows * cols * 4]
+    g = dev(np.ones(cols, np.float32))
+    cfg = puter_b200.RMSNormConfig(1e-6)
+    with pytest.raises(puter_b200.DeviceError) as e:  # partial overlap of input and output
+        d.RMSNorm(cfg, x, g, shifted, rows, cols, O.F32)
+    assert e.value.code == -2
+    r = dev(np.zeros(rows * cols, np.float32))
+    o = empty(rows * cols * 4)
+    with pytest.raises(puter_b200.DeviceError) as e:  # two outputs in one buffer
+        d.AddRMSNormGatedResidual(cfg, x, r, g, None, None, o, o, None, rows, cols, 0, 0, 0, O.F32)
+    assert e.value.code == -2
+
+
 ROPE_CASES = [dict(base=10000.0, start=0, mode=0, scaling=0, factor=1.0, low=0.0, high=0.0, orig_ctx=0),
               dict(base=10000.0, start=5, mode=1, scaling=0, factor=1.0, low=0.0, high=0.0, orig_ctx=0),
               dict(base=500000.0, start=3, mode=1, scaling=1, factor=32.0, low=1.0, high=4.0, orig_ctx=8192),
