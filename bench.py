@@ -139,22 +139,31 @@ class DecodeWorkload:
         self.k, self.v = st["k"], st["v"]
         self.kscale, self.vscale = st.get("k_scale"), st.get("v_scale")
         self.total_pages, self.max_pages = st["total_pages"], st["max_pages"]
-        # this step's host inputs (query rows, page tables, lengths) live in ONE pinned buffer and reach the device in one copy
+        # this step's host inputs (query rows, page tables, lengths) live in ONE pinned buffer and reach the device in one copy;
+        # two device copies of it and of the output alternate, so that the copies of step i+1 / i-1 travel on their own
+        # streams while step i computes
         qb, tb, cb = st["q_host"].numel() * 2, st["table_host"].numel() * 4, st["ctx_host"].numel() * 4
         off_t = (qb + 255) & ~255
         off_c = (off_t + tb + 255) & ~255
         total = off_c + max(cb, 4)
         self.stage_host = torch.zeros(total, dtype=torch.uint8).pin_memory()
-        self.stage_dev = torch.zeros(total, dtype=torch.uint8, device="cuda")
         self.stage_host[:qb].copy_(st["q_host"].view(torch.uint8).view(-1))
         self.stage_host[off_t:off_t + tb].copy_(st["table_host"].view(torch.uint8).view(-1))
         self.stage_host[off_c:off_c + cb].copy_(st["ctx_host"].view(torch.uint8).view(-1))
-        self.stage_dev.copy_(self.stage_host)
-        self.q = self.stage_dev[:qb].view(torch.int16).view(self.batch, HQ * DIM)
-        self.table = self.stage_dev[off_t:off_t + tb].view(torch.int32).view(self.batch, self.max_pages)
-        self.ctx_dev = self.stage_dev[off_c:off_c + cb].view(torch.int32)
-        self.out = torch.zeros(self.batch, HQ * DIM, dtype=torch.int16, device="cuda")
-        self.out_host = torch.zeros(self.batch, HQ * DIM, dtype=torch.int16).pin_memory()
+        self.slots = []
+        for _ in range(2):
+            sd = torch.zeros(total, dtype=torch.uint8, device="cuda")
+            sd.copy_(self.stage_host)
+            self.slots.append(dict(
+                stage=sd, q=sd[:qb].view(torch.int16).view(self.batch, HQ * DIM),
+                table=sd[off_t:off_t + tb].view(torch.int32).view(self.batch, self.max_pages), ctx=sd[off_c:off_c + cb].view(torch.int32),
+                out=torch.zeros(self.batch, HQ * DIM, dtype=torch.int16, device="cuda"),
+                out_host=torch.zeros(self.batch, HQ * DIM, dtype=torch.int16).pin_memory(),
+                ready=torch.cuda.Event(), consumed=torch.cuda.Event(), computed=torch.cuda.Event(), downloaded=torch.cuda.Event()))
+        self.up_stream, self.down_stream = torch.cuda.Stream(), torch.cuda.Stream()
+        self.e2e_i = 0
+        s0 = self.slots[0]
+        self.q, self.table, self.ctx_dev, self.out, self.out_host = s0["q"], s0["table"], s0["ctx"], s0["out"], s0["out_host"]
         self.cfg = MultiHeadAttentionConfig(NumHeads=HQ, HeadDim=DIM, Causal=True, KVHeadCount=HKV)
         self.bytes_per_step = self.data.algorithmic_bytes(self.owned, self.esize)       # this rank
         self.bytes_per_step_global = self.data.algorithmic_bytes(None, self.esize)      # the whole batch
@@ -171,10 +180,31 @@ class DecodeWorkload:
 
     def step_e2e(self):
         # a decode step as the caller sees it: this step's query rows, page tables and lengths arrive from the host (one
-        # copy), the attention rows go back; the KV cache is device-resident state, as in the reference's paged-KV design
-        self.stage_dev.copy_(self.stage_host, non_blocking=True)
-        self.step()
-        self.out_host.copy_(self.out, non_blocking=True)
+        # copy), the attention rows go back; the KV cache is device-resident state, as in the reference's paged-KV design.
+        # Upload, compute and download run on three streams chained by events, over two alternating buffer sets.
+        torch = self.torch
+        s = self.slots[self.e2e_i & 1]
+        self.e2e_i += 1
+        cur = torch.cuda.current_stream()
+        with torch.cuda.stream(self.up_stream):
+            self.up_stream.wait_event(s["consumed"])      # the step that last read this buffer set has run
+            s["stage"].copy_(self.stage_host, non_blocking=True)
+            s["ready"].record(self.up_stream)
+        cur.wait_event(s["ready"])
+        cur.wait_event(s["downloaded"])                    # its previous output rows have left the device
+        self.dev.PagedDecodeAttention(self.cfg, s["q"], self.k, self.v, s["table"], s["ctx"], s["out"], self.batch, self.max_pages,
+                                      self.total_pages, PAGE, self.fmt, kvFormat=self.kvfmt, kScale=self.kscale, vScale=self.vscale)
+        s["consumed"].record(cur)
+        with torch.cuda.stream(self.down_stream):
+            self.down_stream.wait_event(s["consumed"])
+            s["out_host"].copy_(s["out"], non_blocking=True)
+            s["downloaded"].record(self.down_stream)
+
+    def e2e_drain(self):
+        # inside the timed region: the last steps' output rows must have reached the host before the clock stops
+        cur = self.torch.cuda.current_stream()
+        for s in self.slots:
+            cur.wait_event(s["downloaded"])
 
     def config(self):
         return decode_config(self.data, self.fp8, self.world)
@@ -384,9 +414,9 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(fn, steps, sample_clocks=False):
+    def timed(fn, steps, sample_clocks=False, drain=None):
         """Times `steps` calls of fn with CUDA events on the launching stream; returns (max-over-ranks seconds, clocks,
-        per-rank seconds)."""
+        per-rank seconds).  `drain` runs after the last call, inside the timed region (work of side streams joins there)."""
         sampler = ClockSampler(local_rank) if sample_clocks else None
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
@@ -396,6 +426,8 @@ def main():
         start.record()
         for _ in range(steps):
             fn()
+        if drain:
+            drain()
         stop.record()
         barrier()
         clocks = sampler.stop() if sampler else None
@@ -420,7 +452,7 @@ def main():
 
     for _ in range(2):
         wl.step_e2e()
-    sec_e2e, _, _ = timed(wl.step_e2e, args.steps)
+    sec_e2e, _, _ = timed(wl.step_e2e, args.steps, drain=getattr(wl, "e2e_drain", None))
     per_step_e2e = sec_e2e / args.steps
 
     peaks = measured_peaks()

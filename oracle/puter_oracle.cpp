@@ -275,35 +275,151 @@ inline double fast_gelu_tanh64(double v) {
 }
 inline float fast_relu32(float v) { return v > 0 ? v : 0.0f; }
 
-// unary op codes = CUDAUnaryFloat32Op, device/cuda/internal/bridge/core.h:35-70
-enum UnaryOp { U_RELU = 0, U_TANH = 12, U_SIGMOID = 13, U_SILU = 14, U_GELU = 22, U_GELU_TANH = 29 };
+// device/cpu/math/constant.go:3-6: the NaN the log family returns for x <= 0
+inline float nan32() { return u2f(0x7FC00001u); }
+inline double nan64() { uint64_t u = 0x7FF8000000000001ull; double d; std::memcpy(&d, &u, 8); return d; }
 
+// device/cpu/math/f32.go:50-69
+inline float fast_log32(float x) {
+    if (x <= 0) return nan32();
+    uint32_t bits = f2u(x);
+    int32_t e = (int32_t)(bits >> 23) - 127;
+    float m = u2f((bits & 0x007FFFFFu) | (127u << 23));
+    float y = m - 1.0f;
+    float poly = y * (0.9999964239f + y * (-0.4998741238f + y * (0.3317990258f + y * (-0.2407338084f + y * 0.14449244f))));
+    return poly + (float)e * 0.6931471805599453f;
+}
+// device/cpu/math/f64.go:35-55
+inline double fast_log64(double x) {
+    if (x <= 0) return nan64();
+    uint64_t bits;
+    std::memcpy(&bits, &x, 8);
+    int64_t e = (int64_t)(bits >> 52) - 1023;
+    uint64_t mb = (bits & 0x000FFFFFFFFFFFFFull) | (1023ull << 52);
+    double m;
+    std::memcpy(&m, &mb, 8);
+    double y = m - 1.0;
+    double poly = y * (0.9999964239 + y * (-0.4998741238 + y * (0.3317990258 + y * (-0.2407338084 + y * 0.14449244))));
+    return poly + (double)e * 0.6931471805599453;
+}
+
+// device/cpu/math/activation.go:7-16 (Go converts an untyped constant to the type of the expression it sits in)
+constexpr double kSeluAlpha = 1.6732632423543772, kSeluScale = 1.0507009873554805, kLeakySlope = 0.01;
+
+// device/cpu/math/activation.go:34-270, extra_activation.go:3-37: float32 forms
+inline float fast_leaky_relu32(float v) { return v > 0 ? v : (float)kLeakySlope * v; }
+inline float fast_elu32(float v) { return v > 0 ? v : 1.0f * (fast_exp32(v) - 1.0f); }
+inline float fast_celu32(float v) { return v > 0 ? v : 1.0f * (fast_exp32(v / 1.0f) - 1.0f); }
+inline float fast_selu32(float v) { return v > 0 ? (float)kSeluScale * v : (float)(kSeluScale * kSeluAlpha) * (fast_exp32(v) - 1.0f); }
+inline float fast_softplus32(float v) { return v > 20 ? v : fast_log32(1.0f + fast_exp32(v)); }
+inline float fast_mish32(float v) { return v * fast_tanh32(fast_softplus32(v)); }
+inline float fast_softsign32(float v) { return v >= 0 ? v / (1.0f + v) : v / (1.0f - v); }
+inline float fast_hard_sigmoid32(float v) {
+    float s = v / 6.0f + 0.5f;
+    return s < 0 ? 0.0f : (s > 1 ? 1.0f : s);
+}
+inline float fast_hard_swish32(float v) { return v * fast_hard_sigmoid32(v + 3.0f); }
+inline float fast_hard_tanh32(float v) { return v < -1.0f ? -1.0f : (v > 1.0f ? 1.0f : v); }
+inline float fast_log1p32(float v) { return fast_log32(1.0f + v); }
+inline float fast_expm1_32(float v) { return fast_exp32(v) - 1.0f; }
+inline float fast_log_sigmoid32(float v) { return -fast_softplus32(-v); }
+inline float fast_hard_gelu32(float v) {
+    float inner = v + 3.0f;
+    if (inner < 0) inner = 0;
+    if (inner > 6) inner = 6;
+    return v * (inner / 6.0f);
+}
+inline float fast_quick_gelu32(float v) { return v * fast_sigmoid32(1.702f * v); }
+inline float fast_tanh_shrink32(float v) { return v - fast_tanh32(v); }
+
+// float64 forms, the fill functions of the 16-bit lookup tables (device/cpu/activation/lut.go:14-41)
+inline double fast_leaky_relu64(double v) { return v > 0 ? v : kLeakySlope * v; }
+inline double fast_elu64(double v) { return v > 0 ? v : 1.0 * (fast_exp64(v) - 1.0); }
+inline double fast_celu64(double v) { return v > 0 ? v : 1.0 * (fast_exp64(v / 1.0) - 1.0); }
+inline double fast_selu64(double v) { return v > 0 ? kSeluScale * v : kSeluScale * kSeluAlpha * (fast_exp64(v) - 1.0); }
+inline double fast_softplus64(double v) { return v > 20 ? v : fast_log64(1.0 + fast_exp64(v)); }
+inline double fast_mish64(double v) { return v * fast_tanh64(fast_softplus64(v)); }
+inline double fast_softsign64(double v) { return v / (1.0 + std::fabs(v)); }
+inline double fast_hard_sigmoid64(double v) {
+    double s = v / 6.0 + 0.5;
+    return s < 0 ? 0.0 : (s > 1 ? 1.0 : s);
+}
+inline double fast_hard_swish64(double v) { return v * fast_hard_sigmoid64(v + 3.0); }
+inline double fast_hard_tanh64(double v) { return v < -1.0 ? -1.0 : (v > 1.0 ? 1.0 : v); }
+
+// unary op codes = CUDAUnaryFloat32Op, device/cuda/internal/bridge/core.h:35-70
+enum UnaryOp {
+    U_RELU = 0, U_EXP = 8, U_LOG = 9, U_TANH = 12, U_SIGMOID = 13, U_SILU = 14, U_SWISH = 15, U_SOFTSIGN = 16, U_ELU = 17, U_SELU = 18,
+    U_LEAKY_RELU = 19, U_HARD_SIGMOID = 20, U_HARD_SWISH = 21, U_GELU = 22, U_LOG1P = 23, U_EXPM1 = 24, U_CELU = 25, U_SOFTPLUS = 26,
+    U_MISH = 27, U_LOG_SIGMOID = 28, U_GELU_TANH = 29, U_HARD_TANH = 30, U_HARD_GELU = 31, U_QUICK_GELU = 32, U_TANH_SHRINK = 33
+};
+
+// float32 kernels: device/cpu/activation/f32_generic.go:9-222 (one math.Fast*32 call per element; Swish runs the Silu kernel,
+// device/cpu/activation/ops.go:41-43)
 inline float unary32(int op, float v) {
     switch (op) {
         case U_RELU: return fast_relu32(v);
+        case U_EXP: return fast_exp32(v);
+        case U_LOG: return fast_log32(v);
         case U_TANH: return fast_tanh32(v);
         case U_SIGMOID: return fast_sigmoid32(v);
-        case U_SILU: return fast_silu32(v);
+        case U_SILU: case U_SWISH: return fast_silu32(v);
+        case U_SOFTSIGN: return fast_softsign32(v);
+        case U_ELU: return fast_elu32(v);
+        case U_SELU: return fast_selu32(v);
+        case U_LEAKY_RELU: return fast_leaky_relu32(v);
+        case U_HARD_SIGMOID: return fast_hard_sigmoid32(v);
+        case U_HARD_SWISH: return fast_hard_swish32(v);
         case U_GELU: return fast_gelu32(v);
+        case U_LOG1P: return fast_log1p32(v);
+        case U_EXPM1: return fast_expm1_32(v);
+        case U_CELU: return fast_celu32(v);
+        case U_SOFTPLUS: return fast_softplus32(v);
+        case U_MISH: return fast_mish32(v);
+        case U_LOG_SIGMOID: return fast_log_sigmoid32(v);
         case U_GELU_TANH: return fast_gelu_tanh32(v);
+        case U_HARD_TANH: return fast_hard_tanh32(v);
+        case U_HARD_GELU: return fast_hard_gelu32(v);
+        case U_QUICK_GELU: return fast_quick_gelu32(v);
+        case U_TANH_SHRINK: return fast_tanh_shrink32(v);
     }
     return std::numeric_limits<float>::quiet_NaN();
 }
+// table fill functions: device/cpu/activation/lut.go:14-41 (HardGelu, QuickGelu and TanhShrink go through their float32 forms,
+// device/cpu/math/extra_activation.go:19-37)
 inline double unary64(int op, double v) {
     switch (op) {
         case U_RELU: return v > 0 ? v : 0.0;
+        case U_EXP: return fast_exp64(v);
+        case U_LOG: return fast_log64(v);
         case U_TANH: return fast_tanh64(v);
         case U_SIGMOID: return fast_sigmoid64(v);
-        case U_SILU: return fast_silu64(v);
+        case U_SILU: case U_SWISH: return fast_silu64(v);
+        case U_SOFTSIGN: return fast_softsign64(v);
+        case U_ELU: return fast_elu64(v);
+        case U_SELU: return fast_selu64(v);
+        case U_LEAKY_RELU: return fast_leaky_relu64(v);
+        case U_HARD_SIGMOID: return fast_hard_sigmoid64(v);
+        case U_HARD_SWISH: return fast_hard_swish64(v);
         case U_GELU: return fast_gelu64(v);
+        case U_LOG1P: return fast_log64(1.0 + v);
+        case U_EXPM1: return fast_exp64(v) - 1.0;
+        case U_CELU: return fast_celu64(v);
+        case U_SOFTPLUS: return fast_softplus64(v);
+        case U_MISH: return fast_mish64(v);
+        case U_LOG_SIGMOID: return -fast_softplus64(-v);
         case U_GELU_TANH: return fast_gelu_tanh64(v);
+        case U_HARD_TANH: return fast_hard_tanh64(v);
+        case U_HARD_GELU: return (double)fast_hard_gelu32((float)v);
+        case U_QUICK_GELU: return (double)fast_quick_gelu32((float)v);
+        case U_TANH_SHRINK: return (double)fast_tanh_shrink32((float)v);
     }
     return std::numeric_limits<double>::quiet_NaN();
 }
 
 // gated variants (device/cpu/math/activation.go:286-308): SwiGLU/SiGLU activate
 // the gate, GLU/GeGLU/ReGLU/GeGLUTanh activate `up`.
-enum GatedOp { G_SWIGLU = 0, G_GEGLU = 1, G_GLU = 2, G_REGLU = 3, G_SIGLU = 4, G_GEGLU_TANH = 5 };
+enum GatedOp { G_SWIGLU = 0, G_GEGLU = 1, G_GLU = 2, G_REGLU = 3, G_SIGLU = 4, G_GEGLU_TANH = 5, G_SEGLU = 6, G_LINGLU = 7 };
 inline float gated32(int op, float gate, float up) {
     switch (op) {
         case G_SWIGLU: return fast_silu32(gate) * up;
@@ -312,6 +428,8 @@ inline float gated32(int op, float gate, float up) {
         case G_REGLU: return gate * fast_relu32(up);
         case G_SIGLU: return fast_sigmoid32(gate) * up;
         case G_GEGLU_TANH: return gate * fast_gelu_tanh32(up);
+        case G_SEGLU: return up * fast_sigmoid32(gate);  // device/cpu/math/extra_activation.go:88-90
+        case G_LINGLU: return gate * up;                 // extra_activation.go:84-86
     }
     return std::numeric_limits<float>::quiet_NaN();
 }

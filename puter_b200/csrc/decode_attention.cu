@@ -113,6 +113,12 @@ template <bool BF16> __device__ __forceinline__ float round16(float v) {
     return __half2float(__float2half_rn(v));
 }
 
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+    return d;
+}
+
 // tiles of sequence b; clamps negative and over-long contexts and flags them
 __device__ __forceinline__ int seq_tiles(const DecodeParams& p, int b) {
     long long ctx = p.ctxLens ? (long long)p.ctxLens[b] : (long long)p.uniformCtx;
@@ -227,19 +233,24 @@ __device__ __forceinline__ void merge_if_last(const DecodeParams& p, const int* 
     }
 }
 
-template <bool BF16, bool FP8KV, int NS>
-struct DecodeSmem {
-    static constexpr int kRawStage = FP8KV ? 2 * kTile * kHeadDim : 0;      // fp8 staging (K + V) per stage
-    static constexpr int kTileBytes = 2 * kTile * kHeadDim * 2;             // 16-bit K + V tile
-    static constexpr int kPerWarp = FP8KV ? NS * kRawStage + kTileBytes : NS * kTileBytes;
-    static constexpr int kTotal = kPerWarp * kWarps;
-};
+// ---------------------------------------------------------------------------------------------------------
+// 16-bit (bf16 / f16) KV pages.  The TOKENS of a 16-token tile are the M = 16 rows of every m16n8k16 MMA and the (<= 8)
+// query heads of the KV head's group its N = 8 columns: S^T = K Q^T and O^T += V^T P^T.  (With the heads as rows, 12 of
+// 16 rows multiply zeros for a group of 4: twice the MMAs and twice the accumulator registers.)
+//   * K tile rows feed the A operand through a plain ldmatrix, V^T through ldmatrix.trans, both from XOR-swizzled tiles;
+//   * the score accumulator holds (token g, heads 2t, 2t+1); each score is rounded to the storage type before scaling,
+//     as the reference's rounded dot product; the softmax weights stay float32 and enter the P V product as a high and a
+//     low 16-bit part, each turned into the B-operand layout (head g, tokens 2t, 2t+1) by movmatrix;
+//   * the maximum is reduced over the 8 lanes that share a head column; the row sums stay per lane until the end.
+// ---------------------------------------------------------------------------------------------------------
+static constexpr int kStages16 = 3;
+static constexpr int kStage16 = 2 * kTile * kHeadDim * 2;          // K + V bytes of one tile for one head: 8 KB
+static constexpr int kSmem16 = kStages16 * kStage16 * kWarps;      // 192 KB
 
-template <bool BF16, bool FP8KV, int NS, bool SPLIT_P>
-__global__ void __launch_bounds__(kThreads, 1) paged_decode_kernel(DecodeParams p) {
+// NT = n-tiles of 8 query heads per KV head (1: group <= 8, 2: group <= 16)
+template <bool BF16, int NT>
+__global__ void __launch_bounds__(kThreads, 1) paged_decode16_kernel(DecodeParams p) {
     extern __shared__ __align__(128) unsigned char smemRaw[];
-    using SM = DecodeSmem<BF16, FP8KV, NS>;
-    constexpr bool MMA_BF16 = BF16 && !FP8KV;  // fp8 pages are widened to f16, so that path multiplies in f16
     __shared__ int sTileStart[kPrefixSmem + 1];
     const int* ts = p.tileStart;
     if (!ts) {
@@ -256,14 +267,10 @@ __global__ void __launch_bounds__(kThreads, 1) paged_decode_kernel(DecodeParams 
     if (T == 0) return;
     const long long lo = worker * T / p.workers, hi = (worker + 1) * T / p.workers;
     if (lo >= hi) return;
-
-    unsigned char* wsm = smemRaw + (size_t)warp * SM::kPerWarp;
+    unsigned char* wsm = smemRaw + (size_t)warp * (kStages16 * kStage16);
     const uint32_t wsmAddr = smem_u32(wsm);
-    const int es = FP8KV ? 1 : 2;
-    const size_t tokenStride = (size_t)p.kvHeads * kHeadDim * es;  // bytes between tokens of a page
+    const size_t tokenStride = (size_t)p.kvHeads * kHeadDim * 2;  // bytes between tokens of a page
     const bool page16 = (p.pageSize % kTile) == 0;
-
-    // first sequence of the range: largest b with tileStart[b] <= lo
     int seq;
     {
         int a = 0, z = p.batch;
@@ -273,57 +280,62 @@ __global__ void __launch_bounds__(kThreads, 1) paged_decode_kernel(DecodeParams 
         }
         seq = a;
     }
+    // per-lane constants of the copy pattern: lane = (row in a group of 2 tokens, 16-byte chunk of the 256-byte row)
+    const int cpRow = lane >> 4, cpChunk = lane & 15;
+    const size_t cpSrc = (size_t)cpRow * tokenStride + (size_t)cpChunk * 16;
+    // per-lane ldmatrix addresses inside a tile (swizzle: 16-byte chunk ^ (token & 7))
+    const int lmRow = lane & 7, lmMat = lane >> 3;
+    const uint32_t kLm = (uint32_t)(((lmMat & 1) * 8 + lmRow) * 256);   // K: matrices (tok 0-7 | 8-15) x (chunk 2kk | 2kk+1)
+    const int kLmChunk = lmMat >> 1;
+    const uint32_t vLm = (uint32_t)(((lmMat >> 1) * 8 + lmRow) * 256);  // V: matrices (chunk 2dt | 2dt+1) x (tok 0-7 | 8-15)
+    const int vLmChunk = lmMat & 1;
 
     for (int kvh = head0; kvh < p.kvHeads; kvh += p.headsPerPass) {
         int b = seq;
         long long cur = lo;
         while (cur < hi) {
             while (ts[b + 1] <= cur) b++;  // skip empty sequences
-            const long long segStart = ts[b];
-            const long long segEndAll = ts[b + 1];
+            const long long segStart = ts[b], segEndAll = ts[b + 1];
             const long long segEnd = segEndAll < hi ? segEndAll : hi;
             const int tile0 = (int)(cur - segStart), tile1 = (int)(segEnd - segStart);  // local tile range [tile0, tile1)
             const int ctx = seq_ctx(p, b, (int)(segEndAll - segStart));
             const int32_t* table = p.pageTable ? p.pageTable + (size_t)b * p.maxPages : nullptr;
-            const unsigned char* kBase = (const unsigned char*)p.kPages + (size_t)kvh * kHeadDim * es;
-            const unsigned char* vBase = (const unsigned char*)p.vPages + (size_t)kvh * kHeadDim * es;
+            const unsigned char* kBase = (const unsigned char*)p.kPages + (size_t)kvh * kHeadDim * 2;
+            const unsigned char* vBase = (const unsigned char*)p.vPages + (size_t)kvh * kHeadDim * 2;
             if (!table) {
-                kBase += (size_t)b * p.seqStrideKV * es;
-                vBase += (size_t)b * p.seqStrideKV * es;
+                kBase += (size_t)b * p.seqStrideKV * 2;
+                vBase += (size_t)b * p.seqStrideKV * 2;
             }
-
-            // ---- Q fragments (A operand, rows = query heads of this KV head's group) ----
-            uint32_t qa[8][4];
+            // ---- Q as the B operand: k16 step kk: b0 = dims 16kk + 2t, +1 of head g; b1 = dims 16kk + 8 + 2t, +1 ----
+            uint32_t qb[8][NT][2];
             {
-                const size_t qRow = (size_t)b * p.numHeads * kHeadDim;
-                const int h0 = kvh * p.group + g, h1 = h0 + 8;
-                const bool v0 = g < p.group, v1 = g + 8 < p.group;
+                const uint16_t* qRow = (const uint16_t*)p.q + (size_t)b * p.numHeads * kHeadDim;
 #pragma unroll
-                for (int kk = 0; kk < 8; kk++) {
+                for (int nt = 0; nt < NT; nt++) {
+                    const int gi = nt * 8 + g;
 #pragma unroll
-                    for (int part = 0; part < 4; part++) {
-                        const bool valid = (part & 1) ? v1 : v0;
-                        const int h = (part & 1) ? h1 : h0;
-                        const int d = kk * 16 + (part >> 1) * 8 + 2 * t;
-                        uint32_t w = 0;
-                        if (valid) {
-                            w = *(const uint32_t*)((const uint16_t*)p.q + qRow + (size_t)h * kHeadDim + d);
-                            if (BF16 && !MMA_BF16) {  // bf16 query, f16 multiply
-                                w = pack16<false>(__uint_as_float(w << 16), __uint_as_float(w & 0xFFFF0000u));
-                            }
+                    for (int kk = 0; kk < 8; kk++) {
+                        uint32_t w0 = 0, w1 = 0;
+                        if (gi < p.group) {
+                            const uint16_t* src = qRow + (size_t)(kvh * p.group + gi) * kHeadDim + kk * 16 + 2 * t;
+                            w0 = *(const uint32_t*)src;
+                            w1 = *(const uint32_t*)(src + 8);
                         }
-                        qa[kk][part] = w;
+                        qb[kk][nt][0] = w0;
+                        qb[kk][nt][1] = w1;
                     }
                 }
             }
-
-            float oacc[16][4];
+            // O^T: tile dt = dims 16dt .. 16dt+15; [0],[1] = (dim 16dt+g, heads 2t, 2t+1), [2],[3] = (dim 16dt+g+8, heads 2t, 2t+1)
+            float oacc[8][NT][4];
 #pragma unroll
-            for (int j = 0; j < 16; j++) oacc[j][0] = oacc[j][1] = oacc[j][2] = oacc[j][3] = 0.f;
-            float mrow[2] = {-INFINITY, -INFINITY}, lrow[2] = {0.f, 0.f};
-            const float kS = (FP8KV && p.kScale) ? p.kScale[kvh] : 1.0f;
+            for (int dt = 0; dt < 8; dt++)
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++) oacc[dt][nt][0] = oacc[dt][nt][1] = oacc[dt][nt][2] = oacc[dt][nt][3] = 0.f;
+            float mcol[NT][2], lcol[NT][2];  // per head column (heads 8nt + 2t, + 1): running maximum (shared by the warp), this lane's sum
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) { mcol[nt][0] = mcol[nt][1] = -INFINITY; lcol[nt][0] = lcol[nt][1] = 0.f; }
 
-            // page-id cache: lane i holds table[cbase + i]
             int cbase = -0x40000000, cval = 0;
             auto page_of = [&](int entry) -> int {
                 if (!table) return entry;
@@ -339,204 +351,173 @@ __global__ void __launch_bounds__(kThreads, 1) paged_decode_kernel(DecodeParams 
                 }
                 return pg;
             };
-
-            // issue the async copies of local tile `lt` into stage `st`
+            // async copies of local tile `lt` (16 tokens) into stage `st`; rows past the context are zero-filled, never read
             auto issue = [&](int lt, int st) {
                 const int tok0 = lt * kTile;
-                uint32_t dstK, dstV;
-                if (FP8KV) {
-                    dstK = wsmAddr + st * SM::kRawStage;
-                    dstV = dstK + kTile * kHeadDim;
-                } else {
-                    dstK = wsmAddr + st * SM::kTileBytes;
-                    dstV = dstK + kTile * kHeadDim * 2;
-                }
-                constexpr int kChunksPerRow = FP8KV ? 8 : 16;    // 16-byte chunks per (token, head) row
-                constexpr int kRowsPerIter = 32 / kChunksPerRow; // rows covered by one warp-wide copy
-                const int c = lane % kChunksPerRow;
-                size_t pageOff = 0;
-                int inPage0 = 0;
+                const uint32_t dstK = wsmAddr + st * kStage16, dstV = dstK + kTile * kHeadDim * 2;
                 if (page16 || !table) {
                     const int ps = table ? p.pageSize : kTile;
-                    const int entry = tok0 / ps;
-                    inPage0 = tok0 % ps;
-                    pageOff = (size_t)page_of(entry) * ps * tokenStride;
-                }
+                    const size_t pageOff = ((size_t)page_of(tok0 / ps) * ps + (size_t)(tok0 % ps)) * tokenStride;
+                    const unsigned char* ks = kBase + pageOff + cpSrc;
+                    const unsigned char* vs = vBase + pageOff + cpSrc;
+                    const bool full = tok0 + kTile <= ctx;
 #pragma unroll
-                for (int i = 0; i < kTile / kRowsPerIter; i++) {
-                    const int r = i * kRowsPerIter + lane / kChunksPerRow;
-                    const int tok = tok0 + r;
-                    size_t off;
-                    if (page16 || !table) {
-                        off = pageOff + (size_t)(inPage0 + r) * tokenStride;
-                    } else {
+                    for (int i = 0; i < 8; i++) {
+                        const int r = 2 * i + cpRow;
+                        const uint32_t so = (uint32_t)(r * 256) + (uint32_t)((cpChunk ^ (r & 7)) * 16);
+                        const size_t rowOff = (size_t)(2 * i) * tokenStride;
+                        if (full) {
+                            cp_async16(dstK + so, ks + rowOff, 16);
+                            cp_async16(dstV + so, vs + rowOff, 16);
+                        } else {
+                            const bool live = tok0 + r < ctx;
+                            cp_async16(dstK + so, live ? ks + rowOff : kBase, live ? 16 : 0);
+                            cp_async16(dstV + so, live ? vs + rowOff : vBase, live ? 16 : 0);
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 8; i++) {
+                        const int r = 2 * i + cpRow;
+                        const int tok = tok0 + r;
                         int pg = 0;
                         const int entry = tok / p.pageSize;
                         if (tok < ctx && entry < p.maxPages) {
                             pg = table[entry];
                             if (pg < 0 || pg >= p.pageCount) { atomicExch(p.errorFlag, 1); pg = 0; }
                         }
-                        off = ((size_t)pg * p.pageSize + tok % p.pageSize) * tokenStride;
+                        size_t off = ((size_t)pg * p.pageSize + tok % p.pageSize) * tokenStride;
+                        const int bytes = tok < ctx ? 16 : 0;
+                        if (bytes == 0) off = 0;
+                        const uint32_t so = (uint32_t)(r * 256) + (uint32_t)((cpChunk ^ (r & 7)) * 16);
+                        cp_async16(dstK + so, kBase + off + cpChunk * 16, bytes);
+                        cp_async16(dstV + so, vBase + off + cpChunk * 16, bytes);
                     }
-                    const int bytes = tok < ctx ? 16 : 0;  // rows past the context are zero-filled, never read
-                    if (bytes == 0) off = 0;
-                    uint32_t so;
-                    if (FP8KV) so = r * kHeadDim + c * 16;                       // raw staging, linear
-                    else so = r * 256 + ((c ^ (r & 7)) * 16);                   // swizzled 16-bit tile
-                    cp_async16(dstK + so, kBase + off + c * 16, bytes);
-                    cp_async16(dstV + so, vBase + off + c * 16, bytes);
                 }
             };
 
             const int nTiles = tile1 - tile0;
 #pragma unroll
-            for (int s = 0; s < NS - 1; s++) {
+            for (int s = 0; s < kStages16 - 1; s++) {
                 if (s < nTiles) issue(tile0 + s, s);
                 cp_async_commit();
             }
-
+            int stage = 0;
             for (int it = 0; it < nTiles; it++) {
-                cp_async_wait<NS - 2>();
+                cp_async_wait<kStages16 - 2>();
                 __syncwarp();
                 {
-                    const int nx = it + NS - 1;
-                    if (nx < nTiles) issue(tile0 + nx, nx % NS);
+                    const int nx = it + kStages16 - 1;
+                    int nst = stage + kStages16 - 1;
+                    if (nst >= kStages16) nst -= kStages16;
+                    if (nx < nTiles) issue(tile0 + nx, nst);
                     cp_async_commit();
                 }
-                const int st = it % NS;
-                uint32_t tileK, tileV;
-                if (FP8KV) {
-                    // widen the staged fp8 bytes into the (swizzled) f16 tile: lane handles 16-byte chunks
-                    const unsigned char* raw = wsm + st * SM::kRawStage;
-                    unsigned char* tile = wsm + NS * SM::kRawStage;
+                const uint32_t tileK = wsmAddr + stage * kStage16, tileV = tileK + kTile * kHeadDim * 2;
+                if (++stage == kStages16) stage = 0;
+                // ---- S^T = K Q^T : 16 tokens x 8 heads per n-tile ----
+                float sacc[NT][4];
 #pragma unroll
-                    for (int i = 0; i < (2 * kTile * kHeadDim / 16) / 32; i++) {
-                        const int chunk = i * 32 + lane;              // 0..255: K chunks then V chunks
-                        const int which = chunk >> 7;                 // 0 = K, 1 = V
-                        const int r = (chunk & 127) >> 3, c8 = chunk & 7;
-                        const Vec16 in = *(const Vec16*)(raw + chunk * 16);
-                        Vec16 o0, o1;
+                for (int nt = 0; nt < NT; nt++) sacc[nt][0] = sacc[nt][1] = sacc[nt][2] = sacc[nt][3] = 0.f;
 #pragma unroll
-                        for (int w = 0; w < 4; w++) {
-                            __half2_raw a = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(in.w[w] & 0xFFFFu), __NV_E4M3);
-                            __half2_raw bq = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(in.w[w] >> 16), __NV_E4M3);
-                            uint32_t lo2 = (uint32_t)a.x | ((uint32_t)a.y << 16);
-                            uint32_t hi2 = (uint32_t)bq.x | ((uint32_t)bq.y << 16);
-                            if (w < 2) { o0.w[2 * w] = lo2; o0.w[2 * w + 1] = hi2; }
-                            else { o1.w[2 * (w - 2)] = lo2; o1.w[2 * (w - 2) + 1] = hi2; }
-                        }
-                        unsigned char* dst = tile + which * (kTile * 256) + r * 256;
-                        *(Vec16*)(dst + (((2 * c8) ^ (r & 7)) * 16)) = o0;
-                        *(Vec16*)(dst + (((2 * c8 + 1) ^ (r & 7)) * 16)) = o1;
-                    }
-                    __syncwarp();
-                    tileK = wsmAddr + NS * SM::kRawStage;
-                    tileV = tileK + kTile * 256;
-                } else {
-                    tileK = wsmAddr + st * SM::kTileBytes;
-                    tileV = tileK + kTile * 256;
+                for (int kk = 0; kk < 8; kk++) {
+                    uint32_t a[4];
+                    ldmatrix_x4(tileK + kLm + (((2 * kk + kLmChunk) ^ lmRow) * 16), a[0], a[1], a[2], a[3]);
+#pragma unroll
+                    for (int nt = 0; nt < NT; nt++) mma16816<BF16>(sacc[nt], a, qb[kk][nt][0], qb[kk][nt][1]);
                 }
-
-                // ---- S = Q K^T : 16 x 16 ----
-                float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
-                {
-                    const int mi = lane >> 3, r = lane & 7;
-                    const int tok = (mi >> 1) * 8 + r;
-#pragma unroll
-                    for (int kk = 0; kk < 8; kk++) {
-                        const int chunk = 2 * kk + (mi & 1);
-                        uint32_t b0, b1, b2, b3;
-                        ldmatrix_x4(tileK + tok * 256 + ((chunk ^ (tok & 7)) * 16), b0, b1, b2, b3);
-                        mma16816<MMA_BF16>(s0, qa[kk], b0, b1);
-                        mma16816<MMA_BF16>(s1, qa[kk], b2, b3);
-                    }
-                }
-                // ---- scale, mask, online softmax (log2 domain) ----
+                // ---- round, scale, mask, online softmax (log2 domain); sacc[nt] = (token g, heads 2t, 2t+1), (token g+8, ...) ----
                 const int tokBase = (tile0 + it) * kTile;
-                float pv[2][4];  // [row half][4 tokens: 2t, 2t+1, 8+2t, 9+2t]
+                const bool tail = tokBase + kTile > ctx;
+                bool rescale = false;
+                float alpha[NT][2];
 #pragma unroll
-                for (int hrow = 0; hrow < 2; hrow++) {
-                    float x[4] = {s0[2 * hrow], s0[2 * hrow + 1], s1[2 * hrow], s1[2 * hrow + 1]};
-                    float mx = -INFINITY;
+                for (int nt = 0; nt < NT; nt++) {
 #pragma unroll
-                    for (int c = 0; c < 4; c++) {
-                        const int tok = tokBase + (c >> 1) * 8 + 2 * t + (c & 1);
-                        float sc;
-                        if (FP8KV) sc = x[c] * kS * p.scaleLog2;
-                        else sc = round16<BF16>(x[c]) * p.scaleLog2;   // the reference rounds the dot to storage first
-                        x[c] = tok < ctx ? sc : -INFINITY;
-                        mx = fmaxf(mx, x[c]);
-                    }
-                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-                    const float mNew = fmaxf(mrow[hrow], mx);
-                    const float alpha = (mNew == -INFINITY) ? 1.0f : exp2f(mrow[hrow] - mNew);
-                    float sum = 0.f;
+                    for (int j = 0; j < 2; j++) {
+                        float x[2];
 #pragma unroll
-                    for (int c = 0; c < 4; c++) {
-                        const float e = (x[c] == -INFINITY) ? 0.f : exp2f(x[c] - mNew);
-                        pv[hrow][c] = e;
-                        sum += e;
-                    }
-                    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-                    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-                    lrow[hrow] = lrow[hrow] * alpha + sum;
-                    mrow[hrow] = mNew;
-                    if (alpha != 1.0f) {
-#pragma unroll
-                        for (int j = 0; j < 16; j++) {
-                            oacc[j][2 * hrow] *= alpha;
-                            oacc[j][2 * hrow + 1] *= alpha;
+                        for (int r = 0; r < 2; r++) {
+                            float sc = round16<BF16>(sacc[nt][2 * r + j]) * p.scaleLog2;  // the reference rounds the dot to storage first
+                            if (tail && tokBase + 8 * r + g >= ctx) sc = -INFINITY;
+                            x[r] = sc;
                         }
+                        float mx = fmaxf(x[0], x[1]);
+                        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+                        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+                        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+                        const float mNew = fmaxf(mcol[nt][j], mx);
+                        const float a = (mNew == -INFINITY) ? 1.0f : exp2f(mcol[nt][j] - mNew);
+                        const float e0 = (x[0] == -INFINITY) ? 0.f : exp2f(x[0] - mNew);
+                        const float e1 = (x[1] == -INFINITY) ? 0.f : exp2f(x[1] - mNew);
+                        sacc[nt][j] = e0;
+                        sacc[nt][2 + j] = e1;
+                        lcol[nt][j] = lcol[nt][j] * a + (e0 + e1);
+                        mcol[nt][j] = mNew;
+                        alpha[nt][j] = a;
+                        rescale |= a != 1.0f;
                     }
                 }
-                // ---- O += P V ----
-                uint32_t pa[4], pl[4];
-                pa[0] = pack16<MMA_BF16>(pv[0][0], pv[0][1]);
-                pa[1] = pack16<MMA_BF16>(pv[1][0], pv[1][1]);
-                pa[2] = pack16<MMA_BF16>(pv[0][2], pv[0][3]);
-                pa[3] = pack16<MMA_BF16>(pv[1][2], pv[1][3]);
-                if (SPLIT_P) {
-                    // low part: what the 16-bit rounding of P dropped
-                    pl[0] = pack16<MMA_BF16>(pv[0][0] - unpack16_lo<MMA_BF16>(pa[0]), pv[0][1] - unpack16_hi<MMA_BF16>(pa[0]));
-                    pl[1] = pack16<MMA_BF16>(pv[1][0] - unpack16_lo<MMA_BF16>(pa[1]), pv[1][1] - unpack16_hi<MMA_BF16>(pa[1]));
-                    pl[2] = pack16<MMA_BF16>(pv[0][2] - unpack16_lo<MMA_BF16>(pa[2]), pv[0][3] - unpack16_hi<MMA_BF16>(pa[2]));
-                    pl[3] = pack16<MMA_BF16>(pv[1][2] - unpack16_lo<MMA_BF16>(pa[3]), pv[1][3] - unpack16_hi<MMA_BF16>(pa[3]));
-                }
-                {
-                    const int mi = lane >> 3, r = lane & 7;
-                    const int tok = (mi & 1) * 8 + r;
+                if (__any_sync(0xffffffffu, rescale)) {
 #pragma unroll
-                    for (int jj = 0; jj < 8; jj++) {
-                        const int chunk = 2 * jj + (mi >> 1);
-                        uint32_t b0, b1, b2, b3;
-                        ldmatrix_x4_trans(tileV + tok * 256 + ((chunk ^ (tok & 7)) * 16), b0, b1, b2, b3);
-                        mma16816<MMA_BF16>(oacc[2 * jj], pa, b0, b1);
-                        mma16816<MMA_BF16>(oacc[2 * jj + 1], pa, b2, b3);
-                        if (SPLIT_P) {
-                            mma16816<MMA_BF16>(oacc[2 * jj], pl, b0, b1);
-                            mma16816<MMA_BF16>(oacc[2 * jj + 1], pl, b2, b3);
+                    for (int dt = 0; dt < 8; dt++)
+#pragma unroll
+                        for (int nt = 0; nt < NT; nt++) {
+                            oacc[dt][nt][0] *= alpha[nt][0];
+                            oacc[dt][nt][1] *= alpha[nt][1];
+                            oacc[dt][nt][2] *= alpha[nt][0];
+                            oacc[dt][nt][3] *= alpha[nt][1];
                         }
+                }
+                // ---- P^T as B operands, high and low 16-bit parts: (token g, heads 2t, 2t+1) -> movmatrix -> (head g, tokens 2t, 2t+1) ----
+                uint32_t ph[NT][2], pl[NT][2];
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++) {
+#pragma unroll
+                    for (int r = 0; r < 2; r++) {
+                        const float p0 = sacc[nt][2 * r], p1 = sacc[nt][2 * r + 1];
+                        const uint32_t h = pack16<BF16>(p0, p1);
+                        const uint32_t l = pack16<BF16>(p0 - unpack16_lo<BF16>(h), p1 - unpack16_hi<BF16>(h));  // what the rounding of P dropped
+                        ph[nt][r] = movmatrix_trans(h);
+                        pl[nt][r] = movmatrix_trans(l);
+                    }
+                }
+                // ---- O^T += V^T P^T ----
+#pragma unroll
+                for (int dt = 0; dt < 8; dt++) {
+                    uint32_t a[4];  // (dims 16dt+g, tok 2t..), (dims 16dt+8+g, tok 2t..), (dims 16dt+g, tok 8+2t..), (dims 16dt+8+g, tok 8+2t..)
+                    ldmatrix_x4_trans(tileV + vLm + (((2 * dt + vLmChunk) ^ lmRow) * 16), a[0], a[1], a[2], a[3]);
+#pragma unroll
+                    for (int nt = 0; nt < NT; nt++) {
+                        mma16816<BF16>(oacc[dt][nt], a, ph[nt][0], ph[nt][1]);
+                        mma16816<BF16>(oacc[dt][nt], a, pl[nt][0], pl[nt][1]);
                     }
                 }
             }
             cp_async_wait<0>();
             __syncwarp();
-
-            // ---- write the partial of (worker, sequence b) ----
+            // ---- partial of (worker, sequence b, KV head): row sums reduced over the lanes of a head column ----
             {
                 const long long slot = worker + b;
-                const float vS = (FP8KV && p.vScale) ? p.vScale[kvh] : 1.0f;
 #pragma unroll
-                for (int hrow = 0; hrow < 2; hrow++) {
-                    const int gi = g + 8 * hrow;
-                    if (gi < p.group) {
-                        const int head = kvh * p.group + gi;
-                        float* acc = p.partAcc + ((size_t)slot * p.numHeads + head) * kHeadDim;
+                for (int nt = 0; nt < NT; nt++) {
 #pragma unroll
-                        for (int j = 0; j < 16; j++)
-                            *(float2*)(acc + 8 * j + 2 * t) = make_float2(oacc[j][2 * hrow] * vS, oacc[j][2 * hrow + 1] * vS);
-                        if (t == 0) p.partML[(size_t)slot * p.numHeads + head] = make_float2(mrow[hrow], lrow[hrow]);
+                    for (int j = 0; j < 2; j++) {
+                        float l = lcol[nt][j];
+                        l += __shfl_xor_sync(0xffffffffu, l, 4);
+                        l += __shfl_xor_sync(0xffffffffu, l, 8);
+                        l += __shfl_xor_sync(0xffffffffu, l, 16);
+                        const int gi = nt * 8 + 2 * t + j;
+                        if (gi < p.group) {
+                            const int head = kvh * p.group + gi;
+                            float* acc = p.partAcc + ((size_t)slot * p.numHeads + head) * kHeadDim;
+#pragma unroll
+                            for (int dt = 0; dt < 8; dt++) {
+                                acc[16 * dt + g] = oacc[dt][nt][j];
+                                acc[16 * dt + g + 8] = oacc[dt][nt][2 + j];
+                            }
+                            if (g == 0) p.partML[(size_t)slot * p.numHeads + head] = make_float2(mcol[nt][j], l);
+                        }
                     }
                 }
             }
@@ -585,11 +566,6 @@ __device__ __forceinline__ float ex2_approx(float x) {  // 2^x, flush-to-zero, 2
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
-}
-__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
-    uint32_t d;
-    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
-    return d;
 }
 __device__ __forceinline__ void mma16816_f16(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -1008,9 +984,13 @@ int launch_paged_decode(Context* ctx, int dt, int kvDT, const void* q, const voi
             else DECODE_LAUNCH((paged_decode_fp8_kernel<false, 2>), kSmem8);
         }
     } else {
-        constexpr int smem16 = DecodeSmem<true, false, 3>::kTotal;
-        if (bf16) DECODE_LAUNCH((paged_decode_kernel<true, false, 3, true>), smem16);
-        else DECODE_LAUNCH((paged_decode_kernel<false, false, 3, true>), smem16);
+        if (group <= 8) {
+            if (bf16) DECODE_LAUNCH((paged_decode16_kernel<true, 1>), kSmem16);
+            else DECODE_LAUNCH((paged_decode16_kernel<false, 1>), kSmem16);
+        } else {
+            if (bf16) DECODE_LAUNCH((paged_decode16_kernel<true, 2>), kSmem16);
+            else DECODE_LAUNCH((paged_decode16_kernel<false, 2>), kSmem16);
+        }
     }
 #undef DECODE_LAUNCH
     return check_launch(ctx, status, "paged decode attention");
