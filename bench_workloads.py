@@ -135,7 +135,7 @@ class ChainWorkload:
         t = BI.upload_chain(inp, r0, r1)
         self.x, self.r, self.branch, self.gate, self.up, self.gamma = t["x"], t["r"], t["branch"], t["gate"], t["up"], t["gamma"]
         self.mod = t["mod"][first:first + nb].contiguous()
-        i16 = torch.int16
+        i16 = torch.bfloat16  # raw 16-bit storage (NCCL has no int16 collectives)
         if world > 1:
             # the kernels write this rank's rows straight into their place in the gathered tensors, so the all-gathers run in
             # place (no local copy) and the first two overlap the SwiGLU kernel

@@ -57,14 +57,34 @@ typedef enum CUDAElementDType {
     CUDAElementDTypeFloat8E5M2 = 5,
 } CUDAElementDType;
 
-/* subset of CUDAUnaryFloat32Op (core.h:35-70) implemented on this path; other codes return -6 */
+/* CUDAUnaryFloat32Op (core.h:35-70).  Implemented: every activation of device.Activation (device/interface.go:18-74) that has a
+   code here; the plain math codes 1-7, 10, 11 (Abs .. Cos) belong to another op family and return -6. */
 typedef enum CUDAUnaryFloat32Op {
     CUDAUnaryFloat32Relu = 0,
+    CUDAUnaryFloat32Exp = 8,
+    CUDAUnaryFloat32Log = 9,
     CUDAUnaryFloat32Tanh = 12,
     CUDAUnaryFloat32Sigmoid = 13,
     CUDAUnaryFloat32Silu = 14,
+    CUDAUnaryFloat32Swish = 15,
+    CUDAUnaryFloat32Softsign = 16,
+    CUDAUnaryFloat32ELU = 17,
+    CUDAUnaryFloat32SELU = 18,
+    CUDAUnaryFloat32LeakyReLU = 19,
+    CUDAUnaryFloat32HardSigmoid = 20,
+    CUDAUnaryFloat32HardSwish = 21,
     CUDAUnaryFloat32Gelu = 22,
+    CUDAUnaryFloat32Log1p = 23,
+    CUDAUnaryFloat32Expm1 = 24,
+    CUDAUnaryFloat32CELU = 25,
+    CUDAUnaryFloat32Softplus = 26,
+    CUDAUnaryFloat32Mish = 27,
+    CUDAUnaryFloat32LogSigmoid = 28,
     CUDAUnaryFloat32GeluTanh = 29,
+    CUDAUnaryFloat32HardTanh = 30,
+    CUDAUnaryFloat32HardGelu = 31,
+    CUDAUnaryFloat32QuickGelu = 32,
+    CUDAUnaryFloat32TanhShrink = 33,
 } CUDAUnaryFloat32Op;
 
 /* device/cuda/elementwise/arithmetic.h */
@@ -157,7 +177,18 @@ PUTER_DECLARE_GATED(glu)
 PUTER_DECLARE_GATED(reglu)
 PUTER_DECLARE_GATED(siglu)
 PUTER_DECLARE_GATED(geglu_tanh)
+PUTER_DECLARE_GATED(seglu)
+PUTER_DECLARE_GATED(linglu)
 #undef PUTER_DECLARE_GATED
+/* device/cuda/activation/softmax.h:10-19 (device.Activation.Softmax, device/interface.go:65; CPU device/cpu/math/softmax.go:7-33):
+   per row of `cols` elements: max, FastExp32(x - max), sum, multiply by 1 / sum; 16-bit rows are widened, computed in
+   float32 and rounded (device/cpu/activation/softmax.go:43-68).  The Go method takes one vector: rows = 1, cols = count. */
+int cuda_dispatch_softmax(CUDADeviceRef contextRef, int elementDType, CUDABufferRef inputRef, CUDABufferRef outRef, uint32_t rows,
+                          uint32_t cols, uint64_t completionToken, CUDAStatus* status);
+/* NEW (CPU-only in the reference): device.Activation.LogSoftmax, device/interface.go:46; device/cpu/math/softmax.go:38-60:
+   x - max - FastLog32(sum FastExp32(x - max)) */
+int cuda_dispatch_log_softmax(CUDADeviceRef contextRef, int elementDType, CUDABufferRef inputRef, CUDABufferRef outRef, uint32_t rows,
+                              uint32_t cols, uint64_t completionToken, CUDAStatus* status);
 /* NEW: gated residual out = residual + modulation[b, set*3*C + 2*C + c] * branch, b = row / rowsPerBatch
    (execution/math_gated_residual_intrinsic.go:11-17,206-223; device kernel only on Metal) */
 int cuda_dispatch_gated_residual(CUDADeviceRef contextRef, int elementDType, CUDABufferRef residualRef, CUDABufferRef branchRef,
@@ -180,6 +211,12 @@ int cuda_dispatch_rmsnorm_f64(CUDADeviceRef contextRef, int elementDType, CUDABu
 int cuda_dispatch_layernorm(CUDADeviceRef contextRef, int elementDType, CUDABufferRef inputRef, CUDABufferRef scaleRef,
                             CUDABufferRef biasRef, CUDABufferRef outputRef, uint32_t rows, uint32_t cols, float epsilon,
                             uint64_t completionToken, CUDAStatus* status);
+/* The catalog's fused entry layernorm + add -> layernorm_residual (fusion/catalog.go:183-205; four inputs; ULP bound 2; no CUDA
+   kernel in the reference): out = LayerNorm(x, scale, bias) + residual.  The LayerNorm result is rounded to the storage
+   type before the add, as the two separate ops would, so fused and unfused results are equal. */
+int cuda_dispatch_layernorm_residual(CUDADeviceRef contextRef, int elementDType, CUDABufferRef inputRef, CUDABufferRef scaleRef,
+                                     CUDABufferRef biasRef, CUDABufferRef residualRef, CUDABufferRef outputRef, uint32_t rows,
+                                     uint32_t cols, float epsilon, uint64_t completionToken, CUDAStatus* status);
 /* NEW (CPU-only in the reference): device.LayerNorm.AdaptiveRMSNorm, device/interface.go:356-361;
    device/cpu/layernorm/compute.go:209-264,387-482.  modulation is [rows / rowsPerBatch, modulationCols] = [scale | shift | ...]. */
 int cuda_dispatch_adaptive_rmsnorm(CUDADeviceRef contextRef, int elementDType, CUDABufferRef inputRef, CUDABufferRef modulationRef,
@@ -234,6 +271,11 @@ int cuda_dispatch_kv_page_write(CUDADeviceRef contextRef, int elementDType, CUDA
 int cuda_dispatch_kv_page_gather(CUDADeviceRef contextRef, int elementDType, CUDABufferRef storageRef, CUDABufferRef pageTableRef,
                                  CUDABufferRef outputRef, uint32_t pageCount, uint32_t pageSize, uint32_t inner, uint32_t outRows,
                                  uint64_t storageOffset, uint64_t completionToken, CUDAStatus* status);
+/* NEW: device.Shape.LastToken (device/interface.go:622; CPU device/cpu/shape/ops.go:133-160) and the device hook of the
+   shape.last_token intrinsic (execution/shape_intrinsic.go:12-19,489-543): output[b] = input[b, seq - 1, :] for b < batch,
+   rows of `hidden` elements.  `seq` is the LIVE sequence length of a possibly larger allocation. */
+int cuda_dispatch_last_token(CUDADeviceRef contextRef, int elementDType, CUDABufferRef inputRef, CUDABufferRef outRef, uint32_t batch,
+                             uint32_t seq, uint32_t hidden, uint64_t completionToken, CUDAStatus* status);
 /* NEW, no single counterpart in the reference: the KV-cache producer step of a decoder layer in one launch.  Equals
    RoPE(k) (device/interface.go RoPE; device/cpu/rope/compute.go:55-193) at the per-row position positions[row], the result
    rounded to elementDType, then, when kvDType is e4m3, the cast of value / scale[kv head] (convert package rules), then

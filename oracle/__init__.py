@@ -26,7 +26,10 @@ _NP = {F32: np.float32, F16: np.uint16, BF16: np.uint16, E4M3: np.uint8, E5M2: n
 
 # unary op codes = CUDAUnaryFloat32Op (core.h:35-70); gated variants in oracle order
 RELU, TANH, SIGMOID, SILU, GELU, GELU_TANH = 0, 12, 13, 14, 22, 29
-SWIGLU, GEGLU, GLU, REGLU, SIGLU, GEGLU_TANH = 0, 1, 2, 3, 4, 5
+UNARY_CODES = {"Relu": 0, "Exp": 8, "Log": 9, "Tanh": 12, "Sigmoid": 13, "Silu": 14, "Swish": 15, "Softsign": 16, "ELU": 17, "SELU": 18,
+               "LeakyReLU": 19, "HardSigmoid": 20, "HardSwish": 21, "Gelu": 22, "Log1p": 23, "Expm1": 24, "CELU": 25, "Softplus": 26,
+               "Mish": 27, "LogSigmoid": 28, "GeluTanh": 29, "HardTanh": 30, "HardGelu": 31, "QuickGelu": 32, "TanhShrink": 33}
+SWIGLU, GEGLU, GLU, REGLU, SIGLU, GEGLU_TANH, SEGLU, LINGLU = 0, 1, 2, 3, 4, 5, 6, 7
 ADD, SUB, MUL, DIV, MAX, MIN = 0, 1, 2, 3, 4, 5
 
 
@@ -106,6 +109,23 @@ def unary(op: int, dt: int, src: np.ndarray) -> np.ndarray:
     dst = np.empty_like(src)
     _check(lib().oracle_unary(op, dt, _p(src), _p(dst), _ll(src.size)), "unary")
     return dst
+
+
+def softmax_rows(dt: int, x: np.ndarray, log: bool = False) -> np.ndarray:
+    """device.Activation.Softmax / LogSoftmax applied to every row of a [rows, cols] array."""
+    x = np.ascontiguousarray(x, dtype=_NP[dt])
+    rows, cols = x.shape
+    out = np.empty_like(x)
+    _check(lib().oracle_softmax_rows(dt, _p(x), _p(out), _ll(rows), _ll(cols), ctypes.c_int(int(log))), "softmax_rows")
+    return out
+
+
+def last_token(x: np.ndarray, batch: int, seq: int, hidden: int) -> np.ndarray:
+    """device.Shape.LastToken on a [batch, seq, hidden] array of any element type."""
+    x = np.ascontiguousarray(x)
+    out = np.empty((batch, hidden), dtype=x.dtype)
+    _check(lib().oracle_last_token(_p(x), _p(out), _ll(batch), _ll(seq), _ll(hidden * x.dtype.itemsize)), "last_token")
+    return out
 
 
 def gated_tensors(op: int, dt: int, gate: np.ndarray, up: np.ndarray) -> np.ndarray:

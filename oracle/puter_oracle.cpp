@@ -627,6 +627,40 @@ ORACLE_API int oracle_unary(int op, int dt, const void* src, void* dst, long lon
 }
 
 // device.Activation.SwiGLUTensors etc.: device/cpu/activation/compute.go:148-176
+// device.Activation.Softmax / LogSoftmax over each row of `cols` elements: device/cpu/math/softmax.go:7-60 in float32
+// (sequential sum in index order); 16-bit rows are widened into a float32 scratch row and the result rounded
+// (device/cpu/activation/softmax.go:43-68).  The Go method works on one vector: rows = 1.
+ORACLE_API int oracle_softmax_rows(int dt, const void* src, void* dst, long long rows, long long cols, int logSpace) {
+    if (dt != F32 && dt != BF16 && dt != F16) return -1;
+#pragma omp parallel for schedule(static)
+    for (long long r = 0; r < rows; r++) {
+        std::vector<float> x((size_t)cols), y((size_t)cols);
+        for (long long i = 0; i < cols; i++) x[i] = load_typed(src, (size_t)(r * cols + i), dt);
+        float mx = x[0];
+        for (long long i = 1; i < cols; i++) if (x[i] > mx) mx = x[i];
+        float sum = 0.f;
+        if (logSpace) {
+            for (long long i = 0; i < cols; i++) sum += fast_exp32(x[i] - mx);
+            float ls = fast_log32(sum);
+            for (long long i = 0; i < cols; i++) y[i] = x[i] - mx - ls;
+        } else {
+            for (long long i = 0; i < cols; i++) { y[i] = fast_exp32(x[i] - mx); sum += y[i]; }
+            float inv = 1.0f / sum;
+            for (long long i = 0; i < cols; i++) y[i] *= inv;
+        }
+        for (long long i = 0; i < cols; i++) store_typed(dst, (size_t)(r * cols + i), y[i], dt);
+    }
+    return 0;
+}
+
+// device.Shape.LastToken: device/cpu/shape/ops.go:133-160 (byte copy of the final sequence row of every batch item)
+ORACLE_API int oracle_last_token(const void* src, void* dst, long long batch, long long seq, long long hiddenBytes) {
+    if (batch == 0 || seq == 0 || hiddenBytes == 0) return 0;
+    for (long long b = 0; b < batch; b++)
+        std::memcpy((char*)dst + b * hiddenBytes, (const char*)src + ((b * seq + seq - 1) * hiddenBytes), (size_t)hiddenBytes);
+    return 0;
+}
+
 ORACLE_API int oracle_gated_tensors(int op, int dt, void* dst, const void* gate, const void* up, long long n) {
     if (dt != F32 && dt != BF16 && dt != F16) return -1;
 #pragma omp parallel for schedule(static)

@@ -21,7 +21,7 @@ vp, u32, u64, i64, cint, dbl, flt = (ctypes.c_void_p, ctypes.c_uint32, ctypes.c_
                                      ctypes.c_double, ctypes.c_float)
 SP = ctypes.POINTER(CUDAStatus)
 
-_GATED = ["swiglu", "geglu", "glu", "reglu", "siglu", "geglu_tanh"]
+_GATED = ["swiglu", "geglu", "glu", "reglu", "siglu", "geglu_tanh", "seglu", "linglu"]
 
 # name -> (restype, argtypes); mirrors include/puter_b200.h one to one
 SIGNATURES = {
@@ -57,6 +57,10 @@ SIGNATURES = {
     "cuda_dispatch_gated_residual": (cint, [vp, cint, vp, vp, vp, vp, u32, u32, u32, u32, u32, u64, SP]),
     "cuda_dispatch_rmsnorm": (cint, [vp, cint, vp, vp, vp, u32, u32, flt, u64, SP]),
     "cuda_dispatch_layernorm": (cint, [vp, cint, vp, vp, vp, vp, u32, u32, flt, u64, SP]),
+    "cuda_dispatch_layernorm_residual": (cint, [vp, cint, vp, vp, vp, vp, vp, u32, u32, flt, u64, SP]),
+    "cuda_dispatch_softmax": (cint, [vp, cint, vp, vp, u32, u32, u64, SP]),
+    "cuda_dispatch_log_softmax": (cint, [vp, cint, vp, vp, u32, u32, u64, SP]),
+    "cuda_dispatch_last_token": (cint, [vp, cint, vp, vp, u32, u32, u32, u64, SP]),
     "cuda_dispatch_adaptive_rmsnorm": (cint, [vp, cint, vp, vp, vp, u32, u32, u32, u32, dbl, u64, SP]),
     "cuda_dispatch_modulated_layernorm": (cint, [vp, cint, vp, vp, vp, u32, u32, u32, u32, u32, dbl, u64, SP]),
     "cuda_dispatch_rmsnorm_f64": (cint, [vp, cint, vp, vp, vp, u32, u32, dbl, u64, SP]),

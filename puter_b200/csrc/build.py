@@ -23,6 +23,7 @@ SOURCES = [
     "elementwise.cu",
     "norm.cu",
     "layernorm.cu",
+    "softmax.cu",
     "rope.cu",
     "pages.cu",
     "attention_exact.cu",

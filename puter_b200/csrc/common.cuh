@@ -292,6 +292,44 @@ __device__ __forceinline__ float fast_gelu_tanh32(float v) {  // f32.go:101-105
 }
 __device__ __forceinline__ float fast_relu32(float v) { return v > 0.0f ? v : 0.0f; }
 
+// ---- the rest of the activation set (device/cpu/math/f32.go:50-69, activation.go:34-270, extra_activation.go:3-37) ----
+__device__ __forceinline__ float nan32_ref() { return __uint_as_float(0x7FC00001u); }  // math/constant.go:5: what the log family returns for x <= 0
+__device__ __forceinline__ float fast_log32(float x) {
+    if (x <= 0.0f) return nan32_ref();
+    const uint32_t bits = __float_as_uint(x);
+    const int e = (int)(bits >> 23) - 127;
+    const float m = __uint_as_float((bits & 0x007FFFFFu) | (127u << 23));
+    const float y = sub(m, 1.0f);
+    float p = mul(y, 0.14449244f);
+    p = mul(y, add(-0.2407338084f, p));
+    p = mul(y, add(0.3317990258f, p));
+    p = mul(y, add(-0.4998741238f, p));
+    p = mul(y, add(0.9999964239f, p));
+    return add(p, mul((float)e, 0.6931471805599453f));
+}
+__device__ __forceinline__ float fast_leaky_relu32(float v) { return v > 0.0f ? v : mul(0.01f, v); }
+__device__ __forceinline__ float fast_elu32(float v) { return v > 0.0f ? v : sub(fast_exp32(v), 1.0f); }
+__device__ __forceinline__ float fast_selu32(float v) {
+    return v > 0.0f ? mul(1.0507009873554805f, v) : mul((float)(1.0507009873554805 * 1.6732632423543772), sub(fast_exp32(v), 1.0f));
+}
+__device__ __forceinline__ float fast_softplus32(float v) { return v > 20.0f ? v : fast_log32(add(1.0f, fast_exp32(v))); }
+__device__ __forceinline__ float fast_mish32(float v) { return mul(v, fast_tanh32(fast_softplus32(v))); }
+__device__ __forceinline__ float fast_softsign32(float v) { return v >= 0.0f ? divf(v, add(1.0f, v)) : divf(v, sub(1.0f, v)); }
+__device__ __forceinline__ float fast_hard_sigmoid32(float v) {
+    const float s = add(divf(v, 6.0f), 0.5f);
+    return s < 0.0f ? 0.0f : (s > 1.0f ? 1.0f : s);
+}
+__device__ __forceinline__ float fast_hard_swish32(float v) { return mul(v, fast_hard_sigmoid32(add(v, 3.0f))); }
+__device__ __forceinline__ float fast_hard_tanh32(float v) { return v < -1.0f ? -1.0f : (v > 1.0f ? 1.0f : v); }
+__device__ __forceinline__ float fast_hard_gelu32(float v) {
+    float inner = add(v, 3.0f);
+    if (inner < 0.0f) inner = 0.0f;
+    if (inner > 6.0f) inner = 6.0f;
+    return mul(v, divf(inner, 6.0f));
+}
+__device__ __forceinline__ float fast_quick_gelu32(float v) { return mul(v, fast_sigmoid32(mul(1.702f, v))); }
+__device__ __forceinline__ float fast_tanh_shrink32(float v) { return sub(v, fast_tanh32(v)); }
+
 // f64 variants used by the 16-bit LUT semantics (device/cpu/activation/lut.go:48-61, math/f64.go)
 __device__ __forceinline__ double fast_exp64(double x) {
     if (x < -708.3964185322641) return 0.0;
@@ -334,6 +372,34 @@ __device__ __forceinline__ double fast_gelu_tanh64(double v) {
     double cube = __dmul_rn(__dmul_rn(__dmul_rn(0.044715, v), v), v);
     double inner = __dmul_rn(0.7978845608028654, __dadd_rn(v, cube));
     return __dmul_rn(__dmul_rn(0.5, v), __dadd_rn(1.0, fast_tanh64(inner)));
+}
+
+__device__ __forceinline__ double fast_log64(double x) {  // math/f64.go:35-55
+    if (x <= 0.0) return __longlong_as_double(0x7FF8000000000001ll);
+    const unsigned long long bits = (unsigned long long)__double_as_longlong(x);
+    const long long e = (long long)(bits >> 52) - 1023;
+    const double m = __longlong_as_double((long long)((bits & 0x000FFFFFFFFFFFFFull) | (1023ull << 52)));
+    const double y = __dsub_rn(m, 1.0);
+    double p = __dmul_rn(y, 0.14449244);
+    p = __dmul_rn(y, __dadd_rn(-0.2407338084, p));
+    p = __dmul_rn(y, __dadd_rn(0.3317990258, p));
+    p = __dmul_rn(y, __dadd_rn(-0.4998741238, p));
+    p = __dmul_rn(y, __dadd_rn(0.9999964239, p));
+    return __dadd_rn(p, __dmul_rn((double)e, 0.6931471805599453));
+}
+__device__ __forceinline__ double fast_softplus64(double v) { return v > 20.0 ? v : fast_log64(__dadd_rn(1.0, fast_exp64(v))); }
+__device__ __forceinline__ double fast_hard_sigmoid64(double v) {
+    const double s = __dadd_rn(__ddiv_rn(v, 6.0), 0.5);
+    return s < 0.0 ? 0.0 : (s > 1.0 ? 1.0 : s);
+}
+// float64 -> float32 the way the host (amd64 CVTSD2SS) does it, NaN included: the payload's top bits survive, where the
+// GPU's own conversion would return the canonical NaN
+__device__ __forceinline__ float f64_to_f32_host(double d) {
+    if (d != d) {
+        const unsigned long long b = (unsigned long long)__double_as_longlong(d);
+        return __uint_as_float((uint32_t)((b >> 32) & 0x80000000u) | 0x7FC00000u | (uint32_t)((b >> 29) & 0x003FFFFFu));
+    }
+    return (float)d;
 }
 
 // 16-byte vector of raw storage elements

@@ -205,31 +205,52 @@ __device__ __forceinline__ void merge_if_last(const DecodeParams& p, const int* 
         if (!last) return;
         __threadfence();
     }
+    // Four heads per pass: lane = (head within the pass, 16-dimension slice).  Every owner's (max, sum) pair and accumulator
+    // slice is an independent load, so a sequence spread over many workers costs a few L2 round trips, not one per owner.
     uint16_t* orow = (uint16_t*)p.out + (size_t)b * p.numHeads * kHeadDim;
-    for (int gi = 0; gi < p.group; gi++) {
-        const int head = kvh * p.group + gi;
+    const bool allOwn = T >= W;
+    const int hl = lane >> 3, d0 = (lane & 7) * 16;
+    for (int hBase = 0; hBase < p.group; hBase += 4) {
+        const bool valid = hBase + hl < p.group;
+        const int head = kvh * p.group + (valid ? hBase + hl : 0);
+        const float2* mlBase = p.partML + (size_t)b * p.numHeads + head;          // + v * numHeads
+        const float* accBase = p.partAcc + ((size_t)b * p.numHeads + head) * kHeadDim + d0;  // + v * numHeads * 128
         float M = -INFINITY;
+#pragma unroll 4
         for (long long v = v0; v <= v1; v++)
-            if (owns(v)) M = fmaxf(M, __ldcg(&p.partML[(size_t)(v + b) * p.numHeads + head]).x);
+            if (allOwn || owns(v)) M = fmaxf(M, __ldcg(mlBase + (size_t)v * p.numHeads).x);
         float den = 0.f;
-        float4 num = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (long long v = v0; v <= v1; v++) {
-            if (!owns(v)) continue;
-            const float2 ml = __ldcg(&p.partML[(size_t)(v + b) * p.numHeads + head]);
-            const float w = (ml.x == -INFINITY) ? 0.f : exp2f(ml.x - M);
-            const float4 a = ldcg4(p.partAcc + ((size_t)(v + b) * p.numHeads + head) * kHeadDim + 4 * lane);
-            den += ml.y * w;
-            num.x += a.x * w; num.y += a.y * w; num.z += a.z * w; num.w += a.w * w;
-        }
-        float o[4] = {num.x, num.y, num.z, num.w};
-        uint32_t w2[2];
+        float4 num[4];
 #pragma unroll
-        for (int i = 0; i < 2; i++) {
-            const float a = den > 0.f ? o[2 * i] / den : 0.f, c = den > 0.f ? o[2 * i + 1] / den : 0.f;
-            const uint32_t lo = BF16 ? f32_to_bf16_bits(a) : f32_to_f16_bits(a), hi = BF16 ? f32_to_bf16_bits(c) : f32_to_f16_bits(c);
-            w2[i] = lo | (hi << 16);
+        for (int i = 0; i < 4; i++) num[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 2
+        for (long long v = v0; v <= v1; v++) {
+            if (!(allOwn || owns(v))) continue;
+            const float2 ml = __ldcg(mlBase + (size_t)v * p.numHeads);
+            const float* a = accBase + (size_t)v * p.numHeads * kHeadDim;
+            const float4 a0 = ldcg4(a), a1 = ldcg4(a + 4), a2 = ldcg4(a + 8), a3 = ldcg4(a + 12);
+            const float w = (ml.x == -INFINITY) ? 0.f : exp2f(ml.x - M);
+            den += ml.y * w;
+            num[0].x += a0.x * w; num[0].y += a0.y * w; num[0].z += a0.z * w; num[0].w += a0.w * w;
+            num[1].x += a1.x * w; num[1].y += a1.y * w; num[1].z += a1.z * w; num[1].w += a1.w * w;
+            num[2].x += a2.x * w; num[2].y += a2.y * w; num[2].z += a2.z * w; num[2].w += a2.w * w;
+            num[3].x += a3.x * w; num[3].y += a3.y * w; num[3].z += a3.z * w; num[3].w += a3.w * w;
         }
-        *(uint2*)(orow + (size_t)head * kHeadDim + 4 * lane) = make_uint2(w2[0], w2[1]);
+        if (!valid) continue;
+        uint32_t w2[8];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const float o[4] = {num[i].x, num[i].y, num[i].z, num[i].w};
+#pragma unroll
+            for (int j = 0; j < 2; j++) {
+                const float a = den > 0.f ? o[2 * j] / den : 0.f, c = den > 0.f ? o[2 * j + 1] / den : 0.f;
+                const uint32_t lo = BF16 ? f32_to_bf16_bits(a) : f32_to_f16_bits(a), hi = BF16 ? f32_to_bf16_bits(c) : f32_to_f16_bits(c);
+                w2[2 * i + j] = lo | (hi << 16);
+            }
+        }
+        uint4* dst = (uint4*)(orow + (size_t)head * kHeadDim + d0);
+        dst[0] = make_uint4(w2[0], w2[1], w2[2], w2[3]);
+        dst[1] = make_uint4(w2[4], w2[5], w2[6], w2[7]);
     }
 }
 
@@ -1079,8 +1100,8 @@ static int paged_decode_entry(bool noalloc, CUDADeviceRef contextRef, int elemen
     int* flag = nullptr;
     if (errorFlagRef) { PUTER_REQUIRE(errorFlagRef, "errorFlag", 4); flag = (int*)dev_ptr(errorFlagRef); }
     if ((((uintptr_t)dev_ptr(kPagesRef) | (uintptr_t)dev_ptr(vPagesRef)) & 15u) != 0 || ((uintptr_t)dev_ptr(queryRef) & 7u) != 0 ||
-        ((uintptr_t)dev_ptr(outRef) & 7u) != 0)
-        return fail(status, -2, "%s: K/V pools must be 16-byte aligned, query and output rows 8-byte aligned", what);
+        ((uintptr_t)dev_ptr(outRef) & 15u) != 0)
+        return fail(status, -2, "%s: K/V pools and output must be 16-byte aligned, query rows 8-byte aligned", what);
     DecodeScratch fixed{};
     if (noalloc) {
         // carve the fixed array: arrival counters at its end (cleared on the stream before every launch: an earlier call with

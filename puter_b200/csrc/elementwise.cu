@@ -1,6 +1,6 @@
-// Elementwise hot-path ops: unary activations (Silu / Gelu / GeluTanh / Sigmoid / Tanh / Relu),
-// binary arithmetic (Add is the residual add), gated activations (SwiGLU & friends, two-tensor and
-// packed) and the gated residual.
+// Elementwise hot-path ops: the unary activations of device.Activation (Silu / Gelu / GeluTanh and the other
+// 22 that carry a bridge op code), binary arithmetic (Add is the residual add), the eight gated
+// activations (SwiGLU & friends, two-tensor and packed) and the gated residual.
 //
 // Semantics follow the scalar Go code of the reference operation by operation:
 //   f32 unary      FastSilu32 / FastGelu32 / FastGeluTanh32 ...   device/cpu/math/f32.go, activation.go:50-57
@@ -14,34 +14,85 @@
 
 namespace puter {
 
-enum : int { G_SWIGLU = 0, G_GEGLU = 1, G_GLU = 2, G_REGLU = 3, G_SIGLU = 4, G_GEGLU_TANH = 5 };
+enum : int { G_SWIGLU = 0, G_GEGLU = 1, G_GLU = 2, G_REGLU = 3, G_SIGLU = 4, G_GEGLU_TANH = 5, G_SEGLU = 6, G_LINGLU = 7 };
 
+// every activation of device.Activation that has a code in CUDAUnaryFloat32Op (device/cuda/internal/bridge/core.h:35-70)
+#define PUTER_UNARY_OPS(X)                                                                                                   \
+    X(CUDAUnaryFloat32Relu) X(CUDAUnaryFloat32Exp) X(CUDAUnaryFloat32Log) X(CUDAUnaryFloat32Tanh) X(CUDAUnaryFloat32Sigmoid)  \
+    X(CUDAUnaryFloat32Silu) X(CUDAUnaryFloat32Swish) X(CUDAUnaryFloat32Softsign) X(CUDAUnaryFloat32ELU) X(CUDAUnaryFloat32SELU) \
+    X(CUDAUnaryFloat32LeakyReLU) X(CUDAUnaryFloat32HardSigmoid) X(CUDAUnaryFloat32HardSwish) X(CUDAUnaryFloat32Gelu)           \
+    X(CUDAUnaryFloat32Log1p) X(CUDAUnaryFloat32Expm1) X(CUDAUnaryFloat32CELU) X(CUDAUnaryFloat32Softplus) X(CUDAUnaryFloat32Mish) \
+    X(CUDAUnaryFloat32LogSigmoid) X(CUDAUnaryFloat32GeluTanh) X(CUDAUnaryFloat32HardTanh) X(CUDAUnaryFloat32HardGelu)          \
+    X(CUDAUnaryFloat32QuickGelu) X(CUDAUnaryFloat32TanhShrink)
+
+// float32: one math.Fast*32 per element (device/cpu/activation/f32_generic.go:9-222); Swish runs the Silu kernel (ops.go:41-43),
+// CELU with its default alpha of 1 is exp(v / 1) - 1 (math/activation.go:84-90)
 template <int OP> __device__ __forceinline__ float unary32(float v) {
     if (OP == CUDAUnaryFloat32Relu) return fast_relu32(v);
+    if (OP == CUDAUnaryFloat32Exp) return fast_exp32(v);
+    if (OP == CUDAUnaryFloat32Log) return fast_log32(v);
     if (OP == CUDAUnaryFloat32Tanh) return fast_tanh32(v);
     if (OP == CUDAUnaryFloat32Sigmoid) return fast_sigmoid32(v);
-    if (OP == CUDAUnaryFloat32Silu) return fast_silu32(v);
+    if (OP == CUDAUnaryFloat32Silu || OP == CUDAUnaryFloat32Swish) return fast_silu32(v);
+    if (OP == CUDAUnaryFloat32Softsign) return fast_softsign32(v);
+    if (OP == CUDAUnaryFloat32ELU || OP == CUDAUnaryFloat32CELU) return fast_elu32(v);
+    if (OP == CUDAUnaryFloat32SELU) return fast_selu32(v);
+    if (OP == CUDAUnaryFloat32LeakyReLU) return fast_leaky_relu32(v);
+    if (OP == CUDAUnaryFloat32HardSigmoid) return fast_hard_sigmoid32(v);
+    if (OP == CUDAUnaryFloat32HardSwish) return fast_hard_swish32(v);
     if (OP == CUDAUnaryFloat32Gelu) return fast_gelu32(v);
-    return fast_gelu_tanh32(v);
+    if (OP == CUDAUnaryFloat32Log1p) return fast_log32(add(1.0f, v));
+    if (OP == CUDAUnaryFloat32Expm1) return sub(fast_exp32(v), 1.0f);
+    if (OP == CUDAUnaryFloat32Softplus) return fast_softplus32(v);
+    if (OP == CUDAUnaryFloat32Mish) return fast_mish32(v);
+    if (OP == CUDAUnaryFloat32LogSigmoid) return -fast_softplus32(-v);
+    if (OP == CUDAUnaryFloat32GeluTanh) return fast_gelu_tanh32(v);
+    if (OP == CUDAUnaryFloat32HardTanh) return fast_hard_tanh32(v);
+    if (OP == CUDAUnaryFloat32HardGelu) return fast_hard_gelu32(v);
+    if (OP == CUDAUnaryFloat32QuickGelu) return fast_quick_gelu32(v);
+    return fast_tanh_shrink32(v);
 }
+// fill functions of the 16-bit tables (device/cpu/activation/lut.go:14-41); HardGelu, QuickGelu and TanhShrink go through
+// their float32 forms (math/extra_activation.go:19-37)
 __device__ __forceinline__ double unary64(int op, double v) {
     switch (op) {
         case CUDAUnaryFloat32Relu: return v > 0.0 ? v : 0.0;
+        case CUDAUnaryFloat32Exp: return fast_exp64(v);
+        case CUDAUnaryFloat32Log: return fast_log64(v);
         case CUDAUnaryFloat32Tanh: return fast_tanh64(v);
         case CUDAUnaryFloat32Sigmoid: return fast_sigmoid64(v);
-        case CUDAUnaryFloat32Silu: return fast_silu64(v);
+        case CUDAUnaryFloat32Silu: case CUDAUnaryFloat32Swish: return fast_silu64(v);
+        case CUDAUnaryFloat32Softsign: return __ddiv_rn(v, __dadd_rn(1.0, fabs(v)));
+        case CUDAUnaryFloat32ELU: case CUDAUnaryFloat32CELU: return v > 0.0 ? v : __dsub_rn(fast_exp64(v), 1.0);
+        case CUDAUnaryFloat32SELU:
+            return v > 0.0 ? __dmul_rn(1.0507009873554805, v)
+                           : __dmul_rn(1.0507009873554805 * 1.6732632423543772, __dsub_rn(fast_exp64(v), 1.0));
+        case CUDAUnaryFloat32LeakyReLU: return v > 0.0 ? v : __dmul_rn(0.01, v);
+        case CUDAUnaryFloat32HardSigmoid: return fast_hard_sigmoid64(v);
+        case CUDAUnaryFloat32HardSwish: return __dmul_rn(v, fast_hard_sigmoid64(__dadd_rn(v, 3.0)));
         case CUDAUnaryFloat32Gelu: return fast_gelu64(v);
-        default: return fast_gelu_tanh64(v);
+        case CUDAUnaryFloat32Log1p: return fast_log64(__dadd_rn(1.0, v));
+        case CUDAUnaryFloat32Expm1: return __dsub_rn(fast_exp64(v), 1.0);
+        case CUDAUnaryFloat32Softplus: return fast_softplus64(v);
+        case CUDAUnaryFloat32Mish: return __dmul_rn(v, fast_tanh64(fast_softplus64(v)));
+        case CUDAUnaryFloat32LogSigmoid: return -fast_softplus64(-v);
+        case CUDAUnaryFloat32GeluTanh: return fast_gelu_tanh64(v);
+        case CUDAUnaryFloat32HardTanh: return v < -1.0 ? -1.0 : (v > 1.0 ? 1.0 : v);
+        case CUDAUnaryFloat32HardGelu: return (double)fast_hard_gelu32(f64_to_f32_host(v));
+        case CUDAUnaryFloat32QuickGelu: return (double)fast_quick_gelu32(f64_to_f32_host(v));
+        default: return (double)fast_tanh_shrink32(f64_to_f32_host(v));
     }
 }
-// variant asymmetry of the reference (math/activation.go:286-308): SwiGLU/SiGLU activate the gate,
-// GLU/GeGLU/ReGLU/GeGLUTanh activate `up`.
+// variant asymmetry of the reference (math/activation.go:286-308, extra_activation.go:84-90): SwiGLU/SiGLU/SeGLU activate the
+// gate, GLU/GeGLU/ReGLU/GeGLUTanh activate `up`, LinGLU is the plain product.
 template <int OP> __device__ __forceinline__ float gated32(float gate, float up) {
     if (OP == G_SWIGLU) return mul(fast_silu32(gate), up);
     if (OP == G_GEGLU) return mul(gate, fast_gelu32(up));
     if (OP == G_GLU) return mul(gate, fast_sigmoid32(up));
     if (OP == G_REGLU) return mul(gate, fast_relu32(up));
     if (OP == G_SIGLU) return mul(fast_sigmoid32(gate), up);
+    if (OP == G_SEGLU) return mul(up, fast_sigmoid32(gate));
+    if (OP == G_LINGLU) return mul(gate, up);
     return mul(gate, fast_gelu_tanh32(up));
 }
 template <int OP> __device__ __forceinline__ float binary32(float a, float b) {
@@ -126,7 +177,7 @@ __global__ void build_lut_kernel(uint16_t* __restrict__ lut, int op) {
     uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= 65536u) return;
     float x = Storage<DT>::widen((uint16_t)i);
-    lut[i] = Storage<DT>::narrow((float)unary64(op, (double)x));
+    lut[i] = Storage<DT>::narrow(f64_to_f32_host(unary64(op, (double)x)));
 }
 
 __global__ void __launch_bounds__(256) lut_apply_kernel(const uint16_t* __restrict__ src, uint16_t* __restrict__ dst,
@@ -262,13 +313,13 @@ static bool aligned16(const void* a, const void* b = nullptr, const void* c = nu
 
 // lookup tables for the 16-bit unary activations, built on first use and kept for the life of the process
 struct LutKey { int device, dt, op; uint16_t* table; };
-static LutKey g_luts[64];
+static LutKey g_luts[512];
 static int g_lutCount = 0;
 
 static uint16_t* get_lut(Context* ctx, int dt, int op, CUDAStatus* status) {
     for (int i = 0; i < g_lutCount; i++)
         if (g_luts[i].device == ctx->device && g_luts[i].dt == dt && g_luts[i].op == op) return g_luts[i].table;
-    if (g_lutCount >= 64) { fail(status, -7, "cuda: activation table cache full"); return nullptr; }
+    if (g_lutCount >= 512) { fail(status, -7, "cuda: activation table cache full"); return nullptr; }
     uint16_t* t = nullptr;
     if (cudaMalloc((void**)&t, 65536 * 2) != cudaSuccess) { cudaGetLastError(); fail(status, -7, "cuda: activation table allocation failed"); return nullptr; }
     if (dt == DT_BF16) build_lut_kernel<DT_BF16><<<256, 256, 0, ctx->stream>>>(t, op);
@@ -359,11 +410,11 @@ extern "C" int cuda_dispatch_unary_elementwise(CUDADeviceRef contextRef, int ope
     (void)completionToken;
     PUTER_ENTER(ctx);
     if (count == 0) return ok(status);
-    switch (operation) {
-        case CUDAUnaryFloat32Relu: case CUDAUnaryFloat32Tanh: case CUDAUnaryFloat32Sigmoid:
-        case CUDAUnaryFloat32Silu: case CUDAUnaryFloat32Gelu: case CUDAUnaryFloat32GeluTanh: break;
-        default: return fail(status, -6, "cuda: unary elementwise: operation %d is not on this library's path", operation);
-    }
+    bool known = false;
+#define PUTER_KNOWN(OP) known |= operation == OP;
+    PUTER_UNARY_OPS(PUTER_KNOWN)
+#undef PUTER_KNOWN
+    if (!known) return fail(status, -6, "cuda: unary elementwise: operation %d is not on this library's path", operation);
     size_t es = dtype_size(elementDType);
     if (elementDType != DT_F32 && elementDType != DT_F16 && elementDType != DT_BF16)
         return fail(status, -6, "cuda: unary elementwise: unsupported dtype %d", elementDType);
@@ -373,12 +424,9 @@ extern "C" int cuda_dispatch_unary_elementwise(CUDADeviceRef contextRef, int ope
     void* dst = dev_ptr(outRef);
     if (elementDType == DT_F32) {
         switch (operation) {
-            case CUDAUnaryFloat32Relu: return launch_unary_f32<CUDAUnaryFloat32Relu>(ctx, src, dst, count, status);
-            case CUDAUnaryFloat32Tanh: return launch_unary_f32<CUDAUnaryFloat32Tanh>(ctx, src, dst, count, status);
-            case CUDAUnaryFloat32Sigmoid: return launch_unary_f32<CUDAUnaryFloat32Sigmoid>(ctx, src, dst, count, status);
-            case CUDAUnaryFloat32Silu: return launch_unary_f32<CUDAUnaryFloat32Silu>(ctx, src, dst, count, status);
-            case CUDAUnaryFloat32Gelu: return launch_unary_f32<CUDAUnaryFloat32Gelu>(ctx, src, dst, count, status);
-            default: return launch_unary_f32<CUDAUnaryFloat32GeluTanh>(ctx, src, dst, count, status);
+#define PUTER_CASE(OP) case OP: return launch_unary_f32<OP>(ctx, src, dst, count, status);
+            PUTER_UNARY_OPS(PUTER_CASE)
+#undef PUTER_CASE
         }
     }
     uint16_t* lut = get_lut(ctx, elementDType, operation, status);
@@ -426,6 +474,8 @@ PUTER_DEFINE_GATED(glu, G_GLU)
 PUTER_DEFINE_GATED(reglu, G_REGLU)
 PUTER_DEFINE_GATED(siglu, G_SIGLU)
 PUTER_DEFINE_GATED(geglu_tanh, G_GEGLU_TANH)
+PUTER_DEFINE_GATED(seglu, G_SEGLU)
+PUTER_DEFINE_GATED(linglu, G_LINGLU)
 
 extern "C" int cuda_dispatch_gated_residual(CUDADeviceRef contextRef, int elementDType, CUDABufferRef residualRef, CUDABufferRef branchRef,
                                             CUDABufferRef modulationRef, CUDABufferRef outputRef, uint32_t rows, uint32_t lastDim,

@@ -14,11 +14,13 @@
 // bf16 first (reduction/bf16_kernels.go:41-51).  Products and sums of the apply step are rounded one by one (no fused
 // multiply-add), results are rounded to the storage type once.
 //
-// One CTA per row at a time (grid-stride over rows): the row is read from HBM once, widened into shared memory, reduced twice
-// (sum, then squared differences against the mean) and written once: 2 x the row in traffic, the HBM minimum.
+// Every row is read from HBM once and written once: 2 x the row in traffic, the HBM minimum.  Rows that can travel as bulk
+// copies (16-byte aligned, a multiple of 16 bytes) go through the per-warp shared-memory row pipeline of row_pipeline.cuh;
+// other rows take one CTA per row (grid-stride), the row widened into shared memory, reduced twice and written.
 #include <math.h>
 
 #include "common.cuh"
+#include "row_pipeline.cuh"
 
 namespace puter {
 
@@ -70,7 +72,9 @@ struct RowNormParams {
     const void* in;
     const void* p0;   // LayerNorm: scale; the other two: modulation
     const void* p1;   // LayerNorm: bias
+    const void* res;  // LayerNorm only, optional: rows added to the rounded result (the fused layernorm + add)
     void* out;
+    int* errorFlag;
     size_t rows, cols, rowsPerBatch, modCols, set;
     double eps;
 };
@@ -180,12 +184,20 @@ __global__ void __launch_bounds__(256) row_norm_kernel(RowNormParams p) {
                     unpack_row<DT>(*(const Vec16*)((const char*)b + v * 16), bs);
 #pragma unroll
                     for (int i = 0; i < PER; i++) r[i] = add(mul(mul(sub(rowBuf[v * PER + i], mean), inv), gs[i]), bs[i]);
+                    if (p.res) {  // the unfused Add reads the stored (rounded) LayerNorm result
+                        float rs[PER];
+                        unpack_row<DT>(ld_stream((const char*)((const T*)p.res + row * cols) + v * 16), rs);
+#pragma unroll
+                        for (int i = 0; i < PER; i++) r[i] = add(Storage<DT>::widen(Storage<DT>::narrow(r[i])), rs[i]);
+                    }
                     st_stream((char*)o + v * 16, pack_row<DT>(r));
                 }
             } else {
                 for (size_t i = threadIdx.x; i < cols; i += blockDim.x) {
                     const float d = mul(mul(sub(rowBuf[i], mean), inv), Storage<DT>::load(g, i));
-                    Storage<DT>::store(o, i, add(d, Storage<DT>::load(b, i)));
+                    float r = add(d, Storage<DT>::load(b, i));
+                    if (p.res) r = add(Storage<DT>::widen(Storage<DT>::narrow(r)), Storage<DT>::load((const T*)p.res, row * cols + i));
+                    Storage<DT>::store(o, i, r);
                 }
             }
         } else {
@@ -219,40 +231,43 @@ __global__ void __launch_bounds__(256) row_norm_kernel(RowNormParams p) {
     }
 }
 
-// Rows of up to 32 * VPL vectors: one warp per row, the raw 16-byte vectors of the row held in registers (VPL per lane, lane l
-// owns vectors l, l + 32, ...), reductions by shuffles: no shared memory, no CTA-wide barrier between the passes.
 __device__ __forceinline__ float warp_sum_f32(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
     return v;
 }
-template <int DT, int OP, int VPL>
-__global__ void __launch_bounds__(256) row_norm_warp_kernel(RowNormParams p) {
+
+// Vector rows through the shared-memory row pipeline (row_pipeline.cuh): one warp per row, the raw row in a ring stage,
+// two or three passes over it (sum, squared differences, apply) while the next rows of the warp are being copied in.
+template <int DT, int OP>
+__global__ void __launch_bounds__(256) row_norm_ring_kernel(RowNormParams p, int stages) {
     using T = typename Storage<DT>::type;
     constexpr int PER = Per<DT>::kPer;
-    const size_t cols = p.cols, nvec = cols / PER;
+    constexpr int UN = 4;  // vectors per lane handled together: their loads are issued back to back, their sums are independent
+    extern __shared__ __align__(128) unsigned char ringSmem[];
+    const size_t cols = p.cols, nvec = cols / PER, rowBytes = cols * sizeof(T);
     const int lane = threadIdx.x & 31;
-    const size_t warpsTotal = (size_t)gridDim.x * (blockDim.x >> 5);
-    for (size_t row = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < p.rows; row += warpsTotal) {
-        const char* x = (const char*)((const T*)p.in + row * cols);
+    rowpipe::Ring ring(ringSmem, blockDim.x >> 5, stages, rowBytes, p.in, p.rows);
+    for (size_t row = ring.first(); row < p.rows; row = ring.next_row(row)) {
+        const unsigned char* x = ring.acquire(p.errorFlag);
+        if (!x) return;
         char* o = (char*)((T*)p.out + row * cols);
-        Vec16 raw[VPL];
+        float part[UN];
 #pragma unroll
-        for (int k = 0; k < VPL; k++) {
-            const size_t v = lane + (size_t)k * 32;
-            if (v < nvec) raw[k] = ld_stream(x + v * 16);
-        }
-        float acc = 0.f;
+        for (int u = 0; u < UN; u++) part[u] = 0.f;
+        for (size_t v0 = lane; v0 < nvec; v0 += 32 * UN) {
 #pragma unroll
-        for (int k = 0; k < VPL; k++) {
-            if (lane + (size_t)k * 32 < nvec) {
-                float f[PER];
-                unpack_row<DT>(raw[k], f);
+            for (int u = 0; u < UN; u++) {
+                const size_t v = v0 + 32 * (size_t)u;
+                if (v < nvec) {
+                    float f[PER];
+                    unpack_row<DT>(*(const Vec16*)(x + v * 16), f);
 #pragma unroll
-                for (int i = 0; i < PER; i++) acc += OP == OP_ADAPTIVE_RMS ? f[i] * f[i] : f[i];
+                    for (int i = 0; i < PER; i++) part[u] += OP == OP_ADAPTIVE_RMS ? f[i] * f[i] : f[i];
+                }
             }
         }
-        float total = warp_sum_f32(acc);
+        float total = warp_sum_f32((part[0] + part[1]) + (part[2] + part[3]));
         float mean = 0.f, inv;
         if (OP == OP_ADAPTIVE_RMS) {
             inv = (float)(1.0 / sqrt((double)__fdiv_rn(total, (float)cols) + p.eps));
@@ -263,20 +278,24 @@ __global__ void __launch_bounds__(256) row_norm_warp_kernel(RowNormParams p) {
                 if (DT == DT_BF16) total = Storage<DT>::widen(Storage<DT>::narrow(total));
                 mean = __fdiv_rn(total, (float)cols);
             }
-            float sq = 0.f;
 #pragma unroll
-            for (int k = 0; k < VPL; k++) {
-                if (lane + (size_t)k * 32 < nvec) {
-                    float f[PER];
-                    unpack_row<DT>(raw[k], f);
+            for (int u = 0; u < UN; u++) part[u] = 0.f;
+            for (size_t v0 = lane; v0 < nvec; v0 += 32 * UN) {
 #pragma unroll
-                    for (int i = 0; i < PER; i++) {
-                        const float d = sub(f[i], mean);
-                        sq = add(sq, mul(d, d));
+                for (int u = 0; u < UN; u++) {
+                    const size_t v = v0 + 32 * (size_t)u;
+                    if (v < nvec) {
+                        float f[PER];
+                        unpack_row<DT>(*(const Vec16*)(x + v * 16), f);
+#pragma unroll
+                        for (int i = 0; i < PER; i++) {
+                            const float d = sub(f[i], mean);
+                            part[u] = add(part[u], mul(d, d));
+                        }
                     }
                 }
             }
-            sq = warp_sum_f32(sq);
+            const float sq = warp_sum_f32((part[0] + part[1]) + (part[2] + part[3]));
             if (DT == DT_F32) inv = (float)(1.0 / sqrt((double)sq / (double)cols + p.eps));
             else if (OP == OP_LAYERNORM) inv = (float)(1.0 / sqrt((double)add(__fdiv_rn(sq, (float)cols), (float)p.eps)));
             else inv = (float)(1.0 / sqrt((double)__fdiv_rn(sq, (float)cols) + p.eps));
@@ -291,27 +310,48 @@ __global__ void __launch_bounds__(256) row_norm_warp_kernel(RowNormParams p) {
             a0 = (const char*)m;            // AdaptiveRMSNorm: scale; ModulatedLayerNorm: shift
             a1 = (const char*)(m + cols);   // AdaptiveRMSNorm: shift; ModulatedLayerNorm: scale
         }
+        const char* resRow = (OP == OP_LAYERNORM && p.res) ? (const char*)((const T*)p.res + row * cols) : nullptr;
+        for (size_t v0 = lane; v0 < nvec; v0 += 32 * UN) {
+            Vec16 xv[UN], c0v[UN], c1v[UN], rv[UN];
 #pragma unroll
-        for (int k = 0; k < VPL; k++) {
-            const size_t v = lane + (size_t)k * 32;
-            if (v < nvec) {
-                float f[PER], c0[PER], c1[PER], r[PER];
-                unpack_row<DT>(raw[k], f);
-                unpack_row<DT>(*(const Vec16*)(a0 + v * 16), c0);
-                unpack_row<DT>(*(const Vec16*)(a1 + v * 16), c1);
-#pragma unroll
-                for (int i = 0; i < PER; i++) {
-                    if (OP == OP_LAYERNORM) {
-                        r[i] = add(mul(mul(sub(f[i], mean), inv), c0[i]), c1[i]);
-                    } else {
-                        const float scale = OP == OP_ADAPTIVE_RMS ? c0[i] : c1[i], shift = OP == OP_ADAPTIVE_RMS ? c1[i] : c0[i];
-                        const float nrm = mul(OP == OP_ADAPTIVE_RMS ? f[i] : sub(f[i], mean), inv);
-                        r[i] = add(mul(nrm, add(1.0f, scale)), shift);
-                    }
+            for (int u = 0; u < UN; u++) {  // all loads of the batch first
+                const size_t v = v0 + 32 * (size_t)u;
+                if (v < nvec) {
+                    xv[u] = *(const Vec16*)(x + v * 16);
+                    c0v[u] = *(const Vec16*)(a0 + v * 16);
+                    c1v[u] = *(const Vec16*)(a1 + v * 16);
+                    if (resRow) rv[u] = ld_stream(resRow + v * 16);
                 }
-                st_stream(o + v * 16, pack_row<DT>(r));
+            }
+#pragma unroll
+            for (int u = 0; u < UN; u++) {
+                const size_t v = v0 + 32 * (size_t)u;
+                if (v < nvec) {
+                    float f[PER], c0[PER], c1[PER], r[PER];
+                    unpack_row<DT>(xv[u], f);
+                    unpack_row<DT>(c0v[u], c0);
+                    unpack_row<DT>(c1v[u], c1);
+#pragma unroll
+                    for (int i = 0; i < PER; i++) {
+                        if (OP == OP_LAYERNORM) {
+                            r[i] = add(mul(mul(sub(f[i], mean), inv), c0[i]), c1[i]);
+                        } else {
+                            const float scale = OP == OP_ADAPTIVE_RMS ? c0[i] : c1[i], shift = OP == OP_ADAPTIVE_RMS ? c1[i] : c0[i];
+                            const float nrm = mul(OP == OP_ADAPTIVE_RMS ? f[i] : sub(f[i], mean), inv);
+                            r[i] = add(mul(nrm, add(1.0f, scale)), shift);
+                        }
+                    }
+                    if (resRow) {  // the unfused Add reads the stored (rounded) LayerNorm result
+                        float rs[PER];
+                        unpack_row<DT>(rv[u], rs);
+#pragma unroll
+                        for (int i = 0; i < PER; i++) r[i] = add(Storage<DT>::widen(Storage<DT>::narrow(r[i])), rs[i]);
+                    }
+                    st_stream(o + v * 16, pack_row<DT>(r));
+                }
             }
         }
+        ring.release();
     }
 }
 
@@ -325,19 +365,24 @@ int launch_row_norm(Context* ctx, int dt, const RowNormParams& p, CUDAStatus* st
     if (blocks > cap) blocks = cap;
     const size_t es = dt == DT_F32 ? 4 : 2, per = 16 / es;
     // the modulation row of a batch starts at batch * modCols (+ set * 3 * cols) elements and its second half cols further on
-    const bool vec = p.cols % per == 0 && (((uintptr_t)p.in | (uintptr_t)p.out | (uintptr_t)p.p0 | (uintptr_t)p.p1) & 15u) == 0 &&
+    const bool vec = p.cols % per == 0 && (((uintptr_t)p.in | (uintptr_t)p.out | (uintptr_t)p.p0 | (uintptr_t)p.p1 | (uintptr_t)p.res) & 15u) == 0 &&
                      (OP == OP_LAYERNORM || p.modCols % per == 0);
-    // vector rows of up to 512 vectors (4096 16-bit or 2048 float32 elements) take the warp-per-row kernel
-    const size_t nvec = vec ? p.cols / per : 0;
-    const int vpl = nvec == 0 || nvec > 512 ? 0 : nvec <= 128 ? 4 : nvec <= 256 ? 8 : 16;
-    size_t warpBlocks = (p.rows + 7) / 8;
-    if (warpBlocks > cap) warpBlocks = cap;
+    // vector rows that fit the shared-memory row pipeline take the ring kernel; the rest one CTA per row
+    const rowpipe::Plan plan = vec ? rowpipe::plan(p.cols * es) : rowpipe::Plan{0, 0, 0};
+    size_t ringBlocks = 1;
+    if (plan.warps) {
+        size_t perSm = (220 * 1024) / (plan.smem + 1024);
+        if (perSm < 1) perSm = 1;
+        if (perSm > 4) perSm = 4;
+        ringBlocks = (p.rows + plan.warps - 1) / plan.warps;
+        if (ringBlocks > (size_t)ctx->smCount * perSm) ringBlocks = (size_t)ctx->smCount * perSm;
+    }
 #define ROWNORM_LAUNCH(DT)                                                                                          \
     do {                                                                                                            \
-        if (vpl == 4) row_norm_warp_kernel<DT, OP, 4><<<(unsigned)warpBlocks, 256, 0, ctx->stream>>>(p);             \
-        else if (vpl == 8) row_norm_warp_kernel<DT, OP, 8><<<(unsigned)warpBlocks, 256, 0, ctx->stream>>>(p);        \
-        else if (vpl == 16) row_norm_warp_kernel<DT, OP, 16><<<(unsigned)warpBlocks, 256, 0, ctx->stream>>>(p);      \
-        else if (vec) {                                                                                                  \
+        if (plan.warps) {                                                                                           \
+            cudaFuncSetAttribute(row_norm_ring_kernel<DT, OP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan.smem); \
+            row_norm_ring_kernel<DT, OP><<<(unsigned)ringBlocks, plan.warps * 32, plan.smem, ctx->stream>>>(p, plan.stages); \
+        } else if (vec) {                                                                                           \
             if (smem > 48 * 1024) cudaFuncSetAttribute(row_norm_kernel<DT, OP, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
             row_norm_kernel<DT, OP, true><<<(unsigned)blocks, 256, smem, ctx->stream>>>(p);                          \
         } else {                                                                                                    \
@@ -373,9 +418,32 @@ extern "C" int cuda_dispatch_layernorm(CUDADeviceRef contextRef, int elementDTyp
     PUTER_REQUIRE(biasRef, "bias", (size_t)cols * es);
     RowNormParams p = {};
     p.in = dev_ptr(inputRef); p.p0 = dev_ptr(scaleRef); p.p1 = dev_ptr(biasRef); p.out = dev_ptr(outputRef);
-    p.rows = rows; p.cols = cols; p.rowsPerBatch = 1;
+    p.rows = rows; p.cols = cols; p.rowsPerBatch = 1; p.errorFlag = ctx->errorFlag;
     p.eps = epsilon > 0.f ? (double)epsilon : 1e-5;  // the CPU op has no epsilon argument: 1e-5 (compute.go:11)
     return launch_row_norm<OP_LAYERNORM>(ctx, elementDType, p, status, "layernorm");
+}
+
+// The catalog's fused entry layernorm + add -> layernorm_residual (fusion/catalog.go:183-205, four inputs, ULP bound 2):
+// out = LayerNorm(x, scale, bias) + residual, the LayerNorm result rounded to the storage type before the add exactly as the
+// two separate ops would (so the fused result equals the unfused one bit for bit, inside the catalog's bound).
+extern "C" int cuda_dispatch_layernorm_residual(CUDADeviceRef contextRef, int elementDType, CUDABufferRef inputRef, CUDABufferRef scaleRef,
+                                                CUDABufferRef biasRef, CUDABufferRef residualRef, CUDABufferRef outputRef, uint32_t rows,
+                                                uint32_t cols, float epsilon, uint64_t completionToken, CUDAStatus* status) {
+    (void)completionToken;
+    PUTER_ENTER(ctx);
+    if (rows == 0 || cols == 0) return ok(status);
+    const size_t es = dtype_size(elementDType);
+    if (es == 0) return fail(status, -6, "layernorm_residual: unsupported dtype %d", elementDType);
+    PUTER_REQUIRE(inputRef, "input", (size_t)rows * cols * es);
+    PUTER_REQUIRE(residualRef, "residual", (size_t)rows * cols * es);
+    PUTER_REQUIRE(outputRef, "output", (size_t)rows * cols * es);
+    PUTER_REQUIRE(scaleRef, "scale", (size_t)cols * es);
+    PUTER_REQUIRE(biasRef, "bias", (size_t)cols * es);
+    RowNormParams p = {};
+    p.in = dev_ptr(inputRef); p.p0 = dev_ptr(scaleRef); p.p1 = dev_ptr(biasRef); p.res = dev_ptr(residualRef); p.out = dev_ptr(outputRef);
+    p.rows = rows; p.cols = cols; p.rowsPerBatch = 1; p.errorFlag = ctx->errorFlag;
+    p.eps = epsilon > 0.f ? (double)epsilon : 1e-5;
+    return launch_row_norm<OP_LAYERNORM>(ctx, elementDType, p, status, "layernorm_residual");
 }
 
 static int check_modulated(CUDAStatus* status, const char* what, double eps, uint32_t rows, uint32_t rowsPerBatch, uint64_t modCols,
@@ -402,7 +470,7 @@ extern "C" int cuda_dispatch_adaptive_rmsnorm(CUDADeviceRef contextRef, int elem
     PUTER_REQUIRE(modulationRef, "modulation", (size_t)(rows / rowsPerBatch) * modulationCols * es);
     RowNormParams p = {};
     p.in = dev_ptr(inputRef); p.p0 = dev_ptr(modulationRef); p.out = dev_ptr(outputRef);
-    p.rows = rows; p.cols = cols; p.rowsPerBatch = rowsPerBatch; p.modCols = modulationCols; p.eps = epsilon;
+    p.rows = rows; p.cols = cols; p.rowsPerBatch = rowsPerBatch; p.modCols = modulationCols; p.eps = epsilon; p.errorFlag = ctx->errorFlag;
     return launch_row_norm<OP_ADAPTIVE_RMS>(ctx, elementDType, p, status, "adaptive rmsnorm");
 }
 
@@ -423,5 +491,6 @@ extern "C" int cuda_dispatch_modulated_layernorm(CUDADeviceRef contextRef, int e
     RowNormParams p = {};
     p.in = dev_ptr(inputRef); p.p0 = dev_ptr(modulationRef); p.out = dev_ptr(outputRef);
     p.rows = rows; p.cols = cols; p.rowsPerBatch = rowsPerBatch; p.modCols = modulationCols; p.set = set; p.eps = epsilon;
+    p.errorFlag = ctx->errorFlag;
     return launch_row_norm<OP_MODULATED_LN>(ctx, elementDType, p, status, "modulated layernorm");
 }

@@ -55,6 +55,21 @@ __global__ void __launch_bounds__(256) page_gather_kernel(const char* __restrict
     }
 }
 
+// output[b] = input[b, seq - 1, :]: rows of rowBytes, one per batch item (device/cpu/shape/ops.go:133-160)
+__global__ void __launch_bounds__(256) last_token_kernel(const char* __restrict__ in, char* __restrict__ out, size_t batch, size_t seq,
+                                                        size_t rowBytes, int vec) {
+    const size_t unit = vec ? 16 : 1;
+    const size_t perRow = rowBytes / unit;
+    const size_t total = batch * perRow;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const size_t b = i / perRow, c = i % perRow;
+        const size_t src = ((b * seq + seq - 1) * rowBytes) + c * unit;
+        if (vec) st_stream(out + b * rowBytes + c * 16, ld_stream(in + src));
+        else out[b * rowBytes + c] = in[src];
+    }
+}
+
 }  // namespace puter
 
 using namespace puter;
@@ -119,4 +134,22 @@ extern "C" int cuda_dispatch_kv_page_gather(CUDADeviceRef contextRef, int elemen
     page_gather_kernel<<<page_grid(ctx, items), 256, 0, ctx->stream>>>(st, (const int32_t*)dev_ptr(pageTableRef), out, pageCount, pageSize,
                                                                        rowBytes, outRows, vec, ctx->errorFlag);
     return check_launch(ctx, status, "kv page gather");
+}
+
+extern "C" int cuda_dispatch_last_token(CUDADeviceRef contextRef, int elementDType, CUDABufferRef inputRef, CUDABufferRef outRef, uint32_t batch,
+                                        uint32_t seq, uint32_t hidden, uint64_t completionToken, CUDAStatus* status) {
+    (void)completionToken;
+    PUTER_ENTER(ctx);
+    size_t es = dtype_size(elementDType);
+    if (es == 0) return fail(status, -6, "last token: unsupported dtype %d", elementDType);
+    if (batch == 0 || seq == 0 || hidden == 0) return ok(status);  // device/cpu/shape/ops.go:140-142
+    const size_t rowBytes = (size_t)hidden * es;
+    PUTER_REQUIRE(inputRef, "input", (size_t)batch * seq * rowBytes);
+    PUTER_REQUIRE(outRef, "output", (size_t)batch * rowBytes);
+    const char* in = (const char*)dev_ptr(inputRef);
+    char* out = (char*)dev_ptr(outRef);
+    int vec = rowBytes % 16 == 0 && (((uintptr_t)in | (uintptr_t)out) & 15u) == 0;
+    size_t items = (size_t)batch * (vec ? rowBytes / 16 : rowBytes);
+    last_token_kernel<<<page_grid(ctx, items), 256, 0, ctx->stream>>>(in, out, batch, seq, rowBytes, vec);
+    return check_launch(ctx, status, "last token");
 }

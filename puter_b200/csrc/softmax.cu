@@ -1,0 +1,212 @@
+// Row softmax and log-softmax: device.Activation.Softmax / LogSoftmax (device/interface.go:65,46).
+//
+// Reference semantics (device/cpu/math/softmax.go:7-60, device/cpu/activation/softmax.go:17-68), per row:
+//   softmax     max = largest element; e[i] = FastExp32(x[i] - max); sum = sum of e[i]; out[i] = e[i] * (1 / sum)
+//   log-softmax out[i] = x[i] - max - FastLog32(sum of FastExp32(x[i] - max))
+// all in float32; bf16 / f16 rows are widened first and the result rounded once.  The CPU sums left to right, the kernels
+// in a tree, so a result can differ in its last float32 bits (tests allow 1e-5 relative, one unit in the last place for the
+// 16-bit types).  NaN ordering is the reference's too: the maximum is found with `>`, so a NaN never becomes the maximum.
+//
+// Rows that can travel as bulk copies go through the per-warp shared-memory row pipeline (row_pipeline.cuh): the row is read
+// from HBM once, visited three times in shared memory (max, sum of exponentials, result) and written once.  Other rows take
+// one CTA per row with scalar accesses.
+#include <math.h>
+
+#include "common.cuh"
+#include "row_pipeline.cuh"
+
+namespace puter {
+
+namespace {
+
+template <int DT> struct SPer { static constexpr int kPer = DT == DT_F32 ? 4 : 8; };
+template <int DT> __device__ __forceinline__ void s_unpack(const Vec16& v, float* f) {
+    if (DT == DT_F32) {
+#pragma unroll
+        for (int i = 0; i < 4; i++) f[i] = __uint_as_float(v.w[i]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            f[2 * i] = Storage<DT>::widen((uint16_t)(v.w[i] & 0xFFFFu));
+            f[2 * i + 1] = Storage<DT>::widen((uint16_t)(v.w[i] >> 16));
+        }
+    }
+}
+template <int DT> __device__ __forceinline__ Vec16 s_pack(const float* f) {
+    Vec16 v;
+    if (DT == DT_F32) {
+#pragma unroll
+        for (int i = 0; i < 4; i++) v.w[i] = __float_as_uint(f[i]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 4; i++)
+            v.w[i] = (uint32_t)Storage<DT>::narrow(f[2 * i]) | ((uint32_t)Storage<DT>::narrow(f[2 * i + 1]) << 16);
+    }
+    return v;
+}
+
+// the reference's running maximum: `if x > max { max = x }` starting from the first element
+__device__ __forceinline__ float ref_max(float a, float b) { return b > a ? b : a; }
+
+struct SoftmaxParams {
+    const void* in;
+    void* out;
+    size_t rows, cols;
+    int* errorFlag;
+};
+
+template <int DT, bool LOG>
+__global__ void __launch_bounds__(256) softmax_ring_kernel(SoftmaxParams p, int stages) {
+    using T = typename Storage<DT>::type;
+    constexpr int PER = SPer<DT>::kPer;
+    constexpr int UN = 4;  // vectors per lane handled together: independent chains of maxima, exponentials and sums
+    extern __shared__ __align__(128) unsigned char ringSmem[];
+    const size_t cols = p.cols, nvec = cols / PER, rowBytes = cols * sizeof(T);
+    const int lane = threadIdx.x & 31;
+    rowpipe::Ring ring(ringSmem, blockDim.x >> 5, stages, rowBytes, p.in, p.rows);
+    for (size_t row = ring.first(); row < p.rows; row = ring.next_row(row)) {
+        const unsigned char* x = ring.acquire(p.errorFlag);
+        if (!x) return;
+        char* o = (char*)((T*)p.out + row * cols);
+        float part[UN];
+        const float first = Storage<DT>::widen(*(const T*)x);  // the first element seeds the maximum
+#pragma unroll
+        for (int u = 0; u < UN; u++) part[u] = first;
+        for (size_t v0 = lane; v0 < nvec; v0 += 32 * UN) {
+#pragma unroll
+            for (int u = 0; u < UN; u++) {
+                const size_t v = v0 + 32 * (size_t)u;
+                if (v < nvec) {
+                    float f[PER];
+                    s_unpack<DT>(*(const Vec16*)(x + v * 16), f);
+#pragma unroll
+                    for (int i = 0; i < PER; i++) part[u] = ref_max(part[u], f[i]);
+                }
+            }
+        }
+        float mx = ref_max(ref_max(part[0], part[1]), ref_max(part[2], part[3]));
+#pragma unroll
+        for (int s = 16; s > 0; s >>= 1) mx = ref_max(mx, __shfl_xor_sync(0xffffffffu, mx, s));
+#pragma unroll
+        for (int u = 0; u < UN; u++) part[u] = 0.f;
+        for (size_t v0 = lane; v0 < nvec; v0 += 32 * UN) {
+#pragma unroll
+            for (int u = 0; u < UN; u++) {
+                const size_t v = v0 + 32 * (size_t)u;
+                if (v < nvec) {
+                    float f[PER];
+                    s_unpack<DT>(*(const Vec16*)(x + v * 16), f);
+#pragma unroll
+                    for (int i = 0; i < PER; i++) part[u] = add(part[u], fast_exp32(sub(f[i], mx)));
+                }
+            }
+        }
+        float sum = add(add(part[0], part[1]), add(part[2], part[3]));
+#pragma unroll
+        for (int s = 16; s > 0; s >>= 1) sum = add(sum, __shfl_xor_sync(0xffffffffu, sum, s));
+        const float k = LOG ? fast_log32(sum) : divf(1.0f, sum);
+        for (size_t v0 = lane; v0 < nvec; v0 += 32 * UN) {
+#pragma unroll
+            for (int u = 0; u < UN; u++) {
+                const size_t v = v0 + 32 * (size_t)u;
+                if (v < nvec) {
+                    float f[PER];
+                    s_unpack<DT>(*(const Vec16*)(x + v * 16), f);
+#pragma unroll
+                    for (int i = 0; i < PER; i++) f[i] = LOG ? sub(sub(f[i], mx), k) : mul(fast_exp32(sub(f[i], mx)), k);
+                    st_stream(o + v * 16, s_pack<DT>(f));
+                }
+            }
+        }
+        ring.release();
+    }
+}
+
+// any alignment, any length: one CTA per row, scalar accesses, the row re-read from memory (L2) in every pass
+template <int DT, bool LOG>
+__global__ void __launch_bounds__(256) softmax_scalar_kernel(SoftmaxParams p) {
+    using T = typename Storage<DT>::type;
+    __shared__ float red[32];
+    auto block_reduce = [&](float v, bool isMax) {
+#pragma unroll
+        for (int s = 16; s > 0; s >>= 1) {
+            const float o = __shfl_xor_sync(0xffffffffu, v, s);
+            v = isMax ? ref_max(v, o) : add(v, o);
+        }
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+        __syncthreads();
+        if (lane == 0) red[warp] = v;
+        __syncthreads();
+        float t = red[0];
+        for (int w = 1; w < nw; w++) t = isMax ? ref_max(t, red[w]) : add(t, red[w]);
+        return t;
+    };
+    for (size_t row = blockIdx.x; row < p.rows; row += gridDim.x) {
+        const T* x = (const T*)p.in + row * p.cols;
+        T* o = (T*)p.out + row * p.cols;
+        float mx = Storage<DT>::load(x, 0);
+        for (size_t i = threadIdx.x; i < p.cols; i += blockDim.x) mx = ref_max(mx, Storage<DT>::load(x, i));
+        mx = block_reduce(mx, true);
+        float sum = 0.f;
+        for (size_t i = threadIdx.x; i < p.cols; i += blockDim.x) sum = add(sum, fast_exp32(sub(Storage<DT>::load(x, i), mx)));
+        sum = block_reduce(sum, false);
+        const float k = LOG ? fast_log32(sum) : divf(1.0f, sum);
+        for (size_t i = threadIdx.x; i < p.cols; i += blockDim.x) {
+            const float v = Storage<DT>::load(x, i);
+            Storage<DT>::store(o, i, LOG ? sub(sub(v, mx), k) : mul(fast_exp32(sub(v, mx)), k));
+        }
+        __syncthreads();
+    }
+}
+
+template <bool LOG>
+int softmax_entry(CUDADeviceRef contextRef, int dt, CUDABufferRef inputRef, CUDABufferRef outRef, uint32_t rows, uint32_t cols,
+                  CUDAStatus* status) {
+    PUTER_ENTER(ctx);
+    if (rows == 0 || cols == 0) return ok(status);
+    const char* what = LOG ? "log-softmax" : "softmax";
+    if (dt != DT_F32 && dt != DT_F16 && dt != DT_BF16) return fail(status, -6, "%s: unsupported dtype %d", what, dt);
+    const size_t es = dtype_size(dt);
+    PUTER_REQUIRE(inputRef, "input", (size_t)rows * cols * es);
+    PUTER_REQUIRE(outRef, "out", (size_t)rows * cols * es);
+    SoftmaxParams p{dev_ptr(inputRef), dev_ptr(outRef), rows, cols, ctx->errorFlag};
+    const bool vec = ((size_t)cols * es) % 16 == 0 && (((uintptr_t)p.in | (uintptr_t)p.out) & 15u) == 0;
+    const rowpipe::Plan plan = vec ? rowpipe::plan((size_t)cols * es) : rowpipe::Plan{0, 0, 0};
+#define SOFTMAX_LAUNCH(DT)                                                                                                  \
+    do {                                                                                                                    \
+        if (plan.warps) {                                                                                                   \
+            size_t perSm = (220 * 1024) / (plan.smem + 1024);                                                               \
+            perSm = perSm < 1 ? 1 : (perSm > 4 ? 4 : perSm);                                                                \
+            size_t blocks = ((size_t)rows + plan.warps - 1) / plan.warps;                                                   \
+            if (blocks > (size_t)ctx->smCount * perSm) blocks = (size_t)ctx->smCount * perSm;                               \
+            cudaFuncSetAttribute(softmax_ring_kernel<DT, LOG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan.smem); \
+            softmax_ring_kernel<DT, LOG><<<(unsigned)blocks, plan.warps * 32, plan.smem, ctx->stream>>>(p, plan.stages);    \
+        } else {                                                                                                            \
+            size_t blocks = rows, cap = (size_t)ctx->smCount * 8;                                                           \
+            softmax_scalar_kernel<DT, LOG><<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, ctx->stream>>>(p);            \
+        }                                                                                                                   \
+    } while (0)
+    if (dt == DT_F32) SOFTMAX_LAUNCH(DT_F32);
+    else if (dt == DT_BF16) SOFTMAX_LAUNCH(DT_BF16);
+    else SOFTMAX_LAUNCH(DT_F16);
+#undef SOFTMAX_LAUNCH
+    return check_launch(ctx, status, what);
+}
+
+}  // namespace
+
+}  // namespace puter
+
+using namespace puter;
+
+extern "C" int cuda_dispatch_softmax(CUDADeviceRef contextRef, int elementDType, CUDABufferRef inputRef, CUDABufferRef outRef, uint32_t rows,
+                                     uint32_t cols, uint64_t completionToken, CUDAStatus* status) {
+    (void)completionToken;
+    return softmax_entry<false>(contextRef, elementDType, inputRef, outRef, rows, cols, status);
+}
+
+extern "C" int cuda_dispatch_log_softmax(CUDADeviceRef contextRef, int elementDType, CUDABufferRef inputRef, CUDABufferRef outRef,
+                                         uint32_t rows, uint32_t cols, uint64_t completionToken, CUDAStatus* status) {
+    (void)completionToken;
+    return softmax_entry<true>(contextRef, elementDType, inputRef, outRef, rows, cols, status);
+}

@@ -14,9 +14,12 @@ from dataclasses import dataclass
 from . import _lib, dtypes
 
 # op codes (include/puter_b200.h)
-UNARY = {"Relu": 0, "Tanh": 12, "Sigmoid": 13, "Silu": 14, "Gelu": 22, "GeluTanh": 29}
+UNARY = {"ReLU": 0, "Exp": 8, "Log": 9, "Tanh": 12, "Sigmoid": 13, "Silu": 14, "Swish": 15, "Softsign": 16, "ELU": 17, "SELU": 18,
+         "LeakyReLU": 19, "HardSigmoid": 20, "HardSwish": 21, "Gelu": 22, "Log1p": 23, "Expm1": 24, "CELU": 25, "Softplus": 26,
+         "Mish": 27, "LogSigmoid": 28, "GeluTanh": 29, "HardTanh": 30, "HardGelu": 31, "QuickGelu": 32, "TanhShrink": 33}
 BINARY = {"Add": 0, "Sub": 1, "Mul": 2, "Div": 3, "Max": 4, "Min": 5}
-GATED = {"SwiGLU": "swiglu", "GeGLU": "geglu", "GLU": "glu", "ReGLU": "reglu", "SiGLU": "siglu", "GeGLUTanh": "geglu_tanh"}
+GATED = {"SwiGLU": "swiglu", "GeGLU": "geglu", "GLU": "glu", "ReGLU": "reglu", "SiGLU": "siglu", "GeGLUTanh": "geglu_tanh",
+         "SeGLU": "seglu", "LinGLU": "linglu"}
 
 RoPEModeInterleaved, RoPEModeHalf = 0, 1
 RoPEScalingNone, RoPEScalingLlama3 = 0, 1
@@ -173,23 +176,20 @@ class Device:
     def _unary(self, op, dst, src, count, format):
         self._call("cuda_dispatch_unary_elementwise", [src, dst], lambda r: (UNARY[op], format, r[0], r[1], count, 0))
 
-    def Silu(self, dst, src, count, format):
-        self._unary("Silu", dst, src, count, format)
+    def Relu(self, dst, src, count, format):  # kept beside ReLU: the earlier spelling of this mirror
+        self._unary("ReLU", dst, src, count, format)
 
-    def Gelu(self, dst, src, count, format):
-        self._unary("Gelu", dst, src, count, format)
+    def Softmax(self, dst, src, count, format):
+        """device.Activation.Softmax (device/interface.go:65): the softmax of ONE vector of `count` elements."""
+        self._call("cuda_dispatch_softmax", [src, dst], lambda r: (format, r[0], r[1], 1, count, 0))
 
-    def GeluTanh(self, dst, src, count, format):
-        self._unary("GeluTanh", dst, src, count, format)
+    def LogSoftmax(self, dst, src, count, format):
+        """device.Activation.LogSoftmax (device/interface.go:46)."""
+        self._call("cuda_dispatch_log_softmax", [src, dst], lambda r: (format, r[0], r[1], 1, count, 0))
 
-    def Sigmoid(self, dst, src, count, format):
-        self._unary("Sigmoid", dst, src, count, format)
-
-    def Tanh(self, dst, src, count, format):
-        self._unary("Tanh", dst, src, count, format)
-
-    def Relu(self, dst, src, count, format):
-        self._unary("Relu", dst, src, count, format)
+    def SoftmaxRows(self, dst, src, rows, cols, format, log=False):
+        """The bridge's own shape (device/cuda/activation/softmax.h:10-19): an independent softmax per row."""
+        self._call("cuda_dispatch_log_softmax" if log else "cuda_dispatch_softmax", [src, dst], lambda r: (format, r[0], r[1], rows, cols, 0))
 
     def _gated_packed(self, variant, dst, packed, batch, halfCount, format):
         # the C ABI takes (inner = halfCount, count = batch): device/cuda/compute_host.go:1215-1231
@@ -234,6 +234,18 @@ class Device:
     def SiGLUTensors(self, dst, gate, up, count, format):
         self._gated_tensors("SiGLU", dst, gate, up, count, format)
 
+    def SeGLU(self, dst, packed, batch, halfCount, format):
+        self._gated_packed("SeGLU", dst, packed, batch, halfCount, format)
+
+    def SeGLUTensors(self, dst, gate, up, count, format):
+        self._gated_tensors("SeGLU", dst, gate, up, count, format)
+
+    def LinGLU(self, dst, packed, batch, halfCount, format):
+        self._gated_packed("LinGLU", dst, packed, batch, halfCount, format)
+
+    def LinGLUTensors(self, dst, gate, up, count, format):
+        self._gated_tensors("LinGLU", dst, gate, up, count, format)
+
     # ---- Elementwise ----------------------------------------------------------------------------------
     def _binary(self, op, dst, left, right, count, format):
         self._call("cuda_dispatch_binary_elementwise", [left, right, dst], lambda r: (BINARY[op], format, r[0], r[1], r[2], count, 0))
@@ -264,6 +276,11 @@ class Device:
     def LayerNorm(self, input, scale, bias, output, rows, lastDim, format):
         """device.LayerNorm.LayerNorm (device/interface.go:362-366); epsilon 1e-5 as on the CPU."""
         self._call("cuda_dispatch_layernorm", [input, scale, bias, output], lambda r: (format, r[0], r[1], r[2], r[3], rows, lastDim, 0.0, 0))
+
+    def LayerNormResidual(self, input, scale, bias, residual, output, rows, lastDim, format):
+        """The catalog's fused layernorm + add (fusion/catalog.go:183-205): LayerNorm(input, scale, bias) + residual."""
+        self._call("cuda_dispatch_layernorm_residual", [input, scale, bias, residual, output],
+                   lambda r: (format, r[0], r[1], r[2], r[3], r[4], rows, lastDim, 0.0, 0))
 
     def AdaptiveRMSNorm(self, config: RMSNormConfig, input, modulation, output, rows, lastDim, rowsPerBatch, modulationCols, format):
         """device.LayerNorm.AdaptiveRMSNorm (device/interface.go:356-361)."""
@@ -297,6 +314,19 @@ class Device:
 
     def RoPEPairs(self, output, input, cosBuffer, sinBuffer, halfDim, format):
         self._call("cuda_dispatch_rope_pairs", [input, output, cosBuffer, sinBuffer], lambda r: (format, r[0], r[1], r[2], r[3], halfDim, 0))
+
+    # ---- Shape ----------------------------------------------------------------------------------------
+    def LastToken(self, input, output, batch, seq, hidden, format):
+        """device.Shape.LastToken (device/interface.go:622): output[b] = input[b, seq - 1, :]."""
+        self._call("cuda_dispatch_last_token", [input, output], lambda r: (format, r[0], r[1], batch, seq, hidden, 0))
+
+    def IntrinsicLastToken(self, input, output, seq, hiddenBytes, outBytes, format):
+        """Device hook of the shape.last_token intrinsic (execution/shape_intrinsic.go:12-19,489-543): sizes arrive in bytes."""
+        es = dtypes.SIZE[format]
+        if hiddenBytes % es or (hiddenBytes and outBytes % hiddenBytes):
+            raise DeviceError(-2, "shape.last_token: row of %d bytes / output of %d bytes do not fit the element type" % (hiddenBytes, outBytes))
+        batch = outBytes // hiddenBytes if hiddenBytes else 0
+        self.LastToken(input, output, batch, seq, hiddenBytes // es, format)
 
     # ---- Shape: paged KV ------------------------------------------------------------------------------
     def KVPageWrite(self, storage, values, pageIDs, offsets, output, pageCount, pageSize, inner, valueRows, storageOffset, format):
@@ -367,3 +397,18 @@ class Device:
                    [query, kPages, vPages, pageTable, ctxLens, kScale, vScale, output, errorFlag],
                    lambda r: (format, kvf, r[0], r[1], r[2], r[3], r[4], r[5], r[6], r[7], r[8], batch, maxPagesPerSeq, pageCount,
                               pageSize, attn.NumHeads, kv, attn.HeadDim, 0))
+
+
+def _make_unary(name):
+    def method(self, dst, src, count, format):
+        self._unary(name, dst, src, count, format)
+
+    method.__name__ = name
+    method.__qualname__ = f"Device.{name}"
+    method.__doc__ = f"device.Activation.{name}(dst, src, count, format) (device/interface.go:18-74)."
+    return method
+
+
+# one method per unary activation that has a bridge op code: Silu, Gelu, GeluTanh, Sigmoid, Tanh, ReLU, Exp, Log, ...
+for _name in UNARY:
+    setattr(Device, _name, _make_unary(_name))

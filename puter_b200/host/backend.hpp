@@ -112,6 +112,47 @@ class Backend {
     void Gelu(void* dst, void* src, int count, DType f) { unary(CUDAUnaryFloat32Gelu, dst, src, count, f); }
     void GeluTanh(void* dst, void* src, int count, DType f) { unary(CUDAUnaryFloat32GeluTanh, dst, src, count, f); }
     void Sigmoid(void* dst, void* src, int count, DType f) { unary(CUDAUnaryFloat32Sigmoid, dst, src, count, f); }
+    // the rest of the unary set (device/interface.go:18-74): one bridge op code each
+#define PUTER_UNARY_METHOD(Name, Code) \
+    void Name(void* dst, void* src, int count, DType f) { unary(Code, dst, src, count, f); }
+    PUTER_UNARY_METHOD(ReLU, CUDAUnaryFloat32Relu)
+    PUTER_UNARY_METHOD(Tanh, CUDAUnaryFloat32Tanh)
+    PUTER_UNARY_METHOD(Exp, CUDAUnaryFloat32Exp)
+    PUTER_UNARY_METHOD(Log, CUDAUnaryFloat32Log)
+    PUTER_UNARY_METHOD(Log1p, CUDAUnaryFloat32Log1p)
+    PUTER_UNARY_METHOD(Expm1, CUDAUnaryFloat32Expm1)
+    PUTER_UNARY_METHOD(Swish, CUDAUnaryFloat32Swish)
+    PUTER_UNARY_METHOD(Softsign, CUDAUnaryFloat32Softsign)
+    PUTER_UNARY_METHOD(ELU, CUDAUnaryFloat32ELU)
+    PUTER_UNARY_METHOD(CELU, CUDAUnaryFloat32CELU)
+    PUTER_UNARY_METHOD(SELU, CUDAUnaryFloat32SELU)
+    PUTER_UNARY_METHOD(LeakyReLU, CUDAUnaryFloat32LeakyReLU)
+    PUTER_UNARY_METHOD(HardSigmoid, CUDAUnaryFloat32HardSigmoid)
+    PUTER_UNARY_METHOD(HardSwish, CUDAUnaryFloat32HardSwish)
+    PUTER_UNARY_METHOD(HardTanh, CUDAUnaryFloat32HardTanh)
+    PUTER_UNARY_METHOD(HardGelu, CUDAUnaryFloat32HardGelu)
+    PUTER_UNARY_METHOD(QuickGelu, CUDAUnaryFloat32QuickGelu)
+    PUTER_UNARY_METHOD(Softplus, CUDAUnaryFloat32Softplus)
+    PUTER_UNARY_METHOD(Mish, CUDAUnaryFloat32Mish)
+    PUTER_UNARY_METHOD(LogSigmoid, CUDAUnaryFloat32LogSigmoid)
+    PUTER_UNARY_METHOD(TanhShrink, CUDAUnaryFloat32TanhShrink)
+#undef PUTER_UNARY_METHOD
+    void Softmax(void* dst, void* src, int count, DType f) {  // one vector (device/interface.go:65)
+        CUDAStatus st;
+        check(cuda_dispatch_softmax(ctx_, (int)f, ref(src), ref(dst), 1, (uint32_t)count, 0, &st), st);
+    }
+    void LogSoftmax(void* dst, void* src, int count, DType f) {
+        CUDAStatus st;
+        check(cuda_dispatch_log_softmax(ctx_, (int)f, ref(src), ref(dst), 1, (uint32_t)count, 0, &st), st);
+    }
+    void SeGLUTensors(void* dst, void* gate, void* up, int count, DType f) {
+        CUDAStatus st;
+        check(cuda_dispatch_seglu(ctx_, (int)f, ref(dst), ref(gate), ref(up), (uint32_t)count, 0, &st), st);
+    }
+    void LinGLUTensors(void* dst, void* gate, void* up, int count, DType f) {
+        CUDAStatus st;
+        check(cuda_dispatch_linglu(ctx_, (int)f, ref(dst), ref(gate), ref(up), (uint32_t)count, 0, &st), st);
+    }
     void SwiGLU(void* dst, void* packed, int batch, int halfCount, DType f) {
         CUDAStatus st;
         check(cuda_dispatch_swiglu_packed(ctx_, (int)f, ref(dst), ref(packed), (uint32_t)halfCount, (uint32_t)batch, 0, &st), st);
@@ -138,6 +179,22 @@ class Backend {
         CUDAStatus st;
         check(cuda_dispatch_layernorm(ctx_, (int)f, ref(input), ref(scale), ref(bias), ref(output), (uint32_t)rows, (uint32_t)lastDim, 0.0f, 0,
                                       &st), st);
+    }
+    // the catalog's fused layernorm + add (fusion/catalog.go:183-205)
+    void LayerNormResidual(void* input, void* scale, void* bias, void* residual, void* output, int rows, int lastDim, DType f) {
+        CUDAStatus st;
+        check(cuda_dispatch_layernorm_residual(ctx_, (int)f, ref(input), ref(scale), ref(bias), ref(residual), ref(output), (uint32_t)rows,
+                                               (uint32_t)lastDim, 0.0f, 0, &st), st);
+    }
+    // device.Shape.LastToken (device/interface.go:622) and the shape.last_token device hook (execution/shape_intrinsic.go:12-19)
+    void LastToken(void* input, void* output, int batch, int seq, int hidden, DType f) {
+        CUDAStatus st;
+        check(cuda_dispatch_last_token(ctx_, (int)f, ref(input), ref(output), (uint32_t)batch, (uint32_t)seq, (uint32_t)hidden, 0, &st), st);
+    }
+    void IntrinsicLastToken(void* input, void* output, int seq, int hiddenBytes, int outBytes, DType f) {
+        const int es = (f == DType::Float32) ? 4 : (f == DType::Float64) ? 8 : (f == DType::Float16 || f == DType::BFloat16) ? 2 : 1;
+        if (hiddenBytes <= 0) return;
+        LastToken(input, output, outBytes / hiddenBytes, seq, hiddenBytes / es, f);
     }
     void AdaptiveRMSNorm(RMSNormConfig config, void* input, void* modulation, void* output, int rows, int lastDim, int rowsPerBatch,
                          int modulationCols, DType f) {

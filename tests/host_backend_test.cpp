@@ -82,6 +82,32 @@ int main() {
         CHECK(convert::BFloat16ToFloat32(b, back.data(), 5, dst.data(), 5));
         for (int i = 0; i < 5; i++) CHECK(back[i] == src[i]);
     }
+    {   // shape.last_token: [2, 3, 2] -> the final row of each batch item (execution/shape_intrinsic_test.go:53-88); and the
+        // device hook's byte-sized form on a [6, 4] allocation with 3 live rows (execution/bind_test.go:1201-1239)
+        std::vector<float> x = {1, 2, 3, 4, 5, 6, 10, 20, 30, 40, 50, 60};
+        DeviceTensor xt(ctx, 48), ot(ctx, 16);
+        up(b, xt, x);
+        b.LastToken(xt.DispatchPointer(), ot.DispatchPointer(), 2, 3, 2, DType::Float32);
+        auto o = down<float>(b, ot, 4);
+        CHECK(o[0] == 5 && o[1] == 6 && o[2] == 50 && o[3] == 60);
+        std::vector<float> y = {1, 2, 3, 4, 9, 9, 9, 9, 5, 6, 7, 8, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
+        DeviceTensor yt(ctx, 96);
+        up(b, yt, y);
+        b.IntrinsicLastToken(yt.DispatchPointer(), ot.DispatchPointer(), 3, 16, 16, DType::Float32);
+        o = down<float>(b, ot, 4);
+        CHECK(o[0] == 5 && o[1] == 6 && o[2] == 7 && o[3] == 8);
+    }
+    {   // softmax of one vector: [0, 0, 0, 0] -> quarters; log-softmax of the same -> -log(4) by the reference's FastLog32
+        std::vector<float> x(4, 0.f);
+        DeviceTensor xt(ctx, 16), ot(ctx, 16);
+        up(b, xt, x);
+        b.Softmax(ot.DispatchPointer(), xt.DispatchPointer(), 4, DType::Float32);
+        auto o = down<float>(b, ot, 4);
+        for (int i = 0; i < 4; i++) CHECK(o[i] == 0.25f);
+        b.LogSoftmax(ot.DispatchPointer(), xt.DispatchPointer(), 4, DType::Float32);
+        o = down<float>(b, ot, 4);
+        for (int i = 0; i < 4; i++) CHECK(std::fabs(o[i] + 1.3862944f) <= 1e-4f);
+    }
     {   // RMSNorm config validation mirrors RMSNormConfig.Validate
         DeviceTensor x(ctx, 32);
         bool threw = false;
