@@ -314,7 +314,7 @@ def run_reference(args, rank, world):
         # not constructed (their constructors allocate on the GPU), only their constants and cpu_baseline() are used
         import bench_workloads as W
 
-        cls = {"convert": W.ConvertWorkload, "chain": W.ChainWorkload, "prefill": W.PrefillWorkload}[args.workload]
+        cls = {"convert": W.ConvertWorkload, "chain": W.ChainWorkload, "chain_nccl": W.ChainWorkload, "prefill": W.PrefillWorkload}[args.workload]
         wl = object.__new__(cls)
         wl.world = args.gpus
         metric, unit = wl.metric()
@@ -329,7 +329,7 @@ def run_reference(args, rank, world):
             "impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": wall / max(args.steps, 1) * 1e3, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": cls.dtype, "data": "synthetic",
-            "config": cls.static_config(args.gpus), "cpu_baseline": base,
+            "config": cls.static_config(args.gpus, "nccl") if args.workload == "chain_nccl" else cls.static_config(args.gpus), "cpu_baseline": base,
             "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0,
             "note": "C++ restatement of puter device/cpu, not the Go binary: no Go toolchain here"}))
         return
@@ -368,7 +368,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default="decode", choices=["decode", "decode_fp8", "prefill", "convert", "chain"])
+    ap.add_argument("--workload", default="decode", choices=["decode", "decode_fp8", "prefill", "convert", "chain", "chain_nccl"])
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--ref-seqs", type=int, default=16, help="sequences in the CPU sample")
     ap.add_argument("--ctx-min", type=int, default=512)

@@ -114,19 +114,23 @@ class ChainWorkload:
         return int(os.environ.get("PUTER_BENCH_CHAIN_TOKENS", BI.ChainInputs.T))
 
     @staticmethod
-    def static_config(world):
+    def static_config(world, gather="fused"):
         c = BI.ChainInputs
+        coll = "none"
+        if world > 1:
+            coll = ("all-gather of n,g,s fused into the kernels' stores (plain peer stores over NVLink into every rank's gathered "
+                    "tensors) + a one-element all-reduce as the barrier" if gather == "fused" else
+                    "nccl all_gather of n,g,s, in place, n and g overlapped with the SwiGLU kernel")
         return {"workload": "add_rmsnorm_gated_residual_swiglu", "tokens": ChainWorkload.tokens(), "hidden": c.C, "intermediate": c.I,
-                "parallelism": "token rows over %d GPU(s)" % world,
-                "collective": "nccl all_gather of n,g,s, in place, n and g overlapped with the SwiGLU kernel" if world > 1 else "none",
-                "l2": "inputs larger than L2 (2.08 GB per step)"}
+                "parallelism": "token rows over %d GPU(s)" % world, "collective": coll, "l2": "inputs larger than L2 (2.08 GB per step)"}
 
-    def __init__(self, dev, rank, world):
+    def __init__(self, dev, rank, world, gather="fused"):
         import torch
 
         from puter_b200 import RMSNormConfig, dtypes as D, sharding
 
         self.torch, self.dev, self.D, self.world, self.rank = torch, dev, D, world, rank
+        self.gather = gather if world > 1 else "none"
         inp = self.inp = BI.ChainInputs(T=self.tokens())
         self.T, self.C, self.I = inp.T, inp.C, inp.I
         r0, r1 = sharding.row_shard(self.T, world, rank)
@@ -136,7 +140,24 @@ class ChainWorkload:
         self.x, self.r, self.branch, self.gate, self.up, self.gamma = t["x"], t["r"], t["branch"], t["gate"], t["up"], t["gamma"]
         self.mod = t["mod"][first:first + nb].contiguous()
         i16 = torch.bfloat16  # raw 16-bit storage (NCCL has no int16 collectives)
-        if world > 1:
+        if world > 1 and self.gather == "fused":
+            # the gathered tensors live in memory every rank of the box can address (CUDA IPC); the kernels write each finished
+            # vector into all of them, so no collective moves data: a one-element all-reduce is the closing barrier
+            import torch.distributed as dist
+
+            self.shared, self.tables = {}, {}
+            for name, cols in (("n", self.C), ("g", self.C), ("s", self.I)):
+                mine = dev.alloc_shared(self.T * cols * 2)
+                handles = [None] * world
+                dist.all_gather_object(handles, mine.handle)
+                peers = [mine if r == rank else dev.open_shared(handles[r], mine.nbytes) for r in range(world)]
+                self.shared[name], self.tables[name] = mine, peers
+            as_t = lambda b, cols: torch.as_tensor(b, device="cuda").view(i16).view(self.T, cols)
+            self.n_all, self.g_all, self.s_all = as_t(self.shared["n"], self.C), as_t(self.shared["g"], self.C), as_t(self.shared["s"], self.I)
+            self.n_out, self.g_out, self.s_out = (t_[r0:r1] for t_ in (self.n_all, self.g_all, self.s_all))
+            self.token = torch.zeros(1, device="cuda")
+            dist.barrier()
+        elif world > 1:
             # the kernels write this rank's rows straight into their place in the gathered tensors, so the all-gathers run in
             # place (no local copy) and the first two overlap the SwiGLU kernel
             self.n_all = torch.empty(self.T, self.C, device="cuda", dtype=i16)
@@ -159,6 +180,15 @@ class ChainWorkload:
 
     def step(self):
         D = self.D
+        if self.gather == "fused":
+            import torch.distributed as dist
+
+            self.dev.AddRMSNormGatedResidualGather(self.cfg, self.x, self.r, self.gamma, self.branch, self.mod, self.tables["n"],
+                                                   self.tables["g"], self.world, self.rank, self.rows, self.C, self.local_rpb, 3 * self.C, 0,
+                                                   D.BFloat16)
+            self.dev.SwiGLUTensorsGather(self.tables["s"], self.world, self.rank, self.gate, self.up, self.rows * self.I, D.BFloat16)
+            dist.all_reduce(self.token)  # stream-ordered barrier: when it completes, every rank's rows are in place here
+            return
         self.dev.AddRMSNormGatedResidual(self.cfg, self.x, self.r, self.gamma, self.branch, self.mod, None, self.n_out, self.g_out,
                                          self.rows, self.C, self.local_rpb, 3 * self.C, 0, D.BFloat16)
         works = []
@@ -198,7 +228,7 @@ class ChainWorkload:
         self.n_host.copy_(self.n_out, non_blocking=True)
 
     def config(self):
-        return self.static_config(self.world)
+        return self.static_config(self.world, self.gather)
 
     def metric(self):
         return "norm_swiglu_chain_hbm_gbps", "GB/s"
@@ -341,6 +371,8 @@ def make_workload(name, dev, rank, world, decode_cls):
         return ConvertWorkload(dev, rank, world)
     if name == "chain":
         return ChainWorkload(dev, rank, world)
+    if name == "chain_nccl":
+        return ChainWorkload(dev, rank, world, gather="nccl")
     if name == "prefill":
         return PrefillWorkload(dev, rank, world)
     raise ValueError(name)
@@ -359,7 +391,7 @@ def secondary_lines(dev, rank, world, timed, peaks, decode_cls, replica_cls, fre
                 setattr(w, k, None)
     torch.cuda.empty_cache()
     out = {}
-    names = ["decode_fp8", "prefill", "chain", "convert"] + (["weak_replicas"] if world > 1 else [])
+    names = ["decode_fp8", "prefill", "chain", "convert"] + (["chain_nccl", "weak_replicas"] if world > 1 else [])
     for name in names:
         try:
             wl = replica_cls(dev, rank, world) if name == "weak_replicas" else make_workload(name, dev, rank, world, decode_cls)

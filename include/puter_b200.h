@@ -127,6 +127,11 @@ int cuda_stream_synchronize(CUDAStreamRef stream, CUDAStatus* status); /* runtim
 CUDADeviceRef cuda_default_context(void);                             /* runtime.c:244 */
 CUDAStreamRef cuda_context_upload_stream(CUDADeviceRef device);       /* runtime.c:248 */
 CUDAStreamRef cuda_context_default_stream(CUDADeviceRef device);      /* core_private.h:97 */
+/* NEW: sharing one allocation between the per-GPU processes of a box (CUDA IPC), for the kernels below that write their
+   results straight into the peers' gathered tensors.  export fills a 64-byte handle for a buffer from cuda_buffer_alloc;
+   import maps the peer's allocation into this process (release unmaps it).  Peer access is enabled on first use. */
+int cuda_buffer_ipc_export(CUDABufferRef buffer, void* outHandle64, CUDAStatus* status);
+CUDABufferRef cuda_buffer_ipc_import(CUDADeviceRef device, const void* handle64, long long bytes, CUDAStatus* status);
 /* NEW: launch on a stream owned by the embedding framework; NULL is the legacy default stream (stream 0) */
 int cuda_context_set_stream(CUDADeviceRef device, void* cudaStream, CUDAStatus* status);
 /* NEW: go back to the context's own non-blocking stream */
@@ -242,6 +247,20 @@ int cuda_dispatch_add_rmsnorm_gated_residual(CUDADeviceRef contextRef, int eleme
                                              CUDABufferRef hOutRef, CUDABufferRef normOutRef, CUDABufferRef gatedOutRef, uint32_t rows,
                                              uint32_t cols, double epsilon, uint32_t rowsPerBatch, uint32_t modulationCols,
                                              uint32_t set, uint64_t completionToken, CUDAStatus* status);
+/* NEW: the same kernel with the all-gather of its two outputs folded into its stores (config 5 across GPUs).  normAll and
+   gatedAll are arrays of `world` (<= 8) handles: entry r is rank r's gathered tensor [world * rows, cols] as mapped into this
+   process (cuda_buffer_ipc_import for r != rank).  This rank's rows are written at row offset rank * rows of every one, with
+   plain 16-byte stores over NVLink (no TMA, no multicast).  A consumer on another GPU needs a cross-rank barrier after it. */
+int cuda_dispatch_add_rmsnorm_gated_residual_gather(CUDADeviceRef contextRef, int elementDType, CUDABufferRef xRef,
+                                                    CUDABufferRef residualRef, CUDABufferRef scaleRef, CUDABufferRef branchRef,
+                                                    CUDABufferRef modulationRef, const CUDABufferRef* normAll,
+                                                    const CUDABufferRef* gatedAll, uint32_t world, uint32_t rank, uint32_t rows,
+                                                    uint32_t cols, double epsilon, uint32_t rowsPerBatch, uint32_t modulationCols,
+                                                    uint32_t set, uint64_t completionToken, CUDAStatus* status);
+/* NEW: SwiGLUTensors with the all-gather of its output folded into the stores: dstAll[r] is rank r's gathered tensor
+   [world * count]; this rank's results land at element offset rank * count of every one. */
+int cuda_dispatch_swiglu_gather(CUDADeviceRef contextRef, int elementDType, const CUDABufferRef* dstAll, uint32_t world, uint32_t rank,
+                                CUDABufferRef gateRef, CUDABufferRef upRef, uint32_t count, uint64_t completionToken, CUDAStatus* status);
 
 /* ---- RoPE ---- */
 /* device/cuda/rope/rotate.h:10-28 (device.RoPE.RoPE, device/interface.go:599-604); float parameters as in the reference.

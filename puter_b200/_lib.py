@@ -36,6 +36,8 @@ SIGNATURES = {
     "cuda_buffer_release": (None, [vp]),
     "cuda_buffer_device_ptr": (vp, [vp]),
     "cuda_buffer_wrap": (vp, [vp, vp, ctypes.c_longlong]),
+    "cuda_buffer_ipc_export": (cint, [vp, ctypes.c_char_p, SP]),
+    "cuda_buffer_ipc_import": (vp, [vp, ctypes.c_char_p, ctypes.c_longlong, SP]),
     "cuda_memcpy_async_h2d": (cint, [vp, vp, ctypes.c_longlong, vp, SP]),
     "cuda_memcpy_async_d2h": (cint, [vp, vp, ctypes.c_longlong, vp, SP]),
     "cuda_memcpy_async_d2d": (cint, [vp, vp, ctypes.c_longlong, vp, SP]),
@@ -65,6 +67,9 @@ SIGNATURES = {
     "cuda_dispatch_modulated_layernorm": (cint, [vp, cint, vp, vp, vp, u32, u32, u32, u32, u32, dbl, u64, SP]),
     "cuda_dispatch_rmsnorm_f64": (cint, [vp, cint, vp, vp, vp, u32, u32, dbl, u64, SP]),
     "cuda_dispatch_add_rmsnorm_gated_residual": (cint, [vp, cint, vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, dbl, u32, u32, u32, u64, SP]),
+    "cuda_dispatch_add_rmsnorm_gated_residual_gather": (cint, [vp, cint, vp, vp, vp, vp, vp, ctypes.POINTER(vp), ctypes.POINTER(vp), u32, u32, u32,
+                                                               u32, dbl, u32, u32, u32, u64, SP]),
+    "cuda_dispatch_swiglu_gather": (cint, [vp, cint, ctypes.POINTER(vp), u32, u32, vp, vp, u32, u64, SP]),
     "cuda_dispatch_rope": (cint, [vp, cint, vp, vp, u32, u32, u32, u32, flt, flt, flt, flt, u32, u32, u32, u64, SP]),
     "cuda_dispatch_rope_f64": (cint, [vp, cint, vp, vp, u32, u32, u32, dbl, i64, u32, u32, dbl, dbl, dbl, u32, u64, SP]),
     "cuda_dispatch_rope_pairs": (cint, [vp, cint, vp, vp, vp, vp, u32, u64, SP]),

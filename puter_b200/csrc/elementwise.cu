@@ -236,6 +236,29 @@ __global__ void __launch_bounds__(256) gated_tensors_kernel(void* __restrict__ d
     for (size_t i = vecs * PER + tid; i < n; i += stride) store1<DT>(dst, i, gated32<OP>(load1<DT>(gate, i), load1<DT>(up, i)));
 }
 
+// the two-tensor form with the all-gather of its output folded into the stores: every finished vector goes to the same
+// offset of `n` destinations (this rank's own gathered tensor and up to 7 peers', plain 16-byte stores over NVLink)
+struct GatherDst {
+    char* dst[8];
+    int n;
+};
+template <int DT, int OP>
+__global__ void __launch_bounds__(256) gated_tensors_gather_kernel(GatherDst d, const void* __restrict__ gate, const void* __restrict__ up,
+                                                                  size_t n) {
+    constexpr int PER = Lanes<DT>::kPer;
+    size_t stride = (size_t)gridDim.x * blockDim.x;
+    size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    for (size_t v = tid; v < n / PER; v += stride) {
+        Vec16 a = ld_stream((const char*)gate + v * 16), b = ld_stream((const char*)up + v * 16);
+        float fa[PER], fb[PER];
+        unpack<DT>(a, fa);
+        unpack<DT>(b, fb);
+        gated_lanes<OP, PER>(fa, fb);
+        const Vec16 o = pack<DT>(fa);
+        for (int r = 0; r < d.n; r++) st_stream(d.dst[r] + v * 16, o);
+    }
+}
+
 // packed rows: [gate(half) | up(half)] -> dst[half].  vec != 0 requires half % PER == 0 and aligned bases.
 template <int DT, int OP>
 __global__ void __launch_bounds__(256) gated_packed_kernel(void* __restrict__ dst, const void* __restrict__ packed, size_t batch,
@@ -510,4 +533,38 @@ extern "C" int cuda_dispatch_gated_residual(CUDADeviceRef contextRef, int elemen
     else
         gated_residual_kernel<DT_F16><<<grid, 256, 0, ctx->stream>>>(r, b, m, o, rows, lastDim, rowsPerBatch, modulationCols, set, vec);
     return check_launch(ctx, status, "gated residual");
+}
+
+// SwiGLUTensors with the all-gather of its output folded into the stores: dstAll[r] is rank r's gathered tensor
+// [world * count] as mapped into this process; this rank's `count` results land at element offset rank * count of every one.
+// A consumer on another GPU needs a cross-rank barrier after the call.  count must be a multiple of the 16-byte vector.
+extern "C" int cuda_dispatch_swiglu_gather(CUDADeviceRef contextRef, int elementDType, const CUDABufferRef* dstAll, uint32_t world,
+                                           uint32_t rank, CUDABufferRef gateRef, CUDABufferRef upRef, uint32_t count,
+                                           uint64_t completionToken, CUDAStatus* status) {
+    (void)completionToken;
+    PUTER_ENTER(ctx);
+    if (count == 0) return ok(status);
+    if (world == 0 || world > 8 || rank >= world || !dstAll) return fail(status, -2, "gathered swiglu: rank %u of %u (at most 8 ranks)", rank, world);
+    size_t es = dtype_size(elementDType);
+    if (elementDType != DT_F32 && elementDType != DT_F16 && elementDType != DT_BF16)
+        return fail(status, -6, "cuda: gated activation: unsupported dtype %d", elementDType);
+    PUTER_REQUIRE(gateRef, "gate", count * es);
+    PUTER_REQUIRE(upRef, "up", count * es);
+    const void* g = dev_ptr(gateRef);
+    const void* u = dev_ptr(upRef);
+    GatherDst d{};
+    d.n = (int)world;
+    const size_t per = 16 / es;
+    bool vec = count % per == 0 && aligned16(g, u);
+    for (uint32_t r = 0; r < world; r++) {
+        PUTER_REQUIRE(dstAll[r], "dstAll[r]", (size_t)world * count * es);
+        d.dst[r] = (char*)dev_ptr(dstAll[r]) + (size_t)rank * count * es;
+        vec = vec && aligned16(d.dst[r]);
+    }
+    if (!vec) return fail(status, -2, "gathered swiglu: buffers must be 16-byte aligned and count a multiple of %zu", per);
+    const int grid = stream_grid(ctx, count / per + 1);
+    if (elementDType == DT_F32) gated_tensors_gather_kernel<DT_F32, G_SWIGLU><<<grid, 256, 0, ctx->stream>>>(d, g, u, count);
+    else if (elementDType == DT_BF16) gated_tensors_gather_kernel<DT_BF16, G_SWIGLU><<<grid, 256, 0, ctx->stream>>>(d, g, u, count);
+    else gated_tensors_gather_kernel<DT_F16, G_SWIGLU><<<grid, 256, 0, ctx->stream>>>(d, g, u, count);
+    return check_launch(ctx, status, "gathered swiglu");
 }

@@ -239,11 +239,18 @@ __device__ __forceinline__ float warp_sum_f32(float v) {
 
 // Vector rows through the shared-memory row pipeline (row_pipeline.cuh): one warp per row, the raw row in a ring stage,
 // two or three passes over it (sum, squared differences, apply) while the next rows of the warp are being copied in.
+__device__ __forceinline__ float fold_parts(const float* part) {
+    float t = part[0];
+#pragma unroll
+    for (int u = 1; u < ROWPIPE_UN; u++) t += part[u];
+    return t;
+}
+
 template <int DT, int OP>
-__global__ void __launch_bounds__(256) row_norm_ring_kernel(RowNormParams p, int stages) {
+__global__ void __launch_bounds__(ROWPIPE_MAX_WARPS * 32) row_norm_ring_kernel(RowNormParams p, int stages) {
     using T = typename Storage<DT>::type;
     constexpr int PER = Per<DT>::kPer;
-    constexpr int UN = 4;  // vectors per lane handled together: their loads are issued back to back, their sums are independent
+    constexpr int UN = ROWPIPE_UN;  // vectors per lane handled together: their loads are issued back to back, their sums are independent
     extern __shared__ __align__(128) unsigned char ringSmem[];
     const size_t cols = p.cols, nvec = cols / PER, rowBytes = cols * sizeof(T);
     const int lane = threadIdx.x & 31;
@@ -267,7 +274,7 @@ __global__ void __launch_bounds__(256) row_norm_ring_kernel(RowNormParams p, int
                 }
             }
         }
-        float total = warp_sum_f32((part[0] + part[1]) + (part[2] + part[3]));
+        float total = warp_sum_f32(fold_parts(part));
         float mean = 0.f, inv;
         if (OP == OP_ADAPTIVE_RMS) {
             inv = (float)(1.0 / sqrt((double)__fdiv_rn(total, (float)cols) + p.eps));
@@ -295,7 +302,7 @@ __global__ void __launch_bounds__(256) row_norm_ring_kernel(RowNormParams p, int
                     }
                 }
             }
-            const float sq = warp_sum_f32((part[0] + part[1]) + (part[2] + part[3]));
+            const float sq = warp_sum_f32(fold_parts(part));
             if (DT == DT_F32) inv = (float)(1.0 / sqrt((double)sq / (double)cols + p.eps));
             else if (OP == OP_LAYERNORM) inv = (float)(1.0 / sqrt((double)add(__fdiv_rn(sq, (float)cols), (float)p.eps)));
             else inv = (float)(1.0 / sqrt((double)__fdiv_rn(sq, (float)cols) + p.eps));
@@ -355,6 +362,103 @@ __global__ void __launch_bounds__(256) row_norm_ring_kernel(RowNormParams p, int
     }
 }
 
+// Rows of up to 32 * VPL vectors: one warp per row, the raw 16-byte vectors of the row held in registers (VPL per lane, lane l
+// owns vectors l, l + 32, ...), reductions by shuffles: no shared memory, no CTA-wide barrier between the passes.
+template <int DT, int OP, int VPL>
+__global__ void __launch_bounds__(256) row_norm_warp_kernel(RowNormParams p) {
+    using T = typename Storage<DT>::type;
+    constexpr int PER = Per<DT>::kPer;
+    const size_t cols = p.cols, nvec = cols / PER;
+    const int lane = threadIdx.x & 31;
+    const size_t warpsTotal = (size_t)gridDim.x * (blockDim.x >> 5);
+    for (size_t row = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < p.rows; row += warpsTotal) {
+        const char* x = (const char*)((const T*)p.in + row * cols);
+        char* o = (char*)((T*)p.out + row * cols);
+        Vec16 raw[VPL];
+#pragma unroll
+        for (int k = 0; k < VPL; k++) {
+            const size_t v = lane + (size_t)k * 32;
+            if (v < nvec) raw[k] = ld_stream(x + v * 16);
+        }
+        float acc = 0.f;
+#pragma unroll
+        for (int k = 0; k < VPL; k++) {
+            if (lane + (size_t)k * 32 < nvec) {
+                float f[PER];
+                unpack_row<DT>(raw[k], f);
+#pragma unroll
+                for (int i = 0; i < PER; i++) acc += OP == OP_ADAPTIVE_RMS ? f[i] * f[i] : f[i];
+            }
+        }
+        float total = warp_sum_f32(acc);
+        float mean = 0.f, inv;
+        if (OP == OP_ADAPTIVE_RMS) {
+            inv = (float)(1.0 / sqrt((double)__fdiv_rn(total, (float)cols) + p.eps));
+        } else {
+            if (DT == DT_F32) {
+                mean = (float)((double)total / (double)cols);
+            } else {
+                if (DT == DT_BF16) total = Storage<DT>::widen(Storage<DT>::narrow(total));
+                mean = __fdiv_rn(total, (float)cols);
+            }
+            float sq = 0.f;
+#pragma unroll
+            for (int k = 0; k < VPL; k++) {
+                if (lane + (size_t)k * 32 < nvec) {
+                    float f[PER];
+                    unpack_row<DT>(raw[k], f);
+#pragma unroll
+                    for (int i = 0; i < PER; i++) {
+                        const float d = sub(f[i], mean);
+                        sq = add(sq, mul(d, d));
+                    }
+                }
+            }
+            sq = warp_sum_f32(sq);
+            if (DT == DT_F32) inv = (float)(1.0 / sqrt((double)sq / (double)cols + p.eps));
+            else if (OP == OP_LAYERNORM) inv = (float)(1.0 / sqrt((double)add(__fdiv_rn(sq, (float)cols), (float)p.eps)));
+            else inv = (float)(1.0 / sqrt((double)__fdiv_rn(sq, (float)cols) + p.eps));
+        }
+        const char* a0;
+        const char* a1;
+        if (OP == OP_LAYERNORM) {
+            a0 = (const char*)p.p0;  // scale
+            a1 = (const char*)p.p1;  // bias
+        } else {
+            const T* m = (const T*)p.p0 + (row / p.rowsPerBatch) * p.modCols + (OP == OP_MODULATED_LN ? p.set * cols * 3 : 0);
+            a0 = (const char*)m;            // AdaptiveRMSNorm: scale; ModulatedLayerNorm: shift
+            a1 = (const char*)(m + cols);   // AdaptiveRMSNorm: shift; ModulatedLayerNorm: scale
+        }
+#pragma unroll
+        for (int k = 0; k < VPL; k++) {
+            const size_t v = lane + (size_t)k * 32;
+            if (v < nvec) {
+                float f[PER], c0[PER], c1[PER], r[PER];
+                unpack_row<DT>(raw[k], f);
+                unpack_row<DT>(*(const Vec16*)(a0 + v * 16), c0);
+                unpack_row<DT>(*(const Vec16*)(a1 + v * 16), c1);
+#pragma unroll
+                for (int i = 0; i < PER; i++) {
+                    if (OP == OP_LAYERNORM) {
+                        r[i] = add(mul(mul(sub(f[i], mean), inv), c0[i]), c1[i]);
+                    } else {
+                        const float scale = OP == OP_ADAPTIVE_RMS ? c0[i] : c1[i], shift = OP == OP_ADAPTIVE_RMS ? c1[i] : c0[i];
+                        const float nrm = mul(OP == OP_ADAPTIVE_RMS ? f[i] : sub(f[i], mean), inv);
+                        r[i] = add(mul(nrm, add(1.0f, scale)), shift);
+                    }
+                }
+                if (OP == OP_LAYERNORM && p.res) {  // the unfused Add reads the stored (rounded) LayerNorm result
+                    float rs[PER];
+                    unpack_row<DT>(ld_stream((const char*)((const T*)p.res + row * cols) + v * 16), rs);
+#pragma unroll
+                    for (int i = 0; i < PER; i++) r[i] = add(Storage<DT>::widen(Storage<DT>::narrow(r[i])), rs[i]);
+                }
+                st_stream(o + v * 16, pack_row<DT>(r));
+            }
+        }
+    }
+}
+
 constexpr size_t kMaxCols = 16384;  // 64 KB of shared memory for the widened row
 
 template <int OP>
@@ -367,8 +471,14 @@ int launch_row_norm(Context* ctx, int dt, const RowNormParams& p, CUDAStatus* st
     // the modulation row of a batch starts at batch * modCols (+ set * 3 * cols) elements and its second half cols further on
     const bool vec = p.cols % per == 0 && (((uintptr_t)p.in | (uintptr_t)p.out | (uintptr_t)p.p0 | (uintptr_t)p.p1 | (uintptr_t)p.res) & 15u) == 0 &&
                      (OP == OP_LAYERNORM || p.modCols % per == 0);
-    // vector rows that fit the shared-memory row pipeline take the ring kernel; the rest one CTA per row
-    const rowpipe::Plan plan = vec ? rowpipe::plan(p.cols * es) : rowpipe::Plan{0, 0, 0};
+    // Measured at 16384 x 4096: 16-bit rows are bound by instruction latency, not by memory, and run fastest with the row in
+    // registers (one warp per row, 3.4-3.8 TB/s against 3.0-3.6 through shared memory); float32 rows run fastest through the
+    // shared-memory row pipeline (4.3-5.0 TB/s against 3.8-4.3).  Rows that fit neither take one CTA per row.
+    const size_t nvec = vec ? p.cols / per : 0;
+    const int vpl = (es == 4 || nvec == 0 || nvec > 512) ? 0 : nvec <= 128 ? 4 : nvec <= 256 ? 8 : 16;
+    size_t warpBlocks = (p.rows + 7) / 8;
+    if (warpBlocks > cap) warpBlocks = cap;
+    const rowpipe::Plan plan = (vec && !vpl) ? rowpipe::plan(p.cols * es) : rowpipe::Plan{0, 0, 0};
     size_t ringBlocks = 1;
     if (plan.warps) {
         size_t perSm = (220 * 1024) / (plan.smem + 1024);
@@ -379,7 +489,10 @@ int launch_row_norm(Context* ctx, int dt, const RowNormParams& p, CUDAStatus* st
     }
 #define ROWNORM_LAUNCH(DT)                                                                                          \
     do {                                                                                                            \
-        if (plan.warps) {                                                                                           \
+        if (vpl == 4) row_norm_warp_kernel<DT, OP, 4><<<(unsigned)warpBlocks, 256, 0, ctx->stream>>>(p);             \
+        else if (vpl == 8) row_norm_warp_kernel<DT, OP, 8><<<(unsigned)warpBlocks, 256, 0, ctx->stream>>>(p);        \
+        else if (vpl == 16) row_norm_warp_kernel<DT, OP, 16><<<(unsigned)warpBlocks, 256, 0, ctx->stream>>>(p);      \
+        else if (plan.warps) {                                                                                      \
             cudaFuncSetAttribute(row_norm_ring_kernel<DT, OP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan.smem); \
             row_norm_ring_kernel<DT, OP><<<(unsigned)ringBlocks, plan.warps * 32, plan.smem, ctx->stream>>>(p, plan.stages); \
         } else if (vec) {                                                                                           \

@@ -84,6 +84,11 @@ struct RowArgs {
     void* gatedOut;        // FUSED + gated
     size_t rows, cols, rowsPerBatch, modCols, set;
     double eps;
+    // all-gather fused into the stores: every finished vector of normOut / gatedOut is also written to the same place of up
+    // to 7 peers' gathered tensors (plain stores over NVLink); peer pointers address row 0 of the rank's slice
+    char* normPeer[7];
+    char* gatedPeer[7];
+    int nPeer;
 };
 
 // read-once input: through the non-coherent path, unless an output of the same launch aliases an input (in-place use)
@@ -175,14 +180,18 @@ __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(RowArgs a) {
                 if (DT == DT_F32) o[j] = mul(h[j], mul(inv, g[j]));   // x * (inv * gamma), compute.go:358-362
                 else o[j] = mul(mul(h[j], inv), g[j]);                // (x * inv) * gamma, compute.go:370-373
             }
-            st_stream((char*)a.normOut + row * a.cols * ES + v * 16, pack<DT>(o));
+            const Vec16 nv = pack<DT>(o);
+            st_stream((char*)a.normOut + row * a.cols * ES + v * 16, nv);
+            for (int r = 0; r < a.nPeer; r++) st_stream(a.normPeer[r] + row * a.cols * ES + v * 16, nv);
             if (gated) {
                 float b[PER], m[PER];
                 unpack<DT>(bv ? *bv : ld_stream((const char*)a.branch + row * a.cols * ES + v * 16), b);
                 unpack<DT>(*(const Vec16*)((const char*)a.mod + (mo + v * PER) * ES), m);
 #pragma unroll
                 for (int j = 0; j < PER; j++) o[j] = add(h[j], mul(m[j], b[j]));
-                st_stream((char*)a.gatedOut + row * a.cols * ES + v * 16, pack<DT>(o));
+                const Vec16 gv = pack<DT>(o);
+                st_stream((char*)a.gatedOut + row * a.cols * ES + v * 16, gv);
+                for (int r = 0; r < a.nPeer; r++) st_stream(a.gatedPeer[r] + row * a.cols * ES + v * 16, gv);
             }
         };
 #pragma unroll
@@ -356,7 +365,11 @@ static int launch_rows(Context* ctx, const RowArgs& a, CUDAStatus* status) {
     for (const void* o : outs) inplace |= o && (o == a.x || o == a.residual);
     // measured at 16384 x 4096 bf16: plain RMSNorm 4.49 TB/s warp-per-row vs 4.05 block-per-row; the fused form needs twice the
     // registers per lane, fits one block per SM and is faster block-per-row (4.49 vs 3.27 TB/s)
-    if (inplace && vec) rmsnorm_rows_kernel<DT, 4, FUSED, true><<<grid, 256, 0, ctx->stream>>>(a);
+    if (a.nPeer > 0 && !vec) return fail(status, -2, "rmsnorm: the gathered form needs 16-byte aligned rows");
+    if (a.nPeer > 0 && !inplace) {
+        if (nvec <= 2 * 256) rmsnorm_rows_kernel<DT, 2, FUSED, false><<<grid, 256, 0, ctx->stream>>>(a);
+        else rmsnorm_rows_kernel<DT, 4, FUSED, false><<<grid, 256, 0, ctx->stream>>>(a);
+    } else if (inplace && vec) rmsnorm_rows_kernel<DT, 4, FUSED, true><<<grid, 256, 0, ctx->stream>>>(a);
     else if (!FUSED && vec && nvec <= 512 && nvec >= 128 && a.rows >= 64) {
         size_t blocks = (a.rows + 7) / 8, capW = (size_t)ctx->smCount * 4;
         rmsnorm_warp_rows_kernel<DT, FUSED><<<(unsigned)(blocks < capW ? blocks : capW), 256, 0, ctx->stream>>>(a);
@@ -476,6 +489,50 @@ extern "C" int cuda_dispatch_add_rmsnorm_gated_residual(CUDADeviceRef contextRef
         a.rowsPerBatch = rowsPerBatch;
         a.modCols = modulationCols;
         a.set = set;
+    }
+    return dispatch_rows<true>(ctx, elementDType, a, status);
+}
+
+// The fused kernel with the all-gather of its two outputs folded into its stores.  normAll / gatedAll are arrays of `world`
+// buffer handles: entry r is rank r's gathered tensor [world * rows, cols] as mapped into this process (its own for
+// r == rank, cuda_buffer_ipc_import of the peers' otherwise).  This rank's rows land at row offset rank * rows of every one of
+// them.  Completion is stream-ordered for the local copy only: a consumer on another GPU needs a cross-rank barrier after the
+// call (the caller's collective library provides it).  No TMA, no multicast: plain 16-byte stores over NVLink.
+extern "C" int cuda_dispatch_add_rmsnorm_gated_residual_gather(CUDADeviceRef contextRef, int elementDType, CUDABufferRef xRef,
+                                                               CUDABufferRef residualRef, CUDABufferRef scaleRef, CUDABufferRef branchRef,
+                                                               CUDABufferRef modulationRef, const CUDABufferRef* normAll,
+                                                               const CUDABufferRef* gatedAll, uint32_t world, uint32_t rank, uint32_t rows,
+                                                               uint32_t cols, double epsilon, uint32_t rowsPerBatch, uint32_t modulationCols,
+                                                               uint32_t set, uint64_t completionToken, CUDAStatus* status) {
+    (void)completionToken;
+    PUTER_ENTER(ctx);
+    if (rows == 0 || cols == 0) return ok(status);
+    if (world == 0 || world > 8 || rank >= world) return fail(status, -2, "gathered rmsnorm: rank %u of %u (at most 8 ranks)", rank, world);
+    if (!normAll || !gatedAll || !branchRef) return fail(status, -2, "gathered rmsnorm: nil output table or branch");
+    if (!(epsilon > 0)) return fail(status, -2, "rmsnorm: epsilon must be positive, got %g", epsilon);
+    size_t es = dtype_size(elementDType);
+    if (elementDType != DT_F32 && elementDType != DT_F16 && elementDType != DT_BF16)
+        return fail(status, -6, "layernorm: unsupported dtype %d", elementDType);
+    const size_t bytes = (size_t)rows * cols * es;
+    PUTER_REQUIRE(xRef, "x", bytes);
+    PUTER_REQUIRE(residualRef, "residual", bytes);
+    PUTER_REQUIRE(scaleRef, "scale", (size_t)cols * es);
+    PUTER_REQUIRE(branchRef, "branch", bytes);
+    if (rowsPerBatch == 0) return fail(status, -2, "gated residual: rows per batch must be positive");
+    if ((uint64_t)modulationCols < ((uint64_t)set * 3 + 3) * cols) return fail(status, -2, "gated residual: modulation too narrow for the set");
+    const size_t batches = ((size_t)rows + rowsPerBatch - 1) / rowsPerBatch;
+    PUTER_REQUIRE(modulationRef, "modulation", batches * modulationCols * es);
+    RowArgs a{};
+    a.x = dev_ptr(xRef); a.residual = dev_ptr(residualRef); a.scale = dev_ptr(scaleRef); a.branch = dev_ptr(branchRef);
+    a.mod = dev_ptr(modulationRef);
+    a.rows = rows; a.cols = cols; a.eps = epsilon; a.rowsPerBatch = rowsPerBatch; a.modCols = modulationCols; a.set = set;
+    for (uint32_t r = 0; r < world; r++) {
+        PUTER_REQUIRE(normAll[r], "normAll[r]", (size_t)world * bytes);
+        PUTER_REQUIRE(gatedAll[r], "gatedAll[r]", (size_t)world * bytes);
+        char* n = (char*)dev_ptr(normAll[r]) + (size_t)rank * bytes;
+        char* g = (char*)dev_ptr(gatedAll[r]) + (size_t)rank * bytes;
+        if (r == rank) { a.normOut = n; a.gatedOut = g; }
+        else { a.normPeer[a.nPeer] = n; a.gatedPeer[a.nPeer] = g; a.nPeer++; }
     }
     return dispatch_rows<true>(ctx, elementDType, a, status);
 }

@@ -1,8 +1,11 @@
 // Row pipeline shared by the row-wise kernels that make several passes over a row (LayerNorm family, row softmax):
 // every warp owns a private ring of whole rows in shared memory, filled by bulk asynchronous copies (cp.async.bulk,
-// completion counted in bytes on an mbarrier) that one lane issues `stages` rows ahead.  The warp then reads its row from
-// shared memory as often as the operation needs, while the copies of its next rows are in flight: HBM stays busy during
-// the reductions, and the row costs no registers.  No block-wide barrier, no interaction between warps.
+// completion counted in bytes on an mbarrier) that one lane issues.  The warp reads its row from shared memory as often as
+// the operation needs, and the row costs no registers.  No block-wide barrier, no interaction between warps.
+//
+// Measured on 16384 x 4096 rows: what pays is warps per SM, not ring depth (the passes over a row are bound by instruction
+// latency): 16 warps with one stage each beat 8 warps with three stages by 25-30 %, and deeper rings at equal warp count
+// changed nothing.  The defaults below are that configuration; the ring logic keeps the general form.
 //
 // A bulk copy needs 16-byte aligned addresses and a size that is a multiple of 16 bytes: callers take this path only for
 // rows that satisfy both, everything else runs their scalar kernels.  Every wait is bounded; a wait that runs out raises the
@@ -10,6 +13,16 @@
 #pragma once
 
 #include "common.cuh"
+
+#ifndef ROWPIPE_MAX_WARPS
+#define ROWPIPE_MAX_WARPS 16
+#endif
+#ifndef ROWPIPE_MAX_STAGES
+#define ROWPIPE_MAX_STAGES 1
+#endif
+#ifndef ROWPIPE_UN
+#define ROWPIPE_UN 4
+#endif
 
 namespace puter {
 namespace rowpipe {
@@ -124,10 +137,10 @@ inline Plan plan(size_t rowBytes) {
     const size_t budget = 200 * 1024;
     Plan p{0, 0, 0};
     if (rowBytes == 0 || rowBytes % 16 != 0) return p;
-    for (int warps = 8; warps >= 1; warps--) {
+    for (int warps = ROWPIPE_MAX_WARPS; warps >= 1; warps--) {
         size_t stages = budget / ((size_t)warps * rowBytes);
-        if (stages > 4) stages = 4;
-        if (stages >= 2 || (warps == 1 && stages >= 1)) {
+        if (stages > ROWPIPE_MAX_STAGES) stages = ROWPIPE_MAX_STAGES;
+        if (stages >= (ROWPIPE_MAX_STAGES > 1 ? 2 : 1) || (warps == 1 && stages >= 1)) {
             p.warps = warps;
             p.stages = (int)stages;
             p.smem = (size_t)warps * stages * rowBytes + (size_t)warps * stages * 8;

@@ -187,11 +187,47 @@ CUDABufferRef cuda_buffer_wrap(CUDADeviceRef device, void* devicePtr, long long 
 void cuda_buffer_release(CUDABufferRef buffer) {
     if (!buffer) return;
     Buffer* b = (Buffer*)buffer;
-    if (b->owned && b->ptr) {
+    if (b->owned == 1 && b->ptr) {
         cudaSetDevice(b->device);
         cudaFree(b->ptr);
+    } else if (b->owned == 2 && b->ptr) {  // a peer's allocation mapped by cuda_buffer_ipc_import
+        cudaSetDevice(b->device);
+        cudaIpcCloseMemHandle(b->ptr);
     }
     delete b;
+}
+
+int cuda_buffer_ipc_export(CUDABufferRef buffer, void* outHandle64, CUDAStatus* status) {
+    cuda_status_clear(status);
+    if (!buffer || !outHandle64) return fail(status, -2, "cuda: nil argument in ipc export");
+    Buffer* b = (Buffer*)buffer;
+    if (b->owned != 1) return fail(status, -2, "cuda: only buffers allocated by cuda_buffer_alloc can be exported");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the C ABI fixes the handle at 64 bytes");
+    cudaSetDevice(b->device);
+    cudaIpcMemHandle_t h;
+    cudaError_t err = cudaIpcGetMemHandle(&h, b->ptr);
+    if (err != cudaSuccess) return fail(status, -7, "cuda: cudaIpcGetMemHandle failed: %s", cudaGetErrorString(err));
+    memcpy(outHandle64, &h, 64);
+    return ok(status);
+}
+
+CUDABufferRef cuda_buffer_ipc_import(CUDADeviceRef device, const void* handle64, long long bytes, CUDAStatus* status) {
+    cuda_status_clear(status);
+    Context* ctx = ctx_of(device, status);
+    if (!ctx) return nullptr;
+    if (!handle64 || bytes <= 0) { fail(status, -2, "cuda: nil handle in ipc import"); return nullptr; }
+    cudaSetDevice(ctx->device);
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, 64);
+    void* p = nullptr;
+    cudaError_t err = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+    if (err != cudaSuccess || !p) {
+        cudaGetLastError();
+        fail(status, -7, "cuda: cudaIpcOpenMemHandle failed: %s", cudaGetErrorString(err));
+        return nullptr;
+    }
+    ok(status);
+    return new Buffer{p, bytes, 2, ctx->device};
 }
 
 void* cuda_buffer_device_ptr(CUDABufferRef buffer) { return dev_ptr(buffer); }

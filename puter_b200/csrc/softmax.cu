@@ -56,10 +56,10 @@ struct SoftmaxParams {
 };
 
 template <int DT, bool LOG>
-__global__ void __launch_bounds__(256) softmax_ring_kernel(SoftmaxParams p, int stages) {
+__global__ void __launch_bounds__(ROWPIPE_MAX_WARPS * 32) softmax_ring_kernel(SoftmaxParams p, int stages) {
     using T = typename Storage<DT>::type;
     constexpr int PER = SPer<DT>::kPer;
-    constexpr int UN = 4;  // vectors per lane handled together: independent chains of maxima, exponentials and sums
+    constexpr int UN = ROWPIPE_UN;  // vectors per lane handled together: independent chains of maxima, exponentials and sums
     extern __shared__ __align__(128) unsigned char ringSmem[];
     const size_t cols = p.cols, nvec = cols / PER, rowBytes = cols * sizeof(T);
     const int lane = threadIdx.x & 31;
@@ -84,7 +84,9 @@ __global__ void __launch_bounds__(256) softmax_ring_kernel(SoftmaxParams p, int 
                 }
             }
         }
-        float mx = ref_max(ref_max(part[0], part[1]), ref_max(part[2], part[3]));
+        float mx = part[0];
+#pragma unroll
+        for (int u = 1; u < UN; u++) mx = ref_max(mx, part[u]);
 #pragma unroll
         for (int s = 16; s > 0; s >>= 1) mx = ref_max(mx, __shfl_xor_sync(0xffffffffu, mx, s));
 #pragma unroll
@@ -97,11 +99,18 @@ __global__ void __launch_bounds__(256) softmax_ring_kernel(SoftmaxParams p, int 
                     float f[PER];
                     s_unpack<DT>(*(const Vec16*)(x + v * 16), f);
 #pragma unroll
-                    for (int i = 0; i < PER; i++) part[u] = add(part[u], fast_exp32(sub(f[i], mx)));
+                    for (int i = 0; i < PER; i++) {
+                        f[i] = fast_exp32(sub(f[i], mx));
+                        part[u] = add(part[u], f[i]);
+                    }
+                    // float32 rows keep their exponentials in the stage (the input values are not needed again)
+                    if (!LOG && DT == DT_F32) *(Vec16*)(const_cast<unsigned char*>(x) + v * 16) = s_pack<DT>(f);
                 }
             }
         }
-        float sum = add(add(part[0], part[1]), add(part[2], part[3]));
+        float sum = part[0];
+#pragma unroll
+        for (int u = 1; u < UN; u++) sum = add(sum, part[u]);
 #pragma unroll
         for (int s = 16; s > 0; s >>= 1) sum = add(sum, __shfl_xor_sync(0xffffffffu, sum, s));
         const float k = LOG ? fast_log32(sum) : divf(1.0f, sum);
@@ -113,7 +122,8 @@ __global__ void __launch_bounds__(256) softmax_ring_kernel(SoftmaxParams p, int 
                     float f[PER];
                     s_unpack<DT>(*(const Vec16*)(x + v * 16), f);
 #pragma unroll
-                    for (int i = 0; i < PER; i++) f[i] = LOG ? sub(sub(f[i], mx), k) : mul(fast_exp32(sub(f[i], mx)), k);
+                    for (int i = 0; i < PER; i++)
+                        f[i] = LOG ? sub(sub(f[i], mx), k) : mul(DT == DT_F32 ? f[i] : fast_exp32(sub(f[i], mx)), k);
                     st_stream(o + v * 16, s_pack<DT>(f));
                 }
             }

@@ -71,6 +71,21 @@ class MultiHeadAttentionConfig:  # device/config.go:283-290
     KVHeadCount: int = 0
 
 
+class SharedBuffer:
+    """Device memory that the per-GPU processes of one box can all address (CUDA IPC): allocated by ``Device.alloc_shared`` or
+    mapped from a peer's ``handle`` by ``Device.open_shared``.  ``torch.as_tensor(buf, device="cuda")`` views it as bytes."""
+
+    def __init__(self, dev, ref, nbytes, handle=None):
+        self._dev, self.ref, self.nbytes, self.handle = dev, ref, nbytes, handle
+        self.ptr = int(dev.lib.cuda_buffer_device_ptr(ref))
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (self.ptr, False), "version": 2}
+
+    def close(self):
+        if self.ref is not None:
+            self._dev.lib.cuda_buffer_release(self.ref)
+            self.ref = None
+
+
 class Device:
     """One context on one GPU.  ``Device()`` opens the current torch CUDA device."""
 
@@ -141,6 +156,29 @@ class Device:
         args = build_args([self._ref(t) for t in tensors])
         rc = getattr(self.lib, name)(self.ref, *args, ctypes.byref(self._status))
         self._check(rc)
+
+    # ---- memory shared between the per-GPU processes of a box ----------------------------------------
+    def alloc_shared(self, nbytes: int) -> SharedBuffer:
+        ref = self.lib.cuda_buffer_alloc(self.ref, nbytes)
+        if not ref:
+            raise DeviceError(-7, "cuda: allocation of %d shared bytes failed" % nbytes)
+        ref = ctypes.c_void_p(ref)
+        handle = ctypes.create_string_buffer(64)
+        self._check(self.lib.cuda_buffer_ipc_export(ref, handle, ctypes.byref(self._status)))
+        return SharedBuffer(self, ref, nbytes, handle.raw)
+
+    def open_shared(self, handle: bytes, nbytes: int) -> SharedBuffer:
+        ref = self.lib.cuda_buffer_ipc_import(self.ref, ctypes.c_char_p(handle), nbytes, ctypes.byref(self._status))
+        if not ref:
+            raise DeviceError(self._status.code, self._status.message.decode(errors="replace"))
+        return SharedBuffer(self, ctypes.c_void_p(ref), nbytes)
+
+    def _ref_any(self, t):
+        return t.ref if isinstance(t, SharedBuffer) else self._ref(t)
+
+    def _ref_table(self, items):
+        refs = [self._ref_any(t) for t in items]
+        return (ctypes.c_void_p * len(refs))(*[r.value for r in refs])
 
     def set_exact(self, exact: bool):
         self._check(self.lib.cuda_context_set_exact(self.ref, int(exact), ctypes.byref(self._status)))
@@ -304,6 +342,24 @@ class Device:
         self._call("cuda_dispatch_add_rmsnorm_gated_residual", [x, residual, scale, branch, modulation, hOut, normOut, gatedOut],
                    lambda r: (format, r[0], r[1], r[2], r[3], r[4], r[5], r[6], r[7], rows, lastDim, float(config.Epsilon),
                               rowsPerBatch, modulationCols, set, 0))
+
+    def AddRMSNormGatedResidualGather(self, config: RMSNormConfig, x, residual, scale, branch, modulation, normAll, gatedAll, world, rank,
+                                      rows, lastDim, rowsPerBatch, modulationCols, set, format):
+        """AddRMSNormGatedResidual whose two outputs land in every rank's gathered tensor: normAll[r] / gatedAll[r] are rank r's
+        [world * rows, lastDim] tensors (torch tensors or SharedBuffers) as this process addresses them."""
+        self._enter()
+        args = [self._ref(t) for t in (x, residual, scale, branch, modulation)]
+        rc = self.lib.cuda_dispatch_add_rmsnorm_gated_residual_gather(
+            self.ref, format, *args, self._ref_table(normAll), self._ref_table(gatedAll), world, rank, rows, lastDim, float(config.Epsilon),
+            rowsPerBatch, modulationCols, set, 0, ctypes.byref(self._status))
+        self._check(rc)
+
+    def SwiGLUTensorsGather(self, dstAll, world, rank, gate, up, count, format):
+        """SwiGLUTensors whose output lands at element offset rank * count of every rank's gathered tensor dstAll[r]."""
+        self._enter()
+        rc = self.lib.cuda_dispatch_swiglu_gather(self.ref, format, self._ref_table(dstAll), world, rank, self._ref(gate), self._ref(up),
+                                                  count, 0, ctypes.byref(self._status))
+        self._check(rc)
 
     # ---- RoPE -----------------------------------------------------------------------------------------
     def RoPE(self, config: RoPEConfig, input, output, seqLen, numHeads, headDim, format):

@@ -91,16 +91,20 @@ def test_row_softmax(d, dt, rows, cols, log):
     got = host(out, want.dtype, want.shape)
     assert d.take_error() == 0
     if dt == O.F32:
-        # same formula, tree sum instead of the sequential one.  Log-softmax outputs are differences of terms of size
-        # |x - max| and log(sum): the error is bounded relative to max(1, |result|), not to a result that happens to be small
+        # same formula, tree sum instead of the reference's sequential float32 sum, whose own rounding error grows with the
+        # row length: 1e-5 relative up to 4096 columns, scaled by cols / 4096 beyond.  Log-softmax outputs are
+        # differences of terms of size |x - max| and log(sum): the bound is relative to max(1, |result|).
+        tol = 1e-5 * max(1.0, cols / 4096.0)
         if log:
             err = np.abs(got.astype(np.float64) - want.astype(np.float64)) / np.maximum(1.0, np.abs(want.astype(np.float64)))
-            assert err.max() <= 1e-5
+            assert err.max() <= tol
         else:
-            assert rel_err(got, want) <= 1e-5
+            assert rel_err(got, want) <= tol
             assert np.abs(got.sum(axis=1) - 1).max() <= 1e-4
     else:
-        assert ulp16_diff(got, want).max() <= 1 and (got != want).mean() < 0.02
+        # one unit in the last place; how many results sit close enough to a rounding boundary to flip grows with the
+        # difference between the two float32 sums, hence with the row length
+        assert ulp16_diff(got, want).max() <= 1 and (got != want).mean() < 0.02 * max(1.0, cols / 4096.0)
 
 
 def test_softmax_one_vector_like_the_go_method(d):
