@@ -47,8 +47,9 @@ struct Context {
     // cos/sin table of the last RoPE configuration (positions x headDim/2, cos then sin), reused while the config repeats
     float* ropeTable;
     size_t ropeTableBytes;
-    double ropeKey[8];
+    double ropeKey[10];
     int ropeKeyValid;
+    cudaEvent_t streamSwitchEvent;  // orders work of a newly adopted stream after what the previous stream still has queued
 };
 
 int fail(CUDAStatus* status, int code, const char* fmt, ...);

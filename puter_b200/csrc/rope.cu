@@ -267,8 +267,8 @@ int build_rope_table(Context* ctx, float* table, size_t seqLen, int headDim, dou
 // angle evaluation runs once per configuration instead of once per call.
 const float* cached_rope_table(Context* ctx, size_t seqLen, int headDim, double base, long long startPos, int scaling, double factor,
                                double low, double high, int origCtx, CUDAStatus* status) {
-    const double key[8] = {(double)seqLen, (double)headDim, base, (double)startPos, (double)scaling,
-                           scaling ? factor : 0.0, scaling ? low + 1e6 * high : 0.0, scaling ? (double)origCtx : 0.0};
+    const double key[10] = {(double)seqLen, (double)headDim, base, (double)startPos, (double)scaling, scaling ? factor : 0.0,
+                            scaling ? low : 0.0, scaling ? high : 0.0, scaling ? (double)origCtx : 0.0, 0.0};
     const size_t need = seqLen * (size_t)(headDim / 2) * 2 * sizeof(float);
     if (ctx->ropeKeyValid && memcmp(key, ctx->ropeKey, sizeof(key)) == 0 && ctx->ropeTable && ctx->ropeTableBytes >= need)
         return ctx->ropeTable;

@@ -120,6 +120,7 @@ int cuda_open_device_index(int ordinal, CUDADeviceRef* outDevice, CUDAStatus* st
     }
     ctx->stream = ctx->ownStream;
     for (int i = 0; i < 4; i++) cudaEventCreateWithFlags(&ctx->stageEvents[i], cudaEventDisableTiming);
+    cudaEventCreateWithFlags(&ctx->streamSwitchEvent, cudaEventDisableTiming);
     if (cudaMalloc((void**)&ctx->errorFlag, 256) != cudaSuccess) {
         delete ctx;
         return fail(status, -7, "cuda: context allocation failed");
@@ -154,6 +155,7 @@ void cuda_close_device(CUDADeviceRef device) {
     if (ctx->ropeTable) cudaFree(ctx->ropeTable);
     for (int i = 0; i < 4; i++)
         if (ctx->stageEvents[i]) cudaEventDestroy(ctx->stageEvents[i]);
+    if (ctx->streamSwitchEvent) cudaEventDestroy(ctx->streamSwitchEvent);
     cudaStreamDestroy(ctx->ownStream);
     cudaStreamDestroy(ctx->uploadStream);
     {
@@ -289,7 +291,15 @@ int cuda_context_set_stream(CUDADeviceRef device, void* cudaStream, CUDAStatus* 
     cuda_status_clear(status);
     Context* ctx = ctx_of(device, status);
     if (!ctx) return -1;
-    ctx->stream = (cudaStream_t)cudaStream;  // NULL = the legacy default stream
+    cudaStream_t next = (cudaStream_t)cudaStream;  // NULL = the legacy default stream
+    if (next != ctx->stream) {
+        // the context's scratch (workspace, RoPE table, decode counters) may still be read by kernels queued on the old stream:
+        // whatever the new stream launches is ordered after them
+        cudaSetDevice(ctx->device);
+        if (cudaEventRecord(ctx->streamSwitchEvent, ctx->stream) == cudaSuccess) cudaStreamWaitEvent(next, ctx->streamSwitchEvent, 0);
+        cudaGetLastError();
+        ctx->stream = next;
+    }
     return ok(status);
 }
 
@@ -297,7 +307,12 @@ int cuda_context_reset_stream(CUDADeviceRef device, CUDAStatus* status) {
     cuda_status_clear(status);
     Context* ctx = ctx_of(device, status);
     if (!ctx) return -1;
-    ctx->stream = ctx->ownStream;
+    if (ctx->stream != ctx->ownStream) {
+        cudaSetDevice(ctx->device);
+        if (cudaEventRecord(ctx->streamSwitchEvent, ctx->stream) == cudaSuccess) cudaStreamWaitEvent(ctx->ownStream, ctx->streamSwitchEvent, 0);
+        cudaGetLastError();
+        ctx->stream = ctx->ownStream;
+    }
     return ok(status);
 }
 

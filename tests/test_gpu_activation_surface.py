@@ -154,11 +154,20 @@ def test_layernorm_residual_equals_layernorm_then_add(d, dt, rows, cols):
     g = O.from_f32(rng.uniform(0.5, 1.5, cols).astype(np.float32), dt)
     b = O.from_f32(rng.standard_normal(cols).astype(np.float32), dt)
     r = O.from_f32(rng.standard_normal((rows, cols)).astype(np.float32), dt)
-    want = O.binary(O.ADD, dt, O.layernorm(dt, x, g, b), r)
+    ln = O.layernorm(dt, x, g, b)
+    want = O.binary(O.ADD, dt, ln, r)
     out = empty(rows * cols * ES[dt])
     d.LayerNormResidual(dev(x), dev(g), dev(b), dev(r), out, rows, cols, dt)
     got = host(out, O.np_dtype(dt), (rows, cols))
-    close(dt, got, want)
+    if dt == O.F32:
+        close(dt, got, want)
+    else:
+        # the LayerNorm term carries the one-unit-in-the-last-place difference of its summation order; the add can cancel it
+        # against the residual, so the bound is at the size of the terms, not of the sum
+        gf, wf = O.to_f32(got, dt).astype(np.float64), O.to_f32(want, dt).astype(np.float64)
+        size = np.maximum(1.0, np.maximum(np.abs(O.to_f32(ln, dt)), np.abs(wf)))
+        assert (np.abs(gf - wf) <= 2 * (2.0 ** -7 if dt == O.BF16 else 2.0 ** -10) * size).all()
+        assert (got != want).mean() < 0.03
     # the fused entry and the two separate device ops give the same bits
     ln, two = empty(rows * cols * ES[dt]), empty(rows * cols * ES[dt])
     d.LayerNorm(dev(x), dev(g), dev(b), ln, rows, cols, dt)
