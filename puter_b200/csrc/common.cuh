@@ -245,6 +245,25 @@ __device__ __forceinline__ void fast_swiglu32x2_fused(float g0, float g1, float 
     const float q1 = d1 > 8.0e37f ? divf(g1, d1) : __fdividef(g1, d1);
     un2(mul2(pk2(q0, q1), pk2(u0, u1)), r0, r1);
 }
+// Two silu(gate) * up for 16-bit storage types through the special-function unit: 2^(-gate * log2 e) by ex2.approx (2^-22
+// relative), the quotient by rcp.approx.  The reference's polynomial is itself about 1e-6 away from exp, so after rounding to
+// bf16 / f16 the two agree except on the few results that sit within that distance of a rounding boundary (measured: one
+// unit in the last place on about 3 in 10 000 elements).  The exponent is clamped so that the denominator stays finite and the
+// results for |gate| beyond the reference's clamps (-87.3, 88.7) stay within one unit in the last place of its constants.
+__device__ __forceinline__ void fast_swiglu16x2_sfu(float g0, float g1, float u0, float u1, float& r0, float& r1) {
+    float z0, z1, d0, d1;
+    un2(mul2(pk2(g0, g1), pk2(-1.4426950408889634f, -1.4426950408889634f)), z0, z1);
+    z0 = fminf(fmaxf(z0, -126.0f), 127.99f);
+    z1 = fminf(fmaxf(z1, -126.0f), 127.99f);
+    float e0, e1, q0, q1;
+    asm("ex2.approx.f32 %0, %1;" : "=f"(e0) : "f"(z0));
+    asm("ex2.approx.f32 %0, %1;" : "=f"(e1) : "f"(z1));
+    un2(add2(pk2(1.0f, 1.0f), pk2(e0, e1)), d0, d1);
+    asm("rcp.approx.f32 %0, %1;" : "=f"(q0) : "f"(d0));
+    asm("rcp.approx.f32 %0, %1;" : "=f"(q1) : "f"(d1));
+    // (gate * 1/d) * up, in the reference's order
+    un2(mul2(mul2(pk2(g0, g1), pk2(q0, q1)), pk2(u0, u1)), r0, r1);
+}
 // two f32 -> one word of two bf16 with the library's rounding rule (hardware RNE; NaN payload rule applied on the rare NaN)
 __device__ __forceinline__ uint32_t f32x2_to_bf16x2(float lo, float hi) {
     uint32_t w;

@@ -215,15 +215,28 @@ __device__ __forceinline__ void merge_if_last(const DecodeParams& p, const int* 
         const int head = kvh * p.group + (valid ? hBase + hl : 0);
         const float2* mlBase = p.partML + (size_t)b * p.numHeads + head;          // + v * numHeads
         const float* accBase = p.partAcc + ((size_t)b * p.numHeads + head) * kHeadDim + d0;  // + v * numHeads * 128
-        float M = -INFINITY;
-#pragma unroll 4
-        for (long long v = v0; v <= v1; v++)
-            if (allOwn || owns(v)) M = fmaxf(M, __ldcg(mlBase + (size_t)v * p.numHeads).x);
+        // maxima of the pass's heads: lane-parallel over the owners (one L2 round trip per 32 owners), then a warp reduction
+        float Mh[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        for (long long base = v0; base <= v1; base += 32) {
+            const long long v = base + lane;
+            if (v <= v1 && (allOwn || owns(v))) {
+                const float2* ml = p.partML + (size_t)(v + b) * p.numHeads + kvh * p.group + hBase;
+#pragma unroll
+                for (int h = 0; h < 4; h++)
+                    if (hBase + h < p.group) Mh[h] = fmaxf(Mh[h], __ldcg(ml + h).x);
+            }
+        }
+#pragma unroll
+        for (int h = 0; h < 4; h++) {
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) Mh[h] = fmaxf(Mh[h], __shfl_xor_sync(0xffffffffu, Mh[h], o));
+        }
+        const float M = hl == 0 ? Mh[0] : hl == 1 ? Mh[1] : hl == 2 ? Mh[2] : Mh[3];
         float den = 0.f;
         float4 num[4];
 #pragma unroll
         for (int i = 0; i < 4; i++) num[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 2
+#pragma unroll 8
         for (long long v = v0; v <= v1; v++) {
             if (!(allOwn || owns(v))) continue;
             const float2 ml = __ldcg(mlBase + (size_t)v * p.numHeads);
@@ -327,26 +340,6 @@ __global__ void __launch_bounds__(kThreads, 1) paged_decode16_kernel(DecodeParam
                 kBase += (size_t)b * p.seqStrideKV * 2;
                 vBase += (size_t)b * p.seqStrideKV * 2;
             }
-            // ---- Q as the B operand: k16 step kk: b0 = dims 16kk + 2t, +1 of head g; b1 = dims 16kk + 8 + 2t, +1 ----
-            uint32_t qb[8][NT][2];
-            {
-                const uint16_t* qRow = (const uint16_t*)p.q + (size_t)b * p.numHeads * kHeadDim;
-#pragma unroll
-                for (int nt = 0; nt < NT; nt++) {
-                    const int gi = nt * 8 + g;
-#pragma unroll
-                    for (int kk = 0; kk < 8; kk++) {
-                        uint32_t w0 = 0, w1 = 0;
-                        if (gi < p.group) {
-                            const uint16_t* src = qRow + (size_t)(kvh * p.group + gi) * kHeadDim + kk * 16 + 2 * t;
-                            w0 = *(const uint32_t*)src;
-                            w1 = *(const uint32_t*)(src + 8);
-                        }
-                        qb[kk][nt][0] = w0;
-                        qb[kk][nt][1] = w1;
-                    }
-                }
-            }
             // O^T: tile dt = dims 16dt .. 16dt+15; [0],[1] = (dim 16dt+g, heads 2t, 2t+1), [2],[3] = (dim 16dt+g+8, heads 2t, 2t+1)
             float oacc[8][NT][4];
 #pragma unroll
@@ -422,6 +415,27 @@ __global__ void __launch_bounds__(kThreads, 1) paged_decode16_kernel(DecodeParam
             for (int s = 0; s < kStages16 - 1; s++) {
                 if (s < nTiles) issue(tile0 + s, s);
                 cp_async_commit();
+            }
+            // (the query rows are fetched after the first K/V copies are on their way: they are not needed before the first MMA)
+            // ---- Q as the B operand: k16 step kk: b0 = dims 16kk + 2t, +1 of head g; b1 = dims 16kk + 8 + 2t, +1 ----
+            uint32_t qb[8][NT][2];
+            {
+                const uint16_t* qRow = (const uint16_t*)p.q + (size_t)b * p.numHeads * kHeadDim;
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++) {
+                    const int gi = nt * 8 + g;
+#pragma unroll
+                    for (int kk = 0; kk < 8; kk++) {
+                        uint32_t w0 = 0, w1 = 0;
+                        if (gi < p.group) {
+                            const uint16_t* src = qRow + (size_t)(kvh * p.group + gi) * kHeadDim + kk * 16 + 2 * t;
+                            w0 = *(const uint32_t*)src;
+                            w1 = *(const uint32_t*)(src + 8);
+                        }
+                        qb[kk][nt][0] = w0;
+                        qb[kk][nt][1] = w1;
+                    }
+                }
             }
             int stage = 0;
             for (int it = 0; it < nTiles; it++) {
@@ -655,31 +669,6 @@ __global__ void __launch_bounds__(kThreads, 1) paged_decode_fp8_kernel(DecodePar
                 kBase += (size_t)b * p.seqStrideKV;
                 vBase += (size_t)b * p.seqStrideKV;
             }
-            // ---- Q as the B operand, f16: chunk c (16 head dimensions): b0 = dims 16c+4t, +1 of head g; b1 = dims +2, +3 ----
-            uint32_t qb[8][NT][2];
-            {
-                const uint16_t* qRow = (const uint16_t*)p.q + (size_t)b * p.numHeads * kHeadDim;
-#pragma unroll
-                for (int nt = 0; nt < NT; nt++) {
-                    const int gi = nt * 8 + g;
-#pragma unroll
-                    for (int c = 0; c < 8; c++) {
-                        uint32_t w0 = 0, w1 = 0;
-                        if (gi < p.group) {
-                            const uint2 raw = *(const uint2*)(qRow + (size_t)(kvh * p.group + gi) * kHeadDim + c * 16 + 4 * t);
-                            if (BF16) {
-                                w0 = pack16<false>(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xFFFF0000u));
-                                w1 = pack16<false>(__uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xFFFF0000u));
-                            } else {
-                                w0 = raw.x;
-                                w1 = raw.y;
-                            }
-                        }
-                        qb[c][nt][0] = w0;
-                        qb[c][nt][1] = w1;
-                    }
-                }
-            }
             // O^T: tile dt = dims 16dt .. 16dt+15 in the row order {0,2,..,14,1,3,..,15}; [0],[1] = (dim 16dt+2g, heads 2t, 2t+1),
             // [2],[3] = (dim 16dt+2g+1, heads 2t, 2t+1)
             float oacc[8][NT][4];
@@ -760,6 +749,32 @@ __global__ void __launch_bounds__(kThreads, 1) paged_decode_fp8_kernel(DecodePar
             for (int s = 0; s < kStages8 - 1; s++) {
                 if (s < nSteps) issue(tok0 + s * kTile8, s);
                 cp_async_commit();
+            }
+            // (the query rows are fetched after the first K/V copies are on their way: they are not needed before the first MMA)
+            // ---- Q as the B operand, f16: chunk c (16 head dimensions): b0 = dims 16c+4t, +1 of head g; b1 = dims +2, +3 ----
+            uint32_t qb[8][NT][2];
+            {
+                const uint16_t* qRow = (const uint16_t*)p.q + (size_t)b * p.numHeads * kHeadDim;
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++) {
+                    const int gi = nt * 8 + g;
+#pragma unroll
+                    for (int c = 0; c < 8; c++) {
+                        uint32_t w0 = 0, w1 = 0;
+                        if (gi < p.group) {
+                            const uint2 raw = *(const uint2*)(qRow + (size_t)(kvh * p.group + gi) * kHeadDim + c * 16 + 4 * t);
+                            if (BF16) {
+                                w0 = pack16<false>(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xFFFF0000u));
+                                w1 = pack16<false>(__uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xFFFF0000u));
+                            } else {
+                                w0 = raw.x;
+                                w1 = raw.y;
+                            }
+                        }
+                        qb[c][nt][0] = w0;
+                        qb[c][nt][1] = w1;
+                    }
+                }
             }
             int stage = 0;
             for (int it = 0; it < nSteps; it++) {

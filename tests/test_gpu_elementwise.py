@@ -123,9 +123,11 @@ def test_gated_tensors(d, name, code, dt, n):
     if name == "GeGLU":
         assert rel_err(O.to_f32(got, dt), O.to_f32(want, dt)) <= (1e-6 if dt == O.F32 else 1e-2)
     elif name == "SwiGLU" and dt != O.F32:
-        # 16-bit SwiGLU evaluates the reference polynomial with fused multiply-adds: at most one unit in the last place, rarely
+        # 16-bit SwiGLU: at most one unit in the last place.  f16 evaluates the reference polynomial with fused multiply-adds
+        # (differs rarely); bf16 takes the exponential from the special-function unit, which is closer to exp than the
+        # reference's polynomial (about 2e-6 relative apart): results within that distance of a bf16 rounding boundary flip
         diff = ulp16_diff(got, want)
-        assert diff.max() <= 1 and (diff > 0).mean() <= 1e-3
+        assert diff.max() <= 1 and (diff > 0).mean() <= (3e-3 if dt == O.BF16 else 1e-3)
     else:
         assert np.array_equal(got.view(np.uint8), want.view(np.uint8))
 
@@ -143,7 +145,7 @@ def test_swiglu_packed(d, dt, batch, half):
         assert np.array_equal(got.view(np.uint8), want.view(np.uint8))
     else:
         diff = ulp16_diff(got, want)
-        assert diff.max() <= 1 and (diff > 0).mean() <= 1e-3
+        assert diff.max() <= 1 and (diff > 0).mean() <= 3e-3  # bf16: exponential from the special-function unit (see above)
 
 
 @pytest.mark.parametrize("op,code", [("Add", O.ADD), ("Sub", O.SUB), ("Mul", O.MUL), ("Div", O.DIV), ("Max", O.MAX), ("Min", O.MIN)])
