@@ -236,18 +236,35 @@ __device__ __forceinline__ void merge_if_last(const DecodeParams& p, const int* 
         float4 num[4];
 #pragma unroll
         for (int i = 0; i < 4; i++) num[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 8
-        for (long long v = v0; v <= v1; v++) {
-            if (!(allOwn || owns(v))) continue;
-            const float2 ml = __ldcg(mlBase + (size_t)v * p.numHeads);
-            const float* a = accBase + (size_t)v * p.numHeads * kHeadDim;
-            const float4 a0 = ldcg4(a), a1 = ldcg4(a + 4), a2 = ldcg4(a + 8), a3 = ldcg4(a + 12);
-            const float w = (ml.x == -INFINITY) ? 0.f : exp2f(ml.x - M);
-            den += ml.y * w;
-            num[0].x += a0.x * w; num[0].y += a0.y * w; num[0].z += a0.z * w; num[0].w += a0.w * w;
-            num[1].x += a1.x * w; num[1].y += a1.y * w; num[1].z += a1.z * w; num[1].w += a1.w * w;
-            num[2].x += a2.x * w; num[2].y += a2.y * w; num[2].z += a2.z * w; num[2].w += a2.w * w;
-            num[3].x += a3.x * w; num[3].y += a3.y * w; num[3].z += a3.z * w; num[3].w += a3.w * w;
+        // eight owners per round: all their loads are issued before the first is used, so a round costs one L2 round trip
+        constexpr int kBatch = 8;
+        for (long long base = v0; base <= v1; base += kBatch) {
+            float2 ml[kBatch];
+            float4 acc[kBatch][4];
+#pragma unroll
+            for (int k = 0; k < kBatch; k++) {
+                const long long v = base + k;
+                if (v <= v1 && (allOwn || owns(v))) {
+                    ml[k] = __ldcg(mlBase + (size_t)v * p.numHeads);
+                    const float* a = accBase + (size_t)v * p.numHeads * kHeadDim;
+                    acc[k][0] = ldcg4(a);
+                    acc[k][1] = ldcg4(a + 4);
+                    acc[k][2] = ldcg4(a + 8);
+                    acc[k][3] = ldcg4(a + 12);
+                } else {
+                    ml[k] = make_float2(-INFINITY, 0.f);
+                    acc[k][0] = acc[k][1] = acc[k][2] = acc[k][3] = make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+            }
+#pragma unroll
+            for (int k = 0; k < kBatch; k++) {
+                const float w = (ml[k].x == -INFINITY) ? 0.f : exp2f(ml[k].x - M);
+                den += ml[k].y * w;
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    num[i].x += acc[k][i].x * w; num[i].y += acc[k][i].y * w; num[i].z += acc[k][i].z * w; num[i].w += acc[k][i].w * w;
+                }
+            }
         }
         if (!valid) continue;
         uint32_t w2[8];
