@@ -19,9 +19,13 @@
 //     heads), so every SM reads the same number of bytes whatever the context-length mix; a range may
 //     span several sequences and a sequence several ranges;
 //   * each (worker, sequence, KV head) triple leaves an un-normalised partial (max, sum, accumulator) in scratch
-//     memory and bumps a counter; the warp that finds itself last for a (sequence, KV head) merges the partials
-//     in worker order and writes the rounded output rows, so a decode step is ONE launch: the tile prefix sums
-//     are recomputed by every CTA in shared memory (a separate one-block kernel only beyond 1024 sequences);
+//     memory and bumps a counter, so a decode step is ONE launch: the tile prefix sums are recomputed by every CTA in
+//     shared memory (a separate one-block kernel only beyond 1024 sequences).  The grid is launched cooperatively (one
+//     CTA per SM, all resident), and the workers that share a sequence merge it TOGETHER once their own ranges are done:
+//     each waits, bounded, for the sequence's counter, then normalises and writes its own share of the output rows from
+//     one round of loads.  (One warp pulling 30 workers' partials through its SM's L2 port took ~19 us at the end of the
+//     kernel; 30 warps on 30 SMs take ~3.)  Where a cooperative launch is refused, the warp that arrives last for a
+//     (sequence, KV head) merges all of it in worker order;
 //   * the GQA group (<= 16 query heads per KV head) forms the M=16 rows of mma.sync m16n8k16 tiles fed by
 //     ldmatrix from XOR-swizzled shared memory; tensor-core throughput is irrelevant here, the point is to
 //     keep the instruction count per byte far below the issue limit.
@@ -52,12 +56,13 @@ struct DecodeParams {
     const int* tileStart;     // [batch+1] exclusive prefix of tiles per sequence, or nullptr: scanned in shared memory
     float* partAcc;           // [slots, numHeads, 128]
     float2* partML;           // [slots, numHeads]  (max in log2 domain, sum)
-    int* counters;            // [batch, kvHeads] arrivals per (sequence, KV head); zero on entry, zero again on exit
+    int* counters;            // [batch, kvHeads] arrivals (then departures) per (sequence, KV head); zero on entry, zero again on exit
     void* out;                // [batch, numHeads*128]
     int* errorFlag;
     long long seqStrideKV;    // contiguous mode: elements between consecutive sequences' K (and V)
     int batch, maxPages, pageCount, pageSize, numHeads, kvHeads, group, uniformCtx;
     int headsPerPass, groups, workers;  // warps-as-heads per pass, sub-ranges per CTA, total workers
+    int distributed;          // all CTAs of the grid run at the same time (cooperative launch): owners merge together
     float scaleLog2;          // (1/sqrt(headDim)) * log2(e)
     float scale;
 };
@@ -175,68 +180,62 @@ __device__ __forceinline__ long long worker_of_tile(long long g, long long T, lo
 
 __device__ __forceinline__ float4 ldcg4(const float* p) { return __ldcg((const float4*)p); }
 
-// Called by a whole warp once its partial of (worker, sequence b, KV head kvh) is in scratch.  Counts the arrival; the warp
-// that arrives last for (b, kvh) merges the partials of all owning workers in worker order (so the result does not depend on
-// which warp happens to be last), normalises, rounds and writes the group's output rows, and returns the counter to zero.
-// A sequence that lies inside one worker's range needs no counter at all.
-template <bool BF16>
-__device__ __forceinline__ void merge_if_last(const DecodeParams& p, const int* ts, int b, int kvh, int lane) {
-    const long long T = ts[p.batch];
-    const long long s0 = ts[b], s1 = ts[b + 1];
-    const long long W = p.workers;
-    const long long v0 = worker_of_tile(s0, T, W), v1 = worker_of_tile(s1 - 1, T, W);
+// Workers that own tiles of sequence b, in worker order: [v0, v1], of which n have a non-empty range.
+struct SeqOwners {
+    long long T, W, v0, v1;
+    int n;
+    bool allOwn;  // every worker of the grid has a non-empty range (at least as many tiles as workers)
     // workers whose own range is empty (fewer tiles than workers) never write a partial
-    auto owns = [&](long long v) { return (v + 1) * T / W > v * T / W; };
-    int owners = (int)(v1 - v0 + 1);
-    if (T < W) {
-        owners = 0;
-        for (long long v = v0; v <= v1; v++) owners += owns(v) ? 1 : 0;
+    __device__ __forceinline__ bool owns(long long v) const { return allOwn || (v + 1) * T / W > v * T / W; }
+};
+__device__ __forceinline__ SeqOwners seq_owners(const DecodeParams& p, const int* ts, int b) {
+    SeqOwners so;
+    so.T = ts[p.batch];
+    so.W = p.workers;
+    so.v0 = worker_of_tile(ts[b], so.T, so.W);
+    so.v1 = worker_of_tile((long long)ts[b + 1] - 1, so.T, so.W);
+    so.allOwn = so.T >= so.W;
+    so.n = (int)(so.v1 - so.v0 + 1);
+    if (!so.allOwn) {
+        so.n = 0;
+        for (long long v = so.v0; v <= so.v1; v++) so.n += so.owns(v) ? 1 : 0;
     }
-    __threadfence();  // this lane's partial stores are visible device-wide before the arrival is counted
-    __syncwarp();
-    if (owners > 1) {
-        int last = 0;
-        if (lane == 0) {
-            int* c = p.counters + (size_t)b * p.kvHeads + kvh;
-            last = atomicAdd(c, 1) == owners - 1;
-            if (last) *c = 0;  // nobody else touches this counter again in this launch
-        }
-        last = __shfl_sync(0xffffffffu, last, 0);
-        if (!last) return;
-        __threadfence();
+    return so;
+}
+
+template <bool BF16>
+__device__ __forceinline__ void store_out16(uint16_t* dst, const float* num, float den) {
+    uint32_t w2[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const float a = den > 0.f ? num[2 * i] / den : 0.f, c = den > 0.f ? num[2 * i + 1] / den : 0.f;
+        const uint32_t lo = BF16 ? f32_to_bf16_bits(a) : f32_to_f16_bits(a), hi = BF16 ? f32_to_bf16_bits(c) : f32_to_f16_bits(c);
+        w2[i] = lo | (hi << 16);
     }
-    // Four heads per pass: lane = (head within the pass, 16-dimension slice).  Every owner's (max, sum) pair and accumulator
-    // slice is an independent load, so a sequence spread over many workers costs a few L2 round trips, not one per owner.
+    ((uint4*)dst)[0] = make_uint4(w2[0], w2[1], w2[2], w2[3]);
+    ((uint4*)dst)[1] = make_uint4(w2[4], w2[5], w2[6], w2[7]);
+}
+
+// Merge of (sequence b, KV head kvh) with a lane per 16-dimension slice of a head (four heads per pass) and a loop over the
+// owning workers in worker order.  Of the slices, numbered through the group's heads, this call handles those with
+// slice % split == share: split = 1 merges everything, split = n with share = the caller's rank among the owners is one
+// owner's part of a merge that all owners do together.  The whole warp must call it.
+// The loads of eight owners (their (max, sum) pairs and accumulator slices) are all issued before the first is used, and
+// the running maximum is updated per round, so a round costs ONE L2 round trip (about a microsecond on this part).
+template <bool BF16>
+__device__ __forceinline__ void merge_slices(const DecodeParams& p, const SeqOwners& so, int b, int kvh, int lane, int split, int share) {
     uint16_t* orow = (uint16_t*)p.out + (size_t)b * p.numHeads * kHeadDim;
-    const bool allOwn = T >= W;
+    const long long v0 = so.v0, v1 = so.v1;
     const int hl = lane >> 3, d0 = (lane & 7) * 16;
     for (int hBase = 0; hBase < p.group; hBase += 4) {
-        const bool valid = hBase + hl < p.group;
-        const int head = kvh * p.group + (valid ? hBase + hl : 0);
-        const float2* mlBase = p.partML + (size_t)b * p.numHeads + head;          // + v * numHeads
+        const bool valid = hBase + hl < p.group && (hBase * 8 + lane) % split == share;
+        const int head = kvh * p.group + (hBase + hl < p.group ? hBase + hl : 0);
+        const float2* mlBase = p.partML + (size_t)b * p.numHeads + head;                      // + v * numHeads
         const float* accBase = p.partAcc + ((size_t)b * p.numHeads + head) * kHeadDim + d0;  // + v * numHeads * 128
-        // maxima of the pass's heads: lane-parallel over the owners (one L2 round trip per 32 owners), then a warp reduction
-        float Mh[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-        for (long long base = v0; base <= v1; base += 32) {
-            const long long v = base + lane;
-            if (v <= v1 && (allOwn || owns(v))) {
-                const float2* ml = p.partML + (size_t)(v + b) * p.numHeads + kvh * p.group + hBase;
+        float M = -INFINITY, den = 0.f;
+        float num[16];
 #pragma unroll
-                for (int h = 0; h < 4; h++)
-                    if (hBase + h < p.group) Mh[h] = fmaxf(Mh[h], __ldcg(ml + h).x);
-            }
-        }
-#pragma unroll
-        for (int h = 0; h < 4; h++) {
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) Mh[h] = fmaxf(Mh[h], __shfl_xor_sync(0xffffffffu, Mh[h], o));
-        }
-        const float M = hl == 0 ? Mh[0] : hl == 1 ? Mh[1] : hl == 2 ? Mh[2] : Mh[3];
-        float den = 0.f;
-        float4 num[4];
-#pragma unroll
-        for (int i = 0; i < 4; i++) num[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-        // eight owners per round: all their loads are issued before the first is used, so a round costs one L2 round trip
+        for (int i = 0; i < 16; i++) num[i] = 0.f;
         constexpr int kBatch = 8;
         for (long long base = v0; base <= v1; base += kBatch) {
             float2 ml[kBatch];
@@ -244,7 +243,7 @@ __device__ __forceinline__ void merge_if_last(const DecodeParams& p, const int* 
 #pragma unroll
             for (int k = 0; k < kBatch; k++) {
                 const long long v = base + k;
-                if (v <= v1 && (allOwn || owns(v))) {
+                if (valid && v <= v1 && so.owns(v)) {
                     ml[k] = __ldcg(mlBase + (size_t)v * p.numHeads);
                     const float* a = accBase + (size_t)v * p.numHeads * kHeadDim;
                     acc[k][0] = ldcg4(a);
@@ -256,32 +255,181 @@ __device__ __forceinline__ void merge_if_last(const DecodeParams& p, const int* 
                     acc[k][0] = acc[k][1] = acc[k][2] = acc[k][3] = make_float4(0.f, 0.f, 0.f, 0.f);
                 }
             }
+            float Mn = M;
+#pragma unroll
+            for (int k = 0; k < kBatch; k++) Mn = fmaxf(Mn, ml[k].x);
+            if (Mn != M) {  // also the first round with any live owner: M = -inf scales the (zero) sums by zero
+                const float s = (M == -INFINITY) ? 0.f : exp2f(M - Mn);
+                den *= s;
+#pragma unroll
+                for (int i = 0; i < 16; i++) num[i] *= s;
+                M = Mn;
+            }
 #pragma unroll
             for (int k = 0; k < kBatch; k++) {
                 const float w = (ml[k].x == -INFINITY) ? 0.f : exp2f(ml[k].x - M);
                 den += ml[k].y * w;
 #pragma unroll
                 for (int i = 0; i < 4; i++) {
-                    num[i].x += acc[k][i].x * w; num[i].y += acc[k][i].y * w; num[i].z += acc[k][i].z * w; num[i].w += acc[k][i].w * w;
+                    num[4 * i] += acc[k][i].x * w; num[4 * i + 1] += acc[k][i].y * w;
+                    num[4 * i + 2] += acc[k][i].z * w; num[4 * i + 3] += acc[k][i].w * w;
                 }
             }
         }
-        if (!valid) continue;
-        uint32_t w2[8];
+        if (valid) store_out16<BF16>(orow + (size_t)head * kHeadDim + d0, num, den);
+    }
+}
+
+// One owner's part of the merge of (sequence b, KV head kvh) when the sequence is spread over many workers: the owner with
+// rank `share` among the n owners takes the 16-dimension slices share, share + n, ...  For a slice, a LANE PER OWNER loads
+// that owner's (max, sum) pair and 16 accumulator values; the warp reduces them with a fixed shuffle tree that halves the
+// values a lane carries at every level, so lane l ends up with the sum of dimension (l >> 1) of the slice.  More than 32
+// owners take several such units per slice, combined in order with a running maximum.  The loads of four units are issued
+// together: the whole duty is normally one L2 round trip.  The whole warp must call it.
+template <bool BF16>
+__device__ __forceinline__ void merge_across_lanes(const DecodeParams& p, const SeqOwners& so, int b, int kvh, int lane, int share) {
+    uint16_t* orow = (uint16_t*)p.out + (size_t)b * p.numHeads * kHeadDim;
+    const int slices = p.group * 8;
+    const int passes = (int)((so.v1 - so.v0 + 32) / 32);
+    const int mine = share < slices ? (slices - share + so.n - 1) / so.n : 0;  // slices share, share + n, ...
+    const int units = mine * passes;
+    // reversed bit order: the element a lane keeps is picked by its bits 4 (x8), 3 (x4), 2 (x2), 1 (x1)
+    const int elem = ((lane >> 4) & 1) * 8 + ((lane >> 3) & 1) * 4 + ((lane >> 2) & 1) * 2 + ((lane >> 1) & 1);
+    float M = -INFINITY, den = 0.f, num = 0.f;  // running state of the current slice (num: dimension `elem`)
+    constexpr int kUnits = 4;
+    for (int u0 = 0; u0 < units; u0 += kUnits) {
+        float2 ml[kUnits];
+        float4 acc[kUnits][4];
 #pragma unroll
-        for (int i = 0; i < 4; i++) {
-            const float o[4] = {num[i].x, num[i].y, num[i].z, num[i].w};
-#pragma unroll
-            for (int j = 0; j < 2; j++) {
-                const float a = den > 0.f ? o[2 * j] / den : 0.f, c = den > 0.f ? o[2 * j + 1] / den : 0.f;
-                const uint32_t lo = BF16 ? f32_to_bf16_bits(a) : f32_to_f16_bits(a), hi = BF16 ? f32_to_bf16_bits(c) : f32_to_f16_bits(c);
-                w2[2 * i + j] = lo | (hi << 16);
+        for (int k = 0; k < kUnits; k++) {
+            const int u = u0 + k;
+            const int c = share + (u / passes) * so.n;
+            const long long v = so.v0 + (long long)(u % passes) * 32 + lane;
+            if (u < units && v <= so.v1 && so.owns(v)) {
+                const size_t row = (size_t)(v + b) * p.numHeads + kvh * p.group + (c >> 3);
+                ml[k] = __ldcg(p.partML + row);
+                const float* a = p.partAcc + row * kHeadDim + (c & 7) * 16;
+                acc[k][0] = ldcg4(a);
+                acc[k][1] = ldcg4(a + 4);
+                acc[k][2] = ldcg4(a + 8);
+                acc[k][3] = ldcg4(a + 12);
+            } else {
+                ml[k] = make_float2(-INFINITY, 0.f);
+                acc[k][0] = acc[k][1] = acc[k][2] = acc[k][3] = make_float4(0.f, 0.f, 0.f, 0.f);
             }
         }
-        uint4* dst = (uint4*)(orow + (size_t)head * kHeadDim + d0);
-        dst[0] = make_uint4(w2[0], w2[1], w2[2], w2[3]);
-        dst[1] = make_uint4(w2[4], w2[5], w2[6], w2[7]);
+#pragma unroll
+        for (int k = 0; k < kUnits; k++) {
+            const int u = u0 + k;
+            if (u >= units) break;  // uniform over the warp
+            float Mu = ml[k].x;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) Mu = fmaxf(Mu, __shfl_xor_sync(0xffffffffu, Mu, o));
+            const float w = (ml[k].x == -INFINITY) ? 0.f : exp2f(ml[k].x - Mu);
+            float du = ml[k].y * w;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) du += __shfl_xor_sync(0xffffffffu, du, o);
+            float val[16] = {acc[k][0].x * w, acc[k][0].y * w, acc[k][0].z * w, acc[k][0].w * w, acc[k][1].x * w, acc[k][1].y * w,
+                             acc[k][1].z * w, acc[k][1].w * w, acc[k][2].x * w, acc[k][2].y * w, acc[k][2].z * w, acc[k][2].w * w,
+                             acc[k][3].x * w, acc[k][3].y * w, acc[k][3].z * w, acc[k][3].w * w};
+            // reduce-scatter: at the level of lane bit o a lane keeps one half of its values and receives the partner's
+#pragma unroll
+            for (int half = 8, o = 16; half >= 1; half >>= 1, o >>= 1) {
+                const bool upper = (lane & o) != 0;
+#pragma unroll
+                for (int i = 0; i < half; i++) {
+                    const float send = upper ? val[i] : val[i + half];
+                    const float keep = upper ? val[i + half] : val[i];
+                    val[i] = keep + __shfl_xor_sync(0xffffffffu, send, o);
+                }
+            }
+            float nu = val[0] + __shfl_xor_sync(0xffffffffu, val[0], 1);
+            // combine with the slice's earlier units (owners 32 and up)
+            if (u % passes == 0) { M = -INFINITY; den = 0.f; num = 0.f; }
+            const float Mn = fmaxf(M, Mu);
+            const float sOld = (M == -INFINITY) ? 0.f : exp2f(M - Mn), sNew = (Mu == -INFINITY) ? 0.f : exp2f(Mu - Mn);
+            den = den * sOld + du * sNew;
+            num = num * sOld + nu * sNew;
+            M = Mn;
+            if (u % passes == passes - 1 && (lane & 1) == 0) {
+                const int c = share + (u / passes) * so.n;
+                const float o = den > 0.f ? num / den : 0.f;
+                orow[(size_t)(kvh * p.group + (c >> 3)) * kHeadDim + (c & 7) * 16 + elem] = (uint16_t)(BF16 ? f32_to_bf16_bits(o) : f32_to_f16_bits(o));
+            }
+        }
     }
+}
+
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+static constexpr int kMergeSplitMax = 8;          // up to this many owners, every owner loops over all owners for its slices
+static constexpr unsigned kMergeSpinLimit = 1u << 21;  // polls of an arrival counter before a warp gives up (~1 s)
+
+// Called by a whole warp once its partial of (worker, sequence b, KV head kvh) is in scratch.
+//   * A sequence that lies inside one worker's range is normalised and written at once.
+//   * Otherwise the arrival is counted.  Where all CTAs of the grid are known to run at the same time (p.distributed), the
+//     sequence is noted in `duty` and the warp moves on: once its range is done it waits for the other owners and merges ITS
+//     share of the output, so a sequence spread over 30 workers is merged by 30 warps on 30 SMs at once instead of one SM
+//     pulling all of it through its L2 port.  A range has at most two such sequences (its first and its last).
+//   * Without that guarantee the warp that arrives last merges everything, in worker order, and zeroes the counter.
+template <bool BF16>
+__device__ __forceinline__ void segment_done(const DecodeParams& p, const int* ts, int b, int kvh, int lane, int& duty0, int& duty1, int& nDuty) {
+    const SeqOwners so = seq_owners(p, ts, b);
+    __threadfence();  // this lane's partial stores are visible device-wide before the arrival is counted
+    __syncwarp();
+    if (so.n > 1) {
+        int* c = p.counters + (size_t)b * p.kvHeads + kvh;
+        if (p.distributed) {
+            // only the first and the last sequence of a range can be shared with other workers: two notes suffice
+            if (lane == 0) atomicAdd(c, 1);
+            if (nDuty++ == 0) duty0 = b; else duty1 = b;
+            return;
+        }
+        int last = 0;
+        if (lane == 0) {
+            last = atomicAdd(c, 1) == so.n - 1;
+            if (last) *c = 0;  // nobody else touches this counter again in this launch
+        }
+        last = __shfl_sync(0xffffffffu, last, 0);
+        if (!last) return;
+        __threadfence();
+    }
+    merge_slices<BF16>(p, so, b, kvh, lane, 1, 0);
+}
+
+// The deferred part of segment_done: waits (bounded) until all n owners of (b, kvh) have arrived, merges this worker's share,
+// counts the departure; the last to depart returns the counter to zero.
+template <bool BF16>
+__device__ __forceinline__ void finish_duty(const DecodeParams& p, const int* ts, long long worker, int b, int kvh, int lane) {
+    const SeqOwners so = seq_owners(p, ts, b);
+    int* c = p.counters + (size_t)b * p.kvHeads + kvh;
+    int ok = 1;
+    if (lane == 0) {
+        unsigned spins = 0;
+        while (ld_acquire_gpu(c) < so.n) {
+            if (++spins > kMergeSpinLimit) { ok = 0; break; }
+            __nanosleep(40);
+        }
+    }
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    __syncwarp();  // lane 0's acquire load, then this barrier: the other lanes' loads below see the owners' partials
+    if (ok) {
+        int share = (int)(worker - so.v0);
+        if (!so.allOwn) {
+            share = 0;
+            for (long long v = so.v0; v < worker; v++) share += so.owns(v) ? 1 : 0;
+        }
+        if (so.n <= kMergeSplitMax) merge_slices<BF16>(p, so, b, kvh, lane, so.n, share);
+        else merge_across_lanes<BF16>(p, so, b, kvh, lane, share);
+    } else if (lane == 0) {
+        atomicExch(p.errorFlag, 4);  // an owner never arrived: the rows of this sequence are not written
+    }
+    __syncwarp();
+    if (lane == 0 && atomicAdd(c, 1) == 2 * so.n - 1) *c = 0;
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -344,6 +492,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_decode16_kernel(DecodeParam
     for (int kvh = head0; kvh < p.kvHeads; kvh += p.headsPerPass) {
         int b = seq;
         long long cur = lo;
+        int duty0 = 0, duty1 = 0, nDuty = 0;  // sequences shared with other workers whose merge waits for the end of the range
         while (cur < hi) {
             while (ts[b + 1] <= cur) b++;  // skip empty sequences
             const long long segStart = ts[b], segEndAll = ts[b + 1];
@@ -573,10 +722,14 @@ __global__ void __launch_bounds__(kThreads, 1) paged_decode16_kernel(DecodeParam
                     }
                 }
             }
-            merge_if_last<BF16>(p, ts, b, kvh, lane);
+            segment_done<BF16>(p, ts, b, kvh, lane, duty0, duty1, nDuty);
             cur = segEnd;
             if (cur >= segEndAll) b++;
         }
+        // the range's last sequence first: its other owners met it at the start of their ranges and arrived long ago,
+        // while the first sequence waits for a worker that is finishing its own range right now
+        if (nDuty > 1) finish_duty<BF16>(p, ts, worker, duty1, kvh, lane);
+        if (nDuty > 0) finish_duty<BF16>(p, ts, worker, duty0, kvh, lane);
     }
 }
 
@@ -671,6 +824,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_decode_fp8_kernel(DecodePar
     for (int kvh = head0; kvh < p.kvHeads; kvh += p.headsPerPass) {
         int b = seq;
         long long cur = lo;
+        int duty0 = 0, duty1 = 0, nDuty = 0;  // sequences shared with other workers whose merge waits for the end of the range
         while (cur < hi) {
             while (ts[b + 1] <= cur) b++;
             const long long segStart = ts[b], segEndAll = ts[b + 1];
@@ -931,10 +1085,14 @@ __global__ void __launch_bounds__(kThreads, 1) paged_decode_fp8_kernel(DecodePar
                     }
                 }
             }
-            merge_if_last<BF16>(p, ts, b, kvh, lane);
+            segment_done<BF16>(p, ts, b, kvh, lane, duty0, duty1, nDuty);
             cur = segEnd;
             if (cur >= segEndAll) b++;
         }
+        // the range's last sequence first: its other owners met it at the start of their ranges and arrived long ago,
+        // while the first sequence waits for a worker that is finishing its own range right now
+        if (nDuty > 1) finish_duty<BF16>(p, ts, worker, duty1, kvh, lane);
+        if (nDuty > 0) finish_duty<BF16>(p, ts, worker, duty0, kvh, lane);
     }
 }
 
@@ -1026,7 +1184,13 @@ int launch_paged_decode(Context* ctx, int dt, int kvDT, const void* q, const voi
 #define DECODE_LAUNCH(KERNEL, SMEM)                                                             \
     do {                                                                                        \
         cudaFuncSetAttribute(KERNEL, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(SMEM)); \
-        KERNEL<<<(unsigned)ctas, kThreads, SMEM, ctx->stream>>>(p);                             \
+        p.distributed = 1;                                                                      \
+        void* args[] = {&p};                                                                    \
+        if (cudaLaunchCooperativeKernel((const void*)KERNEL, dim3((unsigned)ctas), dim3(kThreads), args, SMEM, ctx->stream) != cudaSuccess) { \
+            cudaGetLastError();                                                                 \
+            p.distributed = 0;                                                                  \
+            KERNEL<<<(unsigned)ctas, kThreads, SMEM, ctx->stream>>>(p);                         \
+        }                                                                                       \
     } while (0)
     if (fp8) {
         if (group <= 8) {
