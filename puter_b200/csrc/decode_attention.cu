@@ -493,19 +493,106 @@ __global__ void __launch_bounds__(kThreads, 1) paged_decode16_kernel(DecodeParam
         int b = seq;
         long long cur = lo;
         int duty0 = 0, duty1 = 0, nDuty = 0;  // sequences shared with other workers whose merge waits for the end of the range
+        // ---- issue cursor: the copies run kStages16 - 1 tiles ahead of the compute and do not stop at a sequence boundary, so
+        // the first tiles of the next sequence are on their way while this one's partial is stored and its arrival counted ----
+        long long ig = lo;                      // next global tile to copy
+        int ib = seq, istage = 0;
+        long long iSegStart = 0, iSegEnd = lo;  // global tiles of sequence ib: [iSegStart, iSegEnd); empty = not set up yet
+        int iCtx = 0;
+        const int32_t* table = nullptr;
+        const unsigned char *kBase = nullptr, *vBase = nullptr;
+        int cbase = -0x40000000, cval = 0;
+        auto page_of = [&](int entry) -> int {
+            if (!table) return entry;
+            if (entry - cbase >= 32 || entry < cbase) {
+                cbase = entry;
+                int idx = entry + lane;
+                cval = idx < p.maxPages ? table[idx] : 0;
+            }
+            int pg = __shfl_sync(0xffffffffu, cval, entry - cbase);
+            if (pg < 0 || pg >= p.pageCount) {
+                if (lane == 0) atomicExch(p.errorFlag, 1);
+                pg = 0;  // never dereference an out-of-range page
+            }
+            return pg;
+        };
+        // async copies of local tile `lt` (16 tokens) of sequence ib into stage `st`; rows past the context are zero-filled, never read
+        auto issue = [&](int lt, int st) {
+            const int ctx = iCtx;
+            const int tok0 = lt * kTile;
+            const uint32_t dstK = wsmAddr + st * kStage16, dstV = dstK + kTile * kHeadDim * 2;
+            if (page16 || !table) {
+                const int ps = table ? p.pageSize : kTile;
+                const size_t pageOff = ((size_t)page_of(tok0 / ps) * ps + (size_t)(tok0 % ps)) * tokenStride;
+                const unsigned char* ks = kBase + pageOff + cpSrc;
+                const unsigned char* vs = vBase + pageOff + cpSrc;
+                const bool full = tok0 + kTile <= ctx;
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    const int r = 2 * i + cpRow;
+                    const uint32_t so = (uint32_t)(r * 256) + (uint32_t)((cpChunk ^ (r & 7)) * 16);
+                    const size_t rowOff = (size_t)(2 * i) * tokenStride;
+                    if (full) {
+                        cp_async16(dstK + so, ks + rowOff, 16);
+                        cp_async16(dstV + so, vs + rowOff, 16);
+                    } else {
+                        const bool live = tok0 + r < ctx;
+                        cp_async16(dstK + so, live ? ks + rowOff : kBase, live ? 16 : 0);
+                        cp_async16(dstV + so, live ? vs + rowOff : vBase, live ? 16 : 0);
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    const int r = 2 * i + cpRow;
+                    const int tok = tok0 + r;
+                    int pg = 0;
+                    const int entry = tok / p.pageSize;
+                    if (tok < ctx && entry < p.maxPages) {
+                        pg = table[entry];
+                        if (pg < 0 || pg >= p.pageCount) { atomicExch(p.errorFlag, 1); pg = 0; }
+                    }
+                    size_t off = ((size_t)pg * p.pageSize + tok % p.pageSize) * tokenStride;
+                    const int bytes = tok < ctx ? 16 : 0;
+                    if (bytes == 0) off = 0;
+                    const uint32_t so = (uint32_t)(r * 256) + (uint32_t)((cpChunk ^ (r & 7)) * 16);
+                    cp_async16(dstK + so, kBase + off + cpChunk * 16, bytes);
+                    cp_async16(dstV + so, vBase + off + cpChunk * 16, bytes);
+                }
+            }
+        };
+        // copies the next tile of the range, if there is one, and closes a copy group either way
+        auto issue_next = [&]() {
+            if (ig < hi) {
+                if (ig >= iSegEnd) {
+                    while (ts[ib + 1] <= ig) ib++;  // skip empty sequences
+                    iSegStart = ts[ib];
+                    iSegEnd = ts[ib + 1];
+                    iCtx = seq_ctx(p, ib, (int)(iSegEnd - iSegStart));
+                    table = p.pageTable ? p.pageTable + (size_t)ib * p.maxPages : nullptr;
+                    kBase = (const unsigned char*)p.kPages + (size_t)kvh * kHeadDim * 2;
+                    vBase = (const unsigned char*)p.vPages + (size_t)kvh * kHeadDim * 2;
+                    if (!table) {
+                        kBase += (size_t)ib * p.seqStrideKV * 2;
+                        vBase += (size_t)ib * p.seqStrideKV * 2;
+                    }
+                    cbase = -0x40000000;
+                }
+                issue((int)(ig - iSegStart), istage);
+            }
+            ig++;
+            if (++istage == kStages16) istage = 0;
+            cp_async_commit();
+        };
+#pragma unroll
+        for (int s = 0; s < kStages16 - 1; s++) issue_next();
+        int stage = 0;
         while (cur < hi) {
             while (ts[b + 1] <= cur) b++;  // skip empty sequences
             const long long segStart = ts[b], segEndAll = ts[b + 1];
             const long long segEnd = segEndAll < hi ? segEndAll : hi;
             const int tile0 = (int)(cur - segStart), tile1 = (int)(segEnd - segStart);  // local tile range [tile0, tile1)
             const int ctx = seq_ctx(p, b, (int)(segEndAll - segStart));
-            const int32_t* table = p.pageTable ? p.pageTable + (size_t)b * p.maxPages : nullptr;
-            const unsigned char* kBase = (const unsigned char*)p.kPages + (size_t)kvh * kHeadDim * 2;
-            const unsigned char* vBase = (const unsigned char*)p.vPages + (size_t)kvh * kHeadDim * 2;
-            if (!table) {
-                kBase += (size_t)b * p.seqStrideKV * 2;
-                vBase += (size_t)b * p.seqStrideKV * 2;
-            }
             // O^T: tile dt = dims 16dt .. 16dt+15; [0],[1] = (dim 16dt+g, heads 2t, 2t+1), [2],[3] = (dim 16dt+g+8, heads 2t, 2t+1)
             float oacc[8][NT][4];
 #pragma unroll
@@ -516,72 +603,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_decode16_kernel(DecodeParam
 #pragma unroll
             for (int nt = 0; nt < NT; nt++) { mcol[nt][0] = mcol[nt][1] = -INFINITY; lcol[nt][0] = lcol[nt][1] = 0.f; }
 
-            int cbase = -0x40000000, cval = 0;
-            auto page_of = [&](int entry) -> int {
-                if (!table) return entry;
-                if (entry - cbase >= 32 || entry < cbase) {
-                    cbase = entry;
-                    int idx = entry + lane;
-                    cval = idx < p.maxPages ? table[idx] : 0;
-                }
-                int pg = __shfl_sync(0xffffffffu, cval, entry - cbase);
-                if (pg < 0 || pg >= p.pageCount) {
-                    if (lane == 0) atomicExch(p.errorFlag, 1);
-                    pg = 0;  // never dereference an out-of-range page
-                }
-                return pg;
-            };
-            // async copies of local tile `lt` (16 tokens) into stage `st`; rows past the context are zero-filled, never read
-            auto issue = [&](int lt, int st) {
-                const int tok0 = lt * kTile;
-                const uint32_t dstK = wsmAddr + st * kStage16, dstV = dstK + kTile * kHeadDim * 2;
-                if (page16 || !table) {
-                    const int ps = table ? p.pageSize : kTile;
-                    const size_t pageOff = ((size_t)page_of(tok0 / ps) * ps + (size_t)(tok0 % ps)) * tokenStride;
-                    const unsigned char* ks = kBase + pageOff + cpSrc;
-                    const unsigned char* vs = vBase + pageOff + cpSrc;
-                    const bool full = tok0 + kTile <= ctx;
-#pragma unroll
-                    for (int i = 0; i < 8; i++) {
-                        const int r = 2 * i + cpRow;
-                        const uint32_t so = (uint32_t)(r * 256) + (uint32_t)((cpChunk ^ (r & 7)) * 16);
-                        const size_t rowOff = (size_t)(2 * i) * tokenStride;
-                        if (full) {
-                            cp_async16(dstK + so, ks + rowOff, 16);
-                            cp_async16(dstV + so, vs + rowOff, 16);
-                        } else {
-                            const bool live = tok0 + r < ctx;
-                            cp_async16(dstK + so, live ? ks + rowOff : kBase, live ? 16 : 0);
-                            cp_async16(dstV + so, live ? vs + rowOff : vBase, live ? 16 : 0);
-                        }
-                    }
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 8; i++) {
-                        const int r = 2 * i + cpRow;
-                        const int tok = tok0 + r;
-                        int pg = 0;
-                        const int entry = tok / p.pageSize;
-                        if (tok < ctx && entry < p.maxPages) {
-                            pg = table[entry];
-                            if (pg < 0 || pg >= p.pageCount) { atomicExch(p.errorFlag, 1); pg = 0; }
-                        }
-                        size_t off = ((size_t)pg * p.pageSize + tok % p.pageSize) * tokenStride;
-                        const int bytes = tok < ctx ? 16 : 0;
-                        if (bytes == 0) off = 0;
-                        const uint32_t so = (uint32_t)(r * 256) + (uint32_t)((cpChunk ^ (r & 7)) * 16);
-                        cp_async16(dstK + so, kBase + off + cpChunk * 16, bytes);
-                        cp_async16(dstV + so, vBase + off + cpChunk * 16, bytes);
-                    }
-                }
-            };
-
             const int nTiles = tile1 - tile0;
-#pragma unroll
-            for (int s = 0; s < kStages16 - 1; s++) {
-                if (s < nTiles) issue(tile0 + s, s);
-                cp_async_commit();
-            }
             // (the query rows are fetched after the first K/V copies are on their way: they are not needed before the first MMA)
             // ---- Q as the B operand: k16 step kk: b0 = dims 16kk + 2t, +1 of head g; b1 = dims 16kk + 8 + 2t, +1 ----
             uint32_t qb[8][NT][2];
@@ -603,17 +625,10 @@ __global__ void __launch_bounds__(kThreads, 1) paged_decode16_kernel(DecodeParam
                     }
                 }
             }
-            int stage = 0;
             for (int it = 0; it < nTiles; it++) {
                 cp_async_wait<kStages16 - 2>();
                 __syncwarp();
-                {
-                    const int nx = it + kStages16 - 1;
-                    int nst = stage + kStages16 - 1;
-                    if (nst >= kStages16) nst -= kStages16;
-                    if (nx < nTiles) issue(tile0 + nx, nst);
-                    cp_async_commit();
-                }
+                issue_next();
                 const uint32_t tileK = wsmAddr + stage * kStage16, tileV = tileK + kTile * kHeadDim * 2;
                 if (++stage == kStages16) stage = 0;
                 // ---- S^T = K Q^T : 16 tokens x 8 heads per n-tile ----
@@ -695,8 +710,6 @@ __global__ void __launch_bounds__(kThreads, 1) paged_decode16_kernel(DecodeParam
                     }
                 }
             }
-            cp_async_wait<0>();
-            __syncwarp();
             // ---- partial of (worker, sequence b, KV head): row sums reduced over the lanes of a head column ----
             {
                 const long long slot = worker + b;
@@ -726,6 +739,8 @@ __global__ void __launch_bounds__(kThreads, 1) paged_decode16_kernel(DecodeParam
             cur = segEnd;
             if (cur >= segEndAll) b++;
         }
+        cp_async_wait<0>();  // only empty groups are left
+        __syncwarp();
         // the range's last sequence first: its other owners met it at the start of their ranges and arrived long ago,
         // while the first sequence waits for a worker that is finishing its own range right now
         if (nDuty > 1) finish_duty<BF16>(p, ts, worker, duty1, kvh, lane);
@@ -825,6 +840,107 @@ __global__ void __launch_bounds__(kThreads, 1) paged_decode_fp8_kernel(DecodePar
         int b = seq;
         long long cur = lo;
         int duty0 = 0, duty1 = 0, nDuty = 0;  // sequences shared with other workers whose merge waits for the end of the range
+        // ---- issue cursor: the copies run kStages8 - 1 steps ahead of the compute and do not stop at a sequence boundary, so
+        // the first steps of the next sequence are on their way while this one's partial is stored and its arrival counted ----
+        long long icur = lo;         // global tile at which the next sequence's share of this range starts
+        int ib = seq, istage = 0;
+        int iTok = 0, iTokEnd = 0;   // tokens of sequence ib still to copy: [iTok, iTokEnd)
+        const int32_t* table = nullptr;
+        const unsigned char *kBase = nullptr, *vBase = nullptr;
+        int cbase = -0x40000000, cval = 0;
+        auto page_of = [&](int entry) -> int {
+            if (!table) return entry;
+            if (entry - cbase >= 32 || entry < cbase) {
+                cbase = entry;
+                int idx = entry + lane;
+                cval = idx < p.maxPages ? table[idx] : 0;
+            }
+            int pg = __shfl_sync(0xffffffffu, cval, entry - cbase);
+            if (pg < 0 || pg >= p.pageCount) {
+                if (lane == 0) atomicExch(p.errorFlag, 1);
+                pg = 0;  // never dereference an out-of-range page
+            }
+            return pg;
+        };
+        // async copies of the 32 tokens starting at `tsk` of sequence ib into stage `st` (rows past the share's end are zero-filled)
+        auto issue = [&](int tsk, int st) {
+            const int tokEnd = iTokEnd;
+            const uint32_t dstK = wsmAddr + st * kStage8, dstV = dstK + kTile8 * kHeadDim;
+            if (page16 || !table) {
+                const int ps = table ? p.pageSize : kTile;
+                const bool full = tsk + kTile8 <= tokEnd;
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    const int tk = tsk + h * kTile;
+                    size_t halfOff = 0;
+                    if (tk < tokEnd) halfOff = ((size_t)page_of(tk / ps) * ps + (size_t)(tk % ps)) * tokenStride;
+                    const unsigned char* ks = kBase + halfOff + cpSrc;
+                    const unsigned char* vs = vBase + halfOff + cpSrc;
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const uint32_t so = (uint32_t)((h * 16 + (i >> 1) * 8) * 128) + ((i & 1) ? cpDstOdd : cpDstEven);
+                        const size_t rowOff = (size_t)(4 * i) * tokenStride;
+                        if (full) {
+                            cp_async16(dstK + so, ks + rowOff, 16);
+                            cp_async16(dstV + so, vs + rowOff, 16);
+                        } else {
+                            const bool live = tk + 4 * i + cpRow < tokEnd;
+                            cp_async16(dstK + so, live ? ks + rowOff : kBase, live ? 16 : 0);
+                            cp_async16(dstV + so, live ? vs + rowOff : vBase, live ? 16 : 0);
+                        }
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    const int r = i * 4 + cpRow;
+                    const int tok = tsk + r;
+                    int pg = 0;
+                    const int entry = tok / p.pageSize;
+                    if (tok < tokEnd && entry < p.maxPages) {
+                        pg = table[entry];
+                        if (pg < 0 || pg >= p.pageCount) { atomicExch(p.errorFlag, 1); pg = 0; }
+                    }
+                    size_t off = ((size_t)pg * p.pageSize + tok % p.pageSize) * tokenStride;
+                    const int bytes = tok < tokEnd ? 16 : 0;
+                    if (bytes == 0) off = 0;
+                    const uint32_t so = r * 128 + ((cpChunk ^ (r & 7)) * 16);
+                    cp_async16(dstK + so, kBase + off + cpChunk * 16, bytes);
+                    cp_async16(dstV + so, vBase + off + cpChunk * 16, bytes);
+                }
+            }
+        };
+        // copies the next 32-token step of the range, if there is one, and closes a copy group either way.  A sequence's share
+        // is cut into steps from its own first token, exactly as the compute loop below counts them.
+        auto issue_next = [&]() {
+            if (iTok >= iTokEnd && icur < hi) {
+                while (ts[ib + 1] <= icur) ib++;  // skip empty sequences
+                const long long s0 = ts[ib], s1 = ts[ib + 1];
+                const long long e = s1 < hi ? s1 : hi;
+                const int ctx = seq_ctx(p, ib, (int)(s1 - s0));
+                const long long endTokL = (e - s0) * kTile;
+                iTok = (int)(icur - s0) * kTile;
+                iTokEnd = (int)(endTokL < ctx ? endTokL : ctx);
+                icur = e;
+                table = p.pageTable ? p.pageTable + (size_t)ib * p.maxPages : nullptr;
+                kBase = (const unsigned char*)p.kPages + (size_t)kvh * kHeadDim;
+                vBase = (const unsigned char*)p.vPages + (size_t)kvh * kHeadDim;
+                if (!table) {
+                    kBase += (size_t)ib * p.seqStrideKV;
+                    vBase += (size_t)ib * p.seqStrideKV;
+                }
+                cbase = -0x40000000;
+            }
+            if (iTok < iTokEnd) {
+                issue(iTok, istage);
+                iTok += kTile8;
+            }
+            if (++istage == kStages8) istage = 0;
+            cp_async_commit();
+        };
+#pragma unroll
+        for (int s = 0; s < kStages8 - 1; s++) issue_next();
+        int stage = 0;
         while (cur < hi) {
             while (ts[b + 1] <= cur) b++;
             const long long segStart = ts[b], segEndAll = ts[b + 1];
@@ -833,13 +949,6 @@ __global__ void __launch_bounds__(kThreads, 1) paged_decode_fp8_kernel(DecodePar
             const int ctx = seq_ctx(p, b, (int)(segEndAll - segStart));
             const long long endTokL = (segEnd - segStart) * kTile;
             const int tokEnd = (int)(endTokL < ctx ? endTokL : ctx);  // this worker's share of the sequence: [tok0, tokEnd)
-            const int32_t* table = p.pageTable ? p.pageTable + (size_t)b * p.maxPages : nullptr;
-            const unsigned char* kBase = (const unsigned char*)p.kPages + (size_t)kvh * kHeadDim;
-            const unsigned char* vBase = (const unsigned char*)p.vPages + (size_t)kvh * kHeadDim;
-            if (!table) {
-                kBase += (size_t)b * p.seqStrideKV;
-                vBase += (size_t)b * p.seqStrideKV;
-            }
             // O^T: tile dt = dims 16dt .. 16dt+15 in the row order {0,2,..,14,1,3,..,15}; [0],[1] = (dim 16dt+2g, heads 2t, 2t+1),
             // [2],[3] = (dim 16dt+2g+1, heads 2t, 2t+1)
             float oacc[8][NT][4];
@@ -852,75 +961,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_decode_fp8_kernel(DecodePar
             for (int nt = 0; nt < NT; nt++) { mcol[nt][0] = mcol[nt][1] = -INFINITY; lcol[nt][0] = lcol[nt][1] = 0.f; }
             const float sScale = (p.kScale ? p.kScale[kvh] : 1.0f) * p.scaleLog2;
 
-            int cbase = -0x40000000, cval = 0;
-            auto page_of = [&](int entry) -> int {
-                if (!table) return entry;
-                if (entry - cbase >= 32 || entry < cbase) {
-                    cbase = entry;
-                    int idx = entry + lane;
-                    cval = idx < p.maxPages ? table[idx] : 0;
-                }
-                int pg = __shfl_sync(0xffffffffu, cval, entry - cbase);
-                if (pg < 0 || pg >= p.pageCount) {
-                    if (lane == 0) atomicExch(p.errorFlag, 1);
-                    pg = 0;  // never dereference an out-of-range page
-                }
-                return pg;
-            };
-            // async copies of the 32 tokens starting at `tsk` into stage `st` (rows past tokEnd are zero-filled)
-            auto issue = [&](int tsk, int st) {
-                const uint32_t dstK = wsmAddr + st * kStage8, dstV = dstK + kTile8 * kHeadDim;
-                if (page16 || !table) {
-                    const int ps = table ? p.pageSize : kTile;
-                    const bool full = tsk + kTile8 <= tokEnd;
-#pragma unroll
-                    for (int h = 0; h < 2; h++) {
-                        const int tk = tsk + h * kTile;
-                        size_t halfOff = 0;
-                        if (tk < tokEnd) halfOff = ((size_t)page_of(tk / ps) * ps + (size_t)(tk % ps)) * tokenStride;
-                        const unsigned char* ks = kBase + halfOff + cpSrc;
-                        const unsigned char* vs = vBase + halfOff + cpSrc;
-#pragma unroll
-                        for (int i = 0; i < 4; i++) {
-                            const uint32_t so = (uint32_t)((h * 16 + (i >> 1) * 8) * 128) + ((i & 1) ? cpDstOdd : cpDstEven);
-                            const size_t rowOff = (size_t)(4 * i) * tokenStride;
-                            if (full) {
-                                cp_async16(dstK + so, ks + rowOff, 16);
-                                cp_async16(dstV + so, vs + rowOff, 16);
-                            } else {
-                                const bool live = tk + 4 * i + cpRow < tokEnd;
-                                cp_async16(dstK + so, live ? ks + rowOff : kBase, live ? 16 : 0);
-                                cp_async16(dstV + so, live ? vs + rowOff : vBase, live ? 16 : 0);
-                            }
-                        }
-                    }
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 8; i++) {
-                        const int r = i * 4 + cpRow;
-                        const int tok = tsk + r;
-                        int pg = 0;
-                        const int entry = tok / p.pageSize;
-                        if (tok < tokEnd && entry < p.maxPages) {
-                            pg = table[entry];
-                            if (pg < 0 || pg >= p.pageCount) { atomicExch(p.errorFlag, 1); pg = 0; }
-                        }
-                        size_t off = ((size_t)pg * p.pageSize + tok % p.pageSize) * tokenStride;
-                        const int bytes = tok < tokEnd ? 16 : 0;
-                        if (bytes == 0) off = 0;
-                        const uint32_t so = r * 128 + ((cpChunk ^ (r & 7)) * 16);
-                        cp_async16(dstK + so, kBase + off + cpChunk * 16, bytes);
-                        cp_async16(dstV + so, vBase + off + cpChunk * 16, bytes);
-                    }
-                }
-            };
-
             const int nSteps = (tokEnd - tok0 + kTile8 - 1) / kTile8;
-#pragma unroll
-            for (int s = 0; s < kStages8 - 1; s++) {
-                if (s < nSteps) issue(tok0 + s * kTile8, s);
-                cp_async_commit();
-            }
             // (the query rows are fetched after the first K/V copies are on their way: they are not needed before the first MMA)
             // ---- Q as the B operand, f16: chunk c (16 head dimensions): b0 = dims 16c+4t, +1 of head g; b1 = dims +2, +3 ----
             uint32_t qb[8][NT][2];
@@ -947,17 +988,10 @@ __global__ void __launch_bounds__(kThreads, 1) paged_decode_fp8_kernel(DecodePar
                     }
                 }
             }
-            int stage = 0;
             for (int it = 0; it < nSteps; it++) {
                 cp_async_wait<kStages8 - 2>();
                 __syncwarp();
-                {
-                    const int nx = it + kStages8 - 1;
-                    int nst = stage + kStages8 - 1;
-                    if (nst >= kStages8) nst -= kStages8;
-                    if (nx < nSteps) issue(tok0 + nx * kTile8, nst);
-                    cp_async_commit();
-                }
+                issue_next();
                 const uint32_t tileK = wsmAddr + stage * kStage8, tileV = tileK + kTile8 * kHeadDim;
                 if (++stage == kStages8) stage = 0;
                 // ---- S^T = K Q^T : 32 tokens x 8 heads per n-tile; two m-tiles of 16 tokens ----
@@ -1059,8 +1093,6 @@ __global__ void __launch_bounds__(kThreads, 1) paged_decode_fp8_kernel(DecodePar
                     }
                 }
             }
-            cp_async_wait<0>();
-            __syncwarp();
             // ---- partial of (worker, sequence b, KV head): row sums reduced over the lanes of a head column ----
             {
                 const long long slot = worker + b;
@@ -1089,6 +1121,8 @@ __global__ void __launch_bounds__(kThreads, 1) paged_decode_fp8_kernel(DecodePar
             cur = segEnd;
             if (cur >= segEndAll) b++;
         }
+        cp_async_wait<0>();  // only empty groups are left
+        __syncwarp();
         // the range's last sequence first: its other owners met it at the start of their ranges and arrived long ago,
         // while the first sequence waits for a worker that is finishing its own range right now
         if (nDuty > 1) finish_duty<BF16>(p, ts, worker, duty1, kvh, lane);
