@@ -272,6 +272,34 @@ __device__ __forceinline__ uint32_t f32x2_to_bf16x2(float lo, float hi) {
     return w;
 }
 
+// Conversions for RESULTS OF ARITHMETIC in the 16-bit row kernels, done by the hardware.  Widening is exact; narrowing is
+// cvt.rn (round to nearest even, overflow to infinity, gradual underflow), the same rounding as the bit arithmetic of
+// Storage<DT>::narrow.  The two differ only in which NaN comes out, and a NaN that has been through float32 arithmetic is the
+// canonical 0x7FFFFFFF on this hardware, which both map to 0x7FFF: the payload rule of Storage<DT>::narrow has nothing left
+// to preserve.  Pure conversions and copies of caller data must not use these.
+template <int DT> __device__ __forceinline__ uint32_t pack16_arith(float lo, float hi) {
+    uint32_t w;
+    if (DT == DT_BF16) asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(w) : "f"(hi), "f"(lo));
+    else asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(w) : "f"(hi), "f"(lo));
+    return w;
+}
+template <int DT> __device__ __forceinline__ void unpack16_arith(uint32_t w, float& lo, float& hi) {
+    if (DT == DT_BF16) {
+        lo = __uint_as_float(w << 16);
+        hi = __uint_as_float(w & 0xFFFF0000u);
+    } else {
+        const float2 t = __half22float2(*(const __half2*)&w);
+        lo = t.x;
+        hi = t.y;
+    }
+}
+// rounds two results to the 16-bit storage type in place and returns the packed word
+template <int DT> __device__ __forceinline__ uint32_t round_pair_arith(float& a, float& b) {
+    const uint32_t w = pack16_arith<DT>(a, b);
+    unpack16_arith<DT>(w, a, b);
+    return w;
+}
+
 // rounds two float32 to the 16-bit storage type: returns the packed word and replaces the inputs by the rounded values
 template <int DT> __device__ __forceinline__ uint32_t round_pair(float& a, float& b) {
     if (DT == DT_BF16) {

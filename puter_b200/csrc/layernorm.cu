@@ -362,14 +362,42 @@ __global__ void __launch_bounds__(ROWPIPE_MAX_WARPS * 32) row_norm_ring_kernel(R
     }
 }
 
-// Rows of up to 32 * VPL vectors: one warp per row, the raw 16-byte vectors of the row held in registers (VPL per lane, lane l
-// owns vectors l, l + 32, ...), reductions by shuffles: no shared memory, no CTA-wide barrier between the passes.
+template <int DT> __device__ __forceinline__ void unpack16_fast(const Vec16& v, float* f) {
+#pragma unroll
+    for (int i = 0; i < 4; i++) unpack16_arith<DT>(v.w[i], f[2 * i], f[2 * i + 1]);
+}
+template <int DT> __device__ __forceinline__ Vec16 pack16_fast(const float* f) {
+    Vec16 v;
+#pragma unroll
+    for (int i = 0; i < 4; i++) v.w[i] = pack16_arith<DT>(f[2 * i], f[2 * i + 1]);
+    return v;
+}
+
+// 16-bit rows of up to 32 * VPL vectors: one warp per row, the raw 16-byte vectors of the row held in registers (VPL per lane,
+// lane l owns vectors l, l + 32, ...), reductions by shuffles: no CTA-wide barrier between the passes.  The kernel is bound by
+// instruction issue (three passes over twice the elements per byte, every product and sum separately rounded), so it is built to
+// spend few instructions per element: conversions by the hardware (pack16_arith), four independent partial sums per lane, and for LayerNorm
+// the scale and bias rows widened to float32 ONCE per CTA into shared memory (as two float4 planes per vector, so that a
+// warp's 16-byte reads are conflict-free) instead of being fetched and widened again for every row.
 template <int DT, int OP, int VPL>
 __global__ void __launch_bounds__(256) row_norm_warp_kernel(RowNormParams p) {
     using T = typename Storage<DT>::type;
-    constexpr int PER = Per<DT>::kPer;
+    constexpr int PER = 8;
+    extern __shared__ float4 sCoef[];  // LayerNorm: [scale lo | scale hi | bias lo | bias hi][nvec]
     const size_t cols = p.cols, nvec = cols / PER;
     const int lane = threadIdx.x & 31;
+    if (OP == OP_LAYERNORM) {
+        for (size_t v = threadIdx.x; v < nvec; v += blockDim.x) {
+            float c0[PER], c1[PER];
+            unpack16_fast<DT>(*(const Vec16*)((const char*)p.p0 + v * 16), c0);
+            unpack16_fast<DT>(*(const Vec16*)((const char*)p.p1 + v * 16), c1);
+            sCoef[v] = make_float4(c0[0], c0[1], c0[2], c0[3]);
+            sCoef[nvec + v] = make_float4(c0[4], c0[5], c0[6], c0[7]);
+            sCoef[2 * nvec + v] = make_float4(c1[0], c1[1], c1[2], c1[3]);
+            sCoef[3 * nvec + v] = make_float4(c1[4], c1[5], c1[6], c1[7]);
+        }
+        __syncthreads();
+    }
     const size_t warpsTotal = (size_t)gridDim.x * (blockDim.x >> 5);
     for (size_t row = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < p.rows; row += warpsTotal) {
         const char* x = (const char*)((const T*)p.in + row * cols);
@@ -380,80 +408,104 @@ __global__ void __launch_bounds__(256) row_norm_warp_kernel(RowNormParams p) {
             const size_t v = lane + (size_t)k * 32;
             if (v < nvec) raw[k] = ld_stream(x + v * 16);
         }
-        float acc = 0.f;
+        float part[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int k = 0; k < VPL; k++) {
             if (lane + (size_t)k * 32 < nvec) {
                 float f[PER];
-                unpack_row<DT>(raw[k], f);
+                unpack16_fast<DT>(raw[k], f);
 #pragma unroll
-                for (int i = 0; i < PER; i++) acc += OP == OP_ADAPTIVE_RMS ? f[i] * f[i] : f[i];
+                for (int i = 0; i < PER; i++) part[i & 3] += OP == OP_ADAPTIVE_RMS ? f[i] * f[i] : f[i];
             }
         }
-        float total = warp_sum_f32(acc);
+        float total = warp_sum_f32((part[0] + part[1]) + (part[2] + part[3]));
         float mean = 0.f, inv;
         if (OP == OP_ADAPTIVE_RMS) {
             inv = (float)(1.0 / sqrt((double)__fdiv_rn(total, (float)cols) + p.eps));
         } else {
-            if (DT == DT_F32) {
-                mean = (float)((double)total / (double)cols);
-            } else {
-                if (DT == DT_BF16) total = Storage<DT>::widen(Storage<DT>::narrow(total));
-                mean = __fdiv_rn(total, (float)cols);
-            }
-            float sq = 0.f;
+            if (DT == DT_BF16) total = Storage<DT>::widen(Storage<DT>::narrow(total));
+            mean = __fdiv_rn(total, (float)cols);
+            float sq[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int k = 0; k < VPL; k++) {
                 if (lane + (size_t)k * 32 < nvec) {
                     float f[PER];
-                    unpack_row<DT>(raw[k], f);
+                    unpack16_fast<DT>(raw[k], f);
 #pragma unroll
                     for (int i = 0; i < PER; i++) {
                         const float d = sub(f[i], mean);
-                        sq = add(sq, mul(d, d));
+                        sq[i & 3] = add(sq[i & 3], mul(d, d));
                     }
                 }
             }
-            sq = warp_sum_f32(sq);
-            if (DT == DT_F32) inv = (float)(1.0 / sqrt((double)sq / (double)cols + p.eps));
-            else if (OP == OP_LAYERNORM) inv = (float)(1.0 / sqrt((double)add(__fdiv_rn(sq, (float)cols), (float)p.eps)));
-            else inv = (float)(1.0 / sqrt((double)__fdiv_rn(sq, (float)cols) + p.eps));
+            const float sqt = warp_sum_f32((sq[0] + sq[1]) + (sq[2] + sq[3]));
+            if (OP == OP_LAYERNORM) inv = (float)(1.0 / sqrt((double)add(__fdiv_rn(sqt, (float)cols), (float)p.eps)));
+            else inv = (float)(1.0 / sqrt((double)__fdiv_rn(sqt, (float)cols) + p.eps));
         }
-        const char* a0;
-        const char* a1;
-        if (OP == OP_LAYERNORM) {
-            a0 = (const char*)p.p0;  // scale
-            a1 = (const char*)p.p1;  // bias
-        } else {
+        const char* a0 = nullptr;
+        const char* a1 = nullptr;
+        if (OP != OP_LAYERNORM) {
             const T* m = (const T*)p.p0 + (row / p.rowsPerBatch) * p.modCols + (OP == OP_MODULATED_LN ? p.set * cols * 3 : 0);
             a0 = (const char*)m;            // AdaptiveRMSNorm: scale; ModulatedLayerNorm: shift
             a1 = (const char*)(m + cols);   // AdaptiveRMSNorm: shift; ModulatedLayerNorm: scale
         }
+        const char* res = (OP == OP_LAYERNORM && p.res) ? (const char*)((const T*)p.res + row * cols) : nullptr;
+        // four vectors per round: their residual / modulation loads are all issued before the first is used (the streaming
+        // stores in between would otherwise keep every load behind the store before it)
+        constexpr int kRound = 4;
 #pragma unroll
-        for (int k = 0; k < VPL; k++) {
-            const size_t v = lane + (size_t)k * 32;
-            if (v < nvec) {
-                float f[PER], c0[PER], c1[PER], r[PER];
-                unpack_row<DT>(raw[k], f);
-                unpack_row<DT>(*(const Vec16*)(a0 + v * 16), c0);
-                unpack_row<DT>(*(const Vec16*)(a1 + v * 16), c1);
+        for (int k0 = 0; k0 < VPL; k0 += kRound) {
+            Vec16 extra0[kRound], extra1[kRound];  // LayerNorm: residual (extra0); the other two: modulation halves
 #pragma unroll
-                for (int i = 0; i < PER; i++) {
+            for (int j = 0; j < kRound; j++) {
+                const size_t v = lane + (size_t)(k0 + j) * 32;
+                if (v < nvec) {
                     if (OP == OP_LAYERNORM) {
-                        r[i] = add(mul(mul(sub(f[i], mean), inv), c0[i]), c1[i]);
+                        if (res) extra0[j] = ld_stream(res + v * 16);
                     } else {
-                        const float scale = OP == OP_ADAPTIVE_RMS ? c0[i] : c1[i], shift = OP == OP_ADAPTIVE_RMS ? c1[i] : c0[i];
-                        const float nrm = mul(OP == OP_ADAPTIVE_RMS ? f[i] : sub(f[i], mean), inv);
-                        r[i] = add(mul(nrm, add(1.0f, scale)), shift);
+                        extra0[j] = *(const Vec16*)(a0 + v * 16);
+                        extra1[j] = *(const Vec16*)(a1 + v * 16);
                     }
                 }
-                if (OP == OP_LAYERNORM && p.res) {  // the unfused Add reads the stored (rounded) LayerNorm result
-                    float rs[PER];
-                    unpack_row<DT>(ld_stream((const char*)((const T*)p.res + row * cols) + v * 16), rs);
+            }
 #pragma unroll
-                    for (int i = 0; i < PER; i++) r[i] = add(Storage<DT>::widen(Storage<DT>::narrow(r[i])), rs[i]);
+            for (int j = 0; j < kRound; j++) {
+                const int k = k0 + j;
+                const size_t v = lane + (size_t)k * 32;
+                if (v < nvec) {
+                    float f[PER], c0[PER], c1[PER], r[PER];
+                    unpack16_fast<DT>(raw[k], f);
+                    if (OP == OP_LAYERNORM) {
+                        *(float4*)(c0) = sCoef[v];
+                        *(float4*)(c0 + 4) = sCoef[nvec + v];
+                        *(float4*)(c1) = sCoef[2 * nvec + v];
+                        *(float4*)(c1 + 4) = sCoef[3 * nvec + v];
+                    } else {
+                        unpack16_fast<DT>(extra0[j], c0);
+                        unpack16_fast<DT>(extra1[j], c1);
+                    }
+#pragma unroll
+                    for (int i = 0; i < PER; i++) {
+                        if (OP == OP_LAYERNORM) {
+                            r[i] = add(mul(mul(sub(f[i], mean), inv), c0[i]), c1[i]);
+                        } else {
+                            const float scale = OP == OP_ADAPTIVE_RMS ? c0[i] : c1[i], shift = OP == OP_ADAPTIVE_RMS ? c1[i] : c0[i];
+                            const float nrm = mul(OP == OP_ADAPTIVE_RMS ? f[i] : sub(f[i], mean), inv);
+                            r[i] = add(mul(nrm, add(1.0f, scale)), shift);
+                        }
+                    }
+                    if (OP == OP_LAYERNORM && res) {  // the unfused Add reads the stored (rounded) LayerNorm result
+                        float rs[PER];
+                        unpack16_fast<DT>(extra0[j], rs);
+#pragma unroll
+                        for (int i = 0; i < PER; i += 2) {
+                            round_pair_arith<DT>(r[i], r[i + 1]);
+                            r[i] = add(r[i], rs[i]);
+                            r[i + 1] = add(r[i + 1], rs[i + 1]);
+                        }
+                    }
+                    st_stream(o + v * 16, pack16_fast<DT>(r));
                 }
-                st_stream(o + v * 16, pack_row<DT>(r));
             }
         }
     }
@@ -487,12 +539,14 @@ int launch_row_norm(Context* ctx, int dt, const RowNormParams& p, CUDAStatus* st
         ringBlocks = (p.rows + plan.warps - 1) / plan.warps;
         if (ringBlocks > (size_t)ctx->smCount * perSm) ringBlocks = (size_t)ctx->smCount * perSm;
     }
+#define ROWNORM_WARP(DT, VPL)                                                                                       \
+    do {                                                                                                            \
+        if (coefSmem > 48 * 1024) cudaFuncSetAttribute(row_norm_warp_kernel<DT, OP, VPL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)coefSmem); \
+        row_norm_warp_kernel<DT, OP, VPL><<<(unsigned)warpBlocks, 256, coefSmem, ctx->stream>>>(p);                 \
+    } while (0)
 #define ROWNORM_LAUNCH(DT)                                                                                          \
     do {                                                                                                            \
-        if (vpl == 4) row_norm_warp_kernel<DT, OP, 4><<<(unsigned)warpBlocks, 256, 0, ctx->stream>>>(p);             \
-        else if (vpl == 8) row_norm_warp_kernel<DT, OP, 8><<<(unsigned)warpBlocks, 256, 0, ctx->stream>>>(p);        \
-        else if (vpl == 16) row_norm_warp_kernel<DT, OP, 16><<<(unsigned)warpBlocks, 256, 0, ctx->stream>>>(p);      \
-        else if (plan.warps) {                                                                                      \
+        if (plan.warps) {                                                                                           \
             cudaFuncSetAttribute(row_norm_ring_kernel<DT, OP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan.smem); \
             row_norm_ring_kernel<DT, OP><<<(unsigned)ringBlocks, plan.warps * 32, plan.smem, ctx->stream>>>(p, plan.stages); \
         } else if (vec) {                                                                                           \
@@ -503,11 +557,22 @@ int launch_row_norm(Context* ctx, int dt, const RowNormParams& p, CUDAStatus* st
             row_norm_kernel<DT, OP, false><<<(unsigned)blocks, 256, smem, ctx->stream>>>(p);                         \
         }                                                                                                           \
     } while (0)
+#define ROWNORM_LAUNCH16(DT)                                                                                        \
+    do {                                                                                                            \
+        if (vpl == 4) ROWNORM_WARP(DT, 4);                                                                          \
+        else if (vpl == 8) ROWNORM_WARP(DT, 8);                                                                     \
+        else if (vpl == 16) ROWNORM_WARP(DT, 16);                                                                   \
+        else ROWNORM_LAUNCH(DT);                                                                                    \
+    } while (0)
+    // LayerNorm's scale and bias rows, widened once per CTA: 2 * cols floats
+    const size_t coefSmem = OP == OP_LAYERNORM ? p.cols * 2 * sizeof(float) : 0;
     if (dt == DT_F32) ROWNORM_LAUNCH(DT_F32);
-    else if (dt == DT_BF16) ROWNORM_LAUNCH(DT_BF16);
-    else if (dt == DT_F16) ROWNORM_LAUNCH(DT_F16);
+    else if (dt == DT_BF16) ROWNORM_LAUNCH16(DT_BF16);
+    else if (dt == DT_F16) ROWNORM_LAUNCH16(DT_F16);
     else return fail(status, -6, "%s: unsupported dtype %d", what, dt);
+#undef ROWNORM_LAUNCH16
 #undef ROWNORM_LAUNCH
+#undef ROWNORM_WARP
     return check_launch(ctx, status, what);
 }
 

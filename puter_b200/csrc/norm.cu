@@ -17,16 +17,14 @@ namespace puter {
 
 template <int DT> struct Lanes { static constexpr int kPer = DT == DT_F32 ? 4 : 8; };
 
+// (16-bit data here always goes through arithmetic before it is stored: the hardware conversions of pack16_arith apply)
 template <int DT> __device__ __forceinline__ void unpack(const Vec16& v, float* f) {
     if (DT == DT_F32) {
 #pragma unroll
         for (int i = 0; i < 4; i++) f[i] = __uint_as_float(v.w[i]);
     } else {
 #pragma unroll
-        for (int i = 0; i < 4; i++) {
-            f[2 * i] = Storage<DT>::widen((uint16_t)(v.w[i] & 0xFFFFu));
-            f[2 * i + 1] = Storage<DT>::widen((uint16_t)(v.w[i] >> 16));
-        }
+        for (int i = 0; i < 4; i++) unpack16_arith<DT>(v.w[i], f[2 * i], f[2 * i + 1]);
     }
 }
 template <int DT> __device__ __forceinline__ Vec16 pack(const float* f) {
@@ -34,13 +32,9 @@ template <int DT> __device__ __forceinline__ Vec16 pack(const float* f) {
     if (DT == DT_F32) {
 #pragma unroll
         for (int i = 0; i < 4; i++) v.w[i] = __float_as_uint(f[i]);
-    } else if (DT == DT_BF16) {
-#pragma unroll
-        for (int i = 0; i < 4; i++) v.w[i] = f32x2_to_bf16x2(f[2 * i], f[2 * i + 1]);
     } else {
 #pragma unroll
-        for (int i = 0; i < 4; i++)
-            v.w[i] = (uint32_t)Storage<DT>::narrow(f[2 * i]) | ((uint32_t)Storage<DT>::narrow(f[2 * i + 1]) << 16);
+        for (int i = 0; i < 4; i++) v.w[i] = pack16_arith<DT>(f[2 * i], f[2 * i + 1]);
     }
     return v;
 }
@@ -135,7 +129,7 @@ __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(RowArgs a) {
                         for (int j = 0; j < PER; j += 2) {
                             f[j] = add(f[j], g[j]);
                             f[j + 1] = add(f[j + 1], g[j + 1]);
-                            in.w[j / 2] = round_pair<DT>(f[j], f[j + 1]);
+                            in.w[j / 2] = round_pair_arith<DT>(f[j], f[j + 1]);
                         }
                     }
                     if (a.hOut) st_stream((char*)a.hOut + row * a.cols * ES + v * 16, in);
@@ -214,6 +208,101 @@ __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(RowArgs a) {
                 hv = *(const Vec16*)(xr + v * 16);
             }
             finish(v, hv, nullptr);
+        }
+    }
+}
+
+// The fused row of the transformer block at its usual width: 16-bit rows of 257..512 vectors (2056..4096 columns), one
+// 256-thread block per row, two vectors per thread.  The generic kernel above spends ~48 instructions per element on this
+// shape and is bound by instruction issue; this one spends about a third of that:
+//   * a thread owns the same two vector positions of every row, so its slice of the scale row (and of the batch's modulation
+//     row, reloaded when the batch changes) is widened to float32 ONCE and stays in registers;
+//   * all six loads of a row (x, residual, branch) are issued before the first is used;
+//   * x + residual stays in float32 registers between the reduction and the outputs; conversions by the hardware;
+//   * one barrier per row: the per-warp partial sums alternate between two shared arrays.
+// Same arithmetic, rounding points and summation tree as the generic kernel: the results are bit-identical.
+template <int DT, bool GATED, bool INPLACE>
+__global__ void __launch_bounds__(256, 3) add_rmsnorm16_kernel(RowArgs a) {
+    constexpr int PER = 8;
+    __shared__ float red[2][8];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const size_t nvec = a.cols / PER, rowBytes = a.cols * 2;
+    const size_t vo[2] = {(size_t)tid * 16, (size_t)(tid + 256) * 16};  // byte offsets of this thread's vectors in a row
+    const bool has1 = (size_t)tid + 256 < nvec;                           // (the first always exists: nvec > 256)
+    float sc[2][PER];
+    unpack<DT>(*(const Vec16*)((const char*)a.scale + vo[0]), sc[0]);
+    if (has1) unpack<DT>(*(const Vec16*)((const char*)a.scale + vo[1]), sc[1]);
+    float md[2][PER];
+    size_t mdBatch = ~(size_t)0;
+    int par = 0;
+    for (size_t row = blockIdx.x; row < a.rows; row += gridDim.x, par ^= 1) {
+        const size_t ro = row * rowBytes;
+        Vec16 xin[2], rin[2], bin[2];
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            if (i == 0 || has1) {
+                xin[i] = ld_in<INPLACE>((const char*)a.x + ro + vo[i]);
+                rin[i] = ld_in<INPLACE>((const char*)a.residual + ro + vo[i]);
+                if (GATED) bin[i] = ld_stream((const char*)a.branch + ro + vo[i]);  // never aliased (checked by the host)
+            }
+        }
+        if (GATED) {
+            const size_t batch = row / a.rowsPerBatch;
+            if (batch != mdBatch) {
+                mdBatch = batch;
+                const char* m = (const char*)a.mod + (batch * a.modCols + a.set * a.cols * 3 + a.cols * 2) * 2;
+                unpack<DT>(*(const Vec16*)(m + vo[0]), md[0]);
+                if (has1) unpack<DT>(*(const Vec16*)(m + vo[1]), md[1]);
+            }
+        }
+        float h[2][PER];
+        float acc = 0.f;
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            if (i == 0 || has1) {
+                float g[PER];
+                unpack<DT>(xin[i], h[i]);
+                unpack<DT>(rin[i], g);
+                Vec16 hv;
+                // the unfused Add would store its result in the 16-bit type: round here, once, pair by pair
+#pragma unroll
+                for (int j = 0; j < PER; j += 2) {
+                    h[i][j] = add(h[i][j], g[j]);
+                    h[i][j + 1] = add(h[i][j + 1], g[j + 1]);
+                    hv.w[j / 2] = round_pair_arith<DT>(h[i][j], h[i][j + 1]);
+                }
+                if (a.hOut) st_stream((char*)a.hOut + ro + vo[i], hv);
+#pragma unroll
+                for (int j = 0; j < PER; j++) acc = fmaf(h[i][j], h[i][j], acc);
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (lane == 0) red[par][warp] = acc;
+        __syncthreads();
+        // the order of the generic kernel's two-level shuffle tree
+        const float* r = red[par];
+        const float total = ((r[0] + r[4]) + (r[2] + r[6])) + ((r[1] + r[5]) + (r[3] + r[7]));
+        const float inv = inv_rms<DT>((double)total, a.cols, a.eps);
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            if (i == 0 || has1) {
+                float o[PER];
+#pragma unroll
+                for (int j = 0; j < PER; j++) o[j] = mul(mul(h[i][j], inv), sc[i][j]);  // (x * inv) * gamma, compute.go:370-373
+                const Vec16 nv = pack<DT>(o);
+                st_stream((char*)a.normOut + ro + vo[i], nv);
+                for (int p = 0; p < a.nPeer; p++) st_stream(a.normPeer[p] + ro + vo[i], nv);
+                if (GATED) {
+                    float b[PER];
+                    unpack<DT>(bin[i], b);
+#pragma unroll
+                    for (int j = 0; j < PER; j++) o[j] = add(h[i][j], mul(md[i][j], b[j]));
+                    const Vec16 gv = pack<DT>(o);
+                    st_stream((char*)a.gatedOut + ro + vo[i], gv);
+                    for (int p = 0; p < a.nPeer; p++) st_stream(a.gatedPeer[p] + ro + vo[i], gv);
+                }
+            }
         }
     }
 }
@@ -366,6 +455,17 @@ static int launch_rows(Context* ctx, const RowArgs& a, CUDAStatus* status) {
     // measured at 16384 x 4096 bf16: plain RMSNorm 4.49 TB/s warp-per-row vs 4.05 block-per-row; the fused form needs twice the
     // registers per lane, fits one block per SM and is faster block-per-row (4.49 vs 3.27 TB/s)
     if (a.nPeer > 0 && !vec) return fail(status, -2, "rmsnorm: the gathered form needs 16-byte aligned rows");
+    if (FUSED && DT != DT_F32 && vec && nvec > 256 && nvec <= 512) {
+        const bool gated = a.branch != nullptr;
+        constexpr int D16 = DT == DT_F32 ? DT_BF16 : DT;  // (never instantiated for float32 rows)
+        const size_t resident = (size_t)ctx->smCount * 3;  // three blocks per SM fit: every block keeps its scale slice for ~rows/444 rows
+        const int g16 = (int)(a.rows < resident ? a.rows : resident);
+        if (gated && inplace) add_rmsnorm16_kernel<D16, true, true><<<g16, 256, 0, ctx->stream>>>(a);
+        else if (gated) add_rmsnorm16_kernel<D16, true, false><<<g16, 256, 0, ctx->stream>>>(a);
+        else if (inplace) add_rmsnorm16_kernel<D16, false, true><<<g16, 256, 0, ctx->stream>>>(a);
+        else add_rmsnorm16_kernel<D16, false, false><<<g16, 256, 0, ctx->stream>>>(a);
+        return check_launch(ctx, status, "add+rmsnorm+gated residual");
+    }
     if (a.nPeer > 0 && !inplace) {
         if (nvec <= 2 * 256) rmsnorm_rows_kernel<DT, 2, FUSED, false><<<grid, 256, 0, ctx->stream>>>(a);
         else rmsnorm_rows_kernel<DT, 4, FUSED, false><<<grid, 256, 0, ctx->stream>>>(a);
