@@ -20,6 +20,7 @@ workload with all host threads.
 from __future__ import annotations
 
 import argparse
+import datetime
 import json
 import os
 import subprocess
@@ -52,7 +53,7 @@ def measured_peaks():
 # clocks sampling (nvidia-smi in the background during the timed region)
 # ------------------------------------------------------------------------------------------------------------
 class ClockSampler:
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+    Q = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, gpu_index: int):
@@ -67,7 +68,17 @@ class ClockSampler:
         except OSError:
             self.proc = None
 
-    def stop(self):
+    @staticmethod
+    def _when(text: str):
+        """nvidia-smi's timestamp (local time, milliseconds) as seconds since the epoch; None if it does not parse."""
+        try:
+            return datetime.datetime.strptime(text.strip(), "%Y/%m/%d %H:%M:%S.%f").timestamp()
+        except ValueError:
+            return None
+
+    def stop(self, window=None):
+        """Median SM clock, maximum power and the throttle reasons seen.  `window` = (t0, t1) in time.time() seconds keeps
+        only the samples taken while the measured loop was running (the sampler starts before it and stops after it)."""
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0, "power_w_max": None}
         if self.proc is None:
             return out
@@ -84,6 +95,10 @@ class ClockSampler:
         for r in rows:
             if len(r) < 9:
                 continue
+            if window is not None:
+                when = self._when(r[0])
+                if when is not None and not (window[0] <= when <= window[1]):
+                    continue
             try:
                 sm.append(float(r[1]))
                 mx.append(float(r[2]))
@@ -376,6 +391,8 @@ def main():
     ap.add_argument("--prefill-batch", type=int, default=4, help="1 gives a profiler-sized prefill case; not a bench number")
     ap.add_argument("--chain-tokens", type=int, default=16384, help="fewer token rows give a profiler-sized chain case; not a bench number")
     ap.add_argument("--sustained-seconds", type=float, default=2.0, help="length of the sustained loop of the headline step (0 = skip)")
+    ap.add_argument("--clock-window", type=float, default=0.3,
+                    help="seconds of the same loop run untimed directly before the timed steps while nvidia-smi samples the clocks")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-secondary", action="store_true")
     args = ap.parse_args()
@@ -416,21 +433,47 @@ def main():
 
     def timed(fn, steps, sample_clocks=False, drain=None):
         """Times `steps` calls of fn with CUDA events on the launching stream; returns (max-over-ranks seconds, clocks,
-        per-rank seconds).  `drain` runs after the last call, inside the timed region (work of side streams joins there)."""
+        per-rank seconds).  `drain` runs after the last call, inside the timed region (work of side streams joins there).
+        With sample_clocks the same call is looped for --clock-window seconds (0.3) directly before the timed steps (untimed, the same count on
+        every rank): nvidia-smi samples every 20 ms and the timed steps alone can be shorter than that, so the clocks are
+        those of the load window that ends with the timed steps."""
         sampler = ClockSampler(local_rank) if sample_clocks else None
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        preroll = 0
+        if sampler:
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            barrier()
+            a.record()
+            for _ in range(3):
+                fn()
+            b.record()
+            torch.cuda.synchronize()
+            est = torch.tensor([a.elapsed_time(b) / 3e3], device="cuda", dtype=torch.float64)
+            if world > 1:
+                dist.all_reduce(est, op=dist.ReduceOp.MAX)
+            preroll = 0 if profiling else min(20000, int(args.clock_window / max(float(est.item()), 1e-6)) + 1)
         barrier()
+        window0 = None
         if sampler:
             sampler.start()
             time.sleep(0.15)
+            window0 = time.time() + 0.04  # the first samples after the load starts still see the idle clocks
+            for i in range(preroll):
+                fn()
+                if i % 64 == 63:
+                    torch.cuda.synchronize()  # keeps the launch queue short
         start.record()
         for _ in range(steps):
             fn()
         if drain:
             drain()
         stop.record()
+        torch.cuda.synchronize()
+        window1 = time.time()
         barrier()
-        clocks = sampler.stop() if sampler else None
+        clocks = sampler.stop((window0, window1)) if sampler else None
+        if clocks is not None:
+            clocks["window"] = "%d untimed steps of the same loop + the timed steps" % preroll
         sec = start.elapsed_time(stop) / 1e3
         per_rank = [sec]
         if world > 1:

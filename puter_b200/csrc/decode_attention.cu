@@ -32,6 +32,7 @@
 //   * fp8-e4m3 KV pages are converted to f16 (exact) on the way from the staging buffer to the tile; the
 //     per-KV-head scales are applied to the scores and to the output.
 #include <math.h>
+#include <stdlib.h>
 #include <mutex>
 
 #include "common.cuh"
@@ -1215,12 +1216,16 @@ int launch_paged_decode(Context* ctx, int dt, int kvDT, const void* q, const voi
 
     const bool bf16 = dt == DT_BF16;
     const bool fp8 = kvDT == DT_E4M3;
+    // PUTER_DECODE_NO_COOPERATIVE (any value) forces the plain launch, in which the last warp to arrive merges a sequence alone:
+    // the path a refused cooperative launch takes, reachable this way for tests
+    const bool cooperative = getenv("PUTER_DECODE_NO_COOPERATIVE") == nullptr;
 #define DECODE_LAUNCH(KERNEL, SMEM)                                                             \
     do {                                                                                        \
         cudaFuncSetAttribute(KERNEL, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(SMEM)); \
-        p.distributed = 1;                                                                      \
+        p.distributed = cooperative ? 1 : 0;                                                    \
         void* args[] = {&p};                                                                    \
-        if (cudaLaunchCooperativeKernel((const void*)KERNEL, dim3((unsigned)ctas), dim3(kThreads), args, SMEM, ctx->stream) != cudaSuccess) { \
+        if (!cooperative ||                                                                     \
+            cudaLaunchCooperativeKernel((const void*)KERNEL, dim3((unsigned)ctas), dim3(kThreads), args, SMEM, ctx->stream) != cudaSuccess) { \
             cudaGetLastError();                                                                 \
             p.distributed = 0;                                                                  \
             KERNEL<<<(unsigned)ctas, kThreads, SMEM, ctx->stream>>>(p);                         \

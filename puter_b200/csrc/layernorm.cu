@@ -511,6 +511,118 @@ __global__ void __launch_bounds__(256) row_norm_warp_kernel(RowNormParams p) {
     }
 }
 
+// float32 rows of up to 256 * VPT vectors (4096 columns at VPT = 4): one 256-thread block per row, the row in registers
+// and the NEXT row of the block already on its way while this one is reduced and written.  Three blocks per SM then keep six
+// rows (96 KB at 4096 columns) in flight, which a row kernel needs against ~2 us of loaded HBM latency; the shared-memory ring
+// of row_norm_ring_kernel holds as many rows but spends a second and third pass of shared-memory reads on each.
+// Statistics as the CPU code: float32 sums (a tree here), mean and variance formed in float64.
+template <int OP, int VPT, bool RES>
+__global__ void __launch_bounds__(256, 3) row_norm_f32_kernel(RowNormParams p) {
+    __shared__ float red[2][2][8];  // [row parity][sum | squared differences][warp]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const size_t cols = p.cols, nvec = cols / 4;
+    bool has[VPT];
+#pragma unroll
+    for (int k = 0; k < VPT; k++) has[k] = (size_t)tid + 256 * (size_t)k < nvec;
+    float4 cur[VPT], nxt[VPT];
+    auto fetch = [&](size_t row, float4* dst) {
+        const float4* x = (const float4*)((const float*)p.in + row * cols);
+#pragma unroll
+        for (int k = 0; k < VPT; k++)
+            if (has[k]) {
+                const Vec16 v = ld_stream(x + tid + 256 * k);
+                dst[k] = make_float4(__uint_as_float(v.w[0]), __uint_as_float(v.w[1]), __uint_as_float(v.w[2]), __uint_as_float(v.w[3]));
+            }
+    };
+    auto block_sum = [&](float v, float* slot) {  // one barrier; `slot` alternates between rows, so no second one is needed
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        if (lane == 0) slot[warp] = v;
+        __syncthreads();
+        return ((slot[0] + slot[4]) + (slot[2] + slot[6])) + ((slot[1] + slot[5]) + (slot[3] + slot[7]));
+    };
+    if (blockIdx.x < p.rows) fetch(blockIdx.x, cur);
+    int par = 0;
+    for (size_t row = blockIdx.x; row < p.rows; row += gridDim.x, par ^= 1) {
+        if (row + gridDim.x < p.rows) fetch(row + gridDim.x, nxt);
+        float4 resv[VPT];
+        const float4* res = RES ? (const float4*)((const float*)p.res + row * cols) : nullptr;
+        if (RES) {
+#pragma unroll
+            for (int k = 0; k < VPT; k++)
+                if (has[k]) {
+                    const Vec16 v = ld_stream(res + tid + 256 * k);
+                    resv[k] = make_float4(__uint_as_float(v.w[0]), __uint_as_float(v.w[1]), __uint_as_float(v.w[2]), __uint_as_float(v.w[3]));
+                }
+        }
+        float part[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int k = 0; k < VPT; k++)
+            if (has[k]) {
+                const float f[4] = {cur[k].x, cur[k].y, cur[k].z, cur[k].w};
+#pragma unroll
+                for (int i = 0; i < 4; i++) part[i] += OP == OP_ADAPTIVE_RMS ? f[i] * f[i] : f[i];
+            }
+        const float total = block_sum((part[0] + part[1]) + (part[2] + part[3]), red[par][0]);
+        float mean = 0.f, inv;
+        if (OP == OP_ADAPTIVE_RMS) {
+            inv = (float)(1.0 / sqrt((double)__fdiv_rn(total, (float)cols) + p.eps));
+        } else {
+            mean = (float)((double)total / (double)cols);
+            float sq[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int k = 0; k < VPT; k++)
+                if (has[k]) {
+                    const float f[4] = {cur[k].x, cur[k].y, cur[k].z, cur[k].w};
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const float d = sub(f[i], mean);
+                        sq[i] = add(sq[i], mul(d, d));
+                    }
+                }
+            const float sqt = block_sum((sq[0] + sq[1]) + (sq[2] + sq[3]), red[par][1]);
+            inv = (float)(1.0 / sqrt((double)sqt / (double)cols + p.eps));
+        }
+        const float4 *a0, *a1;
+        if (OP == OP_LAYERNORM) {
+            a0 = (const float4*)p.p0;  // scale
+            a1 = (const float4*)p.p1;  // bias
+        } else {
+            const float* m = (const float*)p.p0 + (row / p.rowsPerBatch) * p.modCols + (OP == OP_MODULATED_LN ? p.set * cols * 3 : 0);
+            a0 = (const float4*)m;           // AdaptiveRMSNorm: scale; ModulatedLayerNorm: shift
+            a1 = (const float4*)(m + cols);  // AdaptiveRMSNorm: shift; ModulatedLayerNorm: scale
+        }
+        float4* o = (float4*)((float*)p.out + row * cols);
+#pragma unroll
+        for (int k = 0; k < VPT; k++)
+            if (has[k]) {
+                const float4 c0v = a0[tid + 256 * k], c1v = a1[tid + 256 * k];  // a few KB shared by every row: cache hits
+                const float f[4] = {cur[k].x, cur[k].y, cur[k].z, cur[k].w};
+                const float c0[4] = {c0v.x, c0v.y, c0v.z, c0v.w}, c1[4] = {c1v.x, c1v.y, c1v.z, c1v.w};
+                float r[4];
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    if (OP == OP_LAYERNORM) {
+                        r[i] = add(mul(mul(sub(f[i], mean), inv), c0[i]), c1[i]);
+                    } else {
+                        const float scale = OP == OP_ADAPTIVE_RMS ? c0[i] : c1[i], shift = OP == OP_ADAPTIVE_RMS ? c1[i] : c0[i];
+                        const float nrm = mul(OP == OP_ADAPTIVE_RMS ? f[i] : sub(f[i], mean), inv);
+                        r[i] = add(mul(nrm, add(1.0f, scale)), shift);
+                    }
+                }
+                if (RES) {
+                    r[0] = add(r[0], resv[k].x); r[1] = add(r[1], resv[k].y); r[2] = add(r[2], resv[k].z); r[3] = add(r[3], resv[k].w);
+                }
+                Vec16 ov;
+#pragma unroll
+                for (int i = 0; i < 4; i++) ov.w[i] = __float_as_uint(r[i]);
+                st_stream(o + tid + 256 * k, ov);
+            }
+#pragma unroll
+        for (int k = 0; k < VPT; k++) cur[k] = nxt[k];
+    }
+}
+
 constexpr size_t kMaxCols = 16384;  // 64 KB of shared memory for the widened row
 
 template <int OP>
@@ -566,7 +678,18 @@ int launch_row_norm(Context* ctx, int dt, const RowNormParams& p, CUDAStatus* st
     } while (0)
     // LayerNorm's scale and bias rows, widened once per CTA: 2 * cols floats
     const size_t coefSmem = OP == OP_LAYERNORM ? p.cols * 2 * sizeof(float) : 0;
-    if (dt == DT_F32) ROWNORM_LAUNCH(DT_F32);
+    if (dt == DT_F32 && vec && nvec > 256 && nvec <= 1024) {
+        // measured at 16384 x 4096: the register kernel with the next row in flight against the shared-memory ring
+        const size_t resident = (size_t)ctx->smCount * 3;
+        const unsigned g32 = (unsigned)(p.rows < resident ? p.rows : resident);
+        if (OP == OP_LAYERNORM && p.res) {
+            if (nvec <= 512) row_norm_f32_kernel<OP, 2, OP == OP_LAYERNORM><<<g32, 256, 0, ctx->stream>>>(p);
+            else row_norm_f32_kernel<OP, 4, OP == OP_LAYERNORM><<<g32, 256, 0, ctx->stream>>>(p);
+        } else {
+            if (nvec <= 512) row_norm_f32_kernel<OP, 2, false><<<g32, 256, 0, ctx->stream>>>(p);
+            else row_norm_f32_kernel<OP, 4, false><<<g32, 256, 0, ctx->stream>>>(p);
+        }
+    } else if (dt == DT_F32) ROWNORM_LAUNCH(DT_F32);
     else if (dt == DT_BF16) ROWNORM_LAUNCH16(DT_BF16);
     else if (dt == DT_F16) ROWNORM_LAUNCH16(DT_F16);
     else return fail(status, -6, "%s: unsupported dtype %d", what, dt);

@@ -212,6 +212,84 @@ __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(RowArgs a) {
     }
 }
 
+// Plain RMSNorm of rows of up to 256 * VPT vectors: one 256-thread block per row, the row in registers, the thread's slice of
+// the scale row widened once, and the NEXT row of the block already on its way while this one is reduced and written (a row
+// kernel needs several rows per SM in flight against ~2 us of loaded HBM latency).  Arithmetic, rounding points and summation
+// tree of rmsnorm_rows_kernel: bit-identical results.
+template <int DT, int VPT>
+__global__ void __launch_bounds__(256, DT == DT_F32 ? 3 : 4) rmsnorm_ahead_kernel(RowArgs a) {
+    constexpr int PER = Lanes<DT>::kPer;
+    constexpr size_t ES = DT == DT_F32 ? 4 : 2;
+    __shared__ double redD[2][8];
+    __shared__ float redF[2][8];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const size_t nvec = a.cols / PER, rowBytes = a.cols * ES;
+    bool has[VPT];
+    float sc[VPT][PER];
+#pragma unroll
+    for (int k = 0; k < VPT; k++) {
+        has[k] = (size_t)tid + 256 * (size_t)k < nvec;
+        if (has[k]) unpack<DT>(*(const Vec16*)((const char*)a.scale + ((size_t)tid + 256 * k) * 16), sc[k]);
+    }
+    Vec16 cur[VPT], nxt[VPT];
+    auto fetch = [&](size_t row, Vec16* dst) {
+        const char* x = (const char*)a.x + row * rowBytes;
+#pragma unroll
+        for (int k = 0; k < VPT; k++)
+            if (has[k]) dst[k] = ld_stream(x + ((size_t)tid + 256 * k) * 16);
+    };
+    if (blockIdx.x < a.rows) fetch(blockIdx.x, cur);
+    int par = 0;
+    for (size_t row = blockIdx.x; row < a.rows; row += gridDim.x, par ^= 1) {
+        if (row + gridDim.x < a.rows) fetch(row + gridDim.x, nxt);
+        double accD = 0.0;
+        float accF = 0.f;
+#pragma unroll
+        for (int k = 0; k < VPT; k++)
+            if (has[k]) {
+                float f[PER];
+                unpack<DT>(cur[k], f);
+#pragma unroll
+                for (int j = 0; j < PER; j++) {
+                    if (DT == DT_F32) accD += (double)f[j] * (double)f[j];
+                    else accF = fmaf(f[j], f[j], accF);
+                }
+            }
+        double total;
+        if (DT == DT_F32) {
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) accD += __shfl_xor_sync(0xffffffffu, accD, o);
+            if (lane == 0) redD[par][warp] = accD;
+            __syncthreads();
+            const double* r = redD[par];
+            total = ((r[0] + r[4]) + (r[2] + r[6])) + ((r[1] + r[5]) + (r[3] + r[7]));
+        } else {
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) accF += __shfl_xor_sync(0xffffffffu, accF, o);
+            if (lane == 0) redF[par][warp] = accF;
+            __syncthreads();
+            const float* r = redF[par];
+            total = (double)(((r[0] + r[4]) + (r[2] + r[6])) + ((r[1] + r[5]) + (r[3] + r[7])));
+        }
+        const float inv = inv_rms<DT>(total, a.cols, a.eps);
+        char* o = (char*)a.normOut + row * rowBytes;
+#pragma unroll
+        for (int k = 0; k < VPT; k++)
+            if (has[k]) {
+                float h[PER], r[PER];
+                unpack<DT>(cur[k], h);
+#pragma unroll
+                for (int j = 0; j < PER; j++) {
+                    if (DT == DT_F32) r[j] = mul(h[j], mul(inv, sc[k][j]));   // x * (inv * gamma), compute.go:358-362
+                    else r[j] = mul(mul(h[j], inv), sc[k][j]);                // (x * inv) * gamma, compute.go:370-373
+                }
+                st_stream(o + ((size_t)tid + 256 * k) * 16, pack<DT>(r));
+            }
+#pragma unroll
+        for (int k = 0; k < VPT; k++) cur[k] = nxt[k];
+    }
+}
+
 // The fused row of the transformer block at its usual width: 16-bit rows of 257..512 vectors (2056..4096 columns), one
 // 256-thread block per row, two vectors per thread.  The generic kernel above spends ~48 instructions per element on this
 // shape and is bound by instruction issue; this one spends about a third of that:
@@ -469,6 +547,11 @@ static int launch_rows(Context* ctx, const RowArgs& a, CUDAStatus* status) {
     if (a.nPeer > 0 && !inplace) {
         if (nvec <= 2 * 256) rmsnorm_rows_kernel<DT, 2, FUSED, false><<<grid, 256, 0, ctx->stream>>>(a);
         else rmsnorm_rows_kernel<DT, 4, FUSED, false><<<grid, 256, 0, ctx->stream>>>(a);
+    } else if (!FUSED && vec && !inplace && nvec > 256 && nvec <= (DT == DT_F32 ? 1024u : 512u)) {
+        const size_t resident = (size_t)ctx->smCount * (DT == DT_F32 ? 3 : 4);
+        const int ga = (int)(a.rows < resident ? a.rows : resident);
+        if (nvec <= 512) rmsnorm_ahead_kernel<DT, 2><<<ga, 256, 0, ctx->stream>>>(a);
+        else rmsnorm_ahead_kernel<DT, DT == DT_F32 ? 4 : 2><<<ga, 256, 0, ctx->stream>>>(a);  // (16-bit rows never get here)
     } else if (inplace && vec) rmsnorm_rows_kernel<DT, 4, FUSED, true><<<grid, 256, 0, ctx->stream>>>(a);
     else if (!FUSED && vec && nvec <= 512 && nvec >= 128 && a.rows >= 64) {
         size_t blocks = (a.rows + 7) / 8, capW = (size_t)ctx->smCount * 4;

@@ -161,6 +161,42 @@ def test_paged_decode_matches_gather_then_mha(d, dt, kv_dt, ctx_lens, page_size,
         assert err.mean() <= 2e-3
 
 
+@pytest.mark.parametrize("kv_dt", [O.BF16, O.E4M3])
+@pytest.mark.parametrize("ctx_lens,hq,hkv", [([2048, 1500, 16, 999], 32, 8), ([3000], 4, 4), ([90, 300, 40], 16, 2)])
+def test_paged_decode_merge_paths_agree(d, monkeypatch, kv_dt, ctx_lens, hq, hkv):
+    """A sequence spread over several workers is merged by its owners together under a cooperative launch (a share each, one
+    of two routines depending on the number of owners) and by the last warp to arrive under a plain launch.  The plain launch
+    is what a refused cooperative launch falls back to; PUTER_DECODE_NO_COOPERATIVE selects it.  All routes weight the same
+    partials: the results agree to the last bits of the float32 sums and meet the same bound against the oracle."""
+    import puter_b200
+
+    dim, page_size, dt = 128, 16, O.BF16
+    batch = len(ctx_lens)
+    rng = np.random.default_rng(sum(ctx_lens) + hq)
+    table, kq, vq, ks, vs, total, max_pages = make_paged(rng, batch, ctx_lens, page_size, hkv, dim, kv_dt)
+    q = O.from_f32(rng.standard_normal((batch, hq * dim)).astype(np.float32), dt)
+    ctx = np.array(ctx_lens, np.int32)
+    want = O.to_f32(O.paged_decode(dt, kv_dt, q, kq, vq, table, ctx, page_size, hq, hkv, dim, ks, vs), dt)
+    cfg = puter_b200.MultiHeadAttentionConfig(NumHeads=hq, HeadDim=dim, Causal=True, KVHeadCount=hkv)
+    args = (cfg, dev(q), dev(kq), dev(vq), dev(table), dev(ctx))
+    kw = dict(kvFormat=kv_dt, kScale=None if ks is None else dev(ks), vScale=None if vs is None else dev(vs))
+    results = []
+    for plain in (False, True, False):
+        if plain:
+            monkeypatch.setenv("PUTER_DECODE_NO_COOPERATIVE", "1")
+        else:
+            monkeypatch.delenv("PUTER_DECODE_NO_COOPERATIVE", raising=False)
+        out = dev(np.full(q.shape, 0x5151, np.uint16))
+        d.PagedDecodeAttention(*args, out, batch, max_pages, total, page_size, dt, **kw)
+        results.append(host(out, np.uint16, q.shape))
+        assert d.take_error() == 0
+    coop, plain, again = results
+    assert np.array_equal(coop, again)  # the plain launch left the arrival counters at zero, and each route is deterministic
+    assert np.abs(O.to_f32(coop, dt) - want).max() <= 2e-2
+    assert np.abs(O.to_f32(plain, dt) - want).max() <= 2e-2
+    assert (coop != plain).mean() < 0.02  # different summation trees over the same partials: rare last-bit differences only
+
+
 def test_paged_decode_flags_bad_page_ids_and_long_contexts(d):
     import puter_b200
 
