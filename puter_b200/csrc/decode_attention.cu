@@ -73,6 +73,16 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)_
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int bytes) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
 }
+// K/V bytes are read once: marked evict-first in L2 so that they do not push out what is read again (page tables, query rows,
+// the partials of the merge, the kernel's own instructions)
+__device__ __forceinline__ uint64_t l2_evict_first_policy() {
+    uint64_t pol;
+    asm("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ void cp_async16_kv(uint64_t pol, uint32_t dst, const void* src, int bytes) {
+    asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2, %3;" ::"r"(dst), "l"(src), "r"(bytes), "l"(pol) : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
@@ -469,6 +479,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_decode16_kernel(DecodeParam
     if (lo >= hi) return;
     unsigned char* wsm = smemRaw + (size_t)warp * (kStages16 * kStage16);
     const uint32_t wsmAddr = smem_u32(wsm);
+    const uint64_t kvPolicy = l2_evict_first_policy();
     const size_t tokenStride = (size_t)p.kvHeads * kHeadDim * 2;  // bytes between tokens of a page
     const bool page16 = (p.pageSize % kTile) == 0;
     int seq;
@@ -534,12 +545,12 @@ __global__ void __launch_bounds__(kThreads, 1) paged_decode16_kernel(DecodeParam
                     const uint32_t so = (uint32_t)(r * 256) + (uint32_t)((cpChunk ^ (r & 7)) * 16);
                     const size_t rowOff = (size_t)(2 * i) * tokenStride;
                     if (full) {
-                        cp_async16(dstK + so, ks + rowOff, 16);
-                        cp_async16(dstV + so, vs + rowOff, 16);
+                        cp_async16_kv(kvPolicy, dstK + so, ks + rowOff, 16);
+                        cp_async16_kv(kvPolicy, dstV + so, vs + rowOff, 16);
                     } else {
                         const bool live = tok0 + r < ctx;
-                        cp_async16(dstK + so, live ? ks + rowOff : kBase, live ? 16 : 0);
-                        cp_async16(dstV + so, live ? vs + rowOff : vBase, live ? 16 : 0);
+                        cp_async16_kv(kvPolicy, dstK + so, live ? ks + rowOff : kBase, live ? 16 : 0);
+                        cp_async16_kv(kvPolicy, dstV + so, live ? vs + rowOff : vBase, live ? 16 : 0);
                     }
                 }
             } else {
@@ -557,8 +568,8 @@ __global__ void __launch_bounds__(kThreads, 1) paged_decode16_kernel(DecodeParam
                     const int bytes = tok < ctx ? 16 : 0;
                     if (bytes == 0) off = 0;
                     const uint32_t so = (uint32_t)(r * 256) + (uint32_t)((cpChunk ^ (r & 7)) * 16);
-                    cp_async16(dstK + so, kBase + off + cpChunk * 16, bytes);
-                    cp_async16(dstV + so, vBase + off + cpChunk * 16, bytes);
+                    cp_async16_kv(kvPolicy, dstK + so, kBase + off + cpChunk * 16, bytes);
+                    cp_async16_kv(kvPolicy, dstV + so, vBase + off + cpChunk * 16, bytes);
                 }
             }
         };
@@ -816,6 +827,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_decode_fp8_kernel(DecodePar
     if (lo >= hi) return;
     unsigned char* wsm = smemRaw + (size_t)warp * (kStages8 * kStage8);
     const uint32_t wsmAddr = smem_u32(wsm);
+    const uint64_t kvPolicy = l2_evict_first_policy();
     const size_t tokenStride = (size_t)p.kvHeads * kHeadDim;  // bytes between tokens of a page
     const bool page16 = (p.pageSize % kTile) == 0;
     int seq;
@@ -882,12 +894,12 @@ __global__ void __launch_bounds__(kThreads, 1) paged_decode_fp8_kernel(DecodePar
                         const uint32_t so = (uint32_t)((h * 16 + (i >> 1) * 8) * 128) + ((i & 1) ? cpDstOdd : cpDstEven);
                         const size_t rowOff = (size_t)(4 * i) * tokenStride;
                         if (full) {
-                            cp_async16(dstK + so, ks + rowOff, 16);
-                            cp_async16(dstV + so, vs + rowOff, 16);
+                            cp_async16_kv(kvPolicy, dstK + so, ks + rowOff, 16);
+                            cp_async16_kv(kvPolicy, dstV + so, vs + rowOff, 16);
                         } else {
                             const bool live = tk + 4 * i + cpRow < tokEnd;
-                            cp_async16(dstK + so, live ? ks + rowOff : kBase, live ? 16 : 0);
-                            cp_async16(dstV + so, live ? vs + rowOff : vBase, live ? 16 : 0);
+                            cp_async16_kv(kvPolicy, dstK + so, live ? ks + rowOff : kBase, live ? 16 : 0);
+                            cp_async16_kv(kvPolicy, dstV + so, live ? vs + rowOff : vBase, live ? 16 : 0);
                         }
                     }
                 }
@@ -906,8 +918,8 @@ __global__ void __launch_bounds__(kThreads, 1) paged_decode_fp8_kernel(DecodePar
                     const int bytes = tok < tokEnd ? 16 : 0;
                     if (bytes == 0) off = 0;
                     const uint32_t so = r * 128 + ((cpChunk ^ (r & 7)) * 16);
-                    cp_async16(dstK + so, kBase + off + cpChunk * 16, bytes);
-                    cp_async16(dstV + so, vBase + off + cpChunk * 16, bytes);
+                    cp_async16_kv(kvPolicy, dstK + so, kBase + off + cpChunk * 16, bytes);
+                    cp_async16_kv(kvPolicy, dstV + so, vBase + off + cpChunk * 16, bytes);
                 }
             }
         };
