@@ -139,8 +139,10 @@ int cuda_context_reset_stream(CUDADeviceRef device, CUDAStatus* status);
 /* NEW: 1 = always use the kernels that reproduce device/cpu operation order exactly
    (sequential sums); 0 (default) = use the tensor-core / split-KV kernels where they apply */
 int cuda_context_set_exact(CUDADeviceRef device, int exact, CUDAStatus* status);
-/* NEW: synchronises the context's stream, returns the device-side error flag in *outFlag (1 = some call since the
-   last read met an out-of-range page id / offset or an over-long context and skipped it) and clears it */
+/* NEW: synchronises the context's stream, returns the device-side error flag in *outFlag and clears it:
+   1 = some call since the last read met an out-of-range page id / offset or an over-long context and skipped it;
+   3 = a bounded wait on a row copy ran out (row-pipeline kernels); 4 = a bounded wait between the CTAs of a paged decode
+   step ran out (an owner of a split sequence never arrived): the outputs of that call are not valid */
 int cuda_context_take_error(CUDADeviceRef device, int* outFlag, CUDAStatus* status);
 /* NEW: number of kernels this context has launched (diagnostics / benchmarks) */
 unsigned long long cuda_context_launch_count(CUDADeviceRef device);
@@ -345,7 +347,12 @@ int cuda_dispatch_rope_attention_prefill(CUDADeviceRef contextRef, int elementDT
    ctxLens[i] == 0 leaves row i of out untouched.  A page id outside [0,pageCount) is never dereferenced (page 0 is
    read in its place) and a context longer than maxPages*pageSize is cut to that length; either way *errorFlag
    (device int32; NULL = the context's own flag, read with cuda_context_take_error) is set to 1 and the output
-   row of that sequence is not valid. */
+   row of that sequence is not valid.
+   The step is one kernel, launched cooperatively (at most one CTA per SM, all resident at once) so that the CTAs which
+   share a long sequence can wait for one another, bounded, and merge it together; if the device refuses a cooperative
+   launch of that size (SMs reserved for other work), or the environment variable PUTER_DECODE_NO_COOPERATIVE is set,
+   it is launched plainly and the last CTA to finish a sequence merges it alone.  Same results up to the order of the
+   float32 sums. */
 int cuda_dispatch_paged_decode_attention(CUDADeviceRef contextRef, int elementDType, int kvDType, CUDABufferRef queryRef,
                                          CUDABufferRef kPagesRef, CUDABufferRef vPagesRef, CUDABufferRef pageTableRef,
                                          CUDABufferRef ctxLensRef, CUDABufferRef kScaleRef, CUDABufferRef vScaleRef,
