@@ -412,35 +412,49 @@ __device__ __forceinline__ void segment_done(const DecodeParams& p, const int* t
     merge_slices<BF16>(p, so, b, kvh, lane, 1, 0);
 }
 
-// The deferred part of segment_done: waits (bounded) until all n owners of (b, kvh) have arrived, merges this worker's share,
-// counts the departure; the last to depart returns the counter to zero.
+// The deferred part of segment_done, for the one or two sequences a range shares with other workers: waits (bounded) until all
+// owners of each have arrived — lane 0 polls the first counter and lane 1 the second, at the same time — then merges this
+// worker's share of each and counts the departures; the last to depart returns a counter to zero.
+// The range's LAST sequence is merged first: its other owners met it at the start of their ranges and arrived long ago (unless
+// it spans whole ranges), while the first sequence waits for a worker that is finishing its own range right now.
 template <bool BF16>
-__device__ __forceinline__ void finish_duty(const DecodeParams& p, const int* ts, long long worker, int b, int kvh, int lane) {
-    const SeqOwners so = seq_owners(p, ts, b);
-    int* c = p.counters + (size_t)b * p.kvHeads + kvh;
+__device__ __forceinline__ void finish_duties(const DecodeParams& p, const int* ts, long long worker, int nDuty, int duty0, int duty1,
+                                              int kvh, int lane) {
+    if (nDuty == 0) return;
+    const int bA = nDuty > 1 ? duty1 : duty0, bB = duty0;  // order of the merges
+    const SeqOwners soA = seq_owners(p, ts, bA), soB = seq_owners(p, ts, bB);
     int ok = 1;
-    if (lane == 0) {
+    if (lane < nDuty) {
+        const int* c = p.counters + (size_t)(lane == 0 ? bA : bB) * p.kvHeads + kvh;
+        const int need = lane == 0 ? soA.n : soB.n;
         unsigned spins = 0;
-        while (ld_acquire_gpu(c) < so.n) {
+        while (ld_acquire_gpu(c) < need) {
             if (++spins > kMergeSpinLimit) { ok = 0; break; }
             __nanosleep(40);
         }
     }
-    ok = __shfl_sync(0xffffffffu, ok, 0);
-    __syncwarp();  // lane 0's acquire load, then this barrier: the other lanes' loads below see the owners' partials
-    if (ok) {
-        int share = (int)(worker - so.v0);
-        if (!so.allOwn) {
-            share = 0;
-            for (long long v = so.v0; v < worker; v++) share += so.owns(v) ? 1 : 0;
+    const int okA = __shfl_sync(0xffffffffu, ok, 0), okB = __shfl_sync(0xffffffffu, ok, 1);
+    __syncwarp();  // the polling lanes' acquire loads, then this barrier: every lane's loads below see the owners' partials
+    // one copy of the merge code, run once or twice (the second run finds it in the instruction cache)
+#pragma unroll 1
+    for (int d = 0; d < nDuty; d++) {
+        const SeqOwners so = d == 0 ? soA : soB;
+        const int b = d == 0 ? bA : bB, okay = d == 0 ? okA : okB;
+        int* c = p.counters + (size_t)b * p.kvHeads + kvh;
+        if (okay) {
+            int share = (int)(worker - so.v0);
+            if (!so.allOwn) {
+                share = 0;
+                for (long long v = so.v0; v < worker; v++) share += so.owns(v) ? 1 : 0;
+            }
+            if (so.n <= kMergeSplitMax) merge_slices<BF16>(p, so, b, kvh, lane, so.n, share);
+            else merge_across_lanes<BF16>(p, so, b, kvh, lane, share);
+        } else if (lane == 0) {
+            atomicExch(p.errorFlag, 4);  // an owner never arrived: the rows of this sequence are not written
         }
-        if (so.n <= kMergeSplitMax) merge_slices<BF16>(p, so, b, kvh, lane, so.n, share);
-        else merge_across_lanes<BF16>(p, so, b, kvh, lane, share);
-    } else if (lane == 0) {
-        atomicExch(p.errorFlag, 4);  // an owner never arrived: the rows of this sequence are not written
+        __syncwarp();
+        if (lane == 0 && atomicAdd(c, 1) == 2 * so.n - 1) *c = 0;
     }
-    __syncwarp();
-    if (lane == 0 && atomicAdd(c, 1) == 2 * so.n - 1) *c = 0;
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -753,10 +767,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_decode16_kernel(DecodeParam
         }
         cp_async_wait<0>();  // only empty groups are left
         __syncwarp();
-        // the range's last sequence first: its other owners met it at the start of their ranges and arrived long ago,
-        // while the first sequence waits for a worker that is finishing its own range right now
-        if (nDuty > 1) finish_duty<BF16>(p, ts, worker, duty1, kvh, lane);
-        if (nDuty > 0) finish_duty<BF16>(p, ts, worker, duty0, kvh, lane);
+        finish_duties<BF16>(p, ts, worker, nDuty, duty0, duty1, kvh, lane);
     }
 }
 
@@ -1136,10 +1147,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_decode_fp8_kernel(DecodePar
         }
         cp_async_wait<0>();  // only empty groups are left
         __syncwarp();
-        // the range's last sequence first: its other owners met it at the start of their ranges and arrived long ago,
-        // while the first sequence waits for a worker that is finishing its own range right now
-        if (nDuty > 1) finish_duty<BF16>(p, ts, worker, duty1, kvh, lane);
-        if (nDuty > 0) finish_duty<BF16>(p, ts, worker, duty0, kvh, lane);
+        finish_duties<BF16>(p, ts, worker, nDuty, duty0, duty1, kvh, lane);
     }
 }
 
