@@ -184,7 +184,7 @@ class DecodeWorkload:
         self.bytes_per_step_global = self.data.algorithmic_bytes(None, self.esize)      # the whole batch
         # DRAM traffic (ncu dram__bytes_read + write) over algorithmic bytes, from the small-case captures summarised in
         # the profiles folder (bf16 and fp8 decode captures); traffic grows in proportion to the tokens read
-        self.traffic_ratio = (318.7 + 5.2) / 316.8 if fp8 else (635.7 + 5.3) / 633.6
+        self.traffic_ratio = (317.5 + 3.8) / 316.8 if fp8 else (634.3 + 4.2) / 633.6
         self.h2d = qb + tb + cb
         self.d2h = self.out_host.numel() * 2
         torch.cuda.synchronize()
