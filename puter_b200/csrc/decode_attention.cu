@@ -736,9 +736,13 @@ __global__ void __launch_bounds__(kThreads, 1) paged_decode16_kernel(DecodeParam
                     }
                 }
             }
-            // ---- partial of (worker, sequence b, KV head): row sums reduced over the lanes of a head column ----
+            // ---- end of this worker's part of sequence b: row sums reduced over the lanes of a head column, then either the
+            // finished rows (the whole sequence lay inside this range: nothing to merge, no trip through scratch) or the
+            // partial of (worker, sequence, KV head) ----
+            const bool whole = cur == segStart && segEnd == segEndAll;
             {
                 const long long slot = worker + b;
+                uint16_t* orow = (uint16_t*)p.out + (size_t)b * p.numHeads * kHeadDim;
 #pragma unroll
                 for (int nt = 0; nt < NT; nt++) {
 #pragma unroll
@@ -750,18 +754,28 @@ __global__ void __launch_bounds__(kThreads, 1) paged_decode16_kernel(DecodeParam
                         const int gi = nt * 8 + 2 * t + j;
                         if (gi < p.group) {
                             const int head = kvh * p.group + gi;
-                            float* acc = p.partAcc + ((size_t)slot * p.numHeads + head) * kHeadDim;
+                            if (whole) {
+                                uint16_t* o = orow + (size_t)head * kHeadDim;
 #pragma unroll
-                            for (int dt = 0; dt < 8; dt++) {
-                                acc[16 * dt + g] = oacc[dt][nt][j];
-                                acc[16 * dt + g + 8] = oacc[dt][nt][2 + j];
+                                for (int dt = 0; dt < 8; dt++) {
+                                    const float x0 = l > 0.f ? oacc[dt][nt][j] / l : 0.f, x1 = l > 0.f ? oacc[dt][nt][2 + j] / l : 0.f;
+                                    o[16 * dt + g] = (uint16_t)(BF16 ? f32_to_bf16_bits(x0) : f32_to_f16_bits(x0));
+                                    o[16 * dt + g + 8] = (uint16_t)(BF16 ? f32_to_bf16_bits(x1) : f32_to_f16_bits(x1));
+                                }
+                            } else {
+                                float* acc = p.partAcc + ((size_t)slot * p.numHeads + head) * kHeadDim;
+#pragma unroll
+                                for (int dt = 0; dt < 8; dt++) {
+                                    acc[16 * dt + g] = oacc[dt][nt][j];
+                                    acc[16 * dt + g + 8] = oacc[dt][nt][2 + j];
+                                }
+                                if (g == 0) p.partML[(size_t)slot * p.numHeads + head] = make_float2(mcol[nt][j], l);
                             }
-                            if (g == 0) p.partML[(size_t)slot * p.numHeads + head] = make_float2(mcol[nt][j], l);
                         }
                     }
                 }
             }
-            segment_done<BF16>(p, ts, b, kvh, lane, duty0, duty1, nDuty);
+            if (!whole) segment_done<BF16>(p, ts, b, kvh, lane, duty0, duty1, nDuty);
             cur = segEnd;
             if (cur >= segEndAll) b++;
         }
@@ -1117,10 +1131,14 @@ __global__ void __launch_bounds__(kThreads, 1) paged_decode_fp8_kernel(DecodePar
                     }
                 }
             }
-            // ---- partial of (worker, sequence b, KV head): row sums reduced over the lanes of a head column ----
+            // ---- end of this worker's part of sequence b: row sums reduced over the lanes of a head column, then either the
+            // finished rows (the whole sequence lay inside this range: nothing to merge, no trip through scratch) or the
+            // partial of (worker, sequence, KV head) ----
+            const bool whole = cur == segStart && segEnd == segEndAll;
             {
                 const long long slot = worker + b;
                 const float vS = p.vScale ? p.vScale[kvh] : 1.0f;
+                uint16_t* orow = (uint16_t*)p.out + (size_t)b * p.numHeads * kHeadDim;
 #pragma unroll
                 for (int nt = 0; nt < NT; nt++) {
 #pragma unroll
@@ -1132,16 +1150,26 @@ __global__ void __launch_bounds__(kThreads, 1) paged_decode_fp8_kernel(DecodePar
                         const int gi = nt * 8 + 2 * t + j;
                         if (gi < p.group) {
                             const int head = kvh * p.group + gi;
-                            float* acc = p.partAcc + ((size_t)slot * p.numHeads + head) * kHeadDim;
+                            if (whole) {
+                                uint16_t* o = orow + (size_t)head * kHeadDim;
 #pragma unroll
-                            for (int dt = 0; dt < 8; dt++)
-                                *(float2*)(acc + 16 * dt + 2 * g) = make_float2(oacc[dt][nt][j] * vS, oacc[dt][nt][2 + j] * vS);
-                            if (g == 0) p.partML[(size_t)slot * p.numHeads + head] = make_float2(mcol[nt][j], l);
+                                for (int dt = 0; dt < 8; dt++) {
+                                    const float x0 = l > 0.f ? (oacc[dt][nt][j] * vS) / l : 0.f, x1 = l > 0.f ? (oacc[dt][nt][2 + j] * vS) / l : 0.f;
+                                    const uint32_t lo = BF16 ? f32_to_bf16_bits(x0) : f32_to_f16_bits(x0), hi = BF16 ? f32_to_bf16_bits(x1) : f32_to_f16_bits(x1);
+                                    *(uint32_t*)(o + 16 * dt + 2 * g) = lo | (hi << 16);
+                                }
+                            } else {
+                                float* acc = p.partAcc + ((size_t)slot * p.numHeads + head) * kHeadDim;
+#pragma unroll
+                                for (int dt = 0; dt < 8; dt++)
+                                    *(float2*)(acc + 16 * dt + 2 * g) = make_float2(oacc[dt][nt][j] * vS, oacc[dt][nt][2 + j] * vS);
+                                if (g == 0) p.partML[(size_t)slot * p.numHeads + head] = make_float2(mcol[nt][j], l);
+                            }
                         }
                     }
                 }
             }
-            segment_done<BF16>(p, ts, b, kvh, lane, duty0, duty1, nDuty);
+            if (!whole) segment_done<BF16>(p, ts, b, kvh, lane, duty0, duty1, nDuty);
             cur = segEnd;
             if (cur >= segEndAll) b++;
         }
