@@ -70,18 +70,22 @@ struct Ring {
     unsigned char* base;   // this warp's stages
     uint32_t barBase;      // shared address of this warp's first mbarrier
     const char* src;
-    size_t rows, rowBytes, stride, nextIssue;
+    size_t rows, rowBytes, stageBytes, landOffset, stride, nextIssue;
     int stages, stage;
     uint32_t phase;
     int lane;
     int armed;             // stages that have a copy outstanding or landed but not consumed
 
-    __device__ __forceinline__ Ring(unsigned char* smem, int warpsPerBlock, int stages_, size_t rowBytes_, const void* src_, size_t rows_)
-        : src((const char*)src_), rows(rows_), rowBytes(rowBytes_), stages(stages_), stage(0), phase(0), armed(0) {
+    // stageBytes_ > rowBytes_ gives every stage room beyond the row (for results kept in shared memory); the row then lands
+    // landOffset_ bytes into its stage (both multiples of 16) and acquire() still returns the start of the stage
+    __device__ __forceinline__ Ring(unsigned char* smem, int warpsPerBlock, int stages_, size_t rowBytes_, const void* src_, size_t rows_,
+                                    size_t stageBytes_ = 0, size_t landOffset_ = 0)
+        : src((const char*)src_), rows(rows_), rowBytes(rowBytes_), stageBytes(stageBytes_ ? stageBytes_ : rowBytes_), landOffset(landOffset_),
+          stages(stages_), stage(0), phase(0), armed(0) {
         const int warp = threadIdx.x >> 5;
         lane = threadIdx.x & 31;
-        base = smem + (size_t)warp * stages * rowBytes;
-        unsigned char* bars = smem + (size_t)warpsPerBlock * stages * rowBytes + (size_t)warp * stages * 8;
+        base = smem + (size_t)warp * stages * stageBytes;
+        unsigned char* bars = smem + (size_t)warpsPerBlock * stages * stageBytes + (size_t)warp * stages * 8;
         barBase = smem_addr(bars);
         stride = (size_t)gridDim.x * warpsPerBlock;
         nextIssue = (size_t)blockIdx.x * warpsPerBlock + warp;
@@ -100,7 +104,7 @@ struct Ring {
             if (lane == 0) {
                 const uint32_t bar = barBase + 8 * s;
                 mbar_expect_tx(bar, (uint32_t)rowBytes);
-                bulk_load(smem_addr(base + (size_t)s * rowBytes), src + nextIssue * rowBytes, (uint32_t)rowBytes, bar);
+                bulk_load(smem_addr(base + (size_t)s * stageBytes + landOffset), src + nextIssue * rowBytes, (uint32_t)rowBytes, bar);
             }
             nextIssue += stride;
             armed++;
@@ -118,7 +122,7 @@ struct Ring {
             }
             return nullptr;
         }
-        return base + (size_t)stage * rowBytes;
+        return base + (size_t)stage * stageBytes;
     }
     __device__ __forceinline__ void release() {
         __syncwarp();  // every lane has finished reading the stage
@@ -128,7 +132,7 @@ struct Ring {
     }
 };
 
-// Host side: warps per block, stages per warp and dynamic shared memory for rows of `rowBytes` (0 warps: row too long).
+// Host side: warps per block, stages per warp and dynamic shared memory for stages of `rowBytes` (0 warps: row too long).
 struct Plan {
     int warps, stages;
     size_t smem;

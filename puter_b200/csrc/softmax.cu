@@ -20,16 +20,14 @@ namespace puter {
 namespace {
 
 template <int DT> struct SPer { static constexpr int kPer = DT == DT_F32 ? 4 : 8; };
+// (every 16-bit value here goes through float32 arithmetic before it is stored: the hardware conversions of pack16_arith apply)
 template <int DT> __device__ __forceinline__ void s_unpack(const Vec16& v, float* f) {
     if (DT == DT_F32) {
 #pragma unroll
         for (int i = 0; i < 4; i++) f[i] = __uint_as_float(v.w[i]);
     } else {
 #pragma unroll
-        for (int i = 0; i < 4; i++) {
-            f[2 * i] = Storage<DT>::widen((uint16_t)(v.w[i] & 0xFFFFu));
-            f[2 * i + 1] = Storage<DT>::widen((uint16_t)(v.w[i] >> 16));
-        }
+        for (int i = 0; i < 4; i++) unpack16_arith<DT>(v.w[i], f[2 * i], f[2 * i + 1]);
     }
 }
 template <int DT> __device__ __forceinline__ Vec16 s_pack(const float* f) {
@@ -39,8 +37,7 @@ template <int DT> __device__ __forceinline__ Vec16 s_pack(const float* f) {
         for (int i = 0; i < 4; i++) v.w[i] = __float_as_uint(f[i]);
     } else {
 #pragma unroll
-        for (int i = 0; i < 4; i++)
-            v.w[i] = (uint32_t)Storage<DT>::narrow(f[2 * i]) | ((uint32_t)Storage<DT>::narrow(f[2 * i + 1]) << 16);
+        for (int i = 0; i < 4; i++) v.w[i] = pack16_arith<DT>(f[2 * i], f[2 * i + 1]);
     }
     return v;
 }
@@ -63,10 +60,16 @@ __global__ void __launch_bounds__(ROWPIPE_MAX_WARPS * 32) softmax_ring_kernel(So
     extern __shared__ __align__(128) unsigned char ringSmem[];
     const size_t cols = p.cols, nvec = cols / PER, rowBytes = cols * sizeof(T);
     const int lane = threadIdx.x & 31;
-    rowpipe::Ring ring(ringSmem, blockDim.x >> 5, stages, rowBytes, p.in, p.rows);
+    // 16-bit softmax rows: the stage has room for the row's float32 exponentials (cols * 4 bytes); the 16-bit row lands in its
+    // upper half and the exponentials are written from the start of the stage.  The exponentials of vector v overwrite the input
+    // vectors 2v - nvec and 2v - nvec + 1, which are never beyond v: each round loads its vectors first, then stores.
+    constexpr bool WIDE = DT != DT_F32 && !LOG;
+    rowpipe::Ring ring(ringSmem, blockDim.x >> 5, stages, rowBytes, p.in, p.rows, WIDE ? cols * 4 : 0, WIDE ? rowBytes : 0);
     for (size_t row = ring.first(); row < p.rows; row = ring.next_row(row)) {
-        const unsigned char* x = ring.acquire(p.errorFlag);
-        if (!x) return;
+        const unsigned char* stageBase = ring.acquire(p.errorFlag);
+        if (!stageBase) return;
+        const unsigned char* x = stageBase + (WIDE ? rowBytes : 0);
+        float* ex = (float*)const_cast<unsigned char*>(stageBase);
         char* o = (char*)((T*)p.out + row * cols);
         float part[UN];
         const float first = Storage<DT>::widen(*(const T*)x);  // the first element seeds the maximum
@@ -91,20 +94,32 @@ __global__ void __launch_bounds__(ROWPIPE_MAX_WARPS * 32) softmax_ring_kernel(So
         for (int s = 16; s > 0; s >>= 1) mx = ref_max(mx, __shfl_xor_sync(0xffffffffu, mx, s));
 #pragma unroll
         for (int u = 0; u < UN; u++) part[u] = 0.f;
-        for (size_t v0 = lane; v0 < nvec; v0 += 32 * UN) {
+        for (size_t vb = 0; vb < nvec; vb += 32 * UN) {  // the same trip count for every lane: the round has a warp barrier
+            const size_t v0 = vb + lane;
+            Vec16 in[UN];
+#pragma unroll
+            for (int u = 0; u < UN; u++) {
+                const size_t v = v0 + 32 * (size_t)u;
+                if (v < nvec) in[u] = *(const Vec16*)(x + v * 16);
+            }
+            if (WIDE) __syncwarp();  // every lane has read this round's inputs before any lane overwrites them
 #pragma unroll
             for (int u = 0; u < UN; u++) {
                 const size_t v = v0 + 32 * (size_t)u;
                 if (v < nvec) {
                     float f[PER];
-                    s_unpack<DT>(*(const Vec16*)(x + v * 16), f);
+                    s_unpack<DT>(in[u], f);
 #pragma unroll
                     for (int i = 0; i < PER; i++) {
                         f[i] = fast_exp32(sub(f[i], mx));
                         part[u] = add(part[u], f[i]);
                     }
-                    // float32 rows keep their exponentials in the stage (the input values are not needed again)
+                    // the exponentials stay in the stage: the input values are not needed again
                     if (!LOG && DT == DT_F32) *(Vec16*)(const_cast<unsigned char*>(x) + v * 16) = s_pack<DT>(f);
+                    if (WIDE) {
+                        *(float4*)(ex + v * 8) = make_float4(f[0], f[1], f[2], f[3]);
+                        *(float4*)(ex + v * 8 + 4) = make_float4(f[4], f[5], f[6], f[7]);
+                    }
                 }
             }
         }
@@ -120,10 +135,14 @@ __global__ void __launch_bounds__(ROWPIPE_MAX_WARPS * 32) softmax_ring_kernel(So
                 const size_t v = v0 + 32 * (size_t)u;
                 if (v < nvec) {
                     float f[PER];
-                    s_unpack<DT>(*(const Vec16*)(x + v * 16), f);
+                    if (WIDE) {
+                        const float4 a = *(const float4*)(ex + v * 8), b = *(const float4*)(ex + v * 8 + 4);
+                        f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4 % PER] = b.x; f[5 % PER] = b.y; f[6 % PER] = b.z; f[7 % PER] = b.w;
+                    } else {
+                        s_unpack<DT>(*(const Vec16*)(x + v * 16), f);
+                    }
 #pragma unroll
-                    for (int i = 0; i < PER; i++)
-                        f[i] = LOG ? sub(sub(f[i], mx), k) : mul(DT == DT_F32 ? f[i] : fast_exp32(sub(f[i], mx)), k);
+                    for (int i = 0; i < PER; i++) f[i] = LOG ? sub(sub(f[i], mx), k) : mul(f[i], k);
                     st_stream(o + v * 16, s_pack<DT>(f));
                 }
             }
@@ -181,7 +200,8 @@ int softmax_entry(CUDADeviceRef contextRef, int dt, CUDABufferRef inputRef, CUDA
     PUTER_REQUIRE(outRef, "out", (size_t)rows * cols * es);
     SoftmaxParams p{dev_ptr(inputRef), dev_ptr(outRef), rows, cols, ctx->errorFlag};
     const bool vec = ((size_t)cols * es) % 16 == 0 && (((uintptr_t)p.in | (uintptr_t)p.out) & 15u) == 0;
-    const rowpipe::Plan plan = vec ? rowpipe::plan((size_t)cols * es) : rowpipe::Plan{0, 0, 0};
+    // (16-bit softmax stages also hold the row's float32 exponentials)
+    const rowpipe::Plan plan = vec ? rowpipe::plan((size_t)cols * ((es == 2 && !LOG) ? 4 : es)) : rowpipe::Plan{0, 0, 0};
 #define SOFTMAX_LAUNCH(DT)                                                                                                  \
     do {                                                                                                                    \
         if (plan.warps) {                                                                                                   \
