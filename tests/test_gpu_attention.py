@@ -197,6 +197,38 @@ def test_paged_decode_merge_paths_agree(d, monkeypatch, kv_dt, ctx_lens, hq, hkv
     assert (coop != plain).mean() < 0.02  # different summation trees over the same partials: rare last-bit differences only
 
 
+def test_paged_decode_step_replays_from_a_cuda_graph(d):
+    """A decode step is one (cooperative) kernel launch with no host synchronisation and no allocation once the workspace
+    has its size: it can be captured into a CUDA graph and replayed, with the same bits as the eager call."""
+    import puter_b200
+    import torch
+
+    dim, page_size, hq, hkv, dt = 128, 16, 32, 8, O.BF16
+    ctx_lens = [2048, 1500, 16, 999]
+    batch = len(ctx_lens)
+    rng = np.random.default_rng(77)
+    table, kq, vq, _, _, total, max_pages = make_paged(rng, batch, ctx_lens, page_size, hkv, dim, dt)
+    q = O.from_f32(rng.standard_normal((batch, hq * dim)).astype(np.float32), dt)
+    cfg = puter_b200.MultiHeadAttentionConfig(NumHeads=hq, HeadDim=dim, Causal=True, KVHeadCount=hkv)
+    args = (cfg, dev(q), dev(kq), dev(vq), dev(table), dev(np.array(ctx_lens, np.int32)))
+    eager = dev(np.zeros(q.shape, np.uint16))
+    replayed = dev(np.zeros(q.shape, np.uint16))
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        # the eager call sizes the workspace and moves the context to this stream before the capture begins
+        d.PagedDecodeAttention(*args, eager, batch, max_pages, total, page_size, dt)
+        torch.cuda.synchronize()
+        with torch.cuda.graph(graph, stream=side):
+            d.PagedDecodeAttention(*args, replayed, batch, max_pages, total, page_size, dt)
+    assert not host(replayed, np.uint16, q.shape).any()  # capturing ran nothing
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    assert np.array_equal(host(replayed, np.uint16, q.shape), host(eager, np.uint16, q.shape))
+    assert d.take_error() == 0
+
+
 def test_paged_decode_flags_bad_page_ids_and_long_contexts(d):
     import puter_b200
 
