@@ -378,6 +378,59 @@ def make_workload(name, dev, rank, world, decode_cls):
     raise ValueError(name)
 
 
+def row_ops_lines(dev, peaks, rows=16384, cols=4096, reps=20):
+    """The sibling row operators beside config 5's chain (plain RMSNorm, the LayerNorm family with its fused residual form,
+    row softmax / log-softmax) on the chain's row shape, bf16 and float32: CUDA-event time per call over `reps` calls after
+    3 warm-up calls, inputs (134 / 268 MB per tensor) larger than L2.  One GPU; the operators are row-wise and shard by rows
+    like the chain.  Algorithmic bytes: one read and one write of the rows (plus the residual rows for the fused entry)."""
+    import torch
+
+    import puter_b200
+    from puter_b200 import dtypes as D
+
+    def per_call(fn):
+        for _ in range(3):
+            fn()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        for _ in range(reps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / reps / 1e3
+
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    out = {"shape": [rows, cols], "unit": "GB/s", "peak": peaks["hbm_gbs"]}
+    for tdt, name, es, fmt in ((torch.bfloat16, "bf16", 2, D.BFloat16), (torch.float32, "f32", 4, D.Float32)):
+        x = torch.randn(rows, cols, device="cuda", generator=gen).to(tdt)
+        res = torch.randn(rows, cols, device="cuda", generator=gen).to(tdt)
+        scale = (torch.rand(cols, device="cuda", generator=gen) + 0.5).to(tdt)
+        bias = torch.randn(cols, device="cuda", generator=gen).to(tdt)
+        mod = (torch.randn(4, 3 * cols, device="cuda", generator=gen) * 0.1).to(tdt)
+        o = torch.empty_like(x)
+        rpb = rows // 4
+        rms = puter_b200.RMSNormConfig(1e-6)
+        ops = {
+            "rmsnorm": (2, lambda: dev.RMSNorm(rms, x, scale, o, rows, cols, fmt)),
+            "layernorm": (2, lambda: dev.LayerNorm(x, scale, bias, o, rows, cols, fmt)),
+            "layernorm_residual": (3, lambda: dev.LayerNormResidual(x, scale, bias, res, o, rows, cols, fmt)),
+            "adaptive_rmsnorm": (2, lambda: dev.AdaptiveRMSNorm(rms, x, mod, o, rows, cols, rpb, 3 * cols, fmt)),
+            "modulated_layernorm": (2, lambda: dev.ModulatedLayerNorm(puter_b200.ModulatedLayerNormConfig(1e-6, 0), x, mod, o, rows, cols,
+                                                                     rpb, 3 * cols, fmt)),
+            "softmax": (2, lambda: dev.SoftmaxRows(o, x, rows, cols, fmt)),
+            "log_softmax": (2, lambda: dev.SoftmaxRows(o, x, rows, cols, fmt, log=True)),
+        }
+        for op, (tensors, fn) in ops.items():
+            sec = per_call(fn)
+            gbs = tensors * rows * cols * es / sec / 1e9
+            out[f"{op}_{name}"] = {"value": gbs, "ms": sec * 1e3, "roofline_frac": gbs / peaks["hbm_gbs"]}
+        del x, res, o
+        torch.cuda.empty_cache()
+    out["error_flag"] = int(dev.take_error())
+    return out
+
+
 def secondary_lines(dev, rank, world, timed, peaks, decode_cls, replica_cls, free=()):
     """Short measurements of the other configurations, reported beside the headline line.  For N > 1 every entry is the
     strong-scaling split of the one seeded problem; `weak_replicas` repeats the earlier every-rank-runs-everything decode
@@ -420,5 +473,11 @@ def secondary_lines(dev, rank, world, timed, peaks, decode_cls, replica_cls, fre
             torch.cuda.empty_cache()
         except Exception as e:  # a secondary workload must never take the headline number down with it
             out[name] = {"error": str(e)[:300]}
+            torch.cuda.empty_cache()
+    if world == 1:
+        try:
+            out["row_ops"] = row_ops_lines(dev, peaks)
+        except Exception as e:
+            out["row_ops"] = {"error": str(e)[:300]}
             torch.cuda.empty_cache()
     return out
