@@ -10,7 +10,7 @@ metric "decode-attn HBM GB/s" is quoted on.  One step = one decode step over the
 JSON line (rank 0).
 
 For N > 1 launch with torchrun.  The ONE seeded batch is divided among the ranks: whole sequences, assigned
-longest first to the least loaded rank; each rank holds only the KV pages of its own sequences and there is no
+longest first to the least loaded rank, then balanced by exchanges; each rank holds only the KV pages of its own sequences and there is no
 data-path collective (strong scaling: value = bytes of the whole batch / slowest rank's time).
 
 `--impl reference` times the CPU restatement of the reference's device/cpu path (the Go reference cannot be
@@ -127,7 +127,7 @@ def decode_config(batch: BI.DecodeBatch, fp8: bool, world: int) -> dict:
     return {"workload": "paged_decode_fp8kv" if fp8 else "paged_decode_bf16kv", "batch": batch.batch, "query_heads": HQ, "kv_heads": HKV,
             "head_dim": DIM, "page_size": PAGE, "ctx_len": "U[%d,%d] seed 2" % tuple(CTX_RANGE), "kv_tokens": int(batch.ctx.sum()),
             "kv_dtype": "e4m3+f32 scale" if fp8 else "bf16",
-            "parallelism": "whole sequences over %d GPU(s), longest first to the least loaded; no collective" % world,
+            "parallelism": "whole sequences over %d GPU(s), longest first to the least loaded, then balanced by exchanges; no collective" % world,
             "l2": "inputs larger than L2 (KV pools %.2f GB)" % (2 * int(batch.pages_per.sum()) * PAGE * BI.INNER * esize / 1e9)}
 
 

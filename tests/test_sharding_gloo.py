@@ -39,7 +39,7 @@ def test_lpt_assign_balances_context_lengths():
         owned = sharding.lpt_assign(ctx, world)
         assert sorted(i for o in owned for i in o) == list(range(64))
         loads = [int(ctx[o].sum()) for o in owned]
-        assert max(loads) <= 1.05 * (sum(loads) / world)
+        assert max(loads) <= 1.002 * (sum(loads) / world)  # 1.3 % at 8 ranks before the exchange refinement
 
 
 def test_prefill_units():
