@@ -26,11 +26,14 @@
 //     one round of loads.  (One warp pulling 30 workers' partials through its SM's L2 port took ~19 us at the end of the
 //     kernel; 30 warps on 30 SMs take ~3.)  Where a cooperative launch is refused, the warp that arrives last for a
 //     (sequence, KV head) merges all of it in worker order;
-//   * the GQA group (<= 16 query heads per KV head) forms the M=16 rows of mma.sync m16n8k16 tiles fed by
-//     ldmatrix from XOR-swizzled shared memory; tensor-core throughput is irrelevant here, the point is to
-//     keep the instruction count per byte far below the issue limit.
-//   * fp8-e4m3 KV pages are converted to f16 (exact) on the way from the staging buffer to the tile; the
-//     per-KV-head scales are applied to the scores and to the output.
+//   * every warp's copies run two tiles ahead of its compute through the whole range, across sequence boundaries, and
+//     carry an L2 evict-first hint: K/V bytes are read once and must not push out what is read again (page tables,
+//     query rows, the partials, the kernel's instructions);
+//   * the 16 TOKENS of a tile are the M = 16 rows of mma.sync m16n8k16 and the (<= 8, or 2 x 8) query heads of the KV
+//     head's GQA group its N columns, fed by ldmatrix from XOR-swizzled shared memory; tensor-core throughput is
+//     irrelevant here, the point is to keep the instruction count per byte far below the issue limit;
+//   * fp8-e4m3 KV pages stay bytes in shared memory and are widened to f16 (exact) in registers, straight out of
+//     ldmatrix; the per-KV-head scales are applied to the scores and to the output.
 #include <math.h>
 #include <stdlib.h>
 #include <mutex>
