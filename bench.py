@@ -383,7 +383,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default="decode", choices=["decode", "decode_fp8", "prefill", "convert", "chain", "chain_nccl"])
+    ap.add_argument("--workload", default="decode", choices=["decode", "decode_fp8", "prefill", "convert", "chain", "chain_nccl", "row_ops"])
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--ref-seqs", type=int, default=16, help="sequences in the CPU sample")
     ap.add_argument("--ctx-min", type=int, default=512)
@@ -424,6 +424,21 @@ def main():
     from bench_workloads import make_workload  # noqa: E402  (secondary workloads live beside this file)
 
     dev = puter_b200.Device(local_rank)
+    if args.workload == "row_ops":
+        # the sibling row operators on the chain's row shape, one line of per-operator rates (also the `row_ops` entry of the
+        # default run's `secondary`); --steps = timed calls per operator, --warmup = untimed calls before them
+        from bench_workloads import row_ops_lines
+
+        if rank == 0:
+            ops = row_ops_lines(dev, measured_peaks(), reps=max(1, args.steps), warmup=args.warmup)
+            print(json.dumps({"metric": "row_ops_hbm_gbps", "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+                              "higher_is_better": True, "data": "synthetic", "config": {"workload": "row_ops", "rows": ops["shape"][0],
+                                                                                       "cols": ops["shape"][1]},
+                              "row_ops": ops}), flush=True)
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
     wl = make_workload(args.workload, dev, rank, world, DecodeWorkload)
 
     def barrier():

@@ -378,10 +378,10 @@ def make_workload(name, dev, rank, world, decode_cls):
     raise ValueError(name)
 
 
-def row_ops_lines(dev, peaks, rows=16384, cols=4096, reps=20):
+def row_ops_lines(dev, peaks, rows=16384, cols=4096, reps=20, warmup=3):
     """The sibling row operators beside config 5's chain (plain RMSNorm, the LayerNorm family with its fused residual form,
     row softmax / log-softmax) on the chain's row shape, bf16 and float32: CUDA-event time per call over `reps` calls after
-    3 warm-up calls, inputs (134 / 268 MB per tensor) larger than L2.  One GPU; the operators are row-wise and shard by rows
+    `warmup` untimed calls, inputs (134 / 268 MB per tensor) larger than L2.  One GPU; the operators are row-wise and shard by rows
     like the chain.  Algorithmic bytes: one read and one write of the rows (plus the residual rows for the fused entry)."""
     import torch
 
@@ -389,7 +389,7 @@ def row_ops_lines(dev, peaks, rows=16384, cols=4096, reps=20):
     from puter_b200 import dtypes as D
 
     def per_call(fn):
-        for _ in range(3):
+        for _ in range(warmup):
             fn()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
