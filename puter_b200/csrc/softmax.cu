@@ -151,6 +151,89 @@ __global__ void __launch_bounds__(ROWPIPE_MAX_WARPS * 32) softmax_ring_kernel(So
     }
 }
 
+// Rows of up to 256 * VPT vectors (4096 columns): one 256-thread block per row, the row widened into registers (16 values per
+// thread), every exponential computed once and kept there, the block's NEXT row already in flight.  No shared-memory passes: the
+// operator is bound by the instruction count of the reference's polynomial exponential, and three resident blocks per SM (24
+// warps) keep the issue slots fuller than the 12-16 warps of the ring kernel, which still serves longer rows.
+// Maximum as the reference's loop `if x > max { max = x }` seeded with the row's first element: a NaN never replaces the
+// maximum, and a row that STARTS with a NaN keeps it as its maximum.
+template <int DT, bool LOG, int VPT>
+__global__ void __launch_bounds__(256, 3) softmax_block_kernel(SoftmaxParams p) {
+    using T = typename Storage<DT>::type;
+    constexpr int PER = SPer<DT>::kPer;
+    __shared__ float red[2][2][8];  // [row parity][max | sum][warp]
+    __shared__ float firstOf[2];    // [row parity] the row's first element
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const size_t cols = p.cols, nvec = cols / PER;
+    bool has[VPT];
+#pragma unroll
+    for (int k = 0; k < VPT; k++) has[k] = (size_t)tid + 256 * (size_t)k < nvec;
+    Vec16 cur[VPT], nxt[VPT];
+    auto fetch = [&](size_t row, Vec16* dst) {
+        const char* x = (const char*)((const T*)p.in + row * cols);
+#pragma unroll
+        for (int k = 0; k < VPT; k++)
+            if (has[k]) dst[k] = ld_stream(x + ((size_t)tid + 256 * k) * 16);
+    };
+    if (blockIdx.x < p.rows) fetch(blockIdx.x, cur);
+    int par = 0;
+    for (size_t row = blockIdx.x; row < p.rows; row += gridDim.x, par ^= 1) {
+        if (row + gridDim.x < p.rows) fetch(row + gridDim.x, nxt);
+        float f[VPT][PER];
+        float mx = -INFINITY;
+#pragma unroll
+        for (int k = 0; k < VPT; k++)
+            if (has[k]) {
+                s_unpack<DT>(cur[k], f[k]);
+#pragma unroll
+                for (int i = 0; i < PER; i++) mx = ref_max(mx, f[k][i]);
+            }
+        if (tid == 0) firstOf[par] = f[0][0];
+#pragma unroll
+        for (int s = 16; s > 0; s >>= 1) mx = ref_max(mx, __shfl_xor_sync(0xffffffffu, mx, s));
+        if (lane == 0) red[par][0][warp] = mx;
+        __syncthreads();
+        {
+            const float* r = red[par][0];
+            mx = ref_max(ref_max(ref_max(r[0], r[1]), ref_max(r[2], r[3])), ref_max(ref_max(r[4], r[5]), ref_max(r[6], r[7])));
+            const float first = firstOf[par];
+            if (first != first) mx = first;  // the reference's running maximum never leaves a leading NaN
+        }
+        float part[4] = {0.f, 0.f, 0.f, 0.f};
+        float e[VPT][PER];
+#pragma unroll
+        for (int k = 0; k < VPT; k++)
+            if (has[k]) {
+#pragma unroll
+                for (int i = 0; i < PER; i++) {
+                    e[k][i] = fast_exp32(sub(f[k][i], mx));
+                    part[i & 3] = add(part[i & 3], e[k][i]);
+                }
+            }
+        float sum = add(add(part[0], part[1]), add(part[2], part[3]));
+#pragma unroll
+        for (int s = 16; s > 0; s >>= 1) sum = add(sum, __shfl_xor_sync(0xffffffffu, sum, s));
+        if (lane == 0) red[par][1][warp] = sum;
+        __syncthreads();
+        {
+            const float* r = red[par][1];
+            sum = add(add(add(r[0], r[4]), add(r[2], r[6])), add(add(r[1], r[5]), add(r[3], r[7])));
+        }
+        const float kk = LOG ? fast_log32(sum) : divf(1.0f, sum);
+        char* o = (char*)((T*)p.out + row * cols);
+#pragma unroll
+        for (int k = 0; k < VPT; k++)
+            if (has[k]) {
+                float r[PER];
+#pragma unroll
+                for (int i = 0; i < PER; i++) r[i] = LOG ? sub(sub(f[k][i], mx), kk) : mul(e[k][i], kk);
+                st_stream(o + ((size_t)tid + 256 * k) * 16, s_pack<DT>(r));
+            }
+#pragma unroll
+        for (int k = 0; k < VPT; k++) cur[k] = nxt[k];
+    }
+}
+
 // any alignment, any length: one CTA per row, scalar accesses, the row re-read from memory (L2) in every pass
 template <int DT, bool LOG>
 __global__ void __launch_bounds__(256) softmax_scalar_kernel(SoftmaxParams p) {
@@ -204,7 +287,12 @@ int softmax_entry(CUDADeviceRef contextRef, int dt, CUDABufferRef inputRef, CUDA
     const rowpipe::Plan plan = vec ? rowpipe::plan((size_t)cols * ((es == 2 && !LOG) ? 4 : es)) : rowpipe::Plan{0, 0, 0};
 #define SOFTMAX_LAUNCH(DT)                                                                                                  \
     do {                                                                                                                    \
-        if (plan.warps) {                                                                                                   \
+        constexpr int kVpt = DT == DT_F32 ? 4 : 2;                                                                          \
+        const size_t nvecRow = (size_t)cols * es / 16;                                                                      \
+        if (vec && nvecRow > 128u * kVpt && nvecRow <= 256u * kVpt) {                                                       \
+            const size_t resident = (size_t)ctx->smCount * 3;                                                               \
+            softmax_block_kernel<DT, LOG, kVpt><<<(unsigned)(rows < resident ? rows : resident), 256, 0, ctx->stream>>>(p); \
+        } else if (plan.warps) {                                                                                                   \
             size_t perSm = (220 * 1024) / (plan.smem + 1024);                                                               \
             perSm = perSm < 1 ? 1 : (perSm > 4 ? 4 : perSm);                                                                \
             size_t blocks = ((size_t)rows + plan.warps - 1) / plan.warps;                                                   \
