@@ -107,6 +107,76 @@ __global__ void __launch_bounds__(256) rope_rotate_kernel(const void* __restrict
     }
 }
 
+// The usual shapes (the work items of a head are a power of two <= 256 and the rotation has fewer than 2^32 items): a thread keeps
+// its place inside the head for the whole launch and walks (position, head) rows, so the only division per item is one 32-bit
+// position = row / heads; the cos / sin values of an item arrive as 16-byte vectors; results are rounded by the hardware
+// conversion (they come out of float32 arithmetic).  The generic kernel above spent most of its instructions on three
+// 64-bit divisions per item and scalar table loads: 4.1 TB/s on [16384, 32, 128] bf16 against 5.7 here.
+template <int DT, bool HALF>
+__global__ void __launch_bounds__(256) rope_rotate_pow2_kernel(const void* __restrict__ in, void* __restrict__ out,
+                                                              const float* __restrict__ cosT, const float* __restrict__ sinT,
+                                                              uint32_t seqHeads, uint32_t heads, uint32_t headDim, int itemShift) {
+    constexpr int PER = Lanes<DT>::kPer;
+    constexpr size_t ES = DT == DT_F32 ? 4 : 2;
+    const uint32_t half = headDim / 2;
+    const uint32_t j = threadIdx.x & ((1u << itemShift) - 1);
+    const uint32_t rowsPerBlock = 256u >> itemShift;
+    auto pack_arith = [](const float* f) {
+        Vec16 v;
+        if (DT == DT_F32) {
+#pragma unroll
+            for (int i = 0; i < 4; i++) v.w[i] = __float_as_uint(f[i]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 4; i++) v.w[i] = pack16_arith<DT == DT_F32 ? DT_BF16 : DT>(f[2 * i], f[2 * i + 1]);
+        }
+        return v;
+    };
+    for (uint32_t sh = blockIdx.x * rowsPerBlock + (threadIdx.x >> itemShift); sh < seqHeads; sh += gridDim.x * rowsPerBlock) {
+        const uint32_t s = sh / heads;
+        const size_t base = (size_t)sh * headDim;
+        if (HALF) {
+            const uint32_t p0 = j * PER;
+            const Vec16 ve = ld_stream((const char*)in + (base + p0) * ES);
+            const Vec16 vo = ld_stream((const char*)in + (base + half + p0) * ES);
+            float c[PER], sn[PER], e[PER], o[PER], re[PER], ro[PER];
+#pragma unroll
+            for (int i = 0; i < PER; i += 4) {
+                *(float4*)(c + i) = __ldg((const float4*)(cosT + (size_t)s * half + p0 + i));
+                *(float4*)(sn + i) = __ldg((const float4*)(sinT + (size_t)s * half + p0 + i));
+            }
+            unpack<DT>(ve, e);
+            unpack<DT>(vo, o);
+#pragma unroll
+            for (int i = 0; i < PER; i++) {
+                re[i] = sub(mul(e[i], c[i]), mul(o[i], sn[i]));
+                ro[i] = add(mul(e[i], sn[i]), mul(o[i], c[i]));
+            }
+            st_stream((char*)out + (base + p0) * ES, pack_arith(re));
+            st_stream((char*)out + (base + half + p0) * ES, pack_arith(ro));
+        } else {
+            constexpr int PAIRS = PER / 2;
+            const uint32_t p0 = j * PAIRS;
+            const Vec16 v = ld_stream((const char*)in + (base + 2 * p0) * ES);
+            float c[PAIRS], sn[PAIRS], f[PER], r[PER];
+            if (PAIRS == 4) {
+                *(float4*)c = __ldg((const float4*)(cosT + (size_t)s * half + p0));
+                *(float4*)sn = __ldg((const float4*)(sinT + (size_t)s * half + p0));
+            } else {
+                *(float2*)c = __ldg((const float2*)(cosT + (size_t)s * half + p0));
+                *(float2*)sn = __ldg((const float2*)(sinT + (size_t)s * half + p0));
+            }
+            unpack<DT>(v, f);
+#pragma unroll
+            for (int i = 0; i < PAIRS; i++) {
+                r[2 * i] = sub(mul(f[2 * i], c[i]), mul(f[2 * i + 1], sn[i]));
+                r[2 * i + 1] = add(mul(f[2 * i], sn[i]), mul(f[2 * i + 1], c[i]));
+            }
+            st_stream((char*)out + (base + 2 * p0) * ES, pack_arith(r));
+        }
+    }
+}
+
 // KV-cache producer: RoPE(k) at a per-row position, optional e4m3 quantisation with a per-head scale, and the paged write of K
 // and V, in one pass (no reference counterpart as one op: it equals RoPE -> [convert] -> KVPageWrite for K and
 // [convert] -> KVPageWrite for V; device/cpu/rope/compute.go:55-193, execution/page_intrinsic.go:361-438).  Positions, page
@@ -327,9 +397,25 @@ extern "C" int cuda_dispatch_rope_f64(CUDADeviceRef contextRef, int elementDType
     size_t items = vec ? elems / per : elems / 2;
     size_t blocks = (items + 255) / 256, cap = (size_t)ctx->smCount * 16;
     int grid = (int)(blocks < cap ? (blocks ? blocks : 1) : cap);
+    // work items of a head (a vector in interleaved mode, a vector and its partner in half mode)
+    const size_t itemsPerHead = halfMode ? half / per : headDim / per;
+    int itemShift = -1;
+    for (int sft = 0; sft <= 8; sft++)
+        if (itemsPerHead == ((size_t)1 << sft)) itemShift = sft;
+    // the 16-byte table loads need the row of a position (half floats) and the item's offset in it to be 16-byte multiples
+    const size_t tableStep = halfMode ? (size_t)per : (size_t)per / 2;
+    const bool pow2 = vec && itemShift >= 0 && (size_t)seqLen * numHeads < 0xFFFFFFFFull / 2 && (half * 4) % 16 == 0 &&
+                      (tableStep * 4) % (per == 4 && !halfMode ? 8 : 16) == 0 && ((uintptr_t)table & 15u) == 0 && ((size_t)seqLen * half * 4) % 16 == 0;
+    if (pow2) {
+        const uint32_t rowsPerBlock = 256u >> itemShift;
+        const size_t rowBlocks = ((size_t)seqLen * numHeads + rowsPerBlock - 1) / rowsPerBlock;
+        grid = (int)(rowBlocks < cap ? (rowBlocks ? rowBlocks : 1) : cap);
+    }
 #define ROPE_LAUNCH(DT)                                                                                                  \
     do {                                                                                                                 \
-        if (!vec) rope_rotate_scalar_kernel<DT><<<grid, 256, 0, ctx->stream>>>(in, out, cosT, sinT, seqLen, numHeads, headDim, (int)halfMode); \
+        if (pow2 && halfMode) rope_rotate_pow2_kernel<DT, true><<<grid, 256, 0, ctx->stream>>>(in, out, cosT, sinT, seqLen * numHeads, numHeads, headDim, itemShift); \
+        else if (pow2) rope_rotate_pow2_kernel<DT, false><<<grid, 256, 0, ctx->stream>>>(in, out, cosT, sinT, seqLen * numHeads, numHeads, headDim, itemShift); \
+        else if (!vec) rope_rotate_scalar_kernel<DT><<<grid, 256, 0, ctx->stream>>>(in, out, cosT, sinT, seqLen, numHeads, headDim, (int)halfMode); \
         else if (halfMode) rope_rotate_kernel<DT, true><<<grid, 256, 0, ctx->stream>>>(in, out, cosT, sinT, seqLen, numHeads, headDim); \
         else rope_rotate_kernel<DT, false><<<grid, 256, 0, ctx->stream>>>(in, out, cosT, sinT, seqLen, numHeads, headDim); \
     } while (0)
