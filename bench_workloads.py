@@ -429,7 +429,7 @@ def row_ops_lines(dev, peaks, rows=16384, cols=4096, reps=20, warmup=3):
         torch.cuda.empty_cache()
     # the other streaming operators of the path on shapes of the same 8B-class layer, bf16: element-wise add and the gated
     # residual on the chain's rows, a table-driven unary activation, standalone RoPE over [rows, 32 heads, 128], and the paged
-    # KV write / gather of one layer's K rows ([rows, 8 KV heads x 128], page 16, pages in a random permutation)
+    # KV write / gather of K rows ([8 x rows, 8 KV heads x 128], page 16, pages in a random permutation)
     tdt, fmt, es = torch.bfloat16, D.BFloat16, 2
     n = rows * cols
     a = torch.randn(rows, cols, device="cuda", generator=gen).to(tdt)
@@ -437,11 +437,12 @@ def row_ops_lines(dev, peaks, rows=16384, cols=4096, reps=20, warmup=3):
     o = torch.empty_like(a)
     mod = (torch.randn(4, 3 * cols, device="cuda", generator=gen) * 0.1).to(tdt)
     inner, page = 1024, 16
-    pages = rows // page
-    vals = torch.randn(rows, inner, device="cuda", generator=gen).to(tdt)
+    prow = rows * 8  # 131072 token rows of K: 268 MB, larger than L2
+    pages = prow // page
+    vals = torch.randn(prow, inner, device="cuda", generator=gen).to(tdt)
     perm = torch.randperm(pages, device="cuda", generator=gen).to(torch.int32)
-    ids = perm[torch.arange(rows, device="cuda") // page].contiguous()
-    offs = (torch.arange(rows, device="cuda") % page).to(torch.int32).contiguous()
+    ids = perm[torch.arange(prow, device="cuda") // page].contiguous()
+    offs = (torch.arange(prow, device="cuda") % page).to(torch.int32).contiguous()
     storage = torch.zeros(pages * page, inner, device="cuda", dtype=tdt)
     gathered = torch.empty_like(vals)
     rope_cfg = puter_b200.RoPEConfig()
@@ -450,8 +451,8 @@ def row_ops_lines(dev, peaks, rows=16384, cols=4096, reps=20, warmup=3):
         "gated_residual_bf16": (3 * n * es, lambda: dev.GatedResidual(a, b, mod, o, rows, cols, rows // 4, 3 * cols, 0, fmt)),
         "silu_bf16": (2 * n * es, lambda: dev.Silu(o, a, n, fmt)),
         "rope_bf16": (2 * n * es, lambda: dev.RoPE(rope_cfg, a, o, rows, cols // 128, 128, fmt)),
-        "kv_page_write_bf16": (2 * rows * inner * es, lambda: dev.KVPageWrite(storage, vals, ids, offs, storage, pages, page, inner, rows, 0, fmt)),
-        "kv_page_gather_bf16": (2 * rows * inner * es, lambda: dev.KVPageGather(storage, perm, gathered, pages, page, inner, rows, 0, fmt)),
+        "kv_page_write_bf16": (2 * prow * inner * es, lambda: dev.KVPageWrite(storage, vals, ids, offs, storage, pages, page, inner, prow, 0, fmt)),
+        "kv_page_gather_bf16": (2 * prow * inner * es, lambda: dev.KVPageGather(storage, perm, gathered, pages, page, inner, prow, 0, fmt)),
     }
     for op, (nbytes, fn) in stream.items():
         sec = per_call(fn)

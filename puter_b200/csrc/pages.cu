@@ -55,6 +55,63 @@ __global__ void __launch_bounds__(256) page_gather_kernel(const char* __restrict
     }
 }
 
+// Rows of at least 16 vectors (256 bytes; a KV row of 8 heads x 128 bf16 is 2 KB): one WARP per row.  The page of a row is
+// looked up once per row instead of once per 16-byte item, there is no division per item (the element-wise kernels above spend
+// four 64-bit divisions on every item), and a lane has four independent copies in flight.
+__global__ void __launch_bounds__(256) page_write_rows_kernel(char* __restrict__ out, const char* __restrict__ values,
+                                                             const int32_t* __restrict__ pageIDs, const int32_t* __restrict__ offsets,
+                                                             size_t pageCount, size_t pageSize, size_t rowBytes, size_t valueRows,
+                                                             int* __restrict__ errorFlag) {
+    const int lane = threadIdx.x & 31;
+    const size_t perRow = rowBytes / 16;
+    const size_t warps = (size_t)gridDim.x * (blockDim.x >> 5);
+    for (size_t row = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < valueRows; row += warps) {
+        const long long page = pageIDs[row], off = offsets[row];
+        if (page < 0 || page >= (long long)pageCount || off < 0 || off >= (long long)pageSize) {
+            if (lane == 0) atomicExch(errorFlag, 1);
+            continue;
+        }
+        char* dst = out + ((size_t)page * pageSize + (size_t)off) * rowBytes;
+        const char* src = values + row * rowBytes;
+        for (size_t v0 = lane; v0 < perRow; v0 += 128) {
+            Vec16 t[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++)
+                if (v0 + 32 * u < perRow) t[u] = ld_stream(src + (v0 + 32 * u) * 16);
+#pragma unroll
+            for (int u = 0; u < 4; u++)
+                if (v0 + 32 * u < perRow) *(Vec16*)(dst + (v0 + 32 * u) * 16) = t[u];
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256) page_gather_rows_kernel(const char* __restrict__ storage, const int32_t* __restrict__ pageTable,
+                                                              char* __restrict__ out, size_t pageCount, size_t pageSize, size_t rowBytes,
+                                                              size_t outRows, int* __restrict__ errorFlag) {
+    const int lane = threadIdx.x & 31;
+    const size_t perRow = rowBytes / 16;
+    const size_t warps = (size_t)gridDim.x * (blockDim.x >> 5);
+    for (size_t row = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < outRows; row += warps) {
+        const size_t entry = row / pageSize;
+        const long long page = pageTable[entry];
+        if (page < 0 || page >= (long long)pageCount) {
+            if (lane == 0) atomicExch(errorFlag, 1);
+            continue;
+        }
+        const char* src = storage + ((size_t)page * pageSize + (row - entry * pageSize)) * rowBytes;
+        char* dst = out + row * rowBytes;
+        for (size_t v0 = lane; v0 < perRow; v0 += 128) {
+            Vec16 t[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++)
+                if (v0 + 32 * u < perRow) t[u] = ld_stream(src + (v0 + 32 * u) * 16);
+#pragma unroll
+            for (int u = 0; u < 4; u++)
+                if (v0 + 32 * u < perRow) st_stream(dst + (v0 + 32 * u) * 16, t[u]);
+        }
+    }
+}
+
 // output[b] = input[b, seq - 1, :]: rows of rowBytes, one per batch item (device/cpu/shape/ops.go:133-160)
 __global__ void __launch_bounds__(256) last_token_kernel(const char* __restrict__ in, char* __restrict__ out, size_t batch, size_t seq,
                                                         size_t rowBytes, int vec) {
@@ -108,9 +165,14 @@ extern "C" int cuda_dispatch_kv_page_write(CUDADeviceRef contextRef, int element
     const char* vals = (const char*)dev_ptr(valuesRef);
     int vec = rowBytes % 16 == 0 && (((uintptr_t)out | (uintptr_t)vals) & 15u) == 0;
     size_t items = (size_t)valueRows * (vec ? rowBytes / 16 : rowBytes);
-    page_write_kernel<<<page_grid(ctx, items), 256, 0, ctx->stream>>>(out, vals, (const int32_t*)dev_ptr(pageIDsRef),
-                                                                      (const int32_t*)dev_ptr(offsetsRef), pageCount, pageSize, rowBytes,
-                                                                      valueRows, vec, ctx->errorFlag);
+    if (vec && rowBytes >= 256)
+        page_write_rows_kernel<<<page_grid(ctx, (size_t)valueRows * 32), 256, 0, ctx->stream>>>(
+            out, vals, (const int32_t*)dev_ptr(pageIDsRef), (const int32_t*)dev_ptr(offsetsRef), pageCount, pageSize, rowBytes, valueRows,
+            ctx->errorFlag);
+    else
+        page_write_kernel<<<page_grid(ctx, items), 256, 0, ctx->stream>>>(out, vals, (const int32_t*)dev_ptr(pageIDsRef),
+                                                                          (const int32_t*)dev_ptr(offsetsRef), pageCount, pageSize, rowBytes,
+                                                                          valueRows, vec, ctx->errorFlag);
     return check_launch(ctx, status, "kv page write");
 }
 
@@ -131,8 +193,12 @@ extern "C" int cuda_dispatch_kv_page_gather(CUDADeviceRef contextRef, int elemen
     char* out = (char*)dev_ptr(outputRef);
     int vec = rowBytes % 16 == 0 && (((uintptr_t)out | (uintptr_t)st) & 15u) == 0;
     size_t items = (size_t)outRows * (vec ? rowBytes / 16 : rowBytes);
-    page_gather_kernel<<<page_grid(ctx, items), 256, 0, ctx->stream>>>(st, (const int32_t*)dev_ptr(pageTableRef), out, pageCount, pageSize,
-                                                                       rowBytes, outRows, vec, ctx->errorFlag);
+    if (vec && rowBytes >= 256)
+        page_gather_rows_kernel<<<page_grid(ctx, (size_t)outRows * 32), 256, 0, ctx->stream>>>(st, (const int32_t*)dev_ptr(pageTableRef), out,
+                                                                                              pageCount, pageSize, rowBytes, outRows, ctx->errorFlag);
+    else
+        page_gather_kernel<<<page_grid(ctx, items), 256, 0, ctx->stream>>>(st, (const int32_t*)dev_ptr(pageTableRef), out, pageCount, pageSize,
+                                                                           rowBytes, outRows, vec, ctx->errorFlag);
     return check_launch(ctx, status, "kv page gather");
 }
 
