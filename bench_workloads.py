@@ -454,6 +454,12 @@ def row_ops_lines(dev, peaks, rows=16384, cols=4096, reps=20, warmup=3):
         "kv_page_write_bf16": (2 * prow * inner * es, lambda: dev.KVPageWrite(storage, vals, ids, offs, storage, pages, page, inner, prow, 0, fmt)),
         "kv_page_gather_bf16": (2 * prow * inner * es, lambda: dev.KVPageGather(storage, perm, gathered, pages, page, inner, prow, 0, fmt)),
     }
+    # the KV-cache producer on the same rows: RoPE(k) at per-row positions, then the paged write of K and V (2 in, 2 out)
+    vvals = torch.randn(prow, inner, device="cuda", generator=gen).to(tdt)
+    vstorage = torch.zeros(pages * page, inner, device="cuda", dtype=tdt)
+    positions = (torch.arange(prow, device="cuda") % 32768).to(torch.int32).contiguous()
+    stream["rope_kv_page_write_bf16"] = (4 * prow * inner * es, lambda: dev.RoPEKVPageWrite(
+        rope_cfg, vals, vvals, positions, ids, offs, storage, vstorage, prow, inner // 128, 128, pages, page, 32768, fmt))
     for op, (nbytes, fn) in stream.items():
         sec = per_call(fn)
         gbs = nbytes / sec / 1e9

@@ -255,6 +255,108 @@ __global__ void __launch_bounds__(256) rope_kv_page_write_kernel(const uint16_t*
     }
 }
 
+// The same producer with one WARP per row, for head dimensions whose work items per head are a power of two: the row's page,
+// offset and position are looked up once, a lane derives (head, item) with shifts, the cos / sin values of an item arrive as
+// 16-byte vectors and the rotated values are rounded by the hardware conversion.  The element-wise kernel above pays four
+// 64-bit divisions, three row lookups and 8-16 scalar table loads per 16-byte item: 3.6 TB/s on [131072, 8 x 128] bf16
+// against 5.8 here.
+template <int DT, bool HALF, bool FP8>
+__global__ void __launch_bounds__(256) rope_kv_page_write_rows_kernel(const uint16_t* __restrict__ k, const uint16_t* __restrict__ v,
+                                                                     const int32_t* __restrict__ positions, const int32_t* __restrict__ pageIDs,
+                                                                     const int32_t* __restrict__ offsets, void* __restrict__ kPages,
+                                                                     void* __restrict__ vPages, const float* __restrict__ kScale,
+                                                                     const float* __restrict__ vScale, const float* __restrict__ cosT,
+                                                                     const float* __restrict__ sinT, size_t rows, uint32_t heads, uint32_t headDim,
+                                                                     size_t pageCount, size_t pageSize, size_t maxPositions, int kShift, int vShift,
+                                                                     int* __restrict__ errorFlag) {
+    const int lane = threadIdx.x & 31;
+    const uint32_t half = headDim / 2;
+    const uint32_t inner = heads * headDim;
+    const uint32_t kItems = heads << kShift, vItems = heads << vShift;  // per row
+    const size_t warps = (size_t)gridDim.x * (blockDim.x >> 5);
+    auto store8 = [&](void* pool, size_t elem, float* f, float scale) {  // f: values already rounded to the 16-bit type
+        if (FP8) {
+            uint32_t w0 = 0, w1 = 0;
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                w0 |= f32_to_e4m3_bits(__fdiv_rn(f[i], scale)) << (8 * i);
+                w1 |= f32_to_e4m3_bits(__fdiv_rn(f[4 + i], scale)) << (8 * i);
+            }
+            *(uint2*)((char*)pool + elem) = make_uint2(w0, w1);
+        } else {
+            Vec16 o;
+#pragma unroll
+            for (int i = 0; i < 4; i++) o.w[i] = pack16_arith<DT>(f[2 * i], f[2 * i + 1]);
+            *(Vec16*)((char*)pool + elem * 2) = o;
+        }
+    };
+    for (size_t row = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < rows; row += warps) {
+        const long long page = pageIDs[row], off = offsets[row], pos = positions[row];
+        if (page < 0 || page >= (long long)pageCount || off < 0 || off >= (long long)pageSize || pos < 0 || pos >= (long long)maxPositions) {
+            if (lane == 0) atomicExch(errorFlag, 1);
+            continue;
+        }
+        const size_t src = row * inner;
+        const size_t dst = ((size_t)page * pageSize + (size_t)off) * inner;
+        const float* cr = cosT + (size_t)pos * half;
+        const float* sr = sinT + (size_t)pos * half;
+        for (uint32_t it = lane; it < kItems; it += 32) {
+            const uint32_t h = it >> kShift, j = it & ((1u << kShift) - 1);
+            const size_t hs = src + (size_t)h * headDim, hd = dst + (size_t)h * headDim;
+            const float scale = FP8 ? kScale[h] : 1.f;
+            if (HALF) {
+                const uint32_t p0 = j * 8;
+                float c[8], sn[8], e[8], o[8], re[8], ro[8];
+                *(float4*)c = __ldg((const float4*)(cr + p0));
+                *(float4*)(c + 4) = __ldg((const float4*)(cr + p0 + 4));
+                *(float4*)sn = __ldg((const float4*)(sr + p0));
+                *(float4*)(sn + 4) = __ldg((const float4*)(sr + p0 + 4));
+                unpack<DT>(ld_stream((const char*)k + (hs + p0) * 2), e);
+                unpack<DT>(ld_stream((const char*)k + (hs + half + p0) * 2), o);
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    re[i] = sub(mul(e[i], c[i]), mul(o[i], sn[i]));
+                    ro[i] = add(mul(e[i], sn[i]), mul(o[i], c[i]));
+                }
+                if (FP8) {  // rounded to the storage type first, as the separate RoPE op would have stored it
+#pragma unroll
+                    for (int i = 0; i < 8; i += 2) { round_pair_arith<DT>(re[i], re[i + 1]); round_pair_arith<DT>(ro[i], ro[i + 1]); }
+                }
+                store8(kPages, hd + p0, re, scale);
+                store8(kPages, hd + half + p0, ro, scale);
+            } else {
+                const uint32_t p0 = j * 4;
+                float c[4], sn[4], f[8], r[8];
+                *(float4*)c = __ldg((const float4*)(cr + p0));
+                *(float4*)sn = __ldg((const float4*)(sr + p0));
+                unpack<DT>(ld_stream((const char*)k + (hs + 2 * p0) * 2), f);
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    r[2 * i] = sub(mul(f[2 * i], c[i]), mul(f[2 * i + 1], sn[i]));
+                    r[2 * i + 1] = add(mul(f[2 * i], sn[i]), mul(f[2 * i + 1], c[i]));
+                }
+                if (FP8) {
+#pragma unroll
+                    for (int i = 0; i < 8; i += 2) round_pair_arith<DT>(r[i], r[i + 1]);
+                }
+                store8(kPages, hd + 2 * p0, r, scale);
+            }
+        }
+        for (uint32_t it = lane; it < vItems; it += 32) {
+            const uint32_t h = it >> vShift, j = it & ((1u << vShift) - 1);
+            const size_t hs = src + (size_t)h * headDim + j * 8, hd = dst + (size_t)h * headDim + j * 8;
+            const Vec16 raw = ld_stream((const char*)v + hs * 2);
+            if (FP8) {
+                float f[8];
+                unpack<DT>(raw, f);
+                store8(vPages, hd, f, vScale[h]);
+            } else {
+                *(Vec16*)((char*)vPages + hd * 2) = raw;
+            }
+        }
+    }
+}
+
 // scalar path: one thread per pair
 template <int DT>
 __global__ void __launch_bounds__(256) rope_rotate_scalar_kernel(const void* __restrict__ in, void* __restrict__ out,
@@ -500,11 +602,28 @@ extern "C" int cuda_dispatch_rope_kv_page_write(CUDADeviceRef contextRef, int el
     const int grid = (int)(blocks < cap ? (blocks ? blocks : 1) : cap);
     const float* ks = fp8 ? (const float*)dev_ptr(kScaleRef) : nullptr;
     const float* vs = fp8 ? (const float*)dev_ptr(vScaleRef) : nullptr;
+    // one warp per row where the items of a head are a power of two and the table rows can be read as 16-byte vectors
+    int kShift = -1, vShift = -1;
+    for (int sft = 0; sft <= 5; sft++) {
+        if ((halfMode ? half : headDim) / 8 == ((size_t)1 << sft)) kShift = sft;
+        if (headDim / 8 == ((size_t)1 << sft)) vShift = sft;
+    }
+    const bool byRows = kShift >= 0 && vShift >= 0 && half % 4 == 0 && ((uintptr_t)table & 15u) == 0 && ((size_t)maxPositions * half) % 4 == 0;
+    size_t rowBlocks = ((size_t)rows + 7) / 8;
+    const int rowGrid = (int)(rowBlocks < cap ? (rowBlocks ? rowBlocks : 1) : cap);
 #define PRODUCER_LAUNCH(DT, HALF, FP8)                                                                                              \
-    rope_kv_page_write_kernel<DT, HALF, FP8><<<grid, 256, 0, ctx->stream>>>(                                                        \
-        (const uint16_t*)kp, (const uint16_t*)vp, (const int32_t*)dev_ptr(positionsRef), (const int32_t*)dev_ptr(pageIDsRef),        \
-        (const int32_t*)dev_ptr(offsetsRef), kPool, vPool, ks, vs, cosT, sinT, rows, kvHeads, headDim, pageCount, pageSize,          \
-        maxPositions, ctx->errorFlag)
+    do {                                                                                                                            \
+        if (byRows)                                                                                                                 \
+            rope_kv_page_write_rows_kernel<DT, HALF, FP8><<<rowGrid, 256, 0, ctx->stream>>>(                                        \
+                (const uint16_t*)kp, (const uint16_t*)vp, (const int32_t*)dev_ptr(positionsRef), (const int32_t*)dev_ptr(pageIDsRef), \
+                (const int32_t*)dev_ptr(offsetsRef), kPool, vPool, ks, vs, cosT, sinT, rows, kvHeads, headDim, pageCount, pageSize, \
+                maxPositions, kShift, vShift, ctx->errorFlag);                                                                      \
+        else                                                                                                                        \
+            rope_kv_page_write_kernel<DT, HALF, FP8><<<grid, 256, 0, ctx->stream>>>(                                                \
+                (const uint16_t*)kp, (const uint16_t*)vp, (const int32_t*)dev_ptr(positionsRef), (const int32_t*)dev_ptr(pageIDsRef), \
+                (const int32_t*)dev_ptr(offsetsRef), kPool, vPool, ks, vs, cosT, sinT, rows, kvHeads, headDim, pageCount, pageSize, \
+                maxPositions, ctx->errorFlag);                                                                                      \
+    } while (0)
 #define PRODUCER_PICK(DT)                                                  \
     do {                                                                   \
         if (halfMode) { if (fp8) PRODUCER_LAUNCH(DT, true, true); else PRODUCER_LAUNCH(DT, true, false); }   \
