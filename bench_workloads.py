@@ -460,6 +460,11 @@ def row_ops_lines(dev, peaks, rows=16384, cols=4096, reps=20, warmup=3):
     positions = (torch.arange(prow, device="cuda") % 32768).to(torch.int32).contiguous()
     stream["rope_kv_page_write_bf16"] = (4 * prow * inner * es, lambda: dev.RoPEKVPageWrite(
         rope_cfg, vals, vvals, positions, ids, offs, storage, vstorage, prow, inner // 128, 128, pages, page, 32768, fmt))
+    # SwiGLU in the reference's packed form: rows of [gate | up], the 8B-class MLP width, a quarter of the chain's rows
+    prows, phalf = rows // 4, 14336
+    packed = torch.randn(prows, 2 * phalf, device="cuda", generator=gen).to(tdt)
+    pout = torch.empty(prows, phalf, device="cuda", dtype=tdt)
+    stream["swiglu_packed_bf16"] = (3 * prows * phalf * es, lambda: dev.SwiGLU(pout, packed, prows, phalf, fmt))
     for op, (nbytes, fn) in stream.items():
         sec = per_call(fn)
         gbs = nbytes / sec / 1e9
