@@ -44,6 +44,24 @@ def test_unary_f32_every_activation(d, name):
 
 
 @pytest.mark.parametrize("dt", [O.BF16, O.F16])
+@pytest.mark.parametrize("name", ["Silu", "Relu", "Gelu"])
+def test_unary_16bit_large_input_equals_the_table_path(d, name, dt):
+    """From 4 Mi elements on, the 16-bit unary activations read their table from shared memory (a different kernel): its result
+    must be, element for element, what the small-input kernel returns for the same bit pattern."""
+    n = (1 << 22) + 8 * 1000 + 5  # vector body, a second half-round for some threads, and a ragged tail
+    rng = np.random.default_rng(len(name) + dt)
+    x = rng.integers(0, 65536, n, dtype=np.uint32).astype(np.uint16)
+    x[:65536] = np.arange(65536, dtype=np.uint16)
+    table_out = empty(65536 * 2)
+    getattr(d, _method(name))(table_out, dev(np.arange(65536, dtype=np.uint16)), 65536, dt)
+    table = host(table_out, np.uint16)
+    out = empty(n * 2)
+    getattr(d, _method(name))(out, dev(x), n, dt)
+    assert np.array_equal(host(out, np.uint16), table[x])
+    assert d.take_error() == 0
+
+
+@pytest.mark.parametrize("dt", [O.BF16, O.F16])
 @pytest.mark.parametrize("name", sorted(O.UNARY_CODES))
 def test_unary_16bit_tables_every_pattern(d, name, dt):
     code = O.UNARY_CODES[name]
