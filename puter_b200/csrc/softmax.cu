@@ -204,11 +204,18 @@ __global__ void __launch_bounds__(256, 3) softmax_block_kernel(SoftmaxParams p) 
 #pragma unroll
         for (int k = 0; k < VPT; k++)
             if (has[k]) {
+                if (DT == DT_F32) {
 #pragma unroll
-                for (int i = 0; i < PER; i++) {
-                    e[k][i] = fast_exp32(sub(f[k][i], mx));
-                    part[i & 3] = add(part[i & 3], e[k][i]);
+                    for (int i = 0; i < PER; i++) e[k][i] = fast_exp32(sub(f[k][i], mx));
+                } else {
+                    // 16-bit rows: two exponentials at a time on packed fused multiply-adds (the same polynomial and exponent
+                    // splice, each Horner step rounded once instead of twice: within one float32 unit in the last place, far
+                    // below the rounding of the 16-bit result)
+#pragma unroll
+                    for (int i = 0; i < PER; i += 2) fast_exp32x2_fused(sub(f[k][i], mx), sub(f[k][i + 1], mx), e[k][i], e[k][i + 1]);
                 }
+#pragma unroll
+                for (int i = 0; i < PER; i++) part[i & 3] = add(part[i & 3], e[k][i]);
             }
         float sum = add(add(part[0], part[1]), add(part[2], part[3]));
 #pragma unroll
