@@ -42,6 +42,27 @@ def test_lpt_assign_balances_context_lengths():
         assert max(loads) <= 1.002 * (sum(loads) / world)  # 1.3 % at 8 ranks before the exchange refinement
 
 
+def test_lpt_assign_refinement_never_loses_to_plain_lpt_and_is_deterministic():
+    def plain_lpt(costs, world):
+        loads = [0] * world
+        for c in sorted((int(c) for c in costs), reverse=True):
+            loads[loads.index(min(loads))] += c
+        return max(loads)
+
+    rng = np.random.default_rng(7)
+    for trial in range(40):
+        n = int(rng.integers(1, 80))
+        world = int(rng.integers(1, 9))
+        costs = rng.integers(1, 40000, n)
+        owned = sharding.lpt_assign(costs, world)
+        assert owned == sharding.lpt_assign(costs, world)  # same input, same partition
+        assert sorted(i for o in owned for i in o) == list(range(n))
+        assert all(o == sorted(o) for o in owned)
+        assert max(int(costs[o].sum()) if o else 0 for o in owned) <= plain_lpt(costs, world)
+    assert sharding.lpt_assign([], 3) == [[], [], []]
+    assert sharding.lpt_assign([5], 2) == [[0], []]
+
+
 def test_prefill_units():
     for world in (1, 2, 4, 8):
         units = [u for r in range(world) for u in sharding.prefill_units(4, 8, world, r)]
